@@ -1,0 +1,221 @@
+/*
+ * ssconv_b200 — C ABI of the B200 (sm_100a) sparse steerable convolution library.
+ *
+ * This header is the drop-in boundary for the native part of the reference project
+ * (SS_Conv_lib/src, exported to Python as the pybind11 module `ss_conv._ext`,
+ * SS_Conv_lib/src/ss_conv_ops_api.cpp:15-55).  Every entry point is `extern "C"`, takes plain
+ * device pointers and sizes, launches on the CUDA stream passed as `stream`
+ * (a cudaStream_t cast to void*; NULL = legacy default stream) and returns 0 on success or a
+ * non-zero SSC_ERR_* code; ssc_last_error() then holds a human-readable message.  Nothing
+ * here allocates device memory unless stated: results and scratch are caller-provided, so a
+ * host language binding (ctypes, cgo, JNI ...) owns all allocation.  No entry point exits
+ * the process or traps the GPU (the reference calls exit(-1) in
+ * SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:71-75 and throws std::runtime_error
+ * from SS_Conv_lib/src/utils/tensorview.h:70-101).
+ *
+ * Conventions shared by all entry points
+ *   indices      int32 [N,4] rows (batch, x, y, z), row-major
+ *   features     float32 [N,C] row-major
+ *   K            kernel volume kx*ky*kz (<= 256, SS_Conv_lib/src/conv/indice_conv.h:44);
+ *                kernel offset index kappa = (kx_i*ky + ky_i)*kz + kz_i
+ *   nbr          int32 [K, n_out]: nbr[kappa*n_out + o] = input row feeding output row o at
+ *                offset kappa, or -1.  This output-major "neighbour table" is the layout the
+ *                CUDA kernels consume; the reference's indicePairs [K,2,N] (-1 padded) and
+ *                indiceNum [K] are produced beside it for API compatibility.
+ */
+#ifndef SSCONV_B200_H_
+#define SSCONV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SSC_OK 0
+#define SSC_ERR_INVALID 1   /* bad argument (shape, null pointer, unsupported size)          */
+#define SSC_ERR_CUDA 2      /* a CUDA runtime call or launch failed                          */
+#define SSC_ERR_SCRATCH 3   /* scratch buffer too small                                      */
+#define SSC_ERR_DEVICE 4    /* a kernel reported a problem through its status word           */
+
+/* Library identification.  No reference counterpart. */
+int ssc_version(void);
+/* Message of the last failing call on this host thread ("" if none).  Replaces the exception
+ * text of TV_ASSERT_RT_ERR / TV_CHECK_CUDA_ERR (SS_Conv_lib/src/utils/tensorview.h:70-101). */
+const char *ssc_last_error(void);
+/* 1 if the tcgen05 tensor-core kernels were compiled in (always for sm_100a builds). */
+int ssc_has_tcgen05(void);
+
+/* ------------------------------------------------------------------ rulebook generation
+ * Replaces getIndicePair<3> (SS_Conv_lib/src/conv/indice_conv.h:21-131) and the kernels of
+ * SS_Conv_lib/src/conv/indice_cuda_functor.cu:23-241.  Geometry follows getValidOutPos
+ * (SS_Conv_lib/src/conv/geometry.h:18-80).  Output rows are numbered by ascending flat index
+ * ((b*O0+x)*O1+y)*O2+z, the order the reference's GPU path produces
+ * (indice_conv.h:120, indice_cuda_functor.cu:113-129).  Pairs inside one offset are listed by
+ * ascending output row (the reference's order there is atomic-arbitrary).
+ */
+
+/* Bytes of scratch the rulebook entry points need for n_in active inputs, a batch of
+ * `batch` samples and an output grid of out_shape (use the input grid for submanifold). */
+size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int out_shape[3], int K);
+
+/* Submanifold rulebook (stride 1, padding k/2 forced as in indice_conv.h:68-73; output rows
+ * are the input rows, indice_conv.h:96).  Writes nbr [K,n_in]; pairs [K,2,n_in] and
+ * indice_num [K] unless NULL.  status: device int32, set non-zero on a device-side problem
+ * (coordinate out of range, hash overflow); may be NULL. */
+int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, const int shape[3],
+                      const int ksize[3], const int dilation[3], int32_t *nbr, int32_t *pairs,
+                      int32_t *indice_num, int32_t *status, void *scratch, size_t scratch_bytes,
+                      void *stream);
+
+/* Regular / strided (transpose = 0) or transposed (transpose = 1,
+ * getValidOutPosTranspose geometry.h:82-138) rulebook, phase 1: build the input coordinate
+ * hash, mark every reachable output cell and count them.  n_out_dev: device int32 that
+ * receives the number of active outputs; the caller reads it back (one 4-byte copy, the
+ * counterpart of the host sync inside torch::_unique, indice_conv.h:120) to size phase 2. */
+int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int batch, const int in_shape[3],
+                            const int out_shape[3], const int ksize[3], const int stride[3],
+                            const int padding[3], const int dilation[3], int transpose,
+                            int32_t *n_out_dev, int32_t *status, void *scratch,
+                            size_t scratch_bytes, void *stream);
+
+/* Phase 2 (same arguments and the SAME untouched scratch as phase 1): writes
+ * out_indices [n_out,4], nbr [K,n_out], pairs [K,2,n_in] (may be NULL), indice_num [K]. */
+int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batch, const int in_shape[3],
+                           const int out_shape[3], const int ksize[3], const int stride[3],
+                           const int padding[3], const int dilation[3], int transpose, int n_out,
+                           int32_t *out_indices, int32_t *nbr, int32_t *pairs,
+                           int32_t *indice_num, int32_t *status, void *scratch,
+                           size_t scratch_bytes, void *stream);
+
+/* Neighbour table from a reference-format rulebook (indicePairs [K,2,n_cols], indiceNum [K]):
+ * nbr[kappa][pairs[kappa][1-swap][i]] = pairs[kappa][swap][i].  swap = 1 is the "inverse"
+ * convolution of indice_conv.h:301-311 (roles of the two pair rows exchanged). */
+int ssc_pairs_to_nbr(const int32_t *pairs, const int32_t *indice_num, int K, int n_cols,
+                     int n_out, int swap, int32_t *nbr, void *stream);
+
+/* --------------------------------------------------------- steerable kernel materialisation
+ * Replaces SE3Kernel.combination (SS_Conv_lib/ss_conv/utils/kernel.py:267-299) followed by
+ * permute(2,3,4,1,0) (SS_Conv_lib/ss_conv/convolution.py:56):
+ *   filters[kappa][cin][cout] = sum_b weight[woff + (u*m_in+v)*nb + b] * basis[boff + ((b*d_out+a)*d_in+c)*K + kappa]
+ * out_field/in_field map a channel to (block row/col, copy u/v, component a/c) packed as
+ * int32 triples; block_table holds per (i,j) block {basis_offset or -1, weight_offset, nb,
+ * m_in, d_out, d_in} as int32 sextuples, row-major over (i,j). */
+int ssc_materialize(const float *weight, const float *basis, const int32_t *block_table,
+                    int n_blocks_in, const int32_t *out_field, const int32_t *in_field, int c_out,
+                    int c_in, int K, float *filters, void *stream);
+
+/* Pack filters [K,Cin,Cout] fp32 into the tensor-core operand image used by ssc_conv_fwd
+ * with precision SSC_PREC_TF32 (round-to-nearest TF32, K-major, 128-byte swizzled, padded).
+ * ssc_conv_packed_bytes gives the size of `packed`. */
+size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision);
+int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision,
+                          void *packed, void *stream);
+
+/* ------------------------------------------------------------ gather-GEMM-scatter (forward)
+ * Replaces indiceConv<float> (SS_Conv_lib/src/conv/indice_conv.h:247-343) and the gather /
+ * scatter kernels of SS_Conv_lib/src/conv/reordering_cuda_functor.cu:23-159:
+ *   out[o,:] = sum_kappa features[nbr[kappa][o],:] * filters[kappa]   (fp32 accumulate)
+ * as ONE launch, output-stationary (no scatter atomics, deterministic).
+ * precision: SSC_PREC_FP32 = exact fp32 FMA on CUDA cores (filters = [K,Cin,Cout] fp32);
+ *            SSC_PREC_TF32 = tcgen05 tensor cores, TF32 operands (filters = packed image).
+ * epilogue (optional, all pointers may be NULL): per-channel affine scale/shift over the
+ * c_out channels (eval-mode BatchNorm folded), then the gated activation described at
+ * ssc_bn_gate_fwd with gate_of_channel; the output then has c_final channels. */
+#define SSC_PREC_FP32 0
+#define SSC_PREC_TF32 1
+int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
+                 const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
+                 void *stream);
+
+/* ---------------------------------------------------------------------------- sparse pools
+ * Replace indiceMaxPool / indiceAvgPool (SS_Conv_lib/src/pool/indice_maxpool.h:15-50,
+ * SS_Conv_lib/src/pool/indice_avgpool.h:17-52) and their K-launch kernels.  Max: output starts
+ * at zero (indice_maxpool.h:24) so the result is max(0, max_i x_i).  Avg: out = sum_i x_i /
+ * summaryrf[o] accumulated in ascending offset order (indice_avgpool_cuda_functor.cu:43);
+ * summaryrf NULL means "divide by K" (SS_Conv_lib/ss_conv/sp_ops/functional.py:171-176). */
+int ssc_maxpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out, float *out,
+                    void *stream);
+int ssc_avgpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out,
+                    const int32_t *summaryrf, float *out, void *stream);
+/* Replaces indiceSummaryRF (SS_Conv_lib/src/pool/indiceSummaryRF.cu:21-63). */
+int ssc_summary_rf(const int32_t *nbr, int K, int n_out, int32_t *rf, void *stream);
+
+/* Replace global_avgpool_fp / global_maxpool_fp
+ * (SS_Conv_lib/src/pool/global_avgpool_cuda_kernel.cu:16-42,
+ *  SS_Conv_lib/src/pool/global_maxpool_cuda_kernel.cu:16-43): per-sample mean / max over the
+ * row ranges offsets[s]..offsets[s+1]; out [B,C]; maxidx [B,C] (first arg-max row, -1 if empty). */
+int ssc_global_avgpool_fwd(const float *feats, const int32_t *offsets, int n_samples, int c,
+                           float *out, void *stream);
+int ssc_global_maxpool_fwd(const float *feats, const int32_t *offsets, int n_samples, int c,
+                           float *out, int32_t *maxidx, void *stream);
+/* Row offsets [B+1] of a batch-sorted indices [N,4] tensor; replaces the B host syncs of
+ * SparseTensor.get_offsets (SS_Conv_lib/ss_conv/sp_ops/tensor.py:59-65). */
+int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, void *stream);
+
+/* ---------------------------------------------------------------------------- voxelization
+ * ssc_voxel2point_map replaces voxel2point_fp (SS_Conv_lib/src/voxelize/voxel2point_cuda_kernel.cu:16-42):
+ * maps [M, max_active+1] pre-initialised by the caller as in
+ * SS_Conv_lib/ss_conv/sp_ops/functional.py:344-351; modes 3/4 list point ids in ascending
+ * order (the reference's order there is atomic-arbitrary). */
+int ssc_voxel2point_map(const int32_t *inverse, const int32_t *ids, int32_t *maps, int n_point,
+                        int n_voxel, int max_active, int mode, void *stream);
+/* Replaces voxelize_fp (SS_Conv_lib/src/voxelize/voxelize_cuda_kernel.h:18-40). */
+int ssc_voxelize_fwd(const float *feats, float *out, const int32_t *maps, int mode, int n_voxel,
+                     int max_active, int c, void *stream);
+
+/* Fused Point2Voxel core, replacing torch.unique + voxel2point_map + voxelize_fp
+ * (SS_Conv_lib/ss_conv/sp_ops/voxelize.py:85-96).  Phase 1 bins batch-sorted in-range points
+ * into voxels ((p + half)/unit truncated), marks occupied cells and counts them
+ * (n_voxel_dev, max_count_dev: device int32).  Phase 2 writes voxel_indices [M,4] in
+ * ascending (b,x,y,z) order, inverse [N], and the voxel features (mode 1 first / 2 last /
+ * 3 sum / 4 mean over points in ascending point id). */
+size_t ssc_p2v_scratch_bytes(int n_point, int batch, const int grid[3]);
+int ssc_p2v_count(const float *points, const int32_t *batch_ids, int n_point, int batch,
+                  const int grid[3], const float unit[3], int32_t *n_voxel_dev, int32_t *status,
+                  void *scratch, size_t scratch_bytes, void *stream);
+int ssc_p2v_fill(const float *points, const int32_t *batch_ids, const float *feats, int n_point,
+                 int c, int batch, const int grid[3], const float unit[3], int mode, int n_voxel,
+                 int32_t *voxel_indices, int32_t *inverse, float *voxel_feats, void *scratch,
+                 size_t scratch_bytes, void *stream);
+
+/* three_nn / three_interpolate_fp replacements
+ * (SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:8-55, 79-101): unknown [N,4] and
+ * known [M,4] are (batch,x,y,z) float rows; dist2 [N,3] squared distances, idx [N,3].
+ * Same neighbours and tie order as the reference's exhaustive scan. */
+int ssc_three_nn(int n, int m, const float *unknown, const float *known, float *dist2,
+                 int32_t *idx, void *stream);
+int ssc_three_interpolate_fwd(int c, int m, int n, const float *points, const int32_t *idx,
+                              const float *weight, float *out, void *stream);
+
+/* ------------------------------------------------ irrep-wise BatchNorm + gated activation
+ * Replace the torch op chains of BatchNorm.forward (SS_Conv_lib/ss_conv/batchnorm.py:49-136)
+ * and Activation._gate (SS_Conv_lib/ss_conv/activation.py:55-100).
+ * ssc_bn_fold: per-channel scale/shift of eval-mode BN from the running statistics:
+ *   scale[ch] = weight[f]/sqrt(running_var[f]+eps); shift[ch] = bias[s]-running_mean[s]*scale
+ *   for scalar fields, 0 otherwise.  field_of_channel / scalar_of_channel: int32 [C]
+ *   (scalar_of_channel = -1 for l>0).  weight/bias may be NULL (affine=False). */
+int ssc_bn_fold(const float *running_mean, const float *running_var, const float *weight,
+                const float *bias, const int32_t *field_of_channel,
+                const int32_t *scalar_of_channel, int c, float eps, float *scale, float *shift,
+                void *stream);
+/* y = act(x*scale+shift): x [N, c_in_total]; out [N, c_out].  scale/shift NULL = no affine.
+ * gate_of_channel int32 [c_out]: -2 = copy, -1 = scalar activation (scalar_act, bias
+ * scalar_bias[ch] if non-NULL), g>=0 = multiply by gate_act(x[:, c_gate_base+g] (+gate_bias[g])).
+ * NULL gate_of_channel = affine only (c_out == c_in_total).  act codes: 0 identity, 1 relu,
+ * 2 sigmoid. */
+int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const float *scale, const float *shift,
+                    const int32_t *gate_of_channel, int c_out, int c_gate_base, int scalar_act,
+                    int gate_act, const float *scalar_bias, const float *gate_bias, float *out,
+                    void *stream);
+/* Training-mode statistics (batchnorm.py:73-99): mean [n_scalar] of scalar fields and
+ * var [n_field] = batch mean of the squared field norm (about the batch mean for scalars). */
+int ssc_bn_stats(const float *x, int n, int c, const int32_t *field_of_channel,
+                 const int32_t *scalar_of_channel, int n_field, int n_scalar, float *mean,
+                 float *var, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSCONV_B200_H_ */

@@ -1,0 +1,516 @@
+// Rulebook (indice-pair) generation on a GPU coordinate hash.
+//
+// Pipeline (regular / strided / transposed convolution and pooling):
+//   1. hash_insert      : input coordinates -> open-addressing table (4-slot buckets)
+//   2. mark_outputs     : every (input, kernel offset) sets the bit of the output cell it reaches
+//   3. popcount scan    : rank of every set bit = output row (ascending flat index)
+//   4. decode_outputs   : bit -> (b,x,y,z) row of out_indices
+//   5. lookup_neighbours: for each (output, offset) probe the hash warp-cooperatively, write
+//                         the output-major neighbour table nbr[K][n_out], count per chunk
+//   6. scan_chunks + fill_pairs: compact per-offset pair lists [K,2,n_in] (-1 padded), counts
+// Submanifold convolution skips 2-4 (outputs are the inputs).
+// Everything is integer work bound by HBM/L2 traffic; no tensor cores involved.
+#include "ssc_common.cuh"
+
+namespace ssc {
+
+constexpr int kChunk = 1024;  // outputs per block in lookup / fill
+
+struct RulebookScratch {
+  unsigned long long *table;
+  uint32_t n_buckets;
+  uint32_t *bitmap;
+  uint32_t *word_prefix;
+  uint32_t *block_sums;
+  int32_t *chunk_counts;
+  int32_t *misc;  // [0] n_out, [1] status
+  long long n_words;
+  int n_scan_blocks;
+  long long out_cap;
+  int n_chunks_cap;
+  size_t total;
+};
+
+static RulebookScratch carve(void *base, int n_in, int batch, const int out_shape[3], int K) {
+  RulebookScratch s;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void *p = base ? (char *)base + off : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  };
+  long long vol = (long long)out_shape[0] * out_shape[1] * out_shape[2];
+  long long cells = vol * batch;
+  s.n_buckets = hash_buckets_for(n_in);
+  s.table = (unsigned long long *)take((size_t)s.n_buckets * kBucketSlots * 8);
+  s.n_words = (cells + 31) / 32;
+  s.bitmap = (uint32_t *)take((size_t)s.n_words * 4);
+  s.word_prefix = (uint32_t *)take((size_t)s.n_words * 4);
+  s.n_scan_blocks = (int)((s.n_words + 1023) / 1024);
+  s.block_sums = (uint32_t *)take(((size_t)s.n_scan_blocks + 1) * 4);
+  long long cap = (long long)n_in * K;
+  if (cells < cap) cap = cells;
+  if (cap < n_in) cap = n_in;
+  s.out_cap = cap;
+  s.n_chunks_cap = (int)((cap + kChunk - 1) / kChunk) + 1;
+  s.chunk_counts = (int32_t *)take((size_t)s.n_chunks_cap * K * 4);
+  s.misc = (int32_t *)take(256);
+  s.total = off;
+  return s;
+}
+
+// ------------------------------------------------------------------------------- kernels
+__device__ __forceinline__ bool in_range3(int x, int y, int z, const int *shape) {
+  return (unsigned)x < (unsigned)shape[0] && (unsigned)y < (unsigned)shape[1] &&
+         (unsigned)z < (unsigned)shape[2];
+}
+
+__global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int batch,
+                                   Geometry g, unsigned long long *table, uint32_t mask,
+                                   int32_t *status) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  int4 c = indices[j];
+  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) {
+    atomicOr(status, 1);
+    return;
+  }
+  uint32_t key = (uint32_t)(((c.x * g.in_shape[0] + c.y) * g.in_shape[1] + c.z) * g.in_shape[2] + c.w);
+  unsigned long long packed = ((unsigned long long)key << 32) | (uint32_t)j;
+  uint32_t b = hash_mix(key) & mask;
+  for (uint32_t probe = 0; probe <= mask; ++probe) {
+    for (int s = 0; s < kBucketSlots; ++s) {
+      unsigned long long *slot = table + (size_t)b * kBucketSlots + s;
+      unsigned long long old = atomicCAS(slot, kEmptySlot, packed);
+      if (old == kEmptySlot) return;
+      if ((uint32_t)(old >> 32) == key) {  // duplicate coordinate: the largest row wins
+        atomicMax(slot, packed);
+        return;
+      }
+    }
+    b = (b + 1) & mask;
+  }
+  atomicOr(status, 2);  // table full (cannot happen at load factor <= 0.5)
+}
+
+// One thread per (input row, kernel offset): mark the output cell this pair reaches.
+__global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
+                                    uint32_t *bitmap) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long long)n * g.K) return;
+  int j = (int)(t / g.K);
+  int kappa = (int)(t - (long long)j * g.K);
+  int4 c = indices[j];
+  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
+  int kk[3] = {kappa / (g.ksize[1] * g.ksize[2]), (kappa / g.ksize[2]) % g.ksize[1], kappa % g.ksize[2]};
+  int in[3] = {c.y, c.z, c.w};
+  int o[3];
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    if (g.transpose) {
+      o[d] = in[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
+    } else {
+      int num = in[d] + g.padding[d] - kk[d] * g.dilation[d];
+      if (num < 0 || num % g.stride[d] != 0) return;
+      o[d] = num / g.stride[d];
+    }
+    if ((unsigned)o[d] >= (unsigned)g.out_shape[d]) return;
+  }
+  uint32_t flat = (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]);
+  atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
+}
+
+__device__ __forceinline__ uint32_t block_reduce_sum(uint32_t v, uint32_t *smem) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  uint32_t r = 0;
+  if (warp == 0) {
+    r = lane < (blockDim.x >> 5) ? smem[lane] : 0;
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_down_sync(0xffffffffu, r, o);
+  }
+  return r;  // valid in thread 0
+}
+
+// Exclusive scan of one value per thread over a block of up to 1024 threads.
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *smem, uint32_t *total) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t incl = v;
+  for (int o = 1; o < 32; o <<= 1) {
+    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) smem[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = lane < (blockDim.x >> 5) ? smem[lane] : 0;
+    uint32_t wi = w;
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    smem[lane] = wi - w;           // exclusive warp offsets
+    if (lane == 31) smem[32] = wi; // block total
+  }
+  __syncthreads();
+  uint32_t res = smem[warp] + incl - v;
+  if (total) *total = smem[32];
+  __syncthreads();
+  return res;
+}
+
+// 256 threads x 4 words per block.
+__global__ void popc_block_sums_kernel(const uint32_t *__restrict__ bitmap, long long n_words,
+                                       uint32_t *block_sums) {
+  __shared__ uint32_t smem[33];
+  long long base = (long long)blockIdx.x * 1024 + threadIdx.x * 4;
+  uint32_t s = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (base + i < n_words) s += __popc(bitmap[base + i]);
+  uint32_t r = block_reduce_sum(s, smem);
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = r;
+}
+
+// Single block: in-place exclusive scan of block_sums[0..n); writes the total to
+// block_sums[n] and to the two int32 outputs.
+__global__ void scan_block_sums_kernel(uint32_t *block_sums, int n, int32_t *total_a, int32_t *total_b) {
+  __shared__ uint32_t smem[33];
+  uint32_t running = 0;
+  for (int base = 0; base < n; base += blockDim.x) {
+    int i = base + threadIdx.x;
+    uint32_t v = i < n ? block_sums[i] : 0;
+    uint32_t tot;
+    uint32_t ex = block_exclusive_scan(v, smem, &tot);
+    if (i < n) block_sums[i] = running + ex;
+    running += tot;
+  }
+  if (threadIdx.x == 0) {
+    block_sums[n] = running;
+    if (total_a) *total_a = (int32_t)running;
+    if (total_b) *total_b = (int32_t)running;
+  }
+}
+
+__global__ void word_prefix_kernel(const uint32_t *__restrict__ bitmap, long long n_words,
+                                   const uint32_t *__restrict__ block_sums, uint32_t *word_prefix) {
+  __shared__ uint32_t smem[33];
+  long long base = (long long)blockIdx.x * 1024 + threadIdx.x * 4;
+  uint32_t c[4];
+  uint32_t s = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    c[i] = (base + i < n_words) ? __popc(bitmap[base + i]) : 0;
+    s += c[i];
+  }
+  uint32_t ex = block_exclusive_scan(s, smem, nullptr) + block_sums[blockIdx.x];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (base + i < n_words) word_prefix[base + i] = ex;
+    ex += c[i];
+  }
+}
+
+__global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
+                                      const uint32_t *__restrict__ word_prefix, long long n_words,
+                                      Geometry g, int n_out, int4 *out_indices) {
+  long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  uint32_t bits = bitmap[w];
+  uint32_t rank = word_prefix[w];
+  int vol = g.out_shape[0] * g.out_shape[1] * g.out_shape[2];
+  int yz = g.out_shape[1] * g.out_shape[2];
+  while (bits) {
+    int bit = __ffs(bits) - 1;
+    bits &= bits - 1;
+    uint32_t flat = (uint32_t)(w * 32 + bit);
+    int b = flat / vol;
+    int r = flat - b * vol;
+    int x = r / yz;
+    r -= x * yz;
+    int y = r / g.out_shape[2];
+    int z = r - y * g.out_shape[2];
+    if ((int)rank < n_out) out_indices[rank] = make_int4(b, x, y, z);
+    ++rank;
+  }
+}
+
+// grid (chunks, K), block kChunk threads: thread <-> output row; the hash is probed by
+// groups of 4 lanes, each group reading one 32-byte bucket per probe.
+__global__ void __launch_bounds__(kChunk)
+lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, Geometry g,
+                         const unsigned long long *__restrict__ table, uint32_t mask,
+                         int32_t *__restrict__ nbr, int32_t *__restrict__ chunk_counts, int n_chunks) {
+  const unsigned full = 0xffffffffu;
+  int kappa = blockIdx.y;
+  int o = blockIdx.x * kChunk + threadIdx.x;
+  uint32_t key = 0xFFFFFFFFu;
+  if (o < n_out) {
+    int4 c = out_indices[o];
+    int kk[3] = {kappa / (g.ksize[1] * g.ksize[2]), (kappa / g.ksize[2]) % g.ksize[1], kappa % g.ksize[2]};
+    int oc[3] = {c.y, c.z, c.w};
+    int in[3];
+    bool ok = (unsigned)c.x < (unsigned)batch;
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      if (g.transpose) {
+        int num = oc[d] + g.padding[d] - kk[d] * g.dilation[d];
+        ok = ok && num >= 0 && (num % g.stride[d] == 0);
+        in[d] = num / g.stride[d];
+      } else {
+        in[d] = oc[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
+      }
+      ok = ok && (unsigned)in[d] < (unsigned)g.in_shape[d];
+    }
+    if (ok) key = (uint32_t)(((c.x * g.in_shape[0] + in[0]) * g.in_shape[1] + in[1]) * g.in_shape[2] + in[2]);
+  }
+  unsigned lane = threadIdx.x & 31u, sub = lane & 3u, gbase = lane & ~3u;
+  unsigned gmask = 0xFu << gbase;
+  int result = -1;
+#pragma unroll 1
+  for (unsigned i = 0; i < 4; ++i) {
+    uint32_t qkey = __shfl_sync(full, key, gbase + i);
+    int found = -1;
+    if (qkey != 0xFFFFFFFFu) {  // uniform inside the 4-lane group
+      uint32_t b = hash_mix(qkey) & mask;
+      for (uint32_t probe = 0; probe <= mask; ++probe) {
+        unsigned long long slot = table[(size_t)b * kBucketSlots + sub];
+        bool empty = slot == kEmptySlot;
+        bool hit = !empty && (uint32_t)(slot >> 32) == qkey;
+        unsigned hits = __ballot_sync(gmask, hit);
+        unsigned empties = __ballot_sync(gmask, empty);
+        if (hits) {
+          found = (int)__shfl_sync(gmask, (uint32_t)slot, __ffs(hits) - 1);
+          break;
+        }
+        if (empties) break;
+        b = (b + 1) & mask;
+      }
+    }
+    if (sub == i) result = found;
+  }
+  if (o < n_out) nbr[(size_t)kappa * n_out + o] = result;
+  int cnt = __syncthreads_count(o < n_out && result >= 0);
+  if (threadIdx.x == 0) chunk_counts[(size_t)kappa * n_chunks + blockIdx.x] = cnt;
+}
+
+// One block per kernel offset: exclusive scan of its chunk counts, total -> indice_num.
+__global__ void scan_chunks_kernel(int32_t *chunk_counts, int n_chunks, int32_t *indice_num) {
+  __shared__ uint32_t smem[33];
+  int32_t *row = chunk_counts + (size_t)blockIdx.x * n_chunks;
+  uint32_t running = 0;
+  for (int base = 0; base < n_chunks; base += blockDim.x) {
+    int i = base + threadIdx.x;
+    uint32_t v = i < n_chunks ? (uint32_t)row[i] : 0;
+    uint32_t tot;
+    uint32_t ex = block_exclusive_scan(v, smem, &tot);
+    if (i < n_chunks) row[i] = (int32_t)(running + ex);
+    running += tot;
+  }
+  if (threadIdx.x == 0) indice_num[blockIdx.x] = (int32_t)running;
+}
+
+// grid (max(chunks over n_out, chunks over n_in), K), block kChunk.
+__global__ void __launch_bounds__(kChunk)
+fill_pairs_kernel(const int32_t *__restrict__ nbr, int n_out, int n_in,
+                  const int32_t *__restrict__ chunk_offsets, int n_chunks,
+                  const int32_t *__restrict__ indice_num, int32_t *__restrict__ pairs) {
+  __shared__ uint32_t smem[33];
+  int kappa = blockIdx.y;
+  int o = blockIdx.x * kChunk + threadIdx.x;
+  int32_t *row_in = pairs + (size_t)kappa * 2 * n_in;
+  int32_t *row_out = row_in + n_in;
+  int v = -1;
+  if (o < n_out) v = nbr[(size_t)kappa * n_out + o];
+  uint32_t ex = block_exclusive_scan(v >= 0 ? 1u : 0u, smem, nullptr);
+  if (v >= 0) {
+    int pos = chunk_offsets[(size_t)kappa * n_chunks + blockIdx.x] + (int)ex;
+    if (pos < n_in) {
+      row_in[pos] = v;
+      row_out[pos] = o;
+    }
+  }
+  if (o < n_in && o >= indice_num[kappa]) {
+    row_in[o] = -1;
+    row_out[o] = -1;
+  }
+}
+
+__global__ void pairs_to_nbr_kernel(const int32_t *__restrict__ pairs,
+                                    const int32_t *__restrict__ indice_num, int n_cols, int n_out,
+                                    int swap, int32_t *__restrict__ nbr) {
+  int kappa = blockIdx.y;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_cols || i >= indice_num[kappa]) return;
+  const int32_t *row = pairs + (size_t)kappa * 2 * n_cols;
+  int src = row[(swap ? n_cols : 0) + i];
+  int dst = row[(swap ? 0 : n_cols) + i];
+  if ((unsigned)dst < (unsigned)n_out) nbr[(size_t)kappa * n_out + dst] = src;
+}
+
+// ------------------------------------------------------------------------- host drivers
+static int fill_geometry(Geometry &g, const int in_shape[3], const int out_shape[3], const int ksize[3],
+                         const int stride[3], const int padding[3], const int dilation[3], int transpose) {
+  g.K = 1;
+  for (int d = 0; d < 3; ++d) {
+    g.in_shape[d] = in_shape[d];
+    g.out_shape[d] = out_shape[d];
+    g.ksize[d] = ksize[d];
+    g.stride[d] = stride[d];
+    g.padding[d] = padding[d];
+    g.dilation[d] = dilation[d];
+    if (ksize[d] < 1 || stride[d] < 1 || dilation[d] < 1 || in_shape[d] < 1 || out_shape[d] < 1) return -1;
+    g.K *= ksize[d];
+  }
+  g.transpose = transpose;
+  return 0;
+}
+
+static int check_volume(int batch, const int shape[3], const char *what) {
+  long long cells = (long long)batch * shape[0] * shape[1] * shape[2];
+  if (batch < 1 || cells >= 2147483647ll)
+    return fail(SSC_ERR_INVALID, "%s: batch*volume = %lld does not fit the int32 flat index", what, cells);
+  return 0;
+}
+
+static int build_hash(const int32_t *indices, int n_in, int batch, const Geometry &g, RulebookScratch &s,
+                      cudaStream_t st) {
+  cudaMemsetAsync(s.table, 0xFF, (size_t)s.n_buckets * kBucketSlots * 8, st);
+  cudaMemsetAsync(s.misc, 0, 256, st);
+  if (n_in > 0) {
+    hash_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.table,
+                                                           s.n_buckets - 1, s.misc + 1);
+  }
+  SSC_CHECK_LAUNCH("hash_insert");
+  return 0;
+}
+
+static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, int batch, const Geometry &g,
+                              RulebookScratch &s, int32_t *nbr, int32_t *pairs, int32_t *indice_num,
+                              cudaStream_t st) {
+  int K = g.K;
+  int n_chunks = ceil_div(n_out > 0 ? n_out : 1, kChunk);
+  if (n_chunks > s.n_chunks_cap) return fail(SSC_ERR_SCRATCH, "rulebook: n_out exceeds the scratch capacity");
+  dim3 grid(n_chunks, K);
+  lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
+                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks);
+  SSC_CHECK_LAUNCH("lookup_neighbours");
+  if (indice_num == nullptr) return 0;
+  scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num);
+  SSC_CHECK_LAUNCH("scan_chunks");
+  if (pairs != nullptr && n_in > 0) {
+    int n_chunks_in = ceil_div(n_in, kChunk);
+    dim3 grid2(n_chunks > n_chunks_in ? n_chunks : n_chunks_in, K);
+    fill_pairs_kernel<<<grid2, kChunk, 0, st>>>(nbr, n_out, n_in, s.chunk_counts, n_chunks, indice_num, pairs);
+    SSC_CHECK_LAUNCH("fill_pairs");
+  }
+  return 0;
+}
+
+}  // namespace ssc
+
+using namespace ssc;
+
+extern "C" size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int out_shape[3], int K) {
+  if (n_in < 0 || batch < 1 || K < 1) return 0;
+  return carve(nullptr, n_in, batch, out_shape, K).total;
+}
+
+extern "C" int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, const int shape[3],
+                                 const int ksize[3], const int dilation[3], int32_t *nbr, int32_t *pairs,
+                                 int32_t *indice_num, int32_t *status, void *scratch, size_t scratch_bytes,
+                                 void *stream) {
+  SSC_REQUIRE(n_in >= 0 && shape && ksize && dilation, "rulebook_subm: bad arguments");
+  SSC_REQUIRE(n_in == 0 || (indices && nbr), "rulebook_subm: null pointer");
+  int one[3] = {1, 1, 1};
+  int pad[3] = {ksize[0] / 2, ksize[1] / 2, ksize[2] / 2};
+  Geometry g;
+  SSC_REQUIRE(fill_geometry(g, shape, shape, ksize, one, pad, dilation, 0) == 0, "rulebook_subm: bad geometry");
+  SSC_REQUIRE(g.K <= 256, "rulebook_subm: kernel volume %d > 256", g.K);
+  if (int e = check_volume(batch, shape, "rulebook_subm")) return e;
+  RulebookScratch s = carve(scratch, n_in, batch, shape, g.K);
+  if (scratch == nullptr || scratch_bytes < s.total)
+    return fail(SSC_ERR_SCRATCH, "rulebook_subm: scratch %zu < %zu bytes", scratch_bytes, s.total);
+  cudaStream_t st = as_stream(stream);
+  if (int e = build_hash(indices, n_in, batch, g, s, st)) return e;
+  if (int e = lookup_and_compact(indices, n_in, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
+  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
+  SSC_CHECK_LAUNCH("rulebook_subm");
+  return SSC_OK;
+}
+
+extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int batch, const int in_shape[3],
+                                       const int out_shape[3], const int ksize[3], const int stride[3],
+                                       const int padding[3], const int dilation[3], int transpose,
+                                       int32_t *n_out_dev, int32_t *status, void *scratch,
+                                       size_t scratch_bytes, void *stream) {
+  SSC_REQUIRE(n_in >= 0 && in_shape && out_shape && ksize && stride && padding && dilation && n_out_dev,
+              "rulebook_conv_count: bad arguments");
+  Geometry g;
+  SSC_REQUIRE(fill_geometry(g, in_shape, out_shape, ksize, stride, padding, dilation, transpose) == 0,
+              "rulebook_conv_count: bad geometry");
+  SSC_REQUIRE(g.K <= 256, "rulebook_conv_count: kernel volume %d > 256", g.K);
+  if (int e = check_volume(batch, in_shape, "rulebook_conv_count(in)")) return e;
+  if (int e = check_volume(batch, out_shape, "rulebook_conv_count(out)")) return e;
+  RulebookScratch s = carve(scratch, n_in, batch, out_shape, g.K);
+  if (scratch == nullptr || scratch_bytes < s.total)
+    return fail(SSC_ERR_SCRATCH, "rulebook_conv_count: scratch %zu < %zu bytes", scratch_bytes, s.total);
+  cudaStream_t st = as_stream(stream);
+  if (int e = build_hash(indices, n_in, batch, g, s, st)) return e;
+  cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
+  long long threads = (long long)n_in * g.K;
+  if (threads > 0) {
+    mark_outputs_kernel<<<ceil_div(threads, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap);
+    SSC_CHECK_LAUNCH("mark_outputs");
+  }
+  popc_block_sums_kernel<<<s.n_scan_blocks, 256, 0, st>>>(s.bitmap, s.n_words, s.block_sums);
+  scan_block_sums_kernel<<<1, 1024, 0, st>>>(s.block_sums, s.n_scan_blocks, s.misc, n_out_dev);
+  word_prefix_kernel<<<s.n_scan_blocks, 256, 0, st>>>(s.bitmap, s.n_words, s.block_sums, s.word_prefix);
+  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
+  SSC_CHECK_LAUNCH("rulebook_conv_count");
+  return SSC_OK;
+}
+
+extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batch, const int in_shape[3],
+                                      const int out_shape[3], const int ksize[3], const int stride[3],
+                                      const int padding[3], const int dilation[3], int transpose, int n_out,
+                                      int32_t *out_indices, int32_t *nbr, int32_t *pairs, int32_t *indice_num,
+                                      int32_t *status, void *scratch, size_t scratch_bytes, void *stream) {
+  SSC_REQUIRE(n_in >= 0 && n_out >= 0 && in_shape && out_shape && ksize && stride && padding && dilation,
+              "rulebook_conv_fill: bad arguments");
+  SSC_REQUIRE(n_out == 0 || (out_indices && nbr), "rulebook_conv_fill: null pointer");
+  Geometry g;
+  SSC_REQUIRE(fill_geometry(g, in_shape, out_shape, ksize, stride, padding, dilation, transpose) == 0,
+              "rulebook_conv_fill: bad geometry");
+  SSC_REQUIRE(g.K <= 256, "rulebook_conv_fill: kernel volume %d > 256", g.K);
+  RulebookScratch s = carve(scratch, n_in, batch, out_shape, g.K);
+  if (scratch == nullptr || scratch_bytes < s.total)
+    return fail(SSC_ERR_SCRATCH, "rulebook_conv_fill: scratch %zu < %zu bytes", scratch_bytes, s.total);
+  SSC_REQUIRE((long long)n_out <= s.out_cap, "rulebook_conv_fill: n_out %d exceeds the possible maximum", n_out);
+  cudaStream_t st = as_stream(stream);
+  if (n_out > 0) {
+    decode_outputs_kernel<<<ceil_div(s.n_words, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
+                                                                   (int4 *)out_indices);
+    SSC_CHECK_LAUNCH("decode_outputs");
+  }
+  if (int e = lookup_and_compact(out_indices, n_out, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
+  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
+  SSC_CHECK_LAUNCH("rulebook_conv_fill");
+  return SSC_OK;
+}
+
+extern "C" int ssc_pairs_to_nbr(const int32_t *pairs, const int32_t *indice_num, int K, int n_cols, int n_out,
+                                int swap, int32_t *nbr, void *stream) {
+  SSC_REQUIRE(K >= 1 && n_cols >= 0 && n_out >= 0, "pairs_to_nbr: bad sizes");
+  if (n_out == 0) return SSC_OK;
+  SSC_REQUIRE(nbr && indice_num && (n_cols == 0 || pairs), "pairs_to_nbr: null pointer");
+  cudaStream_t st = as_stream(stream);
+  cudaMemsetAsync(nbr, 0xFF, (size_t)K * n_out * 4, st);
+  if (n_cols > 0) {
+    dim3 grid(ceil_div(n_cols, 256), K);
+    pairs_to_nbr_kernel<<<grid, 256, 0, st>>>(pairs, indice_num, n_cols, n_out, swap, nbr);
+  }
+  SSC_CHECK_LAUNCH("pairs_to_nbr");
+  return SSC_OK;
+}
