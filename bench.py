@@ -1,0 +1,360 @@
+"""Benchmark of the sparse steerable convolution hot path on B200.
+
+Headline workload ("cfg2", the configuration the metric is quoted on): a strided
+downsampling SS-Conv layer, irreps (4,4,4,4) = 64 channels in, 64 + 12 gate scalars = 76 out,
+kernel 3, stride 2, padding 1, batch 32 on a 64^3 grid with 16384 ellipsoid-surface points per
+sample (seeded synthetic stand-in for object-surface data), followed by a sparse MaxPool
+(kernel 2, stride 2).  One step = rulebook + filter materialisation + packing +
+gather-GEMM (tcgen05, TF32 operands, fp32 accumulate) + pool rulebook + max pool.
+
+metric  : active input voxels per second through the layer (whole job, all ranks)
+value   : inputs resident in HBM, CUDA-event timed, max over ranks
+e2e     : the same step through the public ss_conv API starting from pinned HOST buffers
+          (H2D of indices+features and D2H of the pooled features inside the timed region)
+roofline: dominant kernel (conv_fwd_tf32_kernel) algorithmic bytes / its CUDA-event time
+cpu_baseline / --impl reference: the reference's own C++ CPU path (oracle/_ref, built from the
+          reference sources) on the box's host cores.
+
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+For N > 1 launch with torch.distributed.run (one rank per GPU); every rank processes its own
+batch of 32 samples (weak scaling, no data-path collective).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "ss-conv_b200"), os.path.join(ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+CFG2 = dict(name="cfg2: SS-Conv (4,4,4,4)->(4,4,4,4)+12 gates, k3 s2 p1, batch 32, 64^3, 16384 pts/sample, + MaxPool k2 s2",
+            batch=32, V=64, n_pts=16384, irreps=(4, 4, 4, 4), k=3, stride=2, pad=1, pool_k=2, pool_s=2)
+ROTATE = 4  # distinct input batches cycled through so the working set exceeds the 126 MB L2
+
+
+def rs_of(irreps, gates=False):
+    rs = [(m, l) for l, m in enumerate(irreps)]
+    if gates:
+        rs = rs + [(sum(irreps[1:]), 0)]
+    return rs
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 7:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.15)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.samples[0][1]),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------ our arm
+class Layer:
+    """The cfg2 layer built from the public ss_conv modules."""
+
+    def __init__(self, cfg, device):
+        from ss_conv.convolution import Convolution
+        from ss_conv.pool import MaxPool
+        torch.manual_seed(1234)
+        self.cfg = cfg
+        self.conv = Convolution(rs_of(cfg["irreps"]), rs_of(cfg["irreps"], gates=True), cfg["k"], stride=cfg["stride"],
+                                padding=cfg["pad"]).to(device)
+        self.conv.train()          # training-mode forward: filters are re-materialised every step
+        self.pool = MaxPool(cfg["pool_k"], stride=cfg["pool_s"])
+
+    def step(self, feats, indices):
+        from ss_conv.sp_ops.tensor import SparseTensor
+        c = self.cfg
+        with torch.no_grad():
+            x = SparseTensor(feats, indices, [c["V"]] * 3, c["batch"])
+            return self.pool(self.conv(x))
+
+
+def make_inputs(cfg, sample_base, n_sets):
+    from ss_conv.utils import synthetic as S
+    sets = []
+    for r in range(n_sets):
+        ids = range(sample_base + r * cfg["batch"], sample_base + (r + 1) * cfg["batch"])
+        ind = S.surface_voxels(ids, cfg["V"], cfg["n_pts"], base_seed=1000)
+        feats = S.features(ind.shape[0], sum(m * (2 * l + 1) for l, m in enumerate(cfg["irreps"])), 77 + r)
+        sets.append((feats, ind))
+    return sets
+
+
+def run_ours(args):
+    from ss_conv import _ext
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = CFG2
+    _ext.set_precision("tf32")
+    layer = Layer(cfg, dev)
+    host_sets = make_inputs(cfg, rank * ROTATE * cfg["batch"], ROTATE)
+    dev_sets = [(torch.from_numpy(f).to(dev), torch.from_numpy(i).to(dev)) for f, i in host_sets]
+    pinned = [(torch.from_numpy(f).pin_memory(), torch.from_numpy(i).pin_memory()) for f, i in host_sets]
+    n_in = [int(i.shape[0]) for _, i in host_sets]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident throughput
+    for w in range(args.warmup):
+        layer.step(*dev_sets[w % ROTATE])
+    barrier()
+    l0 = _ext.kernel_launches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        voxels = 0
+        for s in range(args.steps):
+            out = layer.step(*dev_sets[s % ROTATE])
+            voxels += n_in[s % ROTATE]
+        ev1.record()
+        barrier()
+    launches = _ext.kernel_launches() - l0
+    ms = ev0.elapsed_time(ev1)
+    _ext.check_status(dev)
+    n_out_conv = None
+
+    # ---- end to end from pinned host buffers through the public API
+    def e2e_step(s):
+        f, i = pinned[s % ROTATE]
+        fd = f.to(dev, non_blocking=True)
+        idd = i.to(dev, non_blocking=True)
+        o = layer.step(fd, idd)
+        return o.features.cpu(), o.indices.cpu()
+
+    for w in range(min(args.warmup, 3)):
+        e2e_step(w)
+    barrier()
+    t0 = time.perf_counter()
+    vox_e2e = 0
+    d2h = 0
+    for s in range(args.steps):
+        of, oi = e2e_step(s)
+        vox_e2e += n_in[s % ROTATE]
+        d2h = of.numel() * 4 + oi.numel() * 4
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h2d = int(np.mean([f.numel() * 4 + i.numel() * 4 for f, i in pinned]))
+
+    # ---- dominant kernel alone: conv_fwd_tf32_kernel, CUDA events on the launching stream
+    from ss_conv.sp_ops.ops import get_indice_pairs
+    kern_ms, alg_bytes, flops = [], [], []
+    prepared = []
+    with torch.no_grad():
+        flt = layer.conv.kernel.filters().reshape(-1, layer.conv.in_channels, layer.conv.out_channels)
+        for f, i in dev_sets:
+            outids, pairs, num = get_indice_pairs(i, cfg["batch"], [cfg["V"]] * 3, cfg["k"], cfg["stride"], cfg["pad"])
+            prepared.append((f, _ext.neighbour_table(pairs, num, outids.shape[0]), outids.shape[0], int(num.sum().item())))
+        for it in range(3 + 12):
+            f, nbr, n_out, P = prepared[it % ROTATE]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _ext.conv_forward(f, flt, nbr, n_out, "tf32")
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                kern_ms.append(a.elapsed_time(b))
+                K, ci, co = flt.shape
+                alg_bytes.append(4 * (f.shape[0] * ci + n_out * co + K * ci * co) + 8 * P)
+                flops.append(2.0 * P * ci * co)
+    n_out_conv = prepared[0][2]
+    peak, peak_src = peaks()
+    achieved = float(np.mean(alg_bytes)) / (float(np.mean(kern_ms)) * 1e-3) / 1e9
+
+    # ---- reduce over ranks
+    stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, e2e_s = float(mx[0]), float(mx[1])
+        voxels, vox_e2e, launches = float(sm[2]), float(sm[3]), float(sm[4])
+    if rank == 0:
+        line = {
+            "metric": "active voxels/sec per SS-Conv layer", "value": voxels / (ms * 1e-3), "unit": "voxels/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate",
+            "data": "synthetic (seeded ellipsoid-surface voxels, N(0,1) features, reference-style N(0,1) kernel weights)",
+            "config": {"workload": cfg["name"], "n_in_per_batch": n_in[0], "n_out_conv": n_out_conv,
+                       "c_in": layer.conv.in_channels, "c_out": layer.conv.out_channels,
+                       "l2": "rotating %d distinct input batches (> 126 MB working set) between timed steps" % ROTATE,
+                       "step": "rulebook + materialise + pack + conv + pool rulebook + maxpool",
+                       "parallelism": "sample-sharded x%d, no data-path collective" % world},
+            "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches),
+            "clocks": clk.summary(),
+            "roofline": {"bound": "hbm", "kernel": "conv_fwd_tf32_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
+                         "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(cfg, budget_s=12.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------ CPU reference
+def ref_step_fn(cfg):
+    """One CPU step of the reference's own code path on `n_samples` samples:
+    get_indice_pairs_3d + indice_conv_fp32 + pool rulebook + indice_maxpool_fp32 on CPU tensors
+    (SS_Conv_lib/src/conv/indice_conv.h:21-131,247-343, SS_Conv_lib/src/pool/indice_maxpool.h:15-50).
+    Falls back to the numpy restatement when the compiled reference is absent."""
+    from ref_loader import load_ref_ext
+    import ssconv_oracle as O
+    ext = load_ref_ext()
+    V, k, s, p = cfg["V"], cfg["k"], cfg["stride"], cfg["pad"]
+    osz = O.conv_output_size([V] * 3, [k] * 3, [s] * 3, [p] * 3, [1] * 3)
+    psz = O.conv_output_size(osz, [cfg["pool_k"]] * 3, [cfg["pool_s"]] * 3, [0] * 3, [1] * 3)
+    if ext is not None:
+        def step(feats, ind, W, batch):
+            ti = torch.from_numpy(ind)
+            o, pr, n = ext.get_indice_pairs_3d(ti, batch, osz, [V] * 3, [k] * 3, [s] * 3, [p] * 3, [1] * 3, [0] * 3, 0, 0)
+            y = ext.indice_conv_fp32(torch.from_numpy(feats), torch.from_numpy(W), pr, n, o.shape[0], 0, 0)
+            o2, pr2, n2 = ext.get_indice_pairs_3d(o.contiguous(), batch, psz, osz, [cfg["pool_k"]] * 3, [cfg["pool_s"]] * 3,
+                                                  [0] * 3, [1] * 3, [0] * 3, 0, 0)
+            return ext.indice_maxpool_fp32(y, pr2, n2, o2.shape[0])
+        return step, "reference"
+
+    def step(feats, ind, W, batch):
+        o, pr, n = O.get_indice_pairs(ind, batch, [V] * 3, k, s, p, 1, False)
+        y = O.indice_conv(feats, W, pr, n, o.shape[0])
+        o2, pr2, n2 = O.get_indice_pairs(o, batch, osz, cfg["pool_k"], cfg["pool_s"], 0, 1, False)
+        return O.indice_maxpool(y, pr2, n2, o2.shape[0])
+    return step, "port"
+
+
+def cpu_inputs(cfg, n_samples):
+    from ss_conv.utils import synthetic as S
+    ind = S.surface_voxels(range(n_samples), cfg["V"], cfg["n_pts"], base_seed=1000)
+    ci = sum(m * (2 * l + 1) for l, m in enumerate(cfg["irreps"]))
+    co = ci + sum(cfg["irreps"][1:])
+    feats = S.features(ind.shape[0], ci, 77)
+    W = (np.random.RandomState(5).randn(cfg["k"], cfg["k"], cfg["k"], ci, co) / np.sqrt(ci * cfg["k"] ** 3)).astype(np.float32)
+    return feats, ind, W
+
+
+def cpu_baseline(cfg, budget_s=12.0, n_samples=8):
+    step, kind = ref_step_fn(cfg)
+    feats, ind, W = cpu_inputs(cfg, n_samples)
+    step(feats, ind, W, n_samples)  # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 3 or (time.perf_counter() - t0 < budget_s and reps < 200):
+        step(feats, ind, W, n_samples)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": ind.shape[0] * reps / dt, "unit": "voxels/s", "cores": torch.get_num_threads(), "kind": kind,
+            "host_cpus": os.cpu_count(),
+            "sample": "%d of %d samples of the cfg2 batch (%d active voxels), %d repetitions, same step "
+                      "(rulebook + conv + pool rulebook + maxpool; filters pre-materialised); rulebook/gather/scatter "
+                      "are single-threaded C++ loops, the GEMM uses torch's CPU threads" % (n_samples, cfg["batch"], ind.shape[0], reps)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    cfg = CFG2
+    n_samples = 8
+    step, kind = ref_step_fn(cfg)
+    feats, ind, W = cpu_inputs(cfg, n_samples)
+    for _ in range(max(1, min(args.warmup, 3))):
+        step(feats, ind, W, n_samples)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(feats, ind, W, n_samples)
+    dt = time.perf_counter() - t0
+    value = ind.shape[0] * args.steps / dt
+    sample = ("each step = %d of the %d samples of the cfg2 batch (%d active voxels) through the reference's C++ CPU "
+              "path" % (n_samples, cfg["batch"], ind.shape[0]))
+    line = {"impl": "reference", "metric": "active voxels/sec per SS-Conv layer", "value": value, "unit": "voxels/s",
+            "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic (same generator as the GPU arm)",
+            "config": {"workload": cfg["name"], "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "voxels/s", "cores": torch.get_num_threads(), "kind": kind,
+                             "host_cpus": os.cpu_count(), "sample": sample},
+            "e2e": {"value": value, "unit": "voxels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -44,6 +44,9 @@ int ssc_version(void);
 /* Message of the last failing call on this host thread ("" if none).  Replaces the exception
  * text of TV_ASSERT_RT_ERR / TV_CHECK_CUDA_ERR (SS_Conv_lib/src/utils/tensorview.h:70-101). */
 const char *ssc_last_error(void);
+/* Number of CUDA kernels this library has launched in the calling process (memsets and copies
+ * not counted).  No reference counterpart. */
+unsigned long long ssc_kernel_launches(void);
 /* 1 if the tcgen05 tensor-core kernels were compiled in (always for sm_100a builds). */
 int ssc_has_tcgen05(void);
 
@@ -120,9 +123,8 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  * as ONE launch, output-stationary (no scatter atomics, deterministic).
  * precision: SSC_PREC_FP32 = exact fp32 FMA on CUDA cores (filters = [K,Cin,Cout] fp32);
  *            SSC_PREC_TF32 = tcgen05 tensor cores, TF32 operands (filters = packed image).
- * epilogue (optional, all pointers may be NULL): per-channel affine scale/shift over the
- * c_out channels (eval-mode BatchNorm folded), then the gated activation described at
- * ssc_bn_gate_fwd with gate_of_channel; the output then has c_final channels. */
+ * status: device int32 that receives a non-zero value if a bounded wait inside the kernel
+ * ran out (may be NULL). */
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
@@ -183,9 +185,12 @@ int ssc_p2v_fill(const float *points, const int32_t *batch_ids, const float *fea
 /* three_nn / three_interpolate_fp replacements
  * (SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:8-55, 79-101): unknown [N,4] and
  * known [M,4] are (batch,x,y,z) float rows; dist2 [N,3] squared distances, idx [N,3].
- * Same neighbours and tie order as the reference's exhaustive scan. */
+ * Same neighbours and tie order as the reference's exhaustive scan.  scratch (device,
+ * ssc_three_nn_scratch_bytes(m) bytes) holds the batch-id range of each 1024-row tile of
+ * `known`, which lets a block skip tiles of other samples. */
+size_t ssc_three_nn_scratch_bytes(int m);
 int ssc_three_nn(int n, int m, const float *unknown, const float *known, float *dist2,
-                 int32_t *idx, void *stream);
+                 int32_t *idx, void *scratch, size_t scratch_bytes, void *stream);
 int ssc_three_interpolate_fwd(int c, int m, int n, const float *points, const int32_t *idx,
                               const float *weight, float *out, void *stream);
 
@@ -210,7 +215,8 @@ int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const float *scale, c
                     int gate_act, const float *scalar_bias, const float *gate_bias, float *out,
                     void *stream);
 /* Training-mode statistics (batchnorm.py:73-99): mean [n_scalar] of scalar fields and
- * var [n_field] = batch mean of the squared field norm (about the batch mean for scalars). */
+ * var = batch mean of the squared field norm (about the batch mean for scalars); `var` must
+ * have room for n_field + c floats: the first n_field are the result, the tail is scratch. */
 int ssc_bn_stats(const float *x, int n, int c, const int32_t *field_of_channel,
                  const int32_t *scalar_of_channel, int n_field, int n_scalar, float *mean,
                  float *var, void *stream);

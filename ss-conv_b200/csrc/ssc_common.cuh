@@ -13,6 +13,9 @@ namespace ssc {
 char *error_buffer();
 int fail(int code, const char *fmt, ...);
 
+// Kernel-launch bookkeeping behind ssc_kernel_launches().
+void note_launches(int n);
+
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
 #define SSC_CHECK_LAUNCH(name)                                                     \
@@ -65,5 +68,8 @@ inline uint32_t hash_buckets_for(int n) {
   while (b < want) b <<= 1;
   return b;
 }
+
+int bitmap_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long n_words, const int shape[3],
+                  int n_out, int32_t *out_indices, cudaStream_t st);
 
 }  // namespace ssc

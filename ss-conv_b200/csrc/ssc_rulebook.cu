@@ -11,6 +11,7 @@
 // Submanifold convolution skips 2-4 (outputs are the inputs).
 // Everything is integer work bound by HBM/L2 traffic; no tensor cores involved.
 #include "ssc_common.cuh"
+#include "ssc_scan.cuh"
 
 namespace ssc {
 
@@ -118,98 +119,6 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
   }
   uint32_t flat = (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]);
   atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
-}
-
-__device__ __forceinline__ uint32_t block_reduce_sum(uint32_t v, uint32_t *smem) {
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) smem[warp] = v;
-  __syncthreads();
-  uint32_t r = 0;
-  if (warp == 0) {
-    r = lane < (blockDim.x >> 5) ? smem[lane] : 0;
-    for (int o = 16; o > 0; o >>= 1) r += __shfl_down_sync(0xffffffffu, r, o);
-  }
-  return r;  // valid in thread 0
-}
-
-// Exclusive scan of one value per thread over a block of up to 1024 threads.
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *smem, uint32_t *total) {
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint32_t incl = v;
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) smem[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    uint32_t w = lane < (blockDim.x >> 5) ? smem[lane] : 0;
-    uint32_t wi = w;
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += t;
-    }
-    smem[lane] = wi - w;           // exclusive warp offsets
-    if (lane == 31) smem[32] = wi; // block total
-  }
-  __syncthreads();
-  uint32_t res = smem[warp] + incl - v;
-  if (total) *total = smem[32];
-  __syncthreads();
-  return res;
-}
-
-// 256 threads x 4 words per block.
-__global__ void popc_block_sums_kernel(const uint32_t *__restrict__ bitmap, long long n_words,
-                                       uint32_t *block_sums) {
-  __shared__ uint32_t smem[33];
-  long long base = (long long)blockIdx.x * 1024 + threadIdx.x * 4;
-  uint32_t s = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    if (base + i < n_words) s += __popc(bitmap[base + i]);
-  uint32_t r = block_reduce_sum(s, smem);
-  if (threadIdx.x == 0) block_sums[blockIdx.x] = r;
-}
-
-// Single block: in-place exclusive scan of block_sums[0..n); writes the total to
-// block_sums[n] and to the two int32 outputs.
-__global__ void scan_block_sums_kernel(uint32_t *block_sums, int n, int32_t *total_a, int32_t *total_b) {
-  __shared__ uint32_t smem[33];
-  uint32_t running = 0;
-  for (int base = 0; base < n; base += blockDim.x) {
-    int i = base + threadIdx.x;
-    uint32_t v = i < n ? block_sums[i] : 0;
-    uint32_t tot;
-    uint32_t ex = block_exclusive_scan(v, smem, &tot);
-    if (i < n) block_sums[i] = running + ex;
-    running += tot;
-  }
-  if (threadIdx.x == 0) {
-    block_sums[n] = running;
-    if (total_a) *total_a = (int32_t)running;
-    if (total_b) *total_b = (int32_t)running;
-  }
-}
-
-__global__ void word_prefix_kernel(const uint32_t *__restrict__ bitmap, long long n_words,
-                                   const uint32_t *__restrict__ block_sums, uint32_t *word_prefix) {
-  __shared__ uint32_t smem[33];
-  long long base = (long long)blockIdx.x * 1024 + threadIdx.x * 4;
-  uint32_t c[4];
-  uint32_t s = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    c[i] = (base + i < n_words) ? __popc(bitmap[base + i]) : 0;
-    s += c[i];
-  }
-  uint32_t ex = block_exclusive_scan(s, smem, nullptr) + block_sums[blockIdx.x];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (base + i < n_words) word_prefix[base + i] = ex;
-    ex += c[i];
-  }
 }
 
 __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
@@ -375,12 +284,12 @@ static int check_volume(int batch, const int shape[3], const char *what) {
 }
 
 static int build_hash(const int32_t *indices, int n_in, int batch, const Geometry &g, RulebookScratch &s,
-                      cudaStream_t st) {
+                      int32_t *status, cudaStream_t st) {
   cudaMemsetAsync(s.table, 0xFF, (size_t)s.n_buckets * kBucketSlots * 8, st);
   cudaMemsetAsync(s.misc, 0, 256, st);
   if (n_in > 0) {
-    hash_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.table,
-                                                           s.n_buckets - 1, s.misc + 1);
+    { hash_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.table,
+                                                           s.n_buckets - 1, status ? status : s.misc + 1); note_launches(1); }
   }
   SSC_CHECK_LAUNCH("hash_insert");
   return 0;
@@ -393,18 +302,31 @@ static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, i
   int n_chunks = ceil_div(n_out > 0 ? n_out : 1, kChunk);
   if (n_chunks > s.n_chunks_cap) return fail(SSC_ERR_SCRATCH, "rulebook: n_out exceeds the scratch capacity");
   dim3 grid(n_chunks, K);
-  lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
-                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks);
+  { lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
+                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks); note_launches(1); }
   SSC_CHECK_LAUNCH("lookup_neighbours");
   if (indice_num == nullptr) return 0;
-  scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num);
+  { scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num); note_launches(1); }
   SSC_CHECK_LAUNCH("scan_chunks");
   if (pairs != nullptr && n_in > 0) {
     int n_chunks_in = ceil_div(n_in, kChunk);
     dim3 grid2(n_chunks > n_chunks_in ? n_chunks : n_chunks_in, K);
-    fill_pairs_kernel<<<grid2, kChunk, 0, st>>>(nbr, n_out, n_in, s.chunk_counts, n_chunks, indice_num, pairs);
+    { fill_pairs_kernel<<<grid2, kChunk, 0, st>>>(nbr, n_out, n_in, s.chunk_counts, n_chunks, indice_num, pairs); note_launches(1); }
     SSC_CHECK_LAUNCH("fill_pairs");
   }
+  return 0;
+}
+
+// Rows (b,x,y,z) of every set bit of a cell bitmap over a [batch, shape] grid, in ascending
+// flat-index order (shared with the voxelizer).
+int bitmap_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long n_words, const int shape[3],
+                  int n_out, int32_t *out_indices, cudaStream_t st) {
+  Geometry g;
+  memset(&g, 0, sizeof(g));
+  for (int d = 0; d < 3; ++d) g.out_shape[d] = shape[d];
+  { decode_outputs_kernel<<<ceil_div(n_words, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out,
+                                                                (int4 *)out_indices); note_launches(1); }
+  SSC_CHECK_LAUNCH("bitmap_decode");
   return 0;
 }
 
@@ -433,9 +355,8 @@ extern "C" int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, co
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_subm: scratch %zu < %zu bytes", scratch_bytes, s.total);
   cudaStream_t st = as_stream(stream);
-  if (int e = build_hash(indices, n_in, batch, g, s, st)) return e;
+  if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
   if (int e = lookup_and_compact(indices, n_in, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
-  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
   SSC_CHECK_LAUNCH("rulebook_subm");
   return SSC_OK;
 }
@@ -457,17 +378,14 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_conv_count: scratch %zu < %zu bytes", scratch_bytes, s.total);
   cudaStream_t st = as_stream(stream);
-  if (int e = build_hash(indices, n_in, batch, g, s, st)) return e;
+  if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
   cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
   long long threads = (long long)n_in * g.K;
   if (threads > 0) {
-    mark_outputs_kernel<<<ceil_div(threads, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap);
+    { mark_outputs_kernel<<<ceil_div(threads, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
     SSC_CHECK_LAUNCH("mark_outputs");
   }
-  popc_block_sums_kernel<<<s.n_scan_blocks, 256, 0, st>>>(s.bitmap, s.n_words, s.block_sums);
-  scan_block_sums_kernel<<<1, 1024, 0, st>>>(s.block_sums, s.n_scan_blocks, s.misc, n_out_dev);
-  word_prefix_kernel<<<s.n_scan_blocks, 256, 0, st>>>(s.bitmap, s.n_words, s.block_sums, s.word_prefix);
-  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
+  if (int e = exclusive_scan_u32<true>(s.bitmap, s.n_words, s.word_prefix, s.block_sums, s.misc, n_out_dev, st)) return e;
   SSC_CHECK_LAUNCH("rulebook_conv_count");
   return SSC_OK;
 }
@@ -490,12 +408,11 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
   SSC_REQUIRE((long long)n_out <= s.out_cap, "rulebook_conv_fill: n_out %d exceeds the possible maximum", n_out);
   cudaStream_t st = as_stream(stream);
   if (n_out > 0) {
-    decode_outputs_kernel<<<ceil_div(s.n_words, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
-                                                                   (int4 *)out_indices);
+    { decode_outputs_kernel<<<ceil_div(s.n_words, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
+                                                                   (int4 *)out_indices); note_launches(1); }
     SSC_CHECK_LAUNCH("decode_outputs");
   }
   if (int e = lookup_and_compact(out_indices, n_out, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
-  if (status) cudaMemcpyAsync(status, s.misc + 1, 4, cudaMemcpyDeviceToDevice, st);
   SSC_CHECK_LAUNCH("rulebook_conv_fill");
   return SSC_OK;
 }
@@ -509,7 +426,7 @@ extern "C" int ssc_pairs_to_nbr(const int32_t *pairs, const int32_t *indice_num,
   cudaMemsetAsync(nbr, 0xFF, (size_t)K * n_out * 4, st);
   if (n_cols > 0) {
     dim3 grid(ceil_div(n_cols, 256), K);
-    pairs_to_nbr_kernel<<<grid, 256, 0, st>>>(pairs, indice_num, n_cols, n_out, swap, nbr);
+    { pairs_to_nbr_kernel<<<grid, 256, 0, st>>>(pairs, indice_num, n_cols, n_out, swap, nbr); note_launches(1); }
   }
   SSC_CHECK_LAUNCH("pairs_to_nbr");
   return SSC_OK;

@@ -1,0 +1,474 @@
+"""Native-op module of the B200 build: the names the reference exports from its pybind11
+extension `ss_conv._ext` (SS_Conv_lib/src/ss_conv_ops_api.cpp:15-55), implemented as thin
+ctypes calls into the C-ABI CUDA library libssconv_b200.so (include/ssconv_b200.h).
+
+PyTorch is used only to allocate device memory and to supply the current CUDA stream.  There
+is no CPU path: every function raises if the library is missing or a tensor is not on a CUDA
+device.  Forward / inference entry points are implemented; the backward entry points raise
+NotImplementedError.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libssconv_b200.so")
+
+PREC_FP32, PREC_TF32 = 0, 1
+_precision = os.environ.get("SSCONV_PRECISION", "auto")
+
+c_int, c_size_t, c_void_p, c_float = ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_float
+_I3 = ctypes.c_int * 3
+_F3 = ctypes.c_float * 3
+
+# name -> (restype, argtypes); kept in one table so tests can check it against the header
+SIGNATURES = {
+    "ssc_version": (c_int, []),
+    "ssc_last_error": (ctypes.c_char_p, []),
+    "ssc_has_tcgen05": (c_int, []),
+    "ssc_kernel_launches": (ctypes.c_ulonglong, []),
+    "ssc_rulebook_scratch_bytes": (c_size_t, [c_int, c_int, _I3, c_int]),
+    "ssc_rulebook_subm": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_size_t, c_void_p]),
+    "ssc_rulebook_conv_count": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_void_p,
+                                        c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_rulebook_conv_fill": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_int, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_pairs_to_nbr": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_materialize": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_void_p, c_void_p]),
+    "ssc_conv_packed_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "ssc_conv_pack_filters": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                             c_void_p, c_void_p]),
+    "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_global_avgpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_global_maxpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ssc_batch_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_voxel2point_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "ssc_voxelize_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "ssc_p2v_scratch_bytes": (c_size_t, [c_int, c_int, _I3]),
+    "ssc_p2v_count": (c_int, [c_void_p, c_void_p, c_int, c_int, _I3, _F3, c_void_p, c_void_p, c_void_p, c_size_t,
+                              c_void_p]),
+    "ssc_p2v_fill": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, _I3, _F3, c_int, c_int, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_three_nn_scratch_bytes": (c_size_t, [c_int]),
+    "ssc_three_nn": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_three_interpolate_fwd": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ssc_bn_fold": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
+                            c_void_p, c_void_p]),
+    "ssc_bn_gate_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ssc_bn_stats": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+}
+
+_lib_handle = None
+
+
+def lib():
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib_handle
+    if _lib_handle is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError("libssconv_b200.so is missing: run `python ss-conv_b200/build.py` "
+                               "(there is no CPU or PyTorch fallback)")
+        h = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib_handle = h
+    return _lib_handle
+
+
+def kernel_launches():
+    """CUDA kernels launched by the library in this process so far."""
+    return int(lib().ssc_kernel_launches())
+
+
+def set_precision(mode):
+    """'fp32' (exact CUDA-core path), 'tf32' (tcgen05 tensor cores) or 'auto'
+    (tf32 when the layer has at least 16 input channels)."""
+    global _precision
+    if mode not in ("fp32", "tf32", "auto"):
+        raise ValueError("precision must be 'fp32', 'tf32' or 'auto'")
+    _precision = mode
+
+
+def get_precision():
+    return _precision
+
+
+def _check(rc):
+    if rc != 0:
+        msg = lib().ssc_last_error().decode()
+        if rc == 1:
+            raise ValueError("ssconv_b200: " + msg)
+        raise RuntimeError("ssconv_b200 (code %d): %s" % (rc, msg))
+
+
+def _p(t, dtype=None):
+    """Device pointer of a contiguous CUDA tensor (None -> NULL)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("ssconv_b200 runs on CUDA tensors only (got a %s tensor)" % t.device.type)
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError("expected dtype %s, got %s" % (dtype, t.dtype))
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _i3(v):
+    return _I3(*[int(x) for x in v])
+
+
+_status = {}
+
+
+def status_word(device):
+    """Per-device int32 that kernels OR error bits into (read it with check_status())."""
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronising read of the device status word; raises on a recorded kernel problem."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    s = status_word(device)
+    v = int(s.item())
+    if v != 0:
+        s.zero_()
+        raise RuntimeError("ssconv_b200 kernel status 0x%x (1: coordinate out of range, 2: hash full, "
+                           "16: tensor-core pipeline wait ran out)" % v)
+
+
+# =============================================================================== rulebook
+def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation, subm, transpose,
+                   want_pairs=True):
+    """(outids, nbr[K,n_out], pairs[K,2,n_in] or None, indice_num[K]) for one layer."""
+    L = lib()
+    if indices.dtype != torch.int32:
+        raise TypeError("indices must be int32")
+    indices = indices.contiguous()
+    dev = indices.device
+    n_in = indices.shape[0]
+    K = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
+    grid = spatial_shape if subm else out_shape
+    for shp in (spatial_shape, grid):
+        if int(batch_size) * int(shp[0]) * int(shp[1]) * int(shp[2]) >= 2 ** 31 - 1:
+            raise ValueError("ssconv_b200: batch*volume does not fit the int32 flat index")
+    if K > 256:
+        raise ValueError("ssconv_b200: kernel volume %d > 256" % K)
+    sbytes = L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(grid), K)
+    scratch = torch.empty(max(int(sbytes), 256), dtype=torch.uint8, device=dev)
+    num = torch.empty(K, dtype=torch.int32, device=dev)
+    pairs = torch.empty((K, 2, n_in), dtype=torch.int32, device=dev) if want_pairs else None
+    st = status_word(dev)
+    if subm:
+        nbr = torch.empty((K, n_in), dtype=torch.int32, device=dev)
+        _check(L.ssc_rulebook_subm(_p(indices), n_in, int(batch_size), _i3(spatial_shape), _i3(ksize), _i3(dilation),
+                                   _p(nbr), _p(pairs), _p(num), _p(st), _p(scratch), scratch.numel(), _stream()))
+        return indices, nbr, pairs, num
+    n_out_dev = torch.empty(1, dtype=torch.int32, device=dev)
+    geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
+    _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
+                                     scratch.numel(), _stream()))
+    n_out = int(n_out_dev.item())  # the one host sync of a regular rulebook
+    outids = torch.empty((n_out, 4), dtype=torch.int32, device=dev)
+    nbr = torch.empty((K, n_out), dtype=torch.int32, device=dev)
+    _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, n_out, _p(outids), _p(nbr), _p(pairs),
+                                    _p(num), _p(st), _p(scratch), scratch.numel(), _stream()))
+    return outids, nbr, pairs, num
+
+
+def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
+                        out_padding, subm, transpose):
+    """[outids, indicePairs [K,2,N], indiceNum [K]] as getIndicePair<3> returns them
+    (SS_Conv_lib/src/conv/indice_conv.h:21-131).  The neighbour table the CUDA kernels use is
+    attached to the returned pair tensor as `_ssc_nbr`."""
+    outids, nbr, pairs, num = build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding,
+                                             dilation, bool(subm), bool(transpose))
+    pairs._ssc_nbr = nbr
+    return [outids, pairs, num]
+
+
+def get_indice_pairs_grid_3d(indices, grid, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
+                             out_padding, subm, transpose):
+    """Pre-allocated-grid variant (indice_conv.h:133-244): the grid is not needed here."""
+    return get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
+                               out_padding, subm, transpose)
+
+
+def _no_2d(*a, **k):
+    raise NotImplementedError("2-D rulebooks are not part of the steerable (3-D) path")
+
+
+get_indice_pairs_2d = _no_2d
+get_indice_pairs_grid_2d = _no_2d
+
+
+def neighbour_table(pairs, num, n_out, inverse=False):
+    """nbr [K, n_out] for a reference-format rulebook (cached on the pair tensor when possible)."""
+    nbr = getattr(pairs, "_ssc_nbr", None)
+    if nbr is not None and not inverse and nbr.shape[1] == n_out and nbr.device == pairs.device:
+        return nbr
+    cache = "_ssc_nbr_inv" if inverse else "_ssc_nbr"
+    cached = getattr(pairs, cache, None)
+    if cached is not None and cached.shape[1] == n_out:
+        return cached
+    pairs = pairs.contiguous()
+    K, _, n_cols = pairs.shape
+    nbr = torch.empty((K, n_out), dtype=torch.int32, device=pairs.device)
+    _check(lib().ssc_pairs_to_nbr(_p(pairs, torch.int32), _p(num.to(pairs.device), torch.int32), K, n_cols, int(n_out),
+                                  int(bool(inverse)), _p(nbr), _stream()))
+    try:
+        setattr(pairs, cache, nbr)
+    except Exception:
+        pass
+    return nbr
+
+
+# ============================================================== materialisation and conv
+def materialize(weight, basis, block_table, n_blocks_in, out_field, in_field, c_out, c_in, K):
+    flt = torch.empty((K, c_in, c_out), dtype=torch.float32, device=weight.device)
+    _check(lib().ssc_materialize(_p(weight, torch.float32), _p(basis, torch.float32), _p(block_table, torch.int32),
+                                 int(n_blocks_in), _p(out_field, torch.int32), _p(in_field, torch.int32), int(c_out),
+                                 int(c_in), int(K), _p(flt), _stream()))
+    return flt
+
+
+def pack_filters(filters_kio):
+    """TF32 tensor-core operand image of contiguous filters [K, Cin, Cout]."""
+    K, c_in, c_out = filters_kio.shape
+    nbytes = lib().ssc_conv_packed_bytes(K, c_in, c_out, PREC_TF32)
+    if nbytes == 0:
+        raise ValueError("channel count not supported by the tensor-core path")
+    packed = torch.empty(int(nbytes), dtype=torch.uint8, device=filters_kio.device)
+    _check(lib().ssc_conv_pack_filters(_p(filters_kio, torch.float32), K, c_in, c_out, PREC_TF32, _p(packed), _stream()))
+    return packed
+
+
+def _resolve_precision(c_in, c_out, precision=None):
+    mode = precision or _precision
+    if mode == "auto":
+        mode = "tf32" if (c_in >= 16 and c_out <= 512) else "fp32"
+    return mode
+
+
+def conv_forward(features, filters, nbr, n_out, precision=None):
+    """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch)."""
+    if filters.dim() != 3:
+        filters = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
+    K, c_in, c_out = filters.shape
+    if features.shape[1] != c_in:
+        raise ValueError("features have %d channels, filters expect %d" % (features.shape[1], c_in))
+    features = features.contiguous()
+    out = torch.empty((n_out, c_out), dtype=torch.float32, device=features.device)
+    mode = _resolve_precision(c_in, c_out, precision)
+    st = status_word(features.device)
+    if mode == "tf32":
+        packed = getattr(filters, "_ssc_packed", None)
+        if packed is None or getattr(filters, "_ssc_packed_version", None) != filters._version:
+            packed = pack_filters(filters.contiguous())
+            try:
+                filters._ssc_packed = packed
+                filters._ssc_packed_version = filters._version
+            except Exception:
+                pass
+        _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
+                                  _p(nbr, torch.int32), int(n_out), PREC_TF32, _p(out), _p(st), _stream()))
+    else:
+        filters = filters.contiguous()
+        _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(filters, torch.float32), K,
+                                  c_out, _p(nbr, torch.int32), int(n_out), PREC_FP32, _p(out), _p(st), _stream()))
+    return out
+
+
+def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, inverse, subm):
+    """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:43-45); filters [k,k,k,Cin,Cout]
+    (a permuted view is accepted).  The submanifold centre needs no special case."""
+    if features.dtype != torch.float32:
+        raise TypeError("indice_conv_fp32 expects float32 features")
+    c_in, c_out = filters.shape[-2], filters.shape[-1]
+    cached = getattr(filters, "_ssc_flat", None)
+    if cached is not None and cached[0] == filters._version:
+        flt = cached[1]
+    else:
+        flt = filters.reshape(-1, c_in, c_out).contiguous()  # no copy when already contiguous
+        try:
+            filters._ssc_flat = (filters._version, flt)
+        except Exception:
+            pass
+    nbr = neighbour_table(indice_pairs, indice_num, int(num_act_out), bool(inverse))
+    return conv_forward(features, flt, nbr, int(num_act_out))
+
+
+def _not_built(name):
+    def f(*a, **k):
+        raise NotImplementedError(name + " is not built: this library covers the forward (inference) path; "
+                                  "fp16 storage and the backward kernels are listed as next steps")
+    f.__name__ = name
+    return f
+
+
+indice_conv_half = _not_built("indice_conv_half")
+indice_conv_backward_fp32 = _not_built("indice_conv_backward_fp32")
+indice_conv_backward_half = _not_built("indice_conv_backward_half")
+
+
+# ================================================================================== pools
+def indice_maxpool_fp32(features, indice_pairs, indice_num, num_act):
+    features = features.contiguous()
+    nbr = neighbour_table(indice_pairs, indice_num, int(num_act))
+    out = torch.empty((int(num_act), features.shape[1]), dtype=torch.float32, device=features.device)
+    _check(lib().ssc_maxpool_fwd(_p(features, torch.float32), features.shape[1], _p(nbr), nbr.shape[0], int(num_act),
+                                 _p(out), _stream()))
+    return out
+
+
+def indice_avgpool_fp32(features, indice_pairs, indice_num, num_act, summaryrf):
+    features = features.contiguous()
+    nbr = neighbour_table(indice_pairs, indice_num, int(num_act))
+    out = torch.empty((int(num_act), features.shape[1]), dtype=torch.float32, device=features.device)
+    rf = None if summaryrf is None else summaryrf.to(torch.int32).contiguous()
+    _check(lib().ssc_avgpool_fwd(_p(features, torch.float32), features.shape[1], _p(nbr), nbr.shape[0], int(num_act),
+                                 _p(rf), _p(out), _stream()))
+    return out
+
+
+def indiceSummaryRF(indice_pairs, indice_num, num_act):
+    nbr = neighbour_table(indice_pairs, indice_num, int(num_act))
+    rf = torch.empty(int(num_act), dtype=torch.int32, device=nbr.device)
+    _check(lib().ssc_summary_rf(_p(nbr), nbr.shape[0], int(num_act), _p(rf), _stream()))
+    return rf
+
+
+indice_maxpool_half = _not_built("indice_maxpool_half")
+indice_avgpool_half = _not_built("indice_avgpool_half")
+indice_maxpool_backward_fp32 = _not_built("indice_maxpool_backward_fp32")
+indice_maxpool_backward_half = _not_built("indice_maxpool_backward_half")
+indice_avgpool_backward_fp32 = _not_built("indice_avgpool_backward_fp32")
+indice_avgpool_backward_half = _not_built("indice_avgpool_backward_half")
+indice_field_maxpool_fp32 = _not_built("indice_field_maxpool_fp32")
+indice_field_maxpool_half = _not_built("indice_field_maxpool_half")
+
+
+def global_avgpool_fp(feats, offsets, out, maxidx, n_proposal, c):
+    _check(lib().ssc_global_avgpool_fwd(_p(feats, torch.float32), _p(offsets, torch.int32), int(n_proposal), int(c),
+                                        _p(out, torch.float32), _stream()))
+
+
+def global_maxpool_fp(feats, offsets, out, maxidx, n_proposal, c):
+    _check(lib().ssc_global_maxpool_fwd(_p(feats, torch.float32), _p(offsets, torch.int32), int(n_proposal), int(c),
+                                        _p(out, torch.float32), _p(maxidx, torch.int32), _stream()))
+
+
+global_avgpool_bp = _not_built("global_avgpool_bp")
+global_maxpool_bp = _not_built("global_maxpool_bp")
+
+
+def batch_offsets(indices, batch_size):
+    """Row offsets [B+1] (int32, on device) of the samples of an indices tensor, no host sync."""
+    off = torch.empty(int(batch_size) + 1, dtype=torch.int32, device=indices.device)
+    _check(lib().ssc_batch_offsets(_p(indices.contiguous(), torch.int32), indices.shape[0], int(batch_size), _p(off),
+                                   _stream()))
+    return off
+
+
+# =========================================================================== voxelization
+def voxel2point_map(inverse, ids, output_maps, n_point, max_active, mode):
+    _check(lib().ssc_voxel2point_map(_p(inverse, torch.int32), _p(ids, torch.int32), _p(output_maps, torch.int32),
+                                     int(n_point), output_maps.shape[0], int(max_active), int(mode), _stream()))
+
+
+def voxelize_fp(feats, output_feats, map_rule, mode, n_voxel, max_active, c):
+    _check(lib().ssc_voxelize_fwd(_p(feats, torch.float32), _p(output_feats, torch.float32), _p(map_rule, torch.int32),
+                                  int(mode), int(n_voxel), int(max_active), int(c), _stream()))
+
+
+voxelize_bp = _not_built("voxelize_bp")
+voxelize_idx = _not_built("voxelize_idx")
+point_recover_fp = _not_built("point_recover_fp")
+point_recover_bp = _not_built("point_recover_bp")
+
+
+def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode):
+    """Fused voxelizer core: (voxel_indices [M,4] int32, inverse [N] int32, voxel_feats [M,C])
+    for batch-sorted, in-range points (one host sync for M)."""
+    L = lib()
+    dev = points.device
+    points = points.contiguous().float()
+    feats = feats.contiguous().float()
+    batch_ids = batch_ids.contiguous().to(torch.int32)
+    n = points.shape[0]
+    sbytes = L.ssc_p2v_scratch_bytes(n, int(batch_size), _i3(grid))
+    scratch = torch.empty(max(int(sbytes), 256), dtype=torch.uint8, device=dev)
+    m_dev = torch.empty(1, dtype=torch.int32, device=dev)
+    st = status_word(dev)
+    unit3 = _F3(*[float(u) for u in unit])
+    _check(L.ssc_p2v_count(_p(points), _p(batch_ids), n, int(batch_size), _i3(grid), unit3, _p(m_dev), _p(st),
+                           _p(scratch), scratch.numel(), _stream()))
+    m = int(m_dev.item())
+    vox = torch.empty((m, 4), dtype=torch.int32, device=dev)
+    inverse = torch.empty(n, dtype=torch.int32, device=dev)
+    vfeat = torch.empty((m, feats.shape[1]), dtype=torch.float32, device=dev)
+    _check(L.ssc_p2v_fill(_p(points), _p(batch_ids), _p(feats), n, feats.shape[1], int(batch_size), _i3(grid), unit3,
+                          int(mode), m, _p(vox), _p(inverse), _p(vfeat), _p(scratch), scratch.numel(), _stream()))
+    return vox, inverse, vfeat
+
+
+def three_nn(n, m, unknown, known, dist2, idx):
+    L = lib()
+    sbytes = max(int(L.ssc_three_nn_scratch_bytes(int(m))), 256)
+    scratch = torch.empty(sbytes, dtype=torch.uint8, device=unknown.device)
+    _check(L.ssc_three_nn(int(n), int(m), _p(unknown, torch.float32), _p(known, torch.float32),
+                          _p(dist2, torch.float32), _p(idx, torch.int32), _p(scratch), scratch.numel(), _stream()))
+
+
+def three_interpolate_fp(c, m, n, points, idx, weight, out):
+    _check(lib().ssc_three_interpolate_fwd(int(c), int(m), int(n), _p(points, torch.float32), _p(idx, torch.int32),
+                                           _p(weight, torch.float32), _p(out, torch.float32), _stream()))
+
+
+three_interpolate_bp = _not_built("three_interpolate_bp")
+
+
+# ================================================================ BatchNorm / activation
+def bn_fold(running_mean, running_var, weight, bias, field_of_channel, scalar_of_channel, eps):
+    c = field_of_channel.numel()
+    scale = torch.empty(c, dtype=torch.float32, device=running_var.device)
+    shift = torch.empty_like(scale)
+    _check(lib().ssc_bn_fold(_p(running_mean), _p(running_var), _p(weight), _p(bias), _p(field_of_channel, torch.int32),
+                             _p(scalar_of_channel, torch.int32), c, float(eps), _p(scale), _p(shift), _stream()))
+    return scale, shift
+
+
+def bn_gate_forward(x, scale, shift, gate_of_channel, c_out, c_gate_base, scalar_act, gate_act, scalar_bias,
+                    gate_bias):
+    x = x.contiguous()
+    out = torch.empty((x.shape[0], int(c_out)), dtype=torch.float32, device=x.device)
+    _check(lib().ssc_bn_gate_fwd(_p(x, torch.float32), x.shape[0], x.shape[1], _p(scale), _p(shift),
+                                 _p(gate_of_channel), int(c_out), int(c_gate_base), int(scalar_act), int(gate_act),
+                                 _p(scalar_bias), _p(gate_bias), _p(out), _stream()))
+    return out
+
+
+def bn_stats(x, field_of_channel, scalar_of_channel, n_field, n_scalar):
+    x = x.contiguous()
+    mean = torch.empty(max(n_scalar, 1), dtype=torch.float32, device=x.device)
+    var = torch.empty(n_field + x.shape[1], dtype=torch.float32, device=x.device)
+    _check(lib().ssc_bn_stats(_p(x, torch.float32), x.shape[0], x.shape[1], _p(field_of_channel, torch.int32),
+                              _p(scalar_of_channel, torch.int32), int(n_field), int(n_scalar), _p(mean), _p(var),
+                              _stream()))
+    return mean[:n_scalar], var[:n_field]

@@ -1,0 +1,91 @@
+"""Irrep-wise batch normalisation (interface of SS_Conv_lib/ss_conv/batchnorm.py:13-136)."""
+import torch
+import torch.nn as nn
+
+from . import _ext
+
+
+def _channel_tables(Rs):
+    """Per channel: index of its field (one per irrep copy) and of its scalar slot (-1 for l>0)."""
+    field, scalar = [], []
+    f = s = 0
+    for m, l in Rs:
+        d = 2 * l + 1
+        for _ in range(m):
+            field += [f] * d
+            scalar += [s if d == 1 else -1] * d
+            f += 1
+            if d == 1:
+                s += 1
+    return field, scalar
+
+
+class BatchNorm(nn.Module):
+    """Scalars (l=0) are centred and scaled; fields with l>0 are only scaled by the running mean
+    of their squared norm, which keeps the layer equivariant.  Same parameters and buffers as
+    the reference (`running_mean` [n_scalar], `running_var` [n_fields], `weight`, `bias`).
+
+    Eval mode is one fused CUDA pass y = x*scale + shift with the statistics folded into
+    per-channel constants.  Training mode computes batch statistics on the GPU (two
+    reductions), updates the running buffers and applies the same pass; gradients do not flow
+    through it yet."""
+
+    def __init__(self, Rs, eps=1e-5, momentum=0.1, affine=True, reduce='mean'):
+        super().__init__()
+        self.Rs = Rs
+        self.eps = eps
+        self.momentum = momentum
+        self.affine = affine
+        self.reduce = reduce
+        num_scalar = sum(m for m, l in Rs if l == 0)
+        num_features = sum(m for m, l in Rs)
+        self.register_buffer('running_mean', torch.zeros(num_scalar))
+        self.register_buffer('running_var', torch.ones(num_features))
+        if affine:
+            self.weight = nn.Parameter(torch.ones(num_features))
+            self.bias = nn.Parameter(torch.zeros(num_scalar))
+        else:
+            self.register_parameter('weight', None)
+            self.register_parameter('bias', None)
+        self._tables = None
+
+    def __repr__(self):
+        return "{} (Rs={}, eps={}, momentum={})".format(self.__class__.__name__, self.Rs, self.eps, self.momentum)
+
+    def _device_tables(self, device):
+        if self._tables is None or self._tables[0] != device:
+            field, scalar = _channel_tables(self.Rs)
+            self._tables = (device, torch.tensor(field, dtype=torch.int32, device=device),
+                            torch.tensor(scalar, dtype=torch.int32, device=device))
+        return self._tables[1], self._tables[2]
+
+    def folded_affine(self, device, mean=None, var=None):
+        """(scale, shift) per channel for the given statistics (default: running buffers)."""
+        field, scalar = self._device_tables(device)
+        mean = self.running_mean if mean is None else mean
+        var = self.running_var if var is None else var
+        w = self.weight.detach() if self.affine else None
+        b = self.bias.detach() if self.affine else None
+        if mean.numel() == 0:
+            mean = None
+            b = None
+        return _ext.bn_fold(mean, var, w, b, field, scalar, self.eps)
+
+    def forward(self, input):
+        x = input.features
+        field, scalar = self._device_tables(x.device)
+        if field.numel() != x.size(1):
+            raise AssertionError("`ix` should have reached features.size(1) ({}), but it ended at {}".format(
+                x.size(1), field.numel()))
+        if self.training:
+            if self.reduce != 'mean':
+                raise ValueError("Invalid reduce option {}".format(self.reduce))
+            mean, var = _ext.bn_stats(x, field, scalar, self.running_var.numel(), self.running_mean.numel())
+            scale, shift = self.folded_affine(x.device, mean, var)
+            with torch.no_grad():
+                self.running_mean.mul_(1 - self.momentum).add_(self.momentum * mean)
+                self.running_var.mul_(1 - self.momentum).add_(self.momentum * var)
+        else:
+            scale, shift = self.folded_affine(x.device)
+        input.features = _ext.bn_gate_forward(x, scale, shift, None, x.size(1), 0, 0, 0, None, None)
+        return input

@@ -1,0 +1,97 @@
+"""Sparse convolution module (interface of SS_Conv_lib/ss_conv/sp_ops/conv.py:20-160)."""
+import math
+
+import numpy as np
+import torch
+import torch.nn as nn
+from torch.nn.parameter import Parameter
+
+from .tensor import SparseTensor
+from .ops import get_conv_output_size, get_deconv_output_size, get_indice_pairs, _per_dim
+from .functional import indice_conv, indice_inverse_conv, indice_subm_conv
+
+
+class SparseConvolution(nn.Module):
+    def __init__(self, ndim, in_channels, out_channels, kernel_size=3, stride=1, padding=0, dilation=1, groups=1,
+                 bias=True, subm=False, output_padding=0, transposed=False, inverse=False, indice_key=None):
+        super().__init__()
+        assert groups == 1
+        self.ndim = ndim
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = _per_dim(kernel_size, ndim)
+        self.stride = _per_dim(stride, ndim)
+        self.padding = _per_dim(padding, ndim)
+        self.dilation = _per_dim(dilation, ndim)
+        self.output_padding = _per_dim(output_padding, ndim)
+        for d, s in zip(self.dilation, self.stride):
+            assert s == 1 or d == 1, "don't support this."
+        self.conv1x1 = int(np.prod(self.kernel_size)) == 1
+        self.transposed = transposed
+        self.inverse = inverse
+        self.groups = groups
+        self.subm = subm
+        self.indice_key = indice_key
+        self.init_parameters(bias)
+
+    def calculate_fan_in(self):
+        return self.in_channels * int(np.prod(self.kernel_size))
+
+    def init_parameters(self, bias):
+        self.weight = Parameter(torch.empty(*self.kernel_size, self.in_channels, self.out_channels))
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if bias:
+            self.bias = Parameter(torch.empty(self.out_channels))
+            bound = 1 / math.sqrt(self.calculate_fan_in())
+            nn.init.uniform_(self.bias, -bound, bound)
+        else:
+            self.register_parameter('bias', None)
+
+    def forward(self, input):
+        return self._sparse_conv(input, self.weight)
+
+    def _output_shape(self, spatial_shape):
+        if self.subm:
+            return spatial_shape
+        if self.transposed:
+            return get_deconv_output_size(spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
+                                          self.output_padding)
+        return get_conv_output_size(spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation)
+
+    def _sparse_conv(self, input, weight):
+        """weight: [kx, ky, kz, Cin, Cout].  Rulebooks are cached in input.indice_dict under
+        indice_key; an inverse convolution reuses its partner's rulebook with the pair roles
+        exchanged."""
+        assert isinstance(input, SparseTensor)
+        features, indices = input.features, input.indices
+        spatial_shape, batch_size = input.spatial_shape, input.batch_size
+        out_spatial_shape = self._output_shape(spatial_shape)
+
+        if self.conv1x1:
+            input.features = torch.mm(features, weight.reshape(self.in_channels, self.out_channels))
+            if self.bias is not None:
+                input.features += self.bias
+            return input
+
+        cached = input.find_indice_pair(self.indice_key)
+        if self.inverse:
+            assert cached is not None and self.indice_key is not None
+            _, outids, indice_pairs, indice_pair_num, out_spatial_shape = cached
+            assert indice_pairs.shape[0] == np.prod(self.kernel_size), \
+                "inverse conv must have same kernel size as its couple conv"
+        elif self.indice_key is not None and cached is not None:
+            outids, _, indice_pairs, indice_pair_num, _ = cached
+        else:
+            outids, indice_pairs, indice_pair_num = get_indice_pairs(
+                indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
+                self.output_padding, self.subm, self.transposed, grid=input.grid)
+            input.indice_dict[self.indice_key] = (outids, indices, indice_pairs, indice_pair_num, spatial_shape)
+
+        op = indice_subm_conv if self.subm else (indice_inverse_conv if self.inverse else indice_conv)
+        out_features = op(features, weight, indice_pairs, indice_pair_num, outids.shape[0])
+        if self.bias is not None:
+            out_features += self.bias
+        out = SparseTensor(out_features, outids, out_spatial_shape, batch_size)
+        out.indice_dict = input.indice_dict
+        out.grid = input.grid
+        return out

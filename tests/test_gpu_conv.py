@@ -1,0 +1,129 @@
+"""Gather-GEMM kernels vs the oracle.  Tolerances: exact-fp32 path 2e-5 (summation order
+differs from the reference's GEMM), TF32 tensor-core path 1e-3, both as max|diff|/max|ref|
+against the float64 evaluation of the same contraction."""
+import numpy as np
+import pytest
+import torch
+
+import ssconv_oracle as O
+from gpu_helpers import dev, gpu_rulebook, random_voxels, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = {"fp32": 2e-5, "tf32": 1e-3}
+
+
+def _run(cuda, ind, batch, V, k, s, p, subm, c_in, c_out, precision, seed=0):
+    from ss_conv import _ext
+    rng = np.random.RandomState(seed)
+    feats = rng.randn(ind.shape[0], c_in).astype(np.float32)
+    W = (rng.randn(k, k, k, c_in, c_out) / np.sqrt(c_in * k ** 3)).astype(np.float32)
+    outids, pairs, num = gpu_rulebook(ind, batch, [V] * 3, k, s, p, 1, subm, cuda)
+    _ext.set_precision(precision)
+    try:
+        y = _ext.indice_conv_fp32(dev(feats, cuda), dev(W, cuda), pairs, num, outids.shape[0], 0, int(subm))
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+    ref = O.indice_conv_f64(feats, W, pairs.cpu().numpy(), num.cpu().numpy(), outids.shape[0])
+    return y.cpu().numpy(), ref
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+@pytest.mark.parametrize("c_in,c_out", [(32, 38), (64, 76), (3, 36), (30, 72), (16, 16), (130, 270)])
+def test_conv_channel_shapes(cuda, precision, c_in, c_out):
+    rng = np.random.RandomState(c_in + c_out)
+    ind = random_voxels(rng, 2, 12, 330)           # > 2 row tiles, ragged last tile
+    y, ref = _run(cuda, ind, 2, 12, 3, 1, 1, False, c_in, c_out, precision)
+    assert rel_err(y, ref) <= TOL[precision]
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+@pytest.mark.parametrize("k,s,p,subm", [(3, 2, 1, False), (3, 1, 1, True), (5, 1, 2, True), (2, 2, 0, False)])
+def test_conv_geometries(cuda, precision, k, s, p, subm):
+    rng = np.random.RandomState(k * 7 + s)
+    ind = random_voxels(rng, 3, 14, 400)
+    y, ref = _run(cuda, ind, 3, 14, k, s, p, subm, 32, 48, precision)
+    assert rel_err(y, ref) <= TOL[precision]
+
+
+def test_conv_fp32_matches_reference_oracle_tightly(cuda):
+    rng = np.random.RandomState(1)
+    ind = random_voxels(rng, 2, 10, 200)
+    feats = rng.randn(ind.shape[0], 20).astype(np.float32)
+    W = rng.randn(3, 3, 3, 20, 24).astype(np.float32)
+    from ss_conv import _ext
+    outids, pairs, num = gpu_rulebook(ind, 2, [10] * 3, 3, 1, 1, 1, True, cuda)
+    _ext.set_precision("fp32")
+    try:
+        y = _ext.indice_conv_fp32(dev(feats, cuda), dev(W, cuda), pairs, num, ind.shape[0], 0, 1).cpu().numpy()
+    finally:
+        _ext.set_precision("auto")
+    ref = O.indice_conv(feats, W, pairs.cpu().numpy(), num.cpu().numpy(), ind.shape[0], False, True)
+    assert rel_err(y, ref) <= 2e-6
+
+
+def test_inverse_conv(cuda):
+    """Inverse convolution: the strided layer's rulebook with the pair roles exchanged."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(2)
+    ind = random_voxels(rng, 2, 12, 250)
+    outids, pairs, num = gpu_rulebook(ind, 2, [12] * 3, 3, 2, 1, 1, False, cuda)
+    n_out = outids.shape[0]
+    feats = rng.randn(n_out, 16).astype(np.float32)
+    W = rng.randn(3, 3, 3, 16, 24).astype(np.float32)
+    for precision in ("fp32", "tf32"):
+        _ext.set_precision(precision)
+        try:
+            y = _ext.indice_conv_fp32(dev(feats, cuda), dev(W, cuda), pairs, num, ind.shape[0], 1, 0).cpu().numpy()
+        finally:
+            _ext.set_precision("auto")
+        ref = O.indice_conv_f64(feats, W, pairs.cpu().numpy(), num.cpu().numpy(), ind.shape[0], inverse=True)
+        assert rel_err(y, ref) <= TOL[precision]
+
+
+def test_conv_is_deterministic_and_linear(cuda):
+    from ss_conv import _ext
+    from ss_conv.utils import synthetic as S
+    ind = S.surface_voxels(range(8), 64, 16384, base_seed=50)
+    outids, pairs, num = gpu_rulebook(ind, 8, [64] * 3, 3, 2, 1, 1, False, cuda)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    a = torch.randn(ind.shape[0], 64, generator=g).to(cuda)
+    b = torch.randn(ind.shape[0], 64, generator=g).to(cuda)
+    W = (torch.randn(3, 3, 3, 64, 76, generator=g) / 40).to(cuda)
+    _ext.set_precision("tf32")
+    try:
+        ya = _ext.indice_conv_fp32(a, W, pairs, num, outids.shape[0], 0, 0)
+        ya2 = _ext.indice_conv_fp32(a, W, pairs, num, outids.shape[0], 0, 0)
+        yb = _ext.indice_conv_fp32(b, W, pairs, num, outids.shape[0], 0, 0)
+        yab = _ext.indice_conv_fp32(a + b, W, pairs, num, outids.shape[0], 0, 0)
+        _ext.set_precision("fp32")
+        yf = _ext.indice_conv_fp32(a, W, pairs, num, outids.shape[0], 0, 0)
+    finally:
+        _ext.set_precision("auto")
+    _ext.check_status(cuda)
+    assert torch.equal(ya, ya2)                                   # no atomics: bitwise repeatable
+    scale = float(yf.abs().max())
+    assert float((ya + yb - yab).abs().max()) <= 3e-3 * scale     # linear up to operand rounding
+    assert float((ya - yf).abs().max()) <= 1e-3 * scale           # tensor-core vs exact path
+
+
+def test_materialize_and_pack(cuda, golden):
+    """Materialisation kernel vs the reference's einsum result for the golden layer."""
+    from ss_conv.utils.kernel import SE3Kernel
+    Rs_in = [tuple(int(v) for v in r) for r in golden["meta_Rs_in"]]
+    Rs_out = [tuple(int(v) for v in r) for r in golden["meta_Rs_out"]]
+    k = SE3Kernel(Rs_in, Rs_out, 3)
+    state = {"weight": torch.from_numpy(golden["conv_weight"])}
+    for i in range(len(Rs_out)):
+        for j in range(len(Rs_in)):
+            b = golden["basis_%d_%d" % (i, j)]
+            if b.size:
+                state["kernel_%d_%d" % (i, j)] = torch.from_numpy(b)
+    k.load_state_dict(state)
+    k.to(cuda)
+    flt = k.filters().cpu().numpy()
+    assert flt.shape == golden["conv_filters"].shape
+    assert np.abs(flt - golden["conv_filters"]).max() <= 1e-6
+    W = k().cpu().numpy()                                          # [Cout, Cin, k, k, k] view
+    assert np.abs(W - np.transpose(golden["conv_filters"], (4, 3, 0, 1, 2))).max() <= 1e-6

@@ -1,0 +1,176 @@
+"""Pooling, voxelization, interpolation and BN/activation kernels vs the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import ssconv_oracle as O
+from gpu_helpers import dev, gpu_rulebook, random_voxels, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("c", [64, 30, 3])
+def test_max_and_avg_pool(cuda, c):
+    from ss_conv import _ext
+    rng = np.random.RandomState(c)
+    ind = random_voxels(rng, 3, 12, 400)
+    feats = rng.randn(ind.shape[0], c).astype(np.float32)
+    for k, s, p in ((2, 2, 0), (3, 2, 1)):
+        outids, pairs, num = gpu_rulebook(ind, 3, [12] * 3, k, s, p, 1, False, cuda)
+        pn, nn = pairs.cpu().numpy(), num.cpu().numpy()
+        n_out = outids.shape[0]
+        mx = _ext.indice_maxpool_fp32(dev(feats, cuda), pairs, num, n_out).cpu().numpy()
+        assert np.array_equal(mx, O.indice_maxpool(feats, pn, nn, n_out))          # bit-exact
+        av = _ext.indice_avgpool_fp32(dev(feats, cuda), pairs, num, n_out, None).cpu().numpy()
+        assert np.array_equal(av, O.indice_avgpool(feats, pn, nn, n_out))          # same order, bit-exact
+        rf = _ext.indiceSummaryRF(pairs, num, n_out)
+        assert np.array_equal(rf.cpu().numpy(), O.summary_rf(pn, nn, n_out))
+        av2 = _ext.indice_avgpool_fp32(dev(feats, cuda), pairs, num, n_out, rf).cpu().numpy()
+        assert np.array_equal(av2, O.indice_avgpool(feats, pn, nn, n_out, O.summary_rf(pn, nn, n_out)))
+
+
+def test_pool_modules_and_golden(cuda, golden):
+    from ss_conv.pool import MaxPool, AvgPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    x = SparseTensor(dev(golden["conv_out_features"], cuda), dev(golden["conv_out_indices"], cuda), [10] * 3, 2)
+    z = MaxPool(2, stride=2)(x)
+    zi = z.indices.cpu().numpy()
+    perm = O.renumber_rows(golden["maxpool_out_indices"])
+    assert np.array_equal(zi, golden["maxpool_out_indices"][perm])
+    assert np.array_equal(z.features.cpu().numpy(), golden["maxpool_out_features"][perm])
+    a = AvgPool(3, stride=2, padding=1)(x)
+    assert a.features.shape[0] == a.indices.shape[0] and a.spatial_shape == [5, 5, 5]
+
+
+def test_global_pools(cuda):
+    from ss_conv.pool import GlobalAvgPool, GlobalMaxPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    rng = np.random.RandomState(0)
+    counts = [37, 1, 200, 64, 9]
+    ind = np.concatenate([np.stack([np.full(n, b), np.arange(n) % 16, np.arange(n) // 16, np.zeros(n)], 1)
+                          for b, n in enumerate(counts)]).astype(np.int32)
+    feats = rng.randn(ind.shape[0], 70).astype(np.float32)
+    x = SparseTensor(dev(feats, cuda), dev(ind, cuda), [16] * 3, 5)
+    off = x.get_offsets()
+    assert off.cpu().tolist() == np.concatenate([[0], np.cumsum(counts)]).tolist()
+    avg = GlobalAvgPool()(x).cpu().numpy()
+    ref = O.global_avgpool(feats, off.cpu().numpy())
+    assert np.abs(avg - ref).max() <= 1e-5          # pairwise instead of sequential summation
+    mx = GlobalMaxPool()(x.features, off).cpu().numpy()
+    rmx, rarg = O.global_maxpool(feats, off.cpu().numpy())
+    assert np.array_equal(mx, rmx)
+    from ss_conv import _ext
+    out = torch.zeros(5, 70, device=cuda)
+    arg = torch.zeros(5, 70, dtype=torch.int32, device=cuda)
+    _ext.global_maxpool_fp(x.features, off, out, arg, 5, 70)
+    assert np.array_equal(arg.cpu().numpy(), rarg)
+    # empty sample: mean is NaN (0/0), max is -inf with arg -1, as in the reference kernels
+    off2 = torch.tensor([0, 3, 3, 5], dtype=torch.int32, device=cuda)
+    a2 = GlobalAvgPool()(x.features[:5].contiguous(), off2).cpu().numpy()
+    assert np.isnan(a2[1]).all() and np.isfinite(a2[0]).all()
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3, 4])
+def test_voxel2point_map_and_voxelize(cuda, mode):
+    from ss_conv.sp_ops.functional import voxel2point_mapping, voxelization
+    rng = np.random.RandomState(mode)
+    n, m = 500, 90
+    inverse = rng.randint(0, m, n).astype(np.int32)
+    inverse[:m] = np.arange(m)
+    counts = np.bincount(inverse, minlength=m)
+    max_active = 1 if mode in (1, 2) else int(counts.max())
+    feats = rng.rand(n, 5).astype(np.float32)
+    maps = voxel2point_mapping(dev(inverse, cuda), m, max_active, mode)
+    ref_maps = O.voxel2point_map(inverse, m, max_active, mode)
+    assert np.array_equal(maps.cpu().numpy(), ref_maps)
+    out = voxelization(dev(feats, cuda), maps, mode).cpu().numpy()
+    assert np.array_equal(out, O.voxelize_fp(feats, ref_maps, mode))
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3, 4])
+def test_point2voxel_module(cuda, mode):
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    from ss_conv.utils import synthetic as S
+    pts, fts, ids = S.object_points(range(4), 700, base_seed=9)
+    pts[5] = [0.7, 0.0, 0.0]                        # out of range: dropped
+    V = 16
+    p2v = Point2Voxel([V] * 3, [1.0 / V] * 3, mode)
+    vp, sp, vids, flag = p2v(dev(pts, cuda), dev(fts, cuda), dev(ids, cuda))
+    rp, rfeat, rocc, rids, rinv = O.point2voxel(pts, fts, ids, [V] * 3, [1.0 / V] * 3, mode)
+    assert np.array_equal(vp.cpu().numpy(), rp) and np.array_equal(vids.cpu().numpy(), rids)
+    assert np.array_equal(sp.indices.cpu().numpy(), rocc)
+    assert np.array_equal(sp.features.cpu().numpy(), rfeat)
+    assert flag.cpu().tolist() == [1.0] * 4 and sp.batch_size == 4
+
+
+def test_point2voxel_empty_sample(cuda):
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    rng = np.random.RandomState(0)
+    pts = rng.uniform(-0.4, 0.4, (300, 3)).astype(np.float32)
+    ids = np.repeat(np.arange(3), 100)
+    pts[100:200] = 5.0                              # sample 1 loses every point
+    p2v = Point2Voxel([8] * 3, [0.125] * 3, 4)
+    vp, sp, vids, flag = p2v(dev(pts, cuda), dev(pts, cuda), dev(ids, cuda))
+    assert flag.cpu().tolist() == [1.0, 0.0, 1.0]
+    assert vp.shape[0] == 201 and int((vids == 1).sum()) == 1
+    row = sp.indices.cpu().numpy()
+    assert (row[row[:, 0] == 1][:, 1:] == 4).all()   # the injected zero point sits in the centre cell
+
+
+def test_three_nn_and_interpolate(cuda):
+    from ss_conv.sp_ops.voxelize import Voxel2Point, Point2Voxel
+    from ss_conv.sp_ops.functional import three_nn
+    from ss_conv.utils import synthetic as S
+    pts, fts, ids = S.object_points(range(3), 900, base_seed=3)
+    V = 16
+    p2v = Point2Voxel([V] * 3, [1.0 / V] * 3, 4)
+    vp, sp, vids, _ = p2v(dev(pts, cuda), dev(fts, cuda), dev(ids, cuda))
+    sp.features = torch.randn(sp.features.shape[0], 19, device=cuda)
+    v2p = Voxel2Point(unit_voxel_extent=[1.0 / V] * 3)
+    out = v2p(sp, vp, vids).cpu().numpy()
+    ref, d2, idx = O.voxel2point(sp.features.cpu().numpy(), sp.indices.cpu().numpy(), [V] * 3, [1.0 / V] * 3,
+                                 vp.cpu().numpy(), vids.cpu().numpy())
+    centres, _ = v2p._get_vertice_feats(sp)
+    unknown = torch.cat([vids.float().unsqueeze(1), vp], 1)
+    gd, gi = three_nn(unknown, centres)
+    assert np.array_equal(gi.cpu().numpy(), idx)                    # same neighbours, same tie order
+    assert np.array_equal((gd ** 2).cpu().numpy().round(6), d2.round(6)) or np.allclose(gd.cpu().numpy() ** 2, d2, rtol=1e-6)
+    assert np.abs(out - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+    # a sample with fewer than three voxels keeps +inf distances and index 0
+    unknown2 = torch.tensor([[7.0, 0, 0, 0]], device=cuda)
+    known2 = torch.tensor([[7.0, 1, 0, 0], [3.0, 0, 0, 0]], device=cuda)
+    d, i = three_nn(unknown2, known2)
+    assert i.cpu().tolist() == [[0, 0, 0]] and torch.isinf(d[0, 1]) and float(d[0, 0]) == 1.0
+
+
+def test_batchnorm_activation_golden(cuda, golden):
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.activation import Activation
+    from ss_conv.sp_ops.tensor import SparseTensor
+    Rs_out = [tuple(int(v) for v in r) for r in golden["meta_Rs_out"]]
+    bn = BatchNorm(Rs_out, momentum=0.1).to(cuda)
+    with torch.no_grad():
+        for n in ("running_mean", "running_var", "weight", "bias"):
+            getattr(bn, n).copy_(dev(golden["bn_" + n], cuda))
+    x = dev(golden["conv_out_features"], cuda)
+    ind = dev(golden["conv_out_indices"], cuda)
+    bn.eval()
+    y = bn(SparseTensor(x.clone(), ind, [10] * 3, 2)).features.cpu().numpy()
+    assert np.abs(y - golden["bn_eval_out"]).max() <= 3e-6 * max(1.0, np.abs(y).max())
+    bn.train()
+    yt = bn(SparseTensor(x.clone(), ind, [10] * 3, 2)).features.cpu().numpy()
+    assert np.abs(yt - golden["bn_train_out"]).max() <= 2e-5 * max(1.0, np.abs(yt).max())
+    assert np.allclose(bn.running_mean.cpu().numpy(), golden["bn_train_running_mean"], rtol=1e-5, atol=1e-6)
+    assert np.allclose(bn.running_var.cpu().numpy(), golden["bn_train_running_var"], rtol=1e-5, atol=1e-6)
+    act = Activation(Rs_out[:-1], (torch.relu, torch.sigmoid), bias=True, checkpoint=False).to(cuda)
+    with torch.no_grad():
+        act.scalar_act.bias.copy_(dev(golden["act_scalar_bias"], cuda))
+        act.gate_act.bias.copy_(dev(golden["act_gate_bias"], cuda))
+    z = act(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
+    assert z.shape == golden["act_out"].shape
+    assert np.abs(z - golden["act_out"]).max() <= 3e-6
+    # a non-fusable callable takes the composite path and agrees with the fused kernel
+    act2 = Activation(Rs_out[:-1], (lambda v: torch.relu(v), torch.sigmoid), bias=True, checkpoint=False).to(cuda)
+    act2.load_state_dict(act.state_dict())
+    z2 = act2(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
+    assert np.abs(z2 - z).max() <= 2e-6

@@ -1,0 +1,118 @@
+"""Whole layers through the public ss_conv API vs the reference's own outputs (golden
+fixtures) and the small backbone end to end."""
+import numpy as np
+import pytest
+import torch
+
+import ssconv_oracle as O
+from gpu_helpers import dev, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _load_conv(golden, tag, cuda, **kw):
+    from ss_conv.convolution import Convolution
+    Rs_in = [tuple(int(v) for v in r) for r in golden["meta_Rs_in"]]
+    Rs_out = [tuple(int(v) for v in r) for r in golden["meta_Rs_out"]]
+    conv = Convolution(Rs_in, Rs_out, **kw).eval()
+    state = {"kernel.weight": torch.from_numpy(golden[tag + "_weight"])}
+    for i in range(len(Rs_out)):
+        for j in range(len(Rs_in)):
+            b = golden["basis_%d_%d" % (i, j)]
+            if b.size:
+                state["kernel.kernel_%d_%d" % (i, j)] = torch.from_numpy(b)
+    conv.load_state_dict(state)
+    return conv.to(cuda)
+
+
+@pytest.mark.parametrize("precision,tol", [("fp32", 2e-5), ("tf32", 1e-3)])
+@pytest.mark.parametrize("tag,kw", [("conv", dict(kernel_size=3, stride=1, padding=1)),
+                                    ("strided", dict(kernel_size=3, stride=2, padding=1)),
+                                    ("subm", dict(kernel_size=3, subm=True, padding=1))])
+def test_convolution_layer_matches_reference_output(cuda, golden, tag, kw, precision, tol):
+    from ss_conv import _ext
+    from ss_conv.sp_ops.tensor import SparseTensor
+    conv = _load_conv(golden, tag, cuda, **kw)
+    x = SparseTensor(dev(golden[tag + "_features"], cuda), dev(golden[tag + "_indices"], cuda), [10] * 3, 2)
+    _ext.set_precision(precision)
+    try:
+        with torch.no_grad():
+            y = conv(x)
+    finally:
+        _ext.set_precision("auto")
+    _ext.check_status(cuda)
+    ref_idx = golden[tag + "_out_indices"]
+    perm = O.renumber_rows(ref_idx)                 # reference CPU order -> ascending (b,x,y,z)
+    if tag == "subm":
+        assert np.array_equal(y.indices.cpu().numpy(), ref_idx)
+        perm = np.arange(ref_idx.shape[0])
+    else:
+        assert np.array_equal(y.indices.cpu().numpy(), ref_idx[perm])
+    assert rel_err(y.features.cpu().numpy(), golden[tag + "_out_features"][perm]) <= tol
+
+
+def test_indice_key_reuse_and_state_dict_names(cuda, golden):
+    from ss_conv.sp_ops.tensor import SparseTensor
+    conv_a = _load_conv(golden, "subm", cuda, kernel_size=3, subm=True, padding=1, indice_key="k0")
+    names = set(conv_a.state_dict().keys())
+    assert "kernel.weight" in names and "kernel.kernel_0_0" in names
+    x = SparseTensor(dev(golden["subm_features"], cuda), dev(golden["subm_indices"], cuda), [10] * 3, 2)
+    with torch.no_grad():
+        y1 = conv_a(x)
+    assert "k0" in x.indice_dict and y1.indice_dict is x.indice_dict
+    pairs_first = x.indice_dict["k0"][2]
+    x2 = SparseTensor(x.features, x.indices, [10] * 3, 2)
+    x2.indice_dict = x.indice_dict
+    with torch.no_grad():
+        y2 = conv_a(x2)
+    assert x2.indice_dict["k0"][2] is pairs_first            # rulebook reused, not rebuilt
+    assert torch.equal(y1.features, y2.features)
+
+
+def test_backbone_forward_matches_oracle_chain(cuda):
+    """Point2Voxel -> 2 x (Conv s2 + BN + gate) -> GlobalAvgPool, layer by layer against the
+    oracle fed with the same parameters."""
+    from ss_conv import _ext
+    from ss_conv.convolution import Convolution
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.activation import Activation
+    from ss_conv.pool import GlobalAvgPool
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(0)
+    irreps = [(3,), (4, 2, 1), (6, 3, 2)]
+    pts, fts, ids = S.object_points(range(4), 512, base_seed=21)
+    V = 16
+    x = Point2Voxel([V] * 3, [1.0 / V] * 3, 4)(dev(pts, cuda), dev(fts, cuda), dev(ids, cuda))[1]
+    cur_idx, cur_feat, shape = x.indices.cpu().numpy(), x.features.cpu().numpy(), [V] * 3
+    _ext.set_precision("fp32")
+    try:
+        for li in range(2):
+            Rs_in = [(m, l) for l, m in enumerate(irreps[li])]
+            Rs_act = [(m, l) for l, m in enumerate(irreps[li + 1])]
+            Rs_out = Rs_act + [(sum(irreps[li + 1][1:]), 0)]
+            conv = Convolution(Rs_in, Rs_out, 3, stride=2, padding=1).to(cuda).eval()
+            bn = BatchNorm(Rs_out).to(cuda).eval()
+            with torch.no_grad():
+                bn.running_var.uniform_(0.5, 1.5)
+                bn.running_mean.normal_(0, 0.1)
+            act = Activation(Rs_act, (torch.relu, torch.sigmoid), bias=False, checkpoint=False)
+            with torch.no_grad():
+                x = act(bn(conv(x)))
+            flt = conv.weight.cpu().numpy()
+            outids, pairs, num = O.get_indice_pairs(cur_idx, 4, shape, 3, 2, 1, 1, False)
+            perm = O.renumber_rows(outids)
+            y = O.indice_conv(cur_feat, flt, pairs, num, outids.shape[0])[perm]
+            y = O.batchnorm_eval(y, Rs_out, bn.running_mean.cpu().numpy(), bn.running_var.cpu().numpy(),
+                                 bn.weight.detach().cpu().numpy(), bn.bias.detach().cpu().numpy())
+            y = O.gated_activation(y, Rs_act, "relu", "sigmoid")
+            shape = [s // 2 for s in shape]
+            cur_idx, cur_feat = outids[perm], y
+            assert np.array_equal(x.indices.cpu().numpy(), cur_idx)
+            assert rel_err(x.features.cpu().numpy(), cur_feat) <= 5e-5
+    finally:
+        _ext.set_precision("auto")
+    pooled = GlobalAvgPool()(x).cpu().numpy()
+    counts = np.bincount(cur_idx[:, 0], minlength=4)
+    ref = O.global_avgpool(cur_feat, np.concatenate([[0], np.cumsum(counts)]))
+    assert rel_err(pooled, ref) <= 5e-5
