@@ -257,6 +257,29 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_only(args):
+    """A few launches of one kernel group on the cfg2 inputs (small, fixed launch count)."""
+    from ss_conv import _ext
+    from ss_conv.sp_ops.ops import get_indice_pairs
+    dev = torch.device("cuda", 0)
+    cfg = CFG2
+    _ext.set_precision("tf32")
+    layer = Layer(cfg, dev)
+    f, i = make_inputs(cfg, 0, 1)[0]
+    f, i = torch.from_numpy(f).to(dev), torch.from_numpy(i).to(dev)
+    with torch.no_grad():
+        flt = layer.conv.kernel.filters().reshape(-1, layer.conv.in_channels, layer.conv.out_channels)
+        for _ in range(max(1, args.steps)):
+            outids, pairs, num = get_indice_pairs(i, cfg["batch"], [cfg["V"]] * 3, cfg["k"], cfg["stride"], cfg["pad"])
+            if args.only == "conv":
+                nbr = _ext.neighbour_table(pairs, num, outids.shape[0])
+                for _ in range(4):
+                    _ext.conv_forward(f, flt, nbr, outids.shape[0], "tf32")
+    torch.cuda.synchronize()
+    _ext.check_status(dev)
+    print("only=%s done, n_in=%d n_out=%d" % (args.only, i.shape[0], outids.shape[0]))
+
+
 # ------------------------------------------------------------------------ CPU reference
 def ref_step_fn(cfg):
     """One CPU step of the reference's own code path on `n_samples` samples:
@@ -348,10 +371,14 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, choices=["conv", "rulebook"],
+                    help="run just one kernel group of the cfg2 step a few times (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.only:
+        run_only(args)
     else:
         run_ours(args)
 

@@ -79,14 +79,13 @@ __global__ void bn_colsum_kernel(const float *__restrict__ x, int n, int c, cons
   }
 }
 
-__global__ void bn_finish_mean_kernel(const float *sum_scalar, int n, const int32_t *scalar_of_channel, int c,
-                                      int n_scalar, float *mean, float *chan_mean) {
+// chan_mean[ch] = batch mean of a scalar channel (0 for l>0 channels), from the channel sums.
+__global__ void bn_chan_mean_kernel(const float *sum_scalar, int n, const int32_t *scalar_of_channel, int c,
+                                    float *chan_mean) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n_scalar) mean[i] = sum_scalar[i] / (float)n;
-  if (i < c) {
-    int s = scalar_of_channel[i];
-    chan_mean[i] = s >= 0 ? sum_scalar[s] / (float)n : 0.f;
-  }
+  if (i >= c) return;
+  int s = scalar_of_channel[i];
+  chan_mean[i] = s >= 0 ? sum_scalar[s] / (float)n : 0.f;
 }
 
 __global__ void bn_finish_var_kernel(float *var, int n_field, int n) {
@@ -140,8 +139,8 @@ extern "C" int ssc_bn_stats(const float *x, int n, int c, const int32_t *field_o
   if (row_blocks > 64) row_blocks = 64;
   dim3 grid(ceil_div(c, 32), row_blocks);
   { bn_colsum_kernel<<<grid, block, 0, st>>>(x, n, c, nullptr, mean, scalar_of_channel); note_launches(1); }
-  int m = c > n_scalar ? c : n_scalar;
-  { bn_finish_mean_kernel<<<ceil_div(m, 128), 128, 0, st>>>(mean, n, scalar_of_channel, c, n_scalar, mean, chan_mean); note_launches(1); }
+  { bn_chan_mean_kernel<<<ceil_div(c, 128), 128, 0, st>>>(mean, n, scalar_of_channel, c, chan_mean); note_launches(1); }
+  if (n_scalar > 0) { bn_finish_var_kernel<<<ceil_div(n_scalar, 128), 128, 0, st>>>(mean, n_scalar, n); note_launches(1); }
   { bn_colsum_kernel<<<grid, block, 0, st>>>(x, n, c, chan_mean, var, field_of_channel); note_launches(1); }
   { bn_finish_var_kernel<<<ceil_div(n_field, 128), 128, 0, st>>>(var, n_field, n); note_launches(1); }
   SSC_CHECK_LAUNCH("bn_stats");

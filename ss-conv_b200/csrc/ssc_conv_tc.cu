@@ -1,10 +1,12 @@
 // Output-stationary gather-GEMM on the 5th-generation tensor cores (tcgen05, sm_100a).
 //
-// One CTA owns 128 consecutive output rows.  For every kernel offset that has at least one
+// One CTA owns 128 consecutive output rows.  Its slice of the neighbour table (K x 128 row
+// indices) is staged in shared memory once.  For every kernel offset that has at least one
 // neighbour inside the tile, and every 32-channel slab of the input channels, the CTA
-//   * gathers the 128 neighbour rows (zeros where absent) into shared memory in the
-//     K-major 128-byte-swizzled operand layout, rounding fp32 -> TF32 (round to nearest),
-//   * copies the matching pre-packed filter slab (already in operand layout) beside it,
+//   * gathers the 128 neighbour rows with cp.async (16-byte chunks, zero-filled where a
+//     neighbour is absent) straight into the K-major 128-byte-swizzled operand layout, several
+//     stages ahead of use, then rounds its own chunks fp32 -> TF32 (round to nearest) in place,
+//   * copies the matching pre-packed filter slab (already TF32, already in operand layout),
 //   * lets one thread issue tcgen05.mma (M=128, N<=256, K=8 per instruction) accumulating in
 //     tensor memory (fp32), and commits the group to an mbarrier that frees the stage.
 // Accumulators stay in TMEM across all offsets; the epilogue reads them with tcgen05.ld and
@@ -12,6 +14,8 @@
 //
 // Every wait on an mbarrier is bounded: on expiry the kernel records an error in `status`,
 // stops issuing work, frees its tensor memory and returns.
+#include <stdlib.h>
+
 #include "ssc_common.cuh"
 
 namespace ssc {
@@ -20,6 +24,7 @@ constexpr int TC_M = 128;
 constexpr int TC_SLAB = 32;          // tf32 elements per 128-byte operand row
 constexpr int TC_THREADS = 256;
 constexpr int TC_A_BYTES = TC_M * 128;
+constexpr int TC_CTRL_BYTES = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct TcParams {
@@ -28,11 +33,15 @@ struct TcParams {
   int n_tiles;    // MMA instructions along N per k-step
   int tile_n;     // N of one MMA, multiple of 16, <= 256
   int tmem_cols;  // power of two >= max(32, n_pad)
-  int stages;
+  int stages;     // operand ring depth
+  int lookahead;  // stages of loads in flight ahead of the MMA
   int b_bytes;    // n_pad * 128
+  int nbr_bytes;  // K * 128 * 4
 };
 
-static bool tc_params(int c_in, int c_out, TcParams &p) {
+// Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB] [neighbour slice K x 512 B].
+// Two CTAs per SM are preferred (their barrier stalls overlap) when that leaves >= 3 stages.
+static bool tc_params(int c_in, int c_out, int K, TcParams &p) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   int n16 = (c_out + 15) / 16 * 16;
   p.n_tiles = (n16 + 255) / 256;
@@ -42,15 +51,25 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
   p.tmem_cols = 32;
   while (p.tmem_cols < p.n_pad) p.tmem_cols <<= 1;
   p.b_bytes = p.n_pad * 128;
+  p.nbr_bytes = K * TC_M * 4;
   int stage = TC_A_BYTES + p.b_bytes;
-  int budget = (p.tmem_cols <= 256) ? 108 * 1024 : 216 * 1024;  // two CTAs per SM when TMEM allows
-  p.stages = budget / stage;
-  if (p.stages > 8) p.stages = 8;
-  if (p.stages < 2) {
-    p.stages = (216 * 1024) / stage;
-    if (p.stages > 4) p.stages = 4;
+  int fixed = TC_CTRL_BYTES + p.nbr_bytes + 1024;
+  int two = (112 * 1024 - fixed) / stage;   // per-CTA budget when two CTAs share an SM
+  int one = (226 * 1024 - fixed) / stage;
+  int ctas = (p.tmem_cols <= 256 && two >= 3) ? 2 : 1;
+  if (const char *e = getenv("SSC_TC_CTAS_PER_SM")) {
+    int v = atoi(e);
+    if (v == 1 || (v == 2 && p.tmem_cols <= 256 && two >= 2)) ctas = v;
   }
-  return p.stages >= 2;
+  p.stages = ctas == 2 ? two : one;
+  if (p.stages > 8) p.stages = 8;
+  if (const char *e = getenv("SSC_TC_STAGES")) {
+    int v = atoi(e);
+    if (v >= 2 && v <= p.stages) p.stages = v;
+  }
+  if (p.stages < 2) return false;
+  p.lookahead = p.stages - 2;
+  return true;
 }
 
 // ------------------------------------------------------------------------- PTX wrappers
@@ -108,6 +127,26 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   return r;
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Wait until at most n of this thread's most recent copy groups are still in flight.
+__device__ __forceinline__ void cp_async_wait(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+  }
+}
+
 // Filter packing: filters [K, c_in, c_out] fp32 -> [K][k_slabs][n_pad rows][32 tf32] in the
 // swizzled operand layout (row = output channel, 16-byte chunk index XOR (row & 7)).
 __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int K, int c_in, int c_out, TcParams p,
@@ -150,6 +189,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   int *n_act_s = (int *)(ctrl + 80);
   uint8_t *act_flag = ctrl + 128;                          // [256]
   uint8_t *act_list = ctrl + 128 + 256;                    // [256]
+  int32_t *nbr_s = (int32_t *)(ctrl + TC_CTRL_BYTES);      // [K][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * TC_M;
@@ -167,13 +207,15 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // which kernel offsets touch this tile
+  // stage this tile's slice of the neighbour table and find the offsets that touch it
   for (int kappa = warp; kappa < K; kappa += TC_THREADS / 32) {
     bool any = false;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      int m = m0 + q * 32 + lane;
-      if (m < n_out) any |= nbr[(size_t)kappa * n_out + m] >= 0;
+      int r = q * 32 + lane;
+      int v = (m0 + r < n_out) ? __ldg(nbr + (size_t)kappa * n_out + m0 + r) : -1;
+      nbr_s[kappa * TC_M + r] = v;
+      any |= v >= 0;
     }
     unsigned b = __ballot_sync(0xffffffffu, any);
     if (lane == 0) act_flag[kappa] = b != 0;
@@ -196,53 +238,81 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int g_row = tid >> 3;   // 0..31: row inside a 32-row pass
   const int g_chunk = tid & 7;  // 16-byte chunk inside the 128-byte slab row
   const bool vec_ok = (c_in & 3) == 0;
+  const uint32_t smem_base = smem_u32(smem);
+  // byte offset of this thread's chunk inside an A stage for pass 0 (add pass * 4096)
+  const uint32_t a_off0 = (uint32_t)(g_row >> 3) * 1024u + (uint32_t)(g_row & 7) * 128u +
+                          (uint32_t)((g_chunk ^ (g_row & 7)) << 4);
+
+  // Asynchronous loads of pipeline step `j` into ring slot j % stages.
+  auto issue_loads = [&](int j) {
+    const int s = j % p.stages;
+    const int kappa = act_list[j / p.k_slabs];
+    const int slab = j - (j / p.k_slabs) * p.k_slabs;
+    const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
+    const int ch = slab * TC_SLAB + g_chunk * 4;
+    const int32_t *rows = nbr_s + kappa * TC_M;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      int src = rows[pass * 32 + g_row];
+      uint32_t dst = a_addr + a_off0 + (uint32_t)pass * 4096u;
+      const float *fp = features + (size_t)(src >= 0 ? src : 0) * c_in + ch;
+      if (vec_ok) {
+        int valid = (src >= 0) ? (c_in - ch) * 4 : 0;
+        valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
+        cp_async16(dst, valid > 0 ? (const void *)fp : (const void *)features, (uint32_t)valid);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          bool ok = src >= 0 && ch + q < c_in;
+          cp_async4(dst + 4u * q, ok ? (const void *)(fp + q) : (const void *)features, ok ? 4u : 0u);
+        }
+      }
+    }
+    const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
+    const uint32_t b_addr = a_addr + TC_A_BYTES;
+    for (int i = tid; i < p.n_pad * 8; i += TC_THREADS) cp_async16(b_addr + (uint32_t)i * 16u, bsrc + i, 16u);
+  };
+
+  for (int j = 0; j < p.lookahead; ++j) {
+    if (j < n_iter) issue_loads(j);
+    cp_async_commit();
+  }
 
   for (int it = 0; it < n_iter; ++it) {
     const int s = it % p.stages;
-    const int use = it / p.stages;
-    const int kappa = act_list[it / p.k_slabs];
-    const int slab = it - (it / p.k_slabs) * p.k_slabs;
-    uint8_t *a_s = smem + (size_t)s * stage_bytes;
-    uint8_t *b_s = a_s + TC_A_BYTES;
-    if (use > 0) {
-      if (!mbar_wait(smem_u32(bars + s), (uint32_t)((use - 1) & 1))) abort_flag[it & 1] = 1;
-      tc_fence_after();
-    }
-    // gather the A slab: 4 passes of 32 rows, 8 lanes per row
-    const int32_t *nbr_k = nbr + (size_t)kappa * n_out + m0;
-    const int ch = slab * TC_SLAB + g_chunk * 4;
-#pragma unroll
-    for (int pass = 0; pass < 4; ++pass) {
-      int row = pass * 32 + g_row;
-      int src = (m0 + row < n_out) ? __ldg(nbr_k + row) : -1;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (src >= 0) {
-        const float *fp = features + (size_t)src * c_in + ch;
-        if (vec_ok && ch + 3 < c_in) {
-          v = __ldg((const float4 *)fp);
-        } else {
-          if (ch + 0 < c_in) v.x = __ldg(fp + 0);
-          if (ch + 1 < c_in) v.y = __ldg(fp + 1);
-          if (ch + 2 < c_in) v.z = __ldg(fp + 2);
-          if (ch + 3 < c_in) v.w = __ldg(fp + 3);
-        }
+    // 1. keep `lookahead` steps of loads in flight: refill the slot whose MMAs retired
+    const int nxt = it + p.lookahead;
+    if (nxt < n_iter) {
+      const int prev_use = nxt - p.stages;   // pipeline step that last used this slot
+      if (prev_use >= 0) {
+        if (!mbar_wait(smem_u32(bars + (nxt % p.stages)), (uint32_t)((prev_use / p.stages) & 1))) abort_flag[it & 1] = 1;
+        tc_fence_after();
       }
-      uint4 t = make_uint4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-      uint32_t off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u + (uint32_t)((g_chunk ^ (row & 7)) << 4);
-      *(uint4 *)(a_s + off) = t;
+      issue_loads(nxt);
     }
-    // filter slab: already in operand layout, straight copy
+    cp_async_commit();
+    // 2. this thread's copies for step `it` have landed: round its A chunks to TF32 in place
+    cp_async_wait(p.lookahead);
     {
-      const uint4 *src = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
-      uint4 *dst = (uint4 *)b_s;
-      for (int i = tid; i < p.n_pad * 8; i += TC_THREADS) dst[i] = __ldg(src + i);
+      uint8_t *a_s = smem + (size_t)s * stage_bytes;
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        uint4 *ptr = (uint4 *)(a_s + a_off0 + pass * 4096);
+        uint4 v = *ptr;
+        v.x = to_tf32(__uint_as_float(v.x));
+        v.y = to_tf32(__uint_as_float(v.y));
+        v.z = to_tf32(__uint_as_float(v.z));
+        v.w = to_tf32(__uint_as_float(v.w));
+        *ptr = v;
+      }
     }
     fence_async_smem();
     __syncthreads();
     if (abort_flag[it & 1]) break;
+    // 3. one thread feeds the tensor core
     if (tid == 0) {
       tc_fence_after();
-      uint32_t a_addr = smem_u32(a_s), b_addr = smem_u32(b_s);
+      uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes, b_addr = a_addr + TC_A_BYTES;
       for (int nt = 0; nt < p.n_tiles; ++nt) {
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -254,6 +324,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       mma_commit(smem_u32(bars + s));
     }
   }
+  cp_async_wait(0);
 
   bool ok = !(abort_flag[0] | abort_flag[1]);
   if (ok && n_iter > 0) {
@@ -311,14 +382,14 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 }
 
 static size_t tc_smem_bytes(const TcParams &p) {
-  return (size_t)p.stages * (TC_A_BYTES + p.b_bytes) + 1024 /*align*/ + 1024 /*control*/;
+  return (size_t)p.stages * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES + p.nbr_bytes;
 }
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st) {
   TcParams p;
-  if (!tc_params(c_in, c_out, p)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d not supported (max 512)", c_out);
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
+  if (!tc_params(c_in, c_out, K, p)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
   size_t smem = tc_smem_bytes(p);
   cudaError_t e = cudaFuncSetAttribute(conv_fwd_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
@@ -336,7 +407,7 @@ using namespace ssc;
 extern "C" size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision) {
   if (precision != SSC_PREC_TF32 || K < 1 || c_in < 1 || c_out < 1) return 0;
   TcParams p;
-  if (!tc_params(c_in, c_out, p)) return 0;
+  if (!tc_params(c_in, c_out, 1, p)) return 0;
   return (size_t)K * p.k_slabs * p.b_bytes;
 }
 
@@ -345,7 +416,7 @@ extern "C" int ssc_conv_pack_filters(const float *filters, int K, int c_in, int 
   SSC_REQUIRE(precision == SSC_PREC_TF32, "conv_pack_filters: only SSC_PREC_TF32 has a packed form");
   SSC_REQUIRE(filters && packed && K >= 1 && c_in >= 1 && c_out >= 1, "conv_pack_filters: bad arguments");
   TcParams p;
-  SSC_REQUIRE(tc_params(c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
+  SSC_REQUIRE(tc_params(c_in, c_out, 1, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
   long long total = (long long)K * p.k_slabs * p.n_pad * 8;
   { pack_filters_tf32_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
   SSC_CHECK_LAUNCH("pack_filters_tf32");
