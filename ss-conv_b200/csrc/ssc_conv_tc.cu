@@ -3,10 +3,12 @@
 // One CTA owns 128 consecutive output rows.  Its slice of the neighbour table (K x 128 row
 // indices) is staged in shared memory once.  For every kernel offset that has at least one
 // neighbour inside the tile, and every 32-channel slab of the input channels, the CTA
-//   * gathers the 128 neighbour rows with cp.async (16-byte chunks, zero-filled where a
-//     neighbour is absent) straight into the K-major 128-byte-swizzled operand layout, several
-//     stages ahead of use, then rounds its own chunks fp32 -> TF32 (round to nearest) in place,
-//   * copies the matching pre-packed filter slab (already TF32, already in operand layout),
+//   * gathers the present neighbour rows with cp.async (16-byte chunks) straight into the
+//     K-major 128-byte-swizzled operand layout, several stages ahead of use (chunks of absent
+//     rows stay zero and are only rewritten when they held data before), then rounds its own
+//     chunks fp32 -> TF32 (round to nearest) in place,
+//   * brings in the matching pre-packed filter slab (already TF32, already in operand layout)
+//     with one bulk asynchronous copy that signals an mbarrier,
 //   * lets one thread issue tcgen05.mma (M=128, N<=256, K=8 per instruction) accumulating in
 //     tensor memory (fp32), and commits the group to an mbarrier that frees the stage.
 // Accumulators stay in TMEM across all offsets; the epilogue reads them with tcgen05.ld and
@@ -172,7 +174,7 @@ __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int 
   packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
                      int32_t *status, TcParams p) {
@@ -181,7 +183,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stage_bytes = TC_A_BYTES + p.b_bytes;
   uint8_t *ctrl = smem + (size_t)p.stages * stage_bytes;
-  uint64_t *bars = (uint64_t *)ctrl;                       // [stages]
+  uint64_t *bars = (uint64_t *)ctrl;                       // [stages] slot free (MMAs retired)
+  uint64_t *full_bars = (uint64_t *)(ctrl + 640);          // [stages] filter slab landed
   uint32_t *tmem_slot = (uint32_t *)(ctrl + 64);
   // abort flags are double-buffered by iteration parity so that every thread takes the same
   // decision after the per-iteration barrier
@@ -195,7 +198,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int m0 = blockIdx.x * TC_M;
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(bars + s), 1);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(bars + s), 1);
+      mbar_init(smem_u32(full_bars + s), 1);
+    }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -239,94 +245,127 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int g_chunk = tid & 7;  // 16-byte chunk inside the 128-byte slab row
   const bool vec_ok = (c_in & 3) == 0;
   const uint32_t smem_base = smem_u32(smem);
+  const int S = p.stages, L = p.lookahead;
   // byte offset of this thread's chunk inside an A stage for pass 0 (add pass * 4096)
   const uint32_t a_off0 = (uint32_t)(g_row >> 3) * 1024u + (uint32_t)(g_row & 7) * 128u +
                           (uint32_t)((g_chunk ^ (g_row & 7)) << 4);
+  // Every A chunk starts as zero; bit (slot*4 + pass) of `dirty` says that this thread's chunk
+  // of that slot currently holds gathered data, so absent rows cost nothing unless the chunk
+  // has to be cleared again.
+  uint32_t dirty = 0;
+  for (int sl = 0; sl < S; ++sl)
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass)
+      *(uint4 *)(smem + (size_t)sl * stage_bytes + a_off0 + pass * 4096) = make_uint4(0u, 0u, 0u, 0u);
 
-  // Asynchronous loads of pipeline step `j` into ring slot j % stages.
-  auto issue_loads = [&](int j) {
-    const int s = j % p.stages;
-    const int kappa = act_list[j / p.k_slabs];
-    const int slab = j - (j / p.k_slabs) * p.k_slabs;
-    const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
-    const int ch = slab * TC_SLAB + g_chunk * 4;
+  // producer cursor: pipeline step `nxt`, its ring slot, (offset, slab) and slot-use parity
+  int nxt = 0, slot_n = 0, par_n = 0, act_n = 0, slab_n = 0;
+
+  auto issue_loads = [&]() {
+    const int kappa = act_list[act_n];
+    const uint32_t a_addr = smem_base + (uint32_t)slot_n * (uint32_t)stage_bytes;
+    const int ch = slab_n * TC_SLAB + g_chunk * 4;
     const int32_t *rows = nbr_s + kappa * TC_M;
+    const bool in_range = ch < c_in;
 #pragma unroll
     for (int pass = 0; pass < 4; ++pass) {
-      int src = rows[pass * 32 + g_row];
-      uint32_t dst = a_addr + a_off0 + (uint32_t)pass * 4096u;
-      const float *fp = features + (size_t)(src >= 0 ? src : 0) * c_in + ch;
-      if (vec_ok) {
-        int valid = (src >= 0) ? (c_in - ch) * 4 : 0;
-        valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
-        cp_async16(dst, valid > 0 ? (const void *)fp : (const void *)features, (uint32_t)valid);
-      } else {
+      const int src = rows[pass * 32 + g_row];
+      const uint32_t bit = 1u << (slot_n * 4 + pass);
+      const uint32_t dst = a_addr + a_off0 + (uint32_t)pass * 4096u;
+      if (src >= 0 && in_range) {
+        const float *fp = features + (size_t)src * c_in + ch;
+        if (vec_ok) {
+          cp_async16(dst, fp, 16u);
+        } else {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          bool ok = src >= 0 && ch + q < c_in;
-          cp_async4(dst + 4u * q, ok ? (const void *)(fp + q) : (const void *)features, ok ? 4u : 0u);
+          for (int q = 0; q < 4; ++q) {
+            bool ok = ch + q < c_in;
+            cp_async4(dst + 4u * q, ok ? (const void *)(fp + q) : (const void *)features, ok ? 4u : 0u);
+          }
         }
+        dirty |= bit;
+      } else if (dirty & bit) {
+        *(uint4 *)(smem + (size_t)slot_n * stage_bytes + a_off0 + pass * 4096) = make_uint4(0u, 0u, 0u, 0u);
+        dirty &= ~bit;
       }
     }
-    const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
-    const uint32_t b_addr = a_addr + TC_A_BYTES;
-    for (int i = tid; i < p.n_pad * 8; i += TC_THREADS) cp_async16(b_addr + (uint32_t)i * 16u, bsrc + i, 16u);
+    if (tid == 32) {  // one thread moves the whole pre-packed filter slab with a bulk copy
+      const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab_n) * (size_t)(p.n_pad * 8);
+      const uint32_t bar = smem_u32(full_bars + slot_n);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)p.b_bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       a_addr + TC_A_BYTES),
+                   "l"(bsrc), "r"((uint32_t)p.b_bytes), "r"(bar)
+                   : "memory");
+    }
+    ++nxt;
+    if (++slab_n == p.k_slabs) { slab_n = 0; ++act_n; }
+    if (++slot_n == S) { slot_n = 0; par_n ^= 1; }
   };
 
-  for (int j = 0; j < p.lookahead; ++j) {
-    if (j < n_iter) issue_loads(j);
+  for (int j = 0; j < L; ++j) {
+    if (nxt < n_iter) issue_loads();
     cp_async_commit();
   }
 
-  for (int it = 0; it < n_iter; ++it) {
-    const int s = it % p.stages;
-    // 1. keep `lookahead` steps of loads in flight: refill the slot whose MMAs retired
-    const int nxt = it + p.lookahead;
+  int s = 0, par = 0;  // consumer cursor: ring slot of step `it` and its use parity
+  int it = 0;
+  for (; it < n_iter; ++it) {
+    // 1. keep L steps of loads in flight: refill the slot whose MMAs have retired
     if (nxt < n_iter) {
-      const int prev_use = nxt - p.stages;   // pipeline step that last used this slot
-      if (prev_use >= 0) {
-        if (!mbar_wait(smem_u32(bars + (nxt % p.stages)), (uint32_t)((prev_use / p.stages) & 1))) abort_flag[it & 1] = 1;
+      if (nxt >= S) {
+        if (!mbar_wait(smem_u32(bars + slot_n), (uint32_t)(par_n ^ 1))) abort_flag[it & 1] = 1;
         tc_fence_after();
       }
-      issue_loads(nxt);
+      issue_loads();
     }
     cp_async_commit();
-    // 2. this thread's copies for step `it` have landed: round its A chunks to TF32 in place
-    cp_async_wait(p.lookahead);
+    // 2. this thread's copies for step `it` have landed: round its gathered chunks to TF32
+    cp_async_wait(L);
     {
       uint8_t *a_s = smem + (size_t)s * stage_bytes;
 #pragma unroll
       for (int pass = 0; pass < 4; ++pass) {
-        uint4 *ptr = (uint4 *)(a_s + a_off0 + pass * 4096);
-        uint4 v = *ptr;
-        v.x = to_tf32(__uint_as_float(v.x));
-        v.y = to_tf32(__uint_as_float(v.y));
-        v.z = to_tf32(__uint_as_float(v.z));
-        v.w = to_tf32(__uint_as_float(v.w));
-        *ptr = v;
+        if (dirty & (1u << (s * 4 + pass))) {
+          uint4 *ptr = (uint4 *)(a_s + a_off0 + pass * 4096);
+          uint4 v = *ptr;
+          v.x = to_tf32(__uint_as_float(v.x));
+          v.y = to_tf32(__uint_as_float(v.y));
+          v.z = to_tf32(__uint_as_float(v.z));
+          v.w = to_tf32(__uint_as_float(v.w));
+          *ptr = v;
+        }
       }
     }
     fence_async_smem();
     __syncthreads();
     if (abort_flag[it & 1]) break;
-    // 3. one thread feeds the tensor core
+    // 3. one thread feeds the tensor core once the filter slab has landed too
     if (tid == 0) {
-      tc_fence_after();
-      uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes, b_addr = a_addr + TC_A_BYTES;
-      for (int nt = 0; nt < p.n_tiles; ++nt) {
+      if (!mbar_wait(smem_u32(full_bars + s), (uint32_t)par)) {
+        abort_flag[(it + 1) & 1] = 1;
+      } else {
+        tc_fence_after();
+        uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes, b_addr = a_addr + TC_A_BYTES;
+        for (int nt = 0; nt < p.n_tiles; ++nt) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          uint64_t da = make_desc(a_addr + ks * 32);
-          uint64_t db = make_desc(b_addr + nt * p.tile_n * 128 + ks * 32);
-          mma_tf32(tmem_base + nt * p.tile_n, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks) {
+            uint64_t da = make_desc(a_addr + ks * 32);
+            uint64_t db = make_desc(b_addr + nt * p.tile_n * 128 + ks * 32);
+            mma_tf32(tmem_base + nt * p.tile_n, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          }
         }
       }
       mma_commit(smem_u32(bars + s));
     }
+    if (++s == S) { s = 0; par ^= 1; }
   }
   cp_async_wait(0);
 
   bool ok = !(abort_flag[0] | abort_flag[1]);
+  if (!ok && tid == 32) {  // gave up early: let the filter copies still in flight land (bounded)
+    for (int t = it; t < nxt; ++t) mbar_wait(smem_u32(full_bars + (t % S)), (uint32_t)((t / S) & 1));
+  }
   if (ok && n_iter > 0) {
     int last = n_iter - 1;
     if (!mbar_wait(smem_u32(bars + (last % p.stages)), (uint32_t)((last / p.stages) & 1))) {

@@ -94,31 +94,46 @@ __global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int 
   atomicOr(status, 2);  // table full (cannot happen at load factor <= 0.5)
 }
 
-// One thread per (input row, kernel offset): mark the output cell this pair reaches.
+// One thread per input row, looping over the kernel offsets: mark the output cell each pair
+// reaches.  Lanes of a warp hold neighbouring inputs, so for one offset their cells mostly fall
+// into the same few bitmap words: lanes with the same word combine their bits and only one of
+// them issues the atomic.
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
                                     uint32_t *bitmap) {
-  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= (long long)n * g.K) return;
-  int j = (int)(t / g.K);
-  int kappa = (int)(t - (long long)j * g.K);
-  int4 c = indices[j];
-  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
-  int kk[3] = {kappa / (g.ksize[1] * g.ksize[2]), (kappa / g.ksize[2]) % g.ksize[1], kappa % g.ksize[2]};
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  int4 c = j < n ? indices[j] : make_int4(-1, 0, 0, 0);
+  bool row_ok = j < n && (unsigned)c.x < (unsigned)batch && in_range3(c.y, c.z, c.w, g.in_shape);
   int in[3] = {c.y, c.z, c.w};
-  int o[3];
+  int kk[3] = {0, 0, 0};
+  for (int kappa = 0; kappa < g.K; ++kappa) {
+    bool ok = row_ok;
+    int o[3] = {0, 0, 0};
 #pragma unroll
-  for (int d = 0; d < 3; ++d) {
-    if (g.transpose) {
-      o[d] = in[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
-    } else {
-      int num = in[d] + g.padding[d] - kk[d] * g.dilation[d];
-      if (num < 0 || num % g.stride[d] != 0) return;
-      o[d] = num / g.stride[d];
+    for (int d = 0; d < 3; ++d) {
+      if (g.transpose) {
+        o[d] = in[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
+      } else {
+        int num = in[d] + g.padding[d] - kk[d] * g.dilation[d];
+        ok = ok && num >= 0 && (num % g.stride[d] == 0);
+        o[d] = num / g.stride[d];
+      }
+      ok = ok && (unsigned)o[d] < (unsigned)g.out_shape[d];
     }
-    if ((unsigned)o[d] >= (unsigned)g.out_shape[d]) return;
+    uint32_t flat = ok ? (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]) : 0u;
+    uint32_t word = ok ? (flat >> 5) : 0xFFFFFFFFu;
+    uint32_t bits = ok ? (1u << (flat & 31)) : 0u;
+    unsigned peers = __match_any_sync(0xffffffffu, word);
+    uint32_t merged = __reduce_or_sync(peers, bits);
+    if (ok && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicOr(bitmap + word, merged);
+    // next kernel offset, last dimension fastest
+    if (++kk[2] == g.ksize[2]) {
+      kk[2] = 0;
+      if (++kk[1] == g.ksize[1]) {
+        kk[1] = 0;
+        ++kk[0];
+      }
+    }
   }
-  uint32_t flat = (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]);
-  atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
 }
 
 __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
@@ -176,28 +191,42 @@ lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int ba
   }
   unsigned lane = threadIdx.x & 31u, sub = lane & 3u, gbase = lane & ~3u;
   unsigned gmask = 0xFu << gbase;
+  // Round i serves the query of lane gbase+i; the four first probes are issued together so
+  // that their memory latencies overlap.
+  uint32_t qkey[4], bucket[4];
+  unsigned long long slot[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    qkey[i] = __shfl_sync(full, key, gbase + i);
+    bucket[i] = hash_mix(qkey[i]) & mask;
+    slot[i] = qkey[i] != 0xFFFFFFFFu ? table[(size_t)bucket[i] * kBucketSlots + sub] : kEmptySlot;
+  }
   int result = -1;
-#pragma unroll 1
-  for (unsigned i = 0; i < 4; ++i) {
-    uint32_t qkey = __shfl_sync(full, key, gbase + i);
-    int found = -1;
-    if (qkey != 0xFFFFFFFFu) {  // uniform inside the 4-lane group
-      uint32_t b = hash_mix(qkey) & mask;
-      for (uint32_t probe = 0; probe <= mask; ++probe) {
-        unsigned long long slot = table[(size_t)b * kBucketSlots + sub];
-        bool empty = slot == kEmptySlot;
-        bool hit = !empty && (uint32_t)(slot >> 32) == qkey;
-        unsigned hits = __ballot_sync(gmask, hit);
-        unsigned empties = __ballot_sync(gmask, empty);
-        if (hits) {
-          found = (int)__shfl_sync(gmask, (uint32_t)slot, __ffs(hits) - 1);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    bool empty = slot[i] == kEmptySlot;
+    bool hit = !empty && (uint32_t)(slot[i] >> 32) == qkey[i];
+    unsigned hits = (__ballot_sync(full, hit) >> gbase) & 0xFu;
+    unsigned empties = (__ballot_sync(full, empty) >> gbase) & 0xFu;
+    uint32_t val = __shfl_sync(full, (uint32_t)slot[i], gbase + (hits ? __ffs(hits) - 1 : 0));
+    int found = hits ? (int)val : -1;
+    if (!hits && !empties) {  // full bucket without the key: keep probing (rare, group-uniform)
+      uint32_t b = (bucket[i] + 1) & mask;
+      for (uint32_t probe = 1; probe <= mask; ++probe) {
+        unsigned long long sl = table[(size_t)b * kBucketSlots + sub];
+        bool e2 = sl == kEmptySlot;
+        bool h2 = !e2 && (uint32_t)(sl >> 32) == qkey[i];
+        unsigned hs = __ballot_sync(gmask, h2);
+        unsigned es = __ballot_sync(gmask, e2);
+        if (hs) {
+          found = (int)__shfl_sync(gmask, (uint32_t)sl, __ffs(hs) - 1);
           break;
         }
-        if (empties) break;
+        if (es) break;
         b = (b + 1) & mask;
       }
     }
-    if (sub == i) result = found;
+    if (sub == (unsigned)i) result = found;
   }
   if (o < n_out) nbr[(size_t)kappa * n_out + o] = result;
   int cnt = __syncthreads_count(o < n_out && result >= 0);
@@ -380,9 +409,8 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   cudaStream_t st = as_stream(stream);
   if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
   cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
-  long long threads = (long long)n_in * g.K;
-  if (threads > 0) {
-    { mark_outputs_kernel<<<ceil_div(threads, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+  if (n_in > 0) {
+    { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
     SSC_CHECK_LAUNCH("mark_outputs");
   }
   if (int e = exclusive_scan_u32<true>(s.bitmap, s.n_words, s.word_prefix, s.block_sums, s.misc, n_out_dev, st)) return e;

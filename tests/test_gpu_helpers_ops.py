@@ -172,5 +172,6 @@ def test_batchnorm_activation_golden(cuda, golden):
     # a non-fusable callable takes the composite path and agrees with the fused kernel
     act2 = Activation(Rs_out[:-1], (lambda v: torch.relu(v), torch.sigmoid), bias=True, checkpoint=False).to(cuda)
     act2.load_state_dict(act.state_dict())
-    z2 = act2(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
+    with torch.no_grad():
+        z2 = act2(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
     assert np.abs(z2 - z).max() <= 2e-6
