@@ -13,7 +13,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libssconv_b200.so")
+# SSCONV_B200_LIB selects another build of the same library (e.g. a debug build)
+LIB_PATH = os.environ.get("SSCONV_B200_LIB", os.path.join(_HERE, "libssconv_b200.so"))
 
 PREC_FP32, PREC_TF32 = 0, 1
 _precision = os.environ.get("SSCONV_PRECISION", "auto")
