@@ -1,21 +1,23 @@
 // Output-stationary gather-GEMM on the 5th-generation tensor cores (tcgen05, sm_100a).
 //
 // One CTA owns 128 consecutive output rows and runs a warp-specialised pipeline over the
-// steps (kernel offset with a neighbour in the tile) x (32-channel slab of the input):
-//   * four producer warps, one thread per output row: the thread looks up its neighbour row
-//     for the offset and, if present, pulls the 128-byte slab of that feature row with
-//     cp.async straight into the K-major 128-byte-swizzled operand layout of a ring slot,
-//     several steps ahead of use; rows without a neighbour stay zero (a slot row is cleared
-//     again only if it held data before).  When its copies have landed the thread rounds its
-//     row fp32 -> TF32 (round to nearest) in place and arrives on the slot's "A full" mbarrier.
-//     Producer thread 0 also brings in the pre-packed filter slab (already TF32, already in
-//     operand layout) with one bulk asynchronous copy that completes on the "B full" mbarrier.
-//   * one MMA warp: a single thread waits for both barriers, issues tcgen05.mma (M=128,
-//     N<=256, K=8 per instruction) accumulating in tensor memory (fp32), and commits the
-//     group to the slot's "empty" mbarrier, which lets the producers refill the slot.
+// steps (kernel offset with a neighbour in the tile) x (32-channel slab of the input).  The
+// operand ring has one slot per producer warp:
+//   * producer warp w owns ring slot w and prepares the steps w, w+S, w+2S, ...: each lane
+//     looks up the neighbour rows of its four output rows and pulls the 128-byte slab of every
+//     present feature row with cp.async straight into the K-major 128-byte-swizzled operand
+//     layout; rows without a neighbour stay zero (a slot row is cleared again only if it held
+//     data before).  When its copies have landed the lane rounds its rows fp32 -> TF32 (round
+//     to nearest) in place and arrives on the slot's "A full" mbarrier.  Lane 0 also brings in
+//     the pre-packed filter slab (already TF32, already in operand layout) with one bulk
+//     asynchronous copy that completes on the "B full" mbarrier.  The global-memory latency
+//     of a step is paid inside one warp while the other warps work on the neighbouring steps.
+//   * one MMA warp: a single thread waits for both barriers of a slot, issues tcgen05.mma
+//     (M=128, N<=256, K=8 per instruction) accumulating in tensor memory (fp32), and commits
+//     the group to the slot's "empty" mbarrier, which lets the owner refill the slot.
 // There is no CTA-wide barrier inside the loop.  Accumulators stay in TMEM across all
-// offsets; the producer warps then read them with tcgen05.ld and write each output row
-// exactly once (no scatter atomics, deterministic order).
+// offsets; four warps then read them with tcgen05.ld and write each output row exactly once
+// (no scatter atomics, deterministic order).
 //
 // Every wait on an mbarrier is bounded: on expiry the thread records an error in `status`
 // through a shared flag, every other wait then gives up too, and the kernel frees its tensor
@@ -28,8 +30,8 @@ namespace ssc {
 
 constexpr int TC_M = 128;
 constexpr int TC_SLAB = 32;            // tf32 elements per 128-byte operand row
-constexpr int TC_PRODUCERS = 128;      // producer threads, one per output row
-constexpr int TC_THREADS = 160;        // + one MMA warp
+constexpr int TC_MAX_STAGES = 8;       // producer warps = ring slots
+constexpr int TC_EPI_WARPS = 4;        // warps 0..3 also run the epilogue (one TMEM lane quarter each)
 constexpr int TC_A_BYTES = TC_M * 128;
 constexpr int TC_CTRL_BYTES = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -40,7 +42,8 @@ struct TcParams {
   int n_tiles;    // MMA instructions along N per k-step
   int tile_n;     // N of one MMA, multiple of 16, <= 256
   int tmem_cols;  // power of two >= max(32, n_pad)
-  int stages;     // operand ring depth
+  int stages;     // operand ring depth = number of producer warps (>= 4)
+  int threads;    // (stages + 1) * 32
   int b_bytes;    // n_pad * 128
 };
 
@@ -66,12 +69,14 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
     if (v == 1 || (v == 2 && p.tmem_cols <= 256 && two >= 2)) ctas = v;
   }
   p.stages = ctas == 2 ? two : one;
-  if (p.stages > 8) p.stages = 8;
+  if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
   if (const char *e = getenv("SSC_TC_STAGES")) {
     int v = atoi(e);
     if (v >= 2 && v <= p.stages) p.stages = v;
   }
-  return p.stages >= 2;
+  if (p.stages < 2) return false;
+  p.threads = ((p.stages > TC_EPI_WARPS ? p.stages : TC_EPI_WARPS) + 1) * 32;
+  return true;
 }
 
 // ------------------------------------------------------------------------- PTX wrappers
@@ -179,7 +184,9 @@ __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int 
   packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 2)
+// Warps 0 .. n_prod-1 are producers (warp w <-> ring slot w; with fewer than four slots the
+// spare warps only help in the prologue and epilogue), the last warp issues the MMAs.
+__global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
                      int32_t *status, TcParams p) {
@@ -198,26 +205,28 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   uint8_t *act_list = ctrl + 512;                          // [256]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_warps = blockDim.x >> 5;
+  const int mma_warp = n_warps - 1;
   const int m0 = blockIdx.x * TC_M;
   const int S = p.stages;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(empty_bars + s), 1);
-      mbar_init(smem_u32(fulla_bars + s), TC_PRODUCERS);
+      mbar_init(smem_u32(fulla_bars + s), 32);
       mbar_init(smem_u32(fullb_bars + s), 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == mma_warp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((uint32_t)p.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   } else {
     // which kernel offsets touch this tile
-    for (int kappa = warp; kappa < K; kappa += TC_PRODUCERS / 32) {
+    for (int kappa = warp; kappa < K; kappa += mma_warp) {
       bool any = false;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -227,11 +236,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       unsigned b = __ballot_sync(0xffffffffu, any);
       if (lane == 0) act_flag[kappa] = b != 0;
     }
-    // every A row of every slot starts as zero
-    for (int sl = 0; sl < S; ++sl) {
-      uint4 *row = (uint4 *)(smem + (size_t)sl * stage_bytes + (size_t)(tid >> 3) * 1024 + (size_t)(tid & 7) * 128);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+    // every A row of the slot this warp owns starts as zero
+    if (warp < S) {
+      uint4 *slot = (uint4 *)(smem + (size_t)warp * stage_bytes);
+      for (int i = lane; i < TC_A_BYTES / 16; i += 32) slot[i] = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   tc_fence_before();
@@ -249,28 +257,80 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int n_iter = n_act * p.k_slabs;
   const uint32_t smem_base = smem_u32(smem);
 
-  if (warp < 4) {
-    // ================================ producers: thread <-> output row ======================
-    const int m = m0 + tid;
-    const bool row_valid = m < n_out;
+  if (warp < S) {
+    // ====================== producer warp: steps warp, warp+S, ... into slot `warp` =========
     const bool vec_ok = (c_in & 3) == 0;
-    const int L = S - 1;  // steps of copies in flight ahead of the step being completed
-    // byte offset of this thread's operand row inside an A slot; chunk c sits at (c ^ (row & 7)) * 16
-    const uint32_t row_off = (uint32_t)(tid >> 3) * 1024u + (uint32_t)(tid & 7) * 128u;
-    const uint32_t sw = (uint32_t)(tid & 7);
-    uint32_t dirty = 0;  // bit s: this thread's row of slot s currently holds gathered data
-    uint32_t wrote = (1u << S) - 1u;  // bit s: this thread wrote into slot s since it was last published (all: zero-fill)
-    int src = -1, next_src = -1;
-    if (n_act > 0 && row_valid) next_src = __ldg(nbr + (size_t)act_list[0] * n_out + m);
-    int slot_i = 0, par_i = 0, act_i = 0, slab_i = 0;  // issue cursor
-    int slot_c = 0;                                     // completion cursor
-    bool alive = true;
-    for (int j = 0; j < n_iter + L && alive; ++j) {
-      // ---- complete step j - L: copies landed -> round to TF32 -> publish
-      if (j >= L) {
-        cp_async_wait(L - 1);
-        if (dirty & (1u << slot_c)) {
-          uint8_t *row = smem + (size_t)slot_c * stage_bytes + row_off;
+    const uint32_t slot_addr = smem_base + (uint32_t)warp * (uint32_t)stage_bytes;
+    uint8_t *slot_ptr = smem + (size_t)warp * stage_bytes;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    // row q*32+lane of the slot: 8-row group (q*4 + lane/8), row-in-group lane%8
+    uint32_t row_off[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) row_off[q] = (uint32_t)(q * 4 + (lane >> 3)) * 1024u + sw * 128u;
+    uint32_t dirty = 0;      // bit q: row q*32+lane of the slot currently holds gathered data
+    bool fence_needed = true;  // the prologue zero-fill has to be published once
+    uint32_t par = 0;        // parity of the slot's current use
+    for (int j = warp; j < n_iter; j += S) {
+      const int act = j / p.k_slabs, slab = j - act * p.k_slabs;
+      const int kappa = act_list[act];
+      int src[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        int r = m0 + q * 32 + lane;
+        src[q] = r < n_out ? __ldg(nbr + (size_t)kappa * n_out + r) : -1;
+      }
+      if (j >= S) {
+        if (!mbar_wait(smem_u32(empty_bars + warp), par ^ 1u, abort_flag)) break;
+        tc_fence_after();
+      }
+      if (lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
+        const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
+        const uint32_t bar = smem_u32(fullb_bars + warp);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)p.b_bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         slot_addr + TC_A_BYTES),
+                     "l"(bsrc), "r"((uint32_t)p.b_bytes), "r"(bar)
+                     : "memory");
+      }
+      const int ch0 = slab * TC_SLAB;
+      uint32_t present = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (src[q] >= 0 && ch0 < c_in) {
+          const float *fp = features + (size_t)src[q] * c_in + ch0;
+          const uint32_t a_row = slot_addr + row_off[q];
+          if (vec_ok) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {  // chunks past the last channel are zero-filled
+              bool ok = ch0 + c * 4 < c_in;
+              cp_async16(a_row + ((c ^ sw) << 4), ok ? (const void *)(fp + c * 4) : (const void *)features, ok ? 16u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                bool ok = ch0 + c * 4 + e < c_in;
+                cp_async4(a_row + ((c ^ sw) << 4) + 4u * e, ok ? (const void *)(fp + c * 4 + e) : (const void *)features,
+                          ok ? 4u : 0u);
+              }
+          }
+          present |= 1u << q;
+        } else if (dirty & (1u << q)) {
+          uint4 *row = (uint4 *)(slot_ptr + row_off[q]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+          fence_needed = true;
+        }
+      }
+      dirty = present;
+      cp_async_commit();
+      cp_async_wait(0);
+      // copies landed: round the gathered rows to TF32 in place
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (present & (1u << q)) {
+          uint8_t *row = slot_ptr + row_off[q];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             uint4 *ptr = (uint4 *)(row + ((c ^ sw) << 4));
@@ -281,109 +341,17 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
             v.w = to_tf32(__uint_as_float(v.w));
             *ptr = v;
           }
+          fence_needed = true;
         }
-        if (wrote & (1u << slot_c)) {  // make this thread's writes visible to the tensor core
-          fence_async_smem();
-          wrote &= ~(1u << slot_c);
-        }
-        mbar_arrive(smem_u32(fulla_bars + slot_c));
-        if (++slot_c == S) slot_c = 0;
       }
-      // ---- issue the copies of step j
-      if (j < n_iter) {
-        if (slab_i == 0) {
-          src = next_src;
-          if (act_i + 1 < n_act && row_valid) next_src = __ldg(nbr + (size_t)act_list[act_i + 1] * n_out + m);
-        }
-        if (j >= S) {
-          if (!mbar_wait(smem_u32(empty_bars + slot_i), (uint32_t)(par_i ^ 1), abort_flag)) alive = false;
-          tc_fence_after();
-        }
-        if (alive) {
-          const uint32_t a_row = smem_base + (uint32_t)slot_i * (uint32_t)stage_bytes + row_off;
-          const int ch0 = slab_i * TC_SLAB;
-          if (src >= 0 && ch0 < c_in) {
-            const float *fp = features + (size_t)src * c_in + ch0;
-            if (vec_ok) {
-#pragma unroll
-              for (int c = 0; c < 8; ++c)
-                if (ch0 + c * 4 < c_in) cp_async16(a_row + ((c ^ sw) << 4), fp + c * 4, 16u);
-            } else {
-#pragma unroll
-              for (int c = 0; c < 8; ++c)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  bool ok = ch0 + c * 4 + q < c_in;
-                  cp_async4(a_row + ((c ^ sw) << 4) + 4u * q, ok ? (const void *)(fp + c * 4 + q) : (const void *)features,
-                            ok ? 4u : 0u);
-                }
-            }
-            dirty |= 1u << slot_i;
-            wrote |= 1u << slot_i;
-          } else if (dirty & (1u << slot_i)) {
-            uint8_t *row = smem + (size_t)slot_i * stage_bytes + row_off;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) *(uint4 *)(row + (c << 4)) = make_uint4(0u, 0u, 0u, 0u);
-            dirty &= ~(1u << slot_i);
-            wrote |= 1u << slot_i;
-          }
-          if (tid == 0) {  // the pre-packed filter slab of this step: one bulk copy
-            const uint4 *bsrc = packed + ((size_t)act_list[act_i] * p.k_slabs + slab_i) * (size_t)(p.n_pad * 8);
-            const uint32_t bar = smem_u32(fullb_bars + slot_i);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)p.b_bytes) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             smem_base + (uint32_t)slot_i * (uint32_t)stage_bytes + TC_A_BYTES),
-                         "l"(bsrc), "r"((uint32_t)p.b_bytes), "r"(bar)
-                         : "memory");
-          }
-        }
-        if (++slab_i == p.k_slabs) { slab_i = 0; ++act_i; }
-        if (++slot_i == S) { slot_i = 0; par_i ^= 1; }
+      if (fence_needed) {  // make this lane's writes visible to the tensor core
+        fence_async_smem();
+        fence_needed = false;
       }
-      cp_async_commit();
+      mbar_arrive(smem_u32(fulla_bars + warp));
+      par ^= 1u;
     }
-    cp_async_wait(0);
-
-    // ================================ epilogue: TMEM -> registers -> global ==================
-    bool ok = alive && !*abort_flag;
-    if (ok && n_iter > 0) {
-      int last = n_iter - 1;
-      ok = mbar_wait(smem_u32(empty_bars + (last % S)), (uint32_t)((last / S) & 1), abort_flag);
-    }
-    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
-    tc_fence_after();
-    const int n_cols = (c_out + 15) & ~15;
-    for (int c0 = 0; c0 < n_cols && c0 < p.n_pad; c0 += 16) {
-      uint32_t r[16];
-      if (ok && n_iter > 0) {
-        uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
-#pragma unroll
-        for (int q = 0; q < 16; ++q) r[q] = 0u;
-      }
-      if (row_valid) {
-        float *op = out + (size_t)m * c_out + c0;
-        if ((c_out & 3) == 0) {
-#pragma unroll
-          for (int q = 0; q < 16; q += 4)
-            if (c0 + q < c_out)
-              *(float4 *)(op + q) = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
-                                                __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
-        } else {
-#pragma unroll
-          for (int q = 0; q < 16; ++q)
-            if (c0 + q < c_out) op[q] = __uint_as_float(r[q]);
-        }
-      }
-    }
-  } else if (lane == 0) {
+  } else if (warp == mma_warp && lane == 0) {
     // ================================ MMA issuer ============================================
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     int s = 0, par = 0;
@@ -404,10 +372,54 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       if (++s == S) { s = 0; par ^= 1; }
     }
   }
+
+  // ================================ epilogue: TMEM -> registers -> global ====================
+  if (warp < TC_EPI_WARPS) {
+    __syncwarp();
+    bool ok = !*abort_flag;
+    if (ok && n_iter > 0) {
+      int last = n_iter - 1;
+      ok = mbar_wait(smem_u32(empty_bars + (last % S)), (uint32_t)((last / S) & 1), abort_flag);
+    }
+    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
+    tc_fence_after();
+    const int m = m0 + warp * 32 + lane;
+    const int n_cols = (c_out + 15) & ~15;
+    for (int c0 = 0; c0 < n_cols && c0 < p.n_pad; c0 += 16) {
+      uint32_t r[16];
+      if (ok && n_iter > 0) {
+        uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) r[q] = 0u;
+      }
+      if (m < n_out) {
+        float *op = out + (size_t)m * c_out + c0;
+        if ((c_out & 3) == 0) {
+#pragma unroll
+          for (int q = 0; q < 16; q += 4)
+            if (c0 + q < c_out)
+              *(float4 *)(op + q) = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
+                                                __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q)
+            if (c0 + q < c_out) op[q] = __uint_as_float(r[q]);
+        }
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag && status) atomicOr(status, 16);
-  if (warp == 4) {
+  if (warp == mma_warp) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
                  : "memory");
   }
@@ -426,7 +438,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   cudaError_t e = cudaFuncSetAttribute(conv_fwd_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
   int grid = ceil_div(n_out, TC_M);
-  { conv_fwd_tf32_kernel<<<grid, TC_THREADS, smem, st>>>(features, c_in, (const uint4 *)packed, K, c_out, nbr, n_out,
+  { conv_fwd_tf32_kernel<<<grid, p.threads, smem, st>>>(features, c_in, (const uint4 *)packed, K, c_out, nbr, n_out,
                                                       out, status, p); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;
