@@ -198,9 +198,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   uint64_t *empty_bars = (uint64_t *)ctrl;                 // [stages] slot free (its MMAs retired)
   uint64_t *fulla_bars = (uint64_t *)(ctrl + 64);          // [stages] gathered rows ready
   uint64_t *fullb_bars = (uint64_t *)(ctrl + 128);         // [stages] filter slab landed
-  uint32_t *tmem_slot = (uint32_t *)(ctrl + 192);
-  volatile int *abort_flag = (volatile int *)(ctrl + 196);
-  int *n_act_s = (int *)(ctrl + 200);
+  uint64_t *done_bar = (uint64_t *)(ctrl + 192);           // all MMAs of the tile retired
+  uint32_t *tmem_slot = (uint32_t *)(ctrl + 200);
+  volatile int *abort_flag = (volatile int *)(ctrl + 204);
+  int *n_act_s = (int *)(ctrl + 208);
   uint8_t *act_flag = ctrl + 256;                          // [256]
   uint8_t *act_list = ctrl + 512;                          // [256]
 
@@ -216,6 +217,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       mbar_init(smem_u32(fulla_bars + s), 32);
       mbar_init(smem_u32(fullb_bars + s), 1);
     }
+    mbar_init(smem_u32(done_bar), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -371,16 +373,14 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       mma_commit(smem_u32(empty_bars + s));
       if (++s == S) { s = 0; par ^= 1; }
     }
+    mma_commit(smem_u32(done_bar));  // arrives once everything issued above has retired
   }
 
   // ================================ epilogue: TMEM -> registers -> global ====================
   if (warp < TC_EPI_WARPS) {
     __syncwarp();
     bool ok = !*abort_flag;
-    if (ok && n_iter > 0) {
-      int last = n_iter - 1;
-      ok = mbar_wait(smem_u32(empty_bars + (last % S)), (uint32_t)((last / S) & 1), abort_flag);
-    }
+    if (ok && n_iter > 0) ok = mbar_wait(smem_u32(done_bar), 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     const int m = m0 + warp * 32 + lane;
