@@ -47,7 +47,7 @@ def surface_voxels(sample_ids, V, n_pts, base_seed=0):
         v = np.floor((p + 0.5) * V).astype(np.int64)
         v = np.unique(v, axis=0)
         rows.append(np.concatenate([np.full((v.shape[0], 1), b, dtype=np.int64), v], axis=1))
-    return np.concatenate(rows, axis=0).astype(np.int32)
+    return np.ascontiguousarray(np.concatenate(rows, axis=0), dtype=np.int32)
 
 
 def bernoulli_voxels(sample_ids, V, occupancy, base_seed=0):
@@ -56,7 +56,7 @@ def bernoulli_voxels(sample_ids, V, occupancy, base_seed=0):
         rng = np.random.RandomState(base_seed + int(sid))
         occ = np.argwhere(rng.rand(V, V, V) < occupancy)
         rows.append(np.concatenate([np.full((occ.shape[0], 1), b, dtype=np.int64), occ], axis=1))
-    return np.concatenate(rows, axis=0).astype(np.int32)
+    return np.ascontiguousarray(np.concatenate(rows, axis=0), dtype=np.int32)
 
 
 def object_points(sample_ids, n_pts, base_seed=0):
