@@ -72,6 +72,27 @@ int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, const int sha
                       int32_t *indice_num, int32_t *status, void *scratch, size_t scratch_bytes,
                       void *stream);
 
+/* Submanifold rulebook for callers that must not allocate device memory (no counterpart in
+ * the reference).  Who needs it: a plugin inside a host application that owns every byte of
+ * device memory and lends none, a long-running service whose device pool is frozen after
+ * start-up so that no request can fail or stall on an allocation, a component built without
+ * any allocator.  Same results as ssc_rulebook_subm, but the hash table and the counters sit
+ * in a fixed array inside the library (about 1.1 MB, held by every GPU that loads the library
+ * until the process exits) instead of a caller buffer.  The entry point calls neither
+ * cudaMalloc nor cudaFree nor any allocating library routine; inputs and outputs are still
+ * the caller's.
+ *   Limits   : n_in <= 65536 active voxels, kernel volume <= 256; larger requests are refused
+ *              with SSC_ERR_INVALID and a message naming the limit.
+ *   Set-up   : the first call on each device looks up the array's device address (once per
+ *              device, with that device current).  Make that first call before any stream
+ *              capture begins.
+ *   Sharing  : all calls use the same array and it keeps what the last call left; each call
+ *              clears what it needs cleared.  Two calls that overlap on one GPU (different
+ *              streams or threads) race on it: run them one after the other. */
+int ssc_rulebook_subm_static(const int32_t *indices, int n_in, int batch, const int shape[3],
+                             const int ksize[3], const int dilation[3], int32_t *nbr,
+                             int32_t *pairs, int32_t *indice_num, int32_t *status, void *stream);
+
 /* Regular / strided (transpose = 0) or transposed (transpose = 1,
  * getValidOutPosTranspose geometry.h:82-138) rulebook, phase 1: build the input coordinate
  * hash, mark every reachable output cell and count them.  n_out_dev: device int32 that

@@ -359,6 +359,83 @@ int bitmap_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// Submanifold rulebook for callers that cannot allocate device memory.
+//
+// Some hosts of this library may never call cudaMalloc: a plugin loaded into an application
+// that owns all device memory and hands out none, a service whose device pool is fixed at
+// start-up so that an allocation can neither fail nor stall the device later on, a sandboxed
+// component with no allocator at all.  For them the hash table and the per-chunk counters
+// live in the array below, which every GPU that loads this library keeps until the process
+// exits.  Its size fixes the limits: at most kStaticMaxRows active voxels and a kernel
+// volume of at most 256.
+constexpr int kStaticMaxRows = 65536;
+constexpr size_t kStaticTableBytes = (size_t)(2 * kStaticMaxRows / kBucketSlots) * kBucketSlots * 8;  // 1 MiB
+constexpr size_t kStaticChunkBytes = (size_t)(kStaticMaxRows / kChunk + 2) * 256 * 4;                 // 66 KiB
+constexpr size_t kStaticScratchBytes = kStaticTableBytes + kStaticChunkBytes + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch, looked up once per device (host code cannot use the
+// symbol itself as a pointer).
+static int static_scratch_address(unsigned char **out) {
+  constexpr int kMaxDevices = 64;
+  static unsigned char *address[kMaxDevices] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "rulebook_subm_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SSC_ERR_INVALID, "rulebook_subm_static: device index %d not supported", dev);
+  unsigned char *p = __atomic_load_n(&address[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress((void **)&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(SSC_ERR_CUDA, "rulebook_subm_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    __atomic_store_n(&address[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return 0;
+}
+
+}  // namespace ssc
+
+using namespace ssc;
+
+extern "C" int ssc_rulebook_subm_static(const int32_t *indices, int n_in, int batch, const int shape[3],
+                                        const int ksize[3], const int dilation[3], int32_t *nbr, int32_t *pairs,
+                                        int32_t *indice_num, int32_t *status, void *stream) {
+  SSC_REQUIRE(n_in >= 0 && shape && ksize && dilation, "rulebook_subm_static: bad arguments");
+  if (n_in > kStaticMaxRows)
+    return fail(SSC_ERR_INVALID, "rulebook_subm_static: %d active voxels exceed the built-in scratch (max %d); "
+                                 "use ssc_rulebook_subm with caller scratch", n_in, kStaticMaxRows);
+  SSC_REQUIRE(n_in == 0 || (indices && nbr), "rulebook_subm_static: null pointer");
+  int one[3] = {1, 1, 1};
+  int pad[3] = {ksize[0] / 2, ksize[1] / 2, ksize[2] / 2};
+  Geometry g;
+  SSC_REQUIRE(fill_geometry(g, shape, shape, ksize, one, pad, dilation, 0) == 0, "rulebook_subm_static: bad geometry");
+  SSC_REQUIRE(g.K <= 256, "rulebook_subm_static: kernel volume %d > 256", g.K);
+  if (int e = check_volume(batch, shape, "rulebook_subm_static")) return e;
+  unsigned char *base = nullptr;
+  if (int e = static_scratch_address(&base)) return e;
+  // Lay the pieces the submanifold path touches over the static array.  Everything a call
+  // reads is (re)initialised by that call: the table and the status words are cleared in
+  // build_hash, the chunk counters are fully rewritten by the lookup kernel.
+  RulebookScratch s;
+  memset(&s, 0, sizeof(s));
+  s.n_buckets = hash_buckets_for(n_in);
+  s.table = (unsigned long long *)base;
+  s.chunk_counts = (int32_t *)(base + kStaticTableBytes);
+  s.misc = (int32_t *)(base + kStaticTableBytes + kStaticChunkBytes);
+  s.out_cap = n_in;
+  s.n_chunks_cap = kStaticMaxRows / kChunk + 2;
+  if ((size_t)s.n_buckets * kBucketSlots * 8 > kStaticTableBytes)
+    return fail(SSC_ERR_INVALID, "rulebook_subm_static: hash table does not fit the built-in scratch");
+  cudaStream_t st = as_stream(stream);
+  if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
+  if (int e = lookup_and_compact(indices, n_in, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
+  SSC_CHECK_LAUNCH("rulebook_subm_static");
+  return SSC_OK;
+}
+
+namespace ssc {
 }  // namespace ssc
 
 using namespace ssc;

@@ -32,6 +32,8 @@ SIGNATURES = {
     "ssc_rulebook_scratch_bytes": (c_size_t, [c_int, c_int, _I3, c_int]),
     "ssc_rulebook_subm": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_size_t, c_void_p]),
+    "ssc_rulebook_subm_static": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p]),
     "ssc_rulebook_conv_count": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_void_p,
                                         c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_rulebook_conv_fill": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_int, c_void_p,
