@@ -47,8 +47,7 @@ struct TcParams {
   int b_bytes;    // n_pad * 128
 };
 
-// Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].  Two CTAs per SM are preferred
-// (one CTA's prologue / epilogue overlaps the other's main loop) when that leaves >= 3 stages.
+// Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
 static bool tc_params(int c_in, int c_out, TcParams &p) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   int n16 = (c_out + 15) / 16 * 16;
@@ -61,14 +60,16 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
   p.b_bytes = p.n_pad * 128;
   int stage = TC_A_BYTES + p.b_bytes;
   int fixed = TC_CTRL_BYTES + 1024;
-  int two = (113 * 1024 - fixed) / stage;   // per-CTA budget when two CTAs share an SM
-  int one = (226 * 1024 - fixed) / stage;
-  int ctas = (p.tmem_cols <= 256 && two >= 3) ? 2 : 1;
+  // Resident CTAs hide each other's per-step latencies, so take as many per SM as tensor
+  // memory (512 columns) and shared memory (two ring slots each at least) allow, up to four.
+  int ctas = 512 / p.tmem_cols;
+  if (ctas > 4) ctas = 4;
+  while (ctas > 1 && ((227 * 1024) / ctas - 1024 - fixed) / stage < 2) --ctas;
   if (const char *e = getenv("SSC_TC_CTAS_PER_SM")) {
     int v = atoi(e);
-    if (v == 1 || (v == 2 && p.tmem_cols <= 256 && two >= 2)) ctas = v;
+    if (v >= 1 && v <= ctas) ctas = v;
   }
-  p.stages = ctas == 2 ? two : one;
+  p.stages = ((227 * 1024) / ctas - 1024 - fixed) / stage;
   if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
   if (const char *e = getenv("SSC_TC_STAGES")) {
     int v = atoi(e);
@@ -139,8 +140,10 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return r;
 }
+// .ca: a lane fetches the eight 16-byte chunks of one 128-byte row with eight copies; letting
+// them allocate in L1 turns seven of the eight into L1 hits.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -214,7 +217,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(empty_bars + s), 1);
-      mbar_init(smem_u32(fulla_bars + s), 32);
+      mbar_init(smem_u32(fulla_bars + s), 32u * (uint32_t)(S < TC_EPI_WARPS ? TC_EPI_WARPS / S : 1));
       mbar_init(smem_u32(fullb_bars + s), 1);
     }
     mbar_init(smem_u32(done_bar), 1);
@@ -238,11 +241,12 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       unsigned b = __ballot_sync(0xffffffffu, any);
       if (lane == 0) act_flag[kappa] = b != 0;
     }
-    // every A row of the slot this warp owns starts as zero
-    if (warp < S) {
-      uint4 *slot = (uint4 *)(smem + (size_t)warp * stage_bytes);
+    // every A row of every slot starts as zero
+    for (int sl = warp; sl < S; sl += mma_warp) {
+      uint4 *slot = (uint4 *)(smem + (size_t)sl * stage_bytes);
       for (int i = lane; i < TC_A_BYTES / 16; i += 32) slot[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+    fence_async_smem();  // publish the zero-fill to the tensor core's view of shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -259,35 +263,50 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int n_iter = n_act * p.k_slabs;
   const uint32_t smem_base = smem_u32(smem);
 
-  if (warp < S) {
-    // ====================== producer warp: steps warp, warp+S, ... into slot `warp` =========
+  const int n_prod = S < TC_EPI_WARPS ? (TC_EPI_WARPS / S) * S : S;  // producer warps (2 slots -> 4 warps)
+  if (warp < n_prod) {
+    // ====================== producer warp ====================================================
+    // With S >= 4 ring slots, warp w owns slot w and prepares all 128 rows of the steps
+    // w, w+S, ...; with fewer slots several warps share a slot and split its rows.
+    const int slot = warp % S;
+    const int share = n_prod / S;              // warps per slot
+    const int part = warp / S;                 // which share of the rows this warp prepares
+    const int q_per = 4 / share;               // 32-row groups per warp (share is 1, 2 or 4)
+    const int q0 = part * q_per;
     const bool vec_ok = (c_in & 3) == 0;
-    const uint32_t slot_addr = smem_base + (uint32_t)warp * (uint32_t)stage_bytes;
-    uint8_t *slot_ptr = smem + (size_t)warp * stage_bytes;
+    const uint32_t slot_addr = smem_base + (uint32_t)slot * (uint32_t)stage_bytes;
+    uint8_t *slot_ptr = smem + (size_t)slot * stage_bytes;
     const uint32_t sw = (uint32_t)(lane & 7);
     // row q*32+lane of the slot: 8-row group (q*4 + lane/8), row-in-group lane%8
     uint32_t row_off[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) row_off[q] = (uint32_t)(q * 4 + (lane >> 3)) * 1024u + sw * 128u;
-    uint32_t dirty = 0;      // bit q: row q*32+lane of the slot currently holds gathered data
-    bool fence_needed = true;  // the prologue zero-fill has to be published once
-    uint32_t par = 0;        // parity of the slot's current use
-    for (int j = warp; j < n_iter; j += S) {
-      const int act = j / p.k_slabs, slab = j - act * p.k_slabs;
-      const int kappa = act_list[act];
-      int src[4];
+    uint32_t dirty = 0;        // bit q: row q*32+lane of the slot currently holds gathered data
+    bool fence_needed = false;
+    uint32_t par = 0;          // parity of the slot's current use
+    int src[4], nxt[4];
+    auto load_rows = [&](int j, int *dst) {
+      const int kap = act_list[j / p.k_slabs];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         int r = m0 + q * 32 + lane;
-        src[q] = r < n_out ? __ldg(nbr + (size_t)kappa * n_out + r) : -1;
+        dst[q] = (q >= q0 && q < q0 + q_per && r < n_out) ? __ldg(nbr + (size_t)kap * n_out + r) : -1;
       }
+    };
+    if (slot < n_iter) load_rows(slot, nxt);
+    for (int j = slot; j < n_iter; j += S) {
+      const int act = j / p.k_slabs, slab = j - act * p.k_slabs;
+      const int kappa = act_list[act];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) src[q] = nxt[q];
+      if (j + S < n_iter) load_rows(j + S, nxt);  // neighbour rows of this warp's next step
       if (j >= S) {
-        if (!mbar_wait(smem_u32(empty_bars + warp), par ^ 1u, abort_flag)) break;
+        if (!mbar_wait(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
         tc_fence_after();
       }
-      if (lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
+      if (part == 0 && lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
         const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
-        const uint32_t bar = smem_u32(fullb_bars + warp);
+        const uint32_t bar = smem_u32(fullb_bars + slot);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)p.b_bytes) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                          slot_addr + TC_A_BYTES),
@@ -319,9 +338,9 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
           }
           present |= 1u << q;
         } else if (dirty & (1u << q)) {
-          uint4 *row = (uint4 *)(slot_ptr + row_off[q]);
+          uint8_t *row = slot_ptr + row_off[q];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+          for (int c = 0; c < 8; ++c) *(uint4 *)(row + ((c ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);  // swizzled order: no bank conflicts
           fence_needed = true;
         }
       }
@@ -350,7 +369,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         fence_async_smem();
         fence_needed = false;
       }
-      mbar_arrive(smem_u32(fulla_bars + warp));
+      mbar_arrive(smem_u32(fulla_bars + slot));
       par ^= 1u;
     }
   } else if (warp == mma_warp && lane == 0) {
