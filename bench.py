@@ -118,6 +118,80 @@ class Layer:
             return self.pool(self.conv(x))
 
 
+BACKBONE = dict(name="backbone: Point2Voxel(32^3, mean) + 4 x [SS-Conv k3 s2 p1 + BatchNorm(eval) + gate(relu, sigmoid)] + "
+                     "GlobalAvgPool, irreps (3)->(8,4,2)->(16,8,4)->(32,16,8)->(64,32,16), 1024 points/object, "
+                     "global batch 256 sharded by sample",
+                irreps=[(3,), (8, 4, 2), (16, 8, 4), (32, 16, 8), (64, 32, 16)], V=32, n_pts=1024, global_batch=256)
+
+
+class Backbone:
+    """The 4-stage backbone of the benchmark configurations, from the public ss_conv modules."""
+
+    def __init__(self, cfg, device):
+        from ss_conv.activation import Activation
+        from ss_conv.batchnorm import BatchNorm
+        from ss_conv.convolution import Convolution
+        from ss_conv.pool import GlobalAvgPool
+        from ss_conv.sp_ops.voxelize import Point2Voxel
+        torch.manual_seed(4321)
+        V = cfg["V"]
+        self.p2v = Point2Voxel([V] * 3, [1.0 / V] * 3, 4)
+        self.stages = []
+        for a, b in zip(cfg["irreps"][:-1], cfg["irreps"][1:]):
+            conv = Convolution(rs_of(a), rs_of(b, gates=True), 3, stride=2, padding=1).to(device).eval()
+            bn = BatchNorm(rs_of(b, gates=True)).to(device).eval()
+            with torch.no_grad():
+                bn.running_var.uniform_(0.5, 1.5)
+                bn.running_mean.normal_(0, 0.1)
+            act = Activation(rs_of(b), (torch.relu, torch.sigmoid), bias=False, checkpoint=False)
+            self.stages.append((conv, bn, act))
+        self.pool = GlobalAvgPool()
+
+    def forward(self, points, feats, ids):
+        with torch.no_grad():
+            x = self.p2v(points, feats, ids)[1]
+            for conv, bn, act in self.stages:
+                x = act(bn(conv(x)))
+            return self.pool(x)
+
+
+def run_backbone(args, dev, rank, world, dist):
+    """Backbone samples/s at a global batch of 256 split by sample over the ranks, including the
+    all-gather of the pooled per-sample features (the only collective)."""
+    from ss_conv import parallel
+    from ss_conv.utils import synthetic as S
+    cfg = BACKBONE
+    lo, hi = parallel.shard_range(cfg["global_batch"], rank, world)
+    pts, fts, ids = S.object_points(range(lo, hi), cfg["n_pts"], base_seed=7000)
+    pts, fts, ids = (torch.from_numpy(a).to(dev) for a in (pts, fts, ids))
+    net = Backbone(cfg, dev)
+    steps = max(3, min(args.steps, 15))
+
+    def step():
+        pooled = net.forward(pts, fts, ids)
+        return parallel.all_gather_rows(pooled, cfg["global_batch"])
+
+    for _ in range(3):
+        out = step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        out = step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    assert out.shape == (cfg["global_batch"], 240)
+    return {"metric": "backbone samples/sec", "value": cfg["global_batch"] * steps / (float(ms) * 1e-3), "unit": "samples/s",
+            "global_batch": cfg["global_batch"], "steps": steps, "ms_per_step": float(ms) / steps, "scaling": "strong",
+            "workload": cfg["name"], "collective": "all_gather of pooled [B/G,240] fp32 rows" if world > 1 else "none"}
+
+
 def make_inputs(cfg, sample_base, n_sets):
     from ss_conv.utils import synthetic as S
     sets = []
@@ -221,6 +295,9 @@ def run_ours(args):
     peak, peak_src = peaks()
     achieved = float(np.mean(alg_bytes)) / (float(np.mean(kern_ms)) * 1e-3) / 1e9
 
+    backbone = run_backbone(args, dev, rank, world, dist)
+    _ext.set_precision("tf32")
+
     # ---- reduce over ranks
     stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -249,6 +326,7 @@ def run_ours(args):
                          "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
                          "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
         }
+        line["backbone"] = backbone
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, budget_s=12.0)
         print(json.dumps(line), flush=True)

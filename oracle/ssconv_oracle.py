@@ -29,13 +29,21 @@ def _as3(v):
     return [int(x) for x in v] if isinstance(v, (list, tuple, np.ndarray)) else [int(v)] * 3
 
 
-def _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape):
+def deconv_output_size(in_size, ksize, stride, padding, dilation, output_padding):
+    """SS_Conv_lib/ss_conv/sp_ops/ops.py:26-36."""
+    return [(n - 1) * s - 2 * p + k + op for n, k, s, p, op in zip(in_size, ksize, stride, padding, output_padding)]
+
+
+def _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape, transpose=False):
     """All (input row j, kernel offset kappa, output coord) triples allowed by
     SS_Conv_lib/src/conv/geometry.h:18-80 (getValidOutPos): out*stride - pad + k*dil == in,
     0 <= out < out_shape; kappa = (kx*ky_size + ky)*kz_size + kz (geometry.h:56-65).
     Returned sorted by (j, kappa), which is the reference CPU scan order
     (geometry.h:166-186: inputs ascending, candidates from the largest output coordinate
-    downwards == ascending kappa)."""
+    downwards == ascending kappa).  For the transposed geometry the reference scans candidates
+    from the largest output coordinate too, which is DEscending kappa; callers that need the
+    reference's first-seen numbering there must not rely on this order (the rulebook parity
+    tests compare in canonical order)."""
     n = indices.shape[0]
     kx, ky, kz = ksize
     K = kx * ky * kz
@@ -46,9 +54,12 @@ def _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape):
         valid = np.ones(n, dtype=bool)
         o = np.empty((n, 3), dtype=np.int64)
         for d in range(3):
-            num = coords[:, d] + padding[d] - kk[d] * dilation[d]
-            valid &= (num % stride[d] == 0)
-            od = num // stride[d]
+            if transpose:  # geometry.h:82-138 (getValidOutPosTranspose): out = in*stride - pad + k*dil
+                od = coords[:, d] * stride[d] - padding[d] + kk[d] * dilation[d]
+            else:
+                num = coords[:, d] + padding[d] - kk[d] * dilation[d]
+                valid &= (num % stride[d] == 0)
+                od = num // stride[d]
             valid &= (od >= 0) & (od < out_shape[d])
             o[:, d] = od
         j = np.nonzero(valid)[0]
@@ -63,7 +74,7 @@ def _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape):
 
 
 def get_indice_pairs(indices, batch_size, spatial_shape, ksize=3, stride=1, padding=0, dilation=1,
-                     subm=False):
+                     subm=False, transpose=False, output_padding=0):
     """Rulebook in the reference's CPU order.
 
     Regular conv: SS_Conv_lib/src/conv/geometry.h:140-189 (getIndicePairsConv): outputs are
@@ -81,9 +92,11 @@ def get_indice_pairs(indices, batch_size, spatial_shape, ksize=3, stride=1, padd
         stride = [1, 1, 1]
         padding = [k // 2 for k in ksize]
         out_shape = spatial_shape
+    elif transpose:
+        out_shape = deconv_output_size(spatial_shape, ksize, stride, padding, dilation, _as3(output_padding))
     else:
         out_shape = conv_output_size(spatial_shape, ksize, stride, padding, dilation)
-    j, k, o, K = _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape)
+    j, k, o, K = _candidate_pairs(indices, ksize, stride, padding, dilation, out_shape, transpose and not subm)
     assert K <= 256  # indice_conv.h:44
     vol = out_shape[0] * out_shape[1] * out_shape[2]
     b = indices[j, 0].astype(np.int64)

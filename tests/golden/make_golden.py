@@ -124,6 +124,19 @@ def main():
         out["rb%d_pairs" % ci] = r[1].numpy().copy()
         out["rb%d_num" % ci] = r[2].numpy().copy()
 
+    # ---- transposed rulebooks (getIndicePairsDeConv, geometry.h:191-239)
+    tcases = [(3, 2, 1, 1), (2, 2, 0, 0), (3, 1, 1, 0)]          # (k, stride, pad, output_padding)
+    tind = surface_indices(rng, 2, 8, 90)
+    out["rbt_indices"] = tind
+    out["rbt_cases"] = np.array(tcases, dtype=np.int32)
+    for ci, (k, s, p, op) in enumerate(tcases):
+        osz = [(8 - 1) * s - 2 * p + k + op] * 3
+        r = ext.get_indice_pairs_3d(torch.from_numpy(tind), 2, osz, [8] * 3, [k] * 3, [s] * 3, [p] * 3, [1] * 3,
+                                    [op] * 3, 0, 1)
+        out["rbt%d_outids" % ci] = r[0].numpy().copy()
+        out["rbt%d_pairs" % ci] = r[1].numpy().copy()
+        out["rbt%d_num" % ci] = r[2].numpy().copy()
+
     # ---- one steerable layer through the reference's Python API on CPU tensors
     torch.manual_seed(7)
     Rs_in = [(2, 0), (2, 1), (1, 2)]

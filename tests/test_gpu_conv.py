@@ -127,3 +127,37 @@ def test_materialize_and_pack(cuda, golden):
     assert np.abs(flt - golden["conv_filters"]).max() <= 1e-6
     W = k().cpu().numpy()                                          # [Cout, Cin, k, k, k] view
     assert np.abs(W - np.transpose(golden["conv_filters"], (4, 3, 0, 1, 2))).max() <= 1e-6
+
+
+def test_wide_submanifold_k5_stress(cuda):
+    """The wide, high-order stress shape (256 -> 256 channels, kernel 5, submanifold, ~10 %
+    random occupancy): oracle parity at reduced size, and at full size (batch 16, 48^3) sampled
+    output rows against a direct float64 evaluation of their neighbourhoods."""
+    from ss_conv import _ext
+    from ss_conv.utils import synthetic as S
+    rng = np.random.RandomState(4)
+    small = S.bernoulli_voxels(range(2), 14, 0.1, base_seed=3)
+    y, ref = _run(cuda, small, 2, 14, 5, 1, 2, True, 256, 256, "tf32")
+    assert rel_err(y, ref) <= TOL["tf32"]
+    ind = S.bernoulli_voxels(range(16), 48, 0.10, base_seed=40)
+    n = ind.shape[0]
+    g = torch.Generator(device="cpu").manual_seed(1)
+    feats = torch.randn(n, 256, generator=g).to(cuda)
+    W = (torch.randn(5, 5, 5, 256, 256, generator=g) / 180).to(cuda)
+    outids, pairs, num = gpu_rulebook(ind, 16, [48] * 3, 5, 1, 2, 1, True, cuda)
+    assert int(num[62]) == n and abs(float(num.sum()) / n - 12.5) < 1.0      # ~12.5 neighbours per voxel
+    _ext.set_precision("tf32")
+    try:
+        y = _ext.indice_conv_fp32(feats, W, pairs, num, n, 0, 1)
+        y2 = _ext.indice_conv_fp32(feats, W, pairs, num, n, 0, 1)
+    finally:
+        _ext.set_precision("auto")
+    _ext.check_status(cuda)
+    assert torch.equal(y, y2)
+    nbr = _ext.neighbour_table(pairs, num, n)
+    rows = torch.from_numpy(rng.choice(n, 64, replace=False)).to(cuda)
+    src = nbr[:, rows]                                                      # [125, 64]
+    gathered = feats.double()[src.clamp(min=0).long()] * (src >= 0).unsqueeze(-1)
+    direct = torch.einsum("kri,kio->ro", gathered, W.double().reshape(125, 256, 256))
+    err = float((y[rows].double() - direct).abs().max() / direct.abs().max())
+    assert err <= TOL["tf32"]

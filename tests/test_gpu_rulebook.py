@@ -126,3 +126,17 @@ def test_rulebook_full_size_properties(cuda):
     per_dim = per_dim - ((ind[:, 1:] == 63) & odd)
     assert total == int(per_dim.prod(1).sum())
     assert np.unique(np.concatenate([pairs[k, 1, :num[k]] for k in range(27)])).size == out.shape[0]
+
+
+def test_transposed_rulebook(cuda, golden):
+    """Transposed convolution geometry vs the reference's own output and vs the oracle."""
+    ind = golden["rbt_indices"]
+    for ci, (k, s, p, op) in enumerate(golden["rbt_cases"]):
+        from ss_conv.sp_ops.ops import get_indice_pairs
+        got = get_indice_pairs(dev(ind, cuda), 2, [8] * 3, int(k), int(s), int(p), 1, int(op), False, True)
+        ref = (golden["rbt%d_outids" % ci], golden["rbt%d_pairs" % ci], golden["rbt%d_num" % ci])
+        assert_rulebook_equal(got, ref)
+    rng = np.random.RandomState(9)
+    big = random_voxels(rng, 2, 12, 300)
+    got = gpu_rulebook(big, 2, [12] * 3, 3, 2, 1, 1, False, cuda, transpose=True)
+    assert_rulebook_equal(got, O.get_indice_pairs(big, 2, [12] * 3, 3, 2, 1, 1, False, True, 0))

@@ -120,3 +120,16 @@ def test_helpers_small_cases():
     d2, idx = O.three_nn(unknown, known)
     assert idx[0].tolist() == [0, 1, 3] and d2[0].tolist() == [1, 4, 9]
     assert idx[1].tolist() == [2, 0, 0] and np.isinf(d2[1, 1])
+
+
+def test_transposed_rulebook_matches_reference(golden):
+    """Transposed geometry: compared in canonical order (the oracle does not reproduce the
+    reference's first-seen output numbering for this case)."""
+    ind = golden["rbt_indices"]
+    for ci, (k, s, p, op) in enumerate(golden["rbt_cases"]):
+        got = O.get_indice_pairs(ind, 2, [8] * 3, int(k), int(s), int(p), 1, False, True, int(op))
+        ref = (golden["rbt%d_outids" % ci], golden["rbt%d_pairs" % ci], golden["rbt%d_num" % ci])
+        a, b = O.canonical_rulebook(*got), O.canonical_rulebook(*ref)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[2], b[2])
+        for x, y in zip(a[1], b[1]):
+            assert np.array_equal(x, y)
