@@ -62,8 +62,9 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, enabled=True):
         self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+        self.enabled = enabled  # only rank 0 samples: N polling subprocesses would compete for host cores
 
     def _run(self):
         while not self._stop.is_set():
@@ -75,16 +76,18 @@ class ClockSampler:
                     self.samples.append(f)
             except Exception:
                 pass
-            self._stop.wait(0.15)
+            self._stop.wait(0.25)
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        if self.enabled:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
         return self
 
     def __exit__(self, *a):
         self._stop.set()
-        self._t.join(timeout=6)
+        if self._t is not None:
+            self._t.join(timeout=6)
 
     def summary(self):
         if not self.samples:
@@ -235,7 +238,7 @@ def run_ours(args):
     barrier()
     l0 = _ext.kernel_launches()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    with ClockSampler(local, enabled=(rank == 0)) as clk:
         ev0.record()
         voxels = 0
         for s in range(args.steps):
