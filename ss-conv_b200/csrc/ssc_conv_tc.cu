@@ -25,8 +25,12 @@
 #include <stdlib.h>
 
 #include "ssc_common.cuh"
+#include "ssc_tc_ptx.cuh"
 
 namespace ssc {
+
+int conv_fwd_tf32_ts(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
+                     const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st);
 
 constexpr int TC_M = 128;
 constexpr int TC_SLAB = 32;            // tf32 elements per 128-byte operand row
@@ -34,7 +38,6 @@ constexpr int TC_MAX_STAGES = 8;       // producer warps = ring slots
 constexpr int TC_EPI_WARPS = 4;        // warps 0..3 also run the epilogue (one TMEM lane quarter each)
 constexpr int TC_A_BYTES = TC_M * 128;
 constexpr int TC_CTRL_BYTES = 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct TcParams {
   int k_slabs;    // ceil(c_in / 32)
@@ -80,68 +83,6 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
   return true;
 }
 
-// ------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the limit ran out or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor version 1 (sm_100)
-  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
-  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-  d |= (uint64_t)1 << 46;                 // version
-  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      :
-      : "r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
-}
-// .ca: a lane fetches the eight 16-byte chunks of one 128-byte row with eight copies; letting
-// them allocate in L1 turns seven of the eight into L1 hits.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -452,6 +393,13 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st) {
   TcParams p;
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
+  // Two variants share the packed filter image: the gathered operand in shared memory
+  // (default) or in tensor memory (SSC_TC_VARIANT=tmem, where the shape allows).
+  const char *variant = getenv("SSC_TC_VARIANT");
+  if (variant != nullptr && strcmp(variant, "tmem") == 0) {
+    int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
+    if (rc >= 0) return rc;
+  }
   if (!tc_params(c_in, c_out, p)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
   size_t smem = tc_smem_bytes(p);
   cudaError_t e = cudaFuncSetAttribute(conv_fwd_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -161,3 +161,18 @@ def test_wide_submanifold_k5_stress(cuda):
     direct = torch.einsum("kri,kio->ro", gathered, W.double().reshape(125, 256, 256))
     err = float((y[rows].double() - direct).abs().max() / direct.abs().max())
     assert err <= TOL["tf32"]
+
+
+@pytest.mark.parametrize("c_in,c_out,k,subm", [(64, 76, 3, False), (32, 38, 3, True), (30, 72, 3, False), (130, 200, 3, False),
+                                                 (16, 16, 5, True)])
+def test_conv_tensor_memory_operand_variant(cuda, c_in, c_out, k, subm):
+    """The variant that keeps the gathered operand in tensor memory (SSC_TC_VARIANT=tmem)."""
+    import os
+    rng = np.random.RandomState(c_in * 3 + c_out)
+    ind = random_voxels(rng, 2, 12, 330)
+    os.environ["SSC_TC_VARIANT"] = "tmem"
+    try:
+        y, ref = _run(cuda, ind, 2, 12, k, 1, k // 2, subm, c_in, c_out, "tf32")
+    finally:
+        os.environ.pop("SSC_TC_VARIANT", None)
+    assert rel_err(y, ref) <= TOL["tf32"]
