@@ -171,16 +171,23 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   } else {
-    // which kernel offsets touch this tile
-    for (int kappa = warp; kappa < K; kappa += mma_warp) {
-      bool any = false;
+    // which kernel offsets touch this tile: four offsets per pass so that 16 loads are in
+    // flight per lane before the first ballot
+    for (int k0 = warp * 4; k0 < K; k0 += mma_warp * 4) {
+      int v[4][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        int r = q * 32 + lane;
-        if (m0 + r < n_out) any |= __ldg(nbr + (size_t)kappa * n_out + m0 + r) >= 0;
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          int r = m0 + q * 32 + lane;
+          v[i][q] = (k0 + i < K && r < n_out) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
+        }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        bool any = (v[i][0] >= 0) | (v[i][1] >= 0) | (v[i][2] >= 0) | (v[i][3] >= 0);
+        unsigned b = __ballot_sync(0xffffffffu, any);
+        if (lane == 0 && k0 + i < K) act_flag[k0 + i] = b != 0;
       }
-      unsigned b = __ballot_sync(0xffffffffu, any);
-      if (lane == 0) act_flag[kappa] = b != 0;
     }
     // every A row of every slot starts as zero
     for (int sl = warp; sl < S; sl += mma_warp) {
@@ -315,23 +322,27 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     }
   } else if (warp == mma_warp && lane == 0) {
     // ================================ MMA issuer ============================================
+    // The issuing thread is the serial bottleneck of the pipeline, so its loop is kept to a
+    // handful of instructions: slot index, parity and descriptor halves are running values.
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
-    int s = 0, par = 0;
+    const uint32_t a_lo0 = desc_lo(smem_base), slot_step = (uint32_t)stage_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
+    const uint32_t fulla0 = smem_u32(fulla_bars), fullb0 = smem_u32(fullb_bars), empty0 = smem_u32(empty_bars);
+    uint32_t s = 0, par = 0, a_lo = a_lo0;
     for (int it = 0; it < n_iter; ++it) {
-      if (!mbar_wait(smem_u32(fulla_bars + s), (uint32_t)par, abort_flag)) break;
-      if (!mbar_wait(smem_u32(fullb_bars + s), (uint32_t)par, abort_flag)) break;
+      if (!mbar_wait(fulla0 + s * 8u, par, abort_flag)) break;
+      if (!mbar_wait(fullb0 + s * 8u, par, abort_flag)) break;
       tc_fence_after();
-      const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)stage_bytes, b_addr = a_addr + TC_A_BYTES;
+      const uint32_t fresh = it > 0 ? 1u : 0u;  // the very first MMA overwrites the accumulators
       for (int nt = 0; nt < p.n_tiles; ++nt) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          uint64_t da = make_desc(a_addr + ks * 32);
-          uint64_t db = make_desc(b_addr + nt * p.tile_n * 128 + ks * 32);
-          mma_tf32(tmem_base + nt * p.tile_n, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-        }
+        const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n), bn = a_lo + (TC_A_BYTES >> 4) + (uint32_t)nt * n_step;
+        mma_tf32_ss(dn, a_lo, bn, idesc, fresh);
+        mma_tf32_ss(dn, a_lo + 2u, bn + 2u, idesc, 1u);
+        mma_tf32_ss(dn, a_lo + 4u, bn + 4u, idesc, 1u);
+        mma_tf32_ss(dn, a_lo + 6u, bn + 6u, idesc, 1u);
       }
-      mma_commit(smem_u32(empty_bars + s));
-      if (++s == S) { s = 0; par ^= 1; }
+      mma_commit(empty0 + s * 8u);
+      a_lo += slot_step;
+      if (++s == (uint32_t)S) { s = 0; par ^= 1u; a_lo = a_lo0; }
     }
     mma_commit(smem_u32(done_bar));  // arrives once everything issued above has retired
   }

@@ -12,9 +12,9 @@
 //     trip, no proxy fence.
 //   * the filter slabs (pre-packed TF32 operand images) stream through a small shared-memory
 //     ring, one bulk asynchronous copy per step, issued by a loader thread.
-//   * one thread issues tcgen05.mma with A from tensor memory and B from shared memory.
-//     When two accumulator sets fit, even and odd steps accumulate into different sets so
-//     that consecutive MMAs do not depend on each other; the epilogue adds the sets.
+//   * tcgen05.mma reads A from tensor memory and B from shared memory.  When two accumulator
+//     sets fit, even and odd steps accumulate into different sets, each issued by its own
+//     thread (issuing is the serial bottleneck); the epilogue adds the sets.
 //   * the tile's slice of the neighbour table is staged in shared memory once, so the row
 //     loads of a step depend on no other global load.
 // Every mbarrier wait is bounded (see ssc_conv_tc.cu).
@@ -25,7 +25,7 @@ namespace ssc {
 
 constexpr int TS_M = 128;
 constexpr int TS_SLAB = 32;
-constexpr int TS_THREADS = 192;  // 4 producer warps, MMA warp, filter-loader warp
+constexpr int TS_THREADS = 224;  // 4 producer warps, 2 MMA warps, filter-loader warp
 constexpr int TS_NBUF = 3;       // register sets of row slabs in flight per producer thread
 constexpr int TS_MAX_B_STAGES = 8;
 
@@ -122,7 +122,7 @@ conv_fwd_tf32_ts_kernel(const float *__restrict__ features, int c_in, const uint
       mbar_init(smem_u32(fullb_bars + s), 1);
       mbar_init(smem_u32(emptyb_bars + s), 1);
     }
-    mbar_init(smem_u32(done_bar), 1);
+    mbar_init(smem_u32(done_bar), (uint32_t)p.n_acc);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -132,17 +132,29 @@ conv_fwd_tf32_ts_kernel(const float *__restrict__ features, int c_in, const uint
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   } else if (warp < 4) {
-    for (int kappa = warp; kappa < K; kappa += 4) {  // which kernel offsets touch this tile
-      bool any = false;
+    // which kernel offsets touch this tile (and stage the tile's slice of the neighbour table):
+    // four offsets per pass so that 16 loads are in flight per lane before the first ballot
+    for (int k0 = warp * 4; k0 < K; k0 += 16) {
+      int v[4][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        int r = q * 32 + lane;
-        int v = (m0 + r < n_out) ? __ldg(nbr + (size_t)kappa * n_out + m0 + r) : -1;
-        if (nbr_in_smem) nbr_s[kappa * TS_M + r] = v;
-        any |= v >= 0;
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          int r = m0 + q * 32 + lane;
+          v[i][q] = (k0 + i < K && r < n_out) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
+        }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (k0 + i < K) {
+          if (nbr_in_smem) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) nbr_s[(k0 + i) * TS_M + q * 32 + lane] = v[i][q];
+          }
+          bool any = (v[i][0] >= 0) | (v[i][1] >= 0) | (v[i][2] >= 0) | (v[i][3] >= 0);
+          unsigned b = __ballot_sync(0xffffffffu, any);
+          if (lane == 0) act_flag[k0 + i] = b != 0;
+        }
       }
-      unsigned b = __ballot_sync(0xffffffffu, any);
-      if (lane == 0) act_flag[kappa] = b != 0;
     }
   }
   tc_fence_before();
@@ -277,32 +289,38 @@ conv_fwd_tf32_ts_kernel(const float *__restrict__ features, int c_in, const uint
         }
       }
     }
-  } else if (warp == 4 && lane == 0) {
-    // ============================ MMA issuer ================================================
+  } else if ((warp == 4 || warp == 5) && lane == 0 && (warp - 4) < p.n_acc) {
+    // ============================ MMA issuers ===============================================
+    // Issuing one tcgen05.mma occupies its thread for a couple of hundred cycles, so with two
+    // accumulator sets two threads issue: thread e takes the steps t = e, e+2, ... and
+    // accumulates them into set e (different A slots, filter slabs and TMEM columns, hence no
+    // ordering between the two is needed).
+    const int e = warp - 4, stride = p.n_acc;
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TS_M >> 4) << 24);
-    const uint32_t smem_base = smem_u32(smem);
-    for (int t = 0; t < n_iter; ++t) {
-      const int sa = t % SA, sb = t % SB;
-      if (!mbar_wait(smem_u32(fulla_bars + sa), (uint32_t)((t / SA) & 1), abort_flag)) break;
-      if (!mbar_wait(smem_u32(fullb_bars + sb), (uint32_t)((t / SB) & 1), abort_flag)) break;
+    const uint32_t b_lo0 = desc_lo(smem_u32(smem)), b_step = (uint32_t)p.b_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
+    const uint32_t fulla0 = smem_u32(fulla_bars), fullb0 = smem_u32(fullb_bars);
+    const uint32_t emptya0 = smem_u32(emptya_bars), emptyb0 = smem_u32(emptyb_bars);
+    const uint32_t d0 = tmem_base + (uint32_t)(e * p.n_pad);
+    const uint32_t a_base = tmem_base + (uint32_t)p.a_col0;
+    for (int t = e; t < n_iter; t += stride) {
+      const uint32_t sa = (uint32_t)(t % SA), sb = (uint32_t)(t % SB);
+      if (!mbar_wait(fulla0 + sa * 8u, (uint32_t)((t / SA) & 1), abort_flag)) break;
+      if (!mbar_wait(fullb0 + sb * 8u, (uint32_t)((t / SB) & 1), abort_flag)) break;
       tc_fence_after();
-      const int acc = p.n_acc == 2 ? (t & 1) : 0;
-      const uint32_t d0 = tmem_base + (uint32_t)(acc * p.n_pad);
-      const uint32_t a0 = tmem_base + (uint32_t)(p.a_col0 + sa * TS_SLAB);
-      const uint32_t b_addr = smem_base + (uint32_t)sb * (uint32_t)p.b_bytes;
-      const bool first = t < p.n_acc;  // first step into this accumulator set
+      const uint32_t a_col = a_base + sa * TS_SLAB, b_lo = b_lo0 + sb * b_step;
+      const uint32_t fresh = t < stride ? 0u : 1u;  // the first step into an accumulator set overwrites it
       for (int nt = 0; nt < p.n_tiles; ++nt) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          uint64_t db = make_desc(b_addr + nt * p.tile_n * 128 + ks * 32);
-          mma_tf32_ts(d0 + nt * p.tile_n, a0 + ks * 8, db, idesc, (first && ks == 0) ? 0u : 1u);
-        }
+        const uint32_t dn = d0 + (uint32_t)(nt * p.tile_n), bn = b_lo + (uint32_t)nt * n_step;
+        mma_tf32_ts_lo(dn, a_col, bn, idesc, fresh);
+        mma_tf32_ts_lo(dn, a_col + 8u, bn + 2u, idesc, 1u);
+        mma_tf32_ts_lo(dn, a_col + 16u, bn + 4u, idesc, 1u);
+        mma_tf32_ts_lo(dn, a_col + 24u, bn + 6u, idesc, 1u);
       }
-      mma_commit(smem_u32(emptya_bars + sa));
-      mma_commit(smem_u32(emptyb_bars + sb));
+      mma_commit(emptya0 + sa * 8u);
+      mma_commit(emptyb0 + sb * 8u);
     }
     mma_commit(smem_u32(done_bar));
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == 6 && lane == 0) {
     // ============================ filter-slab loader ========================================
     const uint32_t smem_base = smem_u32(smem);
     for (int j = 0; j < n_iter; ++j) {

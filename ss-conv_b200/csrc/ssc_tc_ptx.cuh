@@ -69,4 +69,34 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
 // .ca: a lane fetches the eight 16-byte chunks of one 128-byte row with eight copies; letting
 // them allocate in L1 turns seven of the eight into L1 hits.
 
+// Shared-memory operand descriptor split into its two 32-bit halves.  The high half is the same
+// for every K-major, 128-byte-swizzled operand; the low half is (address >> 4) | (1 << 16), so
+// stepping 32 bytes along K adds 2 and stepping to another slot adds (slot bytes >> 4).
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], accumulate selects += or =.
+__device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      :
+      : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "r"(0u)
+      : "memory");
+}
+// Same with the A operand read from tensor memory (lane = row, one 32-bit column per element).
+__device__ __forceinline__ void mma_tf32_ts_lo(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      :
+      : "r"(tmem_c), "r"(tmem_a), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "r"(0u)
+      : "memory");
+}
+
 }  // namespace ssc
