@@ -249,7 +249,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       for (int q = 0; q < 4; ++q) src[q] = nxt[q];
       if (j + S < n_iter) load_rows(j + S, nxt);  // neighbour rows of this warp's next step
       if (j >= S) {
-        if (!mbar_wait(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
+        if (!mbar_wait_warp(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
         tc_fence_after();
       }
       if (part == 0 && lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
@@ -351,7 +351,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   if (warp < TC_EPI_WARPS) {
     __syncwarp();
     bool ok = !*abort_flag;
-    if (ok && n_iter > 0) ok = mbar_wait(smem_u32(done_bar), 0u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && n_iter > 0) ok = mbar_wait_warp(smem_u32(done_bar), 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     const int m = m0 + warp * 32 + lane;

@@ -207,7 +207,7 @@ conv_fwd_tf32_ts_kernel(const float *__restrict__ features, int c_in, const uint
     auto publish = [&](int j, const float4 *src_regs, bool present) -> bool {
       const int sa = j % SA, use = j / SA;
       if (use > 0) {
-        if (!mbar_wait(smem_u32(emptya_bars + sa), (uint32_t)((use - 1) & 1), abort_flag)) return false;
+        if (!mbar_wait_warp(smem_u32(emptya_bars + sa), (uint32_t)((use - 1) & 1), abort_flag)) return false;
         tc_fence_after();
       }
       const uint32_t taddr = lane_addr + (uint32_t)(sa * TS_SLAB);
@@ -251,7 +251,8 @@ conv_fwd_tf32_ts_kernel(const float *__restrict__ features, int c_in, const uint
 
     // ============================ epilogue =================================================
     bool ok = alive && !*abort_flag;
-    if (ok && n_iter > 0) ok = mbar_wait(smem_u32(done_bar), 0u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && n_iter > 0) ok = mbar_wait_warp(smem_u32(done_bar), 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const int n_cols = (c_out + 15) & ~15;
