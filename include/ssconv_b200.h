@@ -119,6 +119,14 @@ int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batch, const in
 int ssc_pairs_to_nbr(const int32_t *pairs, const int32_t *indice_num, int K, int n_cols,
                      int n_out, int swap, int32_t *nbr, void *stream);
 
+/* The reverse direction: reference-format pair lists (indicePairs [K,2,n_in], -1 padded, and
+ * indiceNum [K], SS_Conv_lib/src/conv/indice_conv.h:49-53) from a neighbour table, pairs of an
+ * offset in ascending output row.  Lets a caller build rulebooks without pair lists (the CUDA
+ * kernels only need the table) and materialise them on demand. */
+size_t ssc_pairs_from_nbr_scratch_bytes(int K, int n_out);
+int ssc_pairs_from_nbr(const int32_t *nbr, int K, int n_out, int n_in, int32_t *pairs,
+                       int32_t *indice_num, void *scratch, size_t scratch_bytes, void *stream);
+
 /* --------------------------------------------------------- steerable kernel materialisation
  * Replaces SE3Kernel.combination (SS_Conv_lib/ss_conv/utils/kernel.py:267-299) followed by
  * permute(2,3,4,1,0) (SS_Conv_lib/ss_conv/convolution.py:56):

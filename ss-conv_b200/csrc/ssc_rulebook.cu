@@ -94,46 +94,87 @@ __global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int 
   atomicOr(status, 2);  // table full (cannot happen at load factor <= 0.5)
 }
 
-// One thread per input row, looping over the kernel offsets: mark the output cell each pair
-// reaches.  Lanes of a warp hold neighbouring inputs, so for one offset their cells mostly fall
-// into the same few bitmap words: lanes with the same word combine their bits and only one of
-// them issues the atomic.
+// One thread per input row: mark every output cell the row reaches.  The per-dimension
+// candidates (kernel index -> output coordinate, at most kMarkMaxK per dimension) are worked
+// out once, so the loop over the kernel volume has no division; bits that fall into the same
+// bitmap word (consecutive kz) are merged before the atomic.
+constexpr int kMarkMaxK = 8;
+
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
                                     uint32_t *bitmap) {
   int j = blockIdx.x * blockDim.x + threadIdx.x;
-  int4 c = j < n ? indices[j] : make_int4(-1, 0, 0, 0);
-  bool row_ok = j < n && (unsigned)c.x < (unsigned)batch && in_range3(c.y, c.z, c.w, g.in_shape);
-  int in[3] = {c.y, c.z, c.w};
-  int kk[3] = {0, 0, 0};
-  for (int kappa = 0; kappa < g.K; ++kappa) {
-    bool ok = row_ok;
-    int o[3] = {0, 0, 0};
+  if (j >= n) return;
+  int4 c = indices[j];
+  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
+  const int in[3] = {c.y, c.z, c.w};
+  int cand[3][kMarkMaxK];  // output coordinate for kernel index k along the dimension, or -1
 #pragma unroll
-    for (int d = 0; d < 3; ++d) {
-      if (g.transpose) {
-        o[d] = in[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
-      } else {
-        int num = in[d] + g.padding[d] - kk[d] * g.dilation[d];
-        ok = ok && num >= 0 && (num % g.stride[d] == 0);
-        o[d] = num / g.stride[d];
+  for (int d = 0; d < 3; ++d) {
+#pragma unroll
+    for (int k = 0; k < kMarkMaxK; ++k) {
+      int o = -1;
+      if (k < g.ksize[d]) {
+        if (g.transpose) {
+          o = in[d] * g.stride[d] - g.padding[d] + k * g.dilation[d];
+        } else {
+          int num = in[d] + g.padding[d] - k * g.dilation[d];
+          o = (num >= 0 && num % g.stride[d] == 0) ? num / g.stride[d] : -1;
+        }
+        if ((unsigned)o >= (unsigned)g.out_shape[d]) o = -1;
       }
-      ok = ok && (unsigned)o[d] < (unsigned)g.out_shape[d];
-    }
-    uint32_t flat = ok ? (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]) : 0u;
-    uint32_t word = ok ? (flat >> 5) : 0xFFFFFFFFu;
-    uint32_t bits = ok ? (1u << (flat & 31)) : 0u;
-    unsigned peers = __match_any_sync(0xffffffffu, word);
-    uint32_t merged = __reduce_or_sync(peers, bits);
-    if (ok && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicOr(bitmap + word, merged);
-    // next kernel offset, last dimension fastest
-    if (++kk[2] == g.ksize[2]) {
-      kk[2] = 0;
-      if (++kk[1] == g.ksize[1]) {
-        kk[1] = 0;
-        ++kk[0];
-      }
+      cand[d][k] = o;
     }
   }
+  const int base_b = c.x * g.out_shape[0];
+#pragma unroll
+  for (int kx = 0; kx < kMarkMaxK; ++kx) {
+    if (cand[0][kx] < 0) continue;
+#pragma unroll
+    for (int ky = 0; ky < kMarkMaxK; ++ky) {
+      if (cand[1][ky] < 0) continue;
+      const uint32_t row = (uint32_t)((base_b + cand[0][kx]) * g.out_shape[1] + cand[1][ky]) * (uint32_t)g.out_shape[2];
+      uint32_t word = 0xFFFFFFFFu, bits = 0u;
+#pragma unroll
+      for (int kz = 0; kz < kMarkMaxK; ++kz) {
+        if (cand[2][kz] < 0) continue;
+        const uint32_t flat = row + (uint32_t)cand[2][kz];
+        if ((flat >> 5) != word) {
+          if (bits) atomicOr(bitmap + word, bits);
+          word = flat >> 5;
+          bits = 0u;
+        }
+        bits |= 1u << (flat & 31);
+      }
+      if (bits) atomicOr(bitmap + word, bits);
+    }
+  }
+}
+
+// General fallback (a kernel extent above kMarkMaxK): one thread per (input row, kernel offset).
+__global__ void mark_outputs_generic_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
+                                            uint32_t *bitmap) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long long)n * g.K) return;
+  int j = (int)(t / g.K);
+  int kappa = (int)(t - (long long)j * g.K);
+  int4 c = indices[j];
+  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
+  int kk[3] = {kappa / (g.ksize[1] * g.ksize[2]), (kappa / g.ksize[2]) % g.ksize[1], kappa % g.ksize[2]};
+  int in[3] = {c.y, c.z, c.w};
+  int o[3];
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    if (g.transpose) {
+      o[d] = in[d] * g.stride[d] - g.padding[d] + kk[d] * g.dilation[d];
+    } else {
+      int num = in[d] + g.padding[d] - kk[d] * g.dilation[d];
+      if (num < 0 || num % g.stride[d] != 0) return;
+      o[d] = num / g.stride[d];
+    }
+    if ((unsigned)o[d] >= (unsigned)g.out_shape[d]) return;
+  }
+  uint32_t flat = (uint32_t)(((c.x * g.out_shape[0] + o[0]) * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2]);
+  atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
 }
 
 __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
@@ -285,6 +326,16 @@ __global__ void pairs_to_nbr_kernel(const int32_t *__restrict__ pairs,
   int src = row[(swap ? n_cols : 0) + i];
   int dst = row[(swap ? 0 : n_cols) + i];
   if ((unsigned)dst < (unsigned)n_out) nbr[(size_t)kappa * n_out + dst] = src;
+}
+
+// Per-chunk count of present neighbours (the counting half of lookup_neighbours, for tables
+// that already exist).
+__global__ void __launch_bounds__(kChunk)
+count_chunks_kernel(const int32_t *__restrict__ nbr, int n_out, int32_t *__restrict__ chunk_counts, int n_chunks) {
+  int kappa = blockIdx.y;
+  int o = blockIdx.x * kChunk + threadIdx.x;
+  int cnt = __syncthreads_count(o < n_out && nbr[(size_t)kappa * n_out + o] >= 0);
+  if (threadIdx.x == 0) chunk_counts[(size_t)kappa * n_chunks + blockIdx.x] = cnt;
 }
 
 // ------------------------------------------------------------------------- host drivers
@@ -487,7 +538,11 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
   cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
   if (n_in > 0) {
-    { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+    if (g.ksize[0] <= kMarkMaxK && g.ksize[1] <= kMarkMaxK && g.ksize[2] <= kMarkMaxK) {
+      { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+    } else {
+      { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+    }
     SSC_CHECK_LAUNCH("mark_outputs");
   }
   if (int e = exclusive_scan_u32<true>(s.bitmap, s.n_words, s.word_prefix, s.block_sums, s.misc, n_out_dev, st)) return e;
@@ -534,5 +589,31 @@ extern "C" int ssc_pairs_to_nbr(const int32_t *pairs, const int32_t *indice_num,
     { pairs_to_nbr_kernel<<<grid, 256, 0, st>>>(pairs, indice_num, n_cols, n_out, swap, nbr); note_launches(1); }
   }
   SSC_CHECK_LAUNCH("pairs_to_nbr");
+  return SSC_OK;
+}
+
+extern "C" size_t ssc_pairs_from_nbr_scratch_bytes(int K, int n_out) {
+  if (K < 1 || n_out < 0) return 0;
+  return (size_t)K * (size_t)ceil_div(n_out > 0 ? n_out : 1, kChunk) * 4 + 256;
+}
+
+extern "C" int ssc_pairs_from_nbr(const int32_t *nbr, int K, int n_out, int n_in, int32_t *pairs, int32_t *indice_num,
+                                  void *scratch, size_t scratch_bytes, void *stream) {
+  SSC_REQUIRE(K >= 1 && K <= 256 && n_out >= 0 && n_in >= 0, "pairs_from_nbr: bad sizes");
+  SSC_REQUIRE(indice_num && (n_in == 0 || pairs) && (n_out == 0 || nbr), "pairs_from_nbr: null pointer");
+  if (scratch == nullptr || scratch_bytes < ssc_pairs_from_nbr_scratch_bytes(K, n_out))
+    return fail(SSC_ERR_SCRATCH, "pairs_from_nbr: scratch too small");
+  cudaStream_t st = as_stream(stream);
+  int n_chunks = ceil_div(n_out > 0 ? n_out : 1, kChunk);
+  int32_t *chunk_counts = (int32_t *)scratch;
+  dim3 grid(n_chunks, K);
+  { count_chunks_kernel<<<grid, kChunk, 0, st>>>(nbr, n_out, chunk_counts, n_chunks); note_launches(1); }
+  { scan_chunks_kernel<<<K, 256, 0, st>>>(chunk_counts, n_chunks, indice_num); note_launches(1); }
+  if (n_in > 0) {
+    int n_chunks_in = ceil_div(n_in, kChunk);
+    dim3 grid2(n_chunks > n_chunks_in ? n_chunks : n_chunks_in, K);
+    { fill_pairs_kernel<<<grid2, kChunk, 0, st>>>(nbr, n_out, n_in, chunk_counts, n_chunks, indice_num, pairs); note_launches(1); }
+  }
+  SSC_CHECK_LAUNCH("pairs_from_nbr");
   return SSC_OK;
 }

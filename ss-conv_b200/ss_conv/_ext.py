@@ -39,6 +39,8 @@ SIGNATURES = {
     "ssc_rulebook_conv_fill": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_pairs_to_nbr": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_pairs_from_nbr_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "ssc_pairs_from_nbr": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_materialize": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                 c_void_p, c_void_p]),
     "ssc_conv_packed_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
@@ -206,6 +208,15 @@ def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, st
     return [outids, pairs, num]
 
 
+def get_indice_pairs_lazy(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation, subm,
+                          transpose):
+    """Same as get_indice_pairs_3d but the pair lists are a LazyPairs (no pair-list kernels run
+    unless somebody looks at them).  Used by the layers of this package."""
+    outids, nbr, _, num = build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding,
+                                         dilation, bool(subm), bool(transpose), want_pairs=False)
+    return [outids, LazyPairs(nbr, indices.shape[0]), num]
+
+
 def get_indice_pairs_grid_3d(indices, grid, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
                              out_padding, subm, transpose):
     """Pre-allocated-grid variant (indice_conv.h:133-244): the grid is not needed here."""
@@ -221,8 +232,54 @@ get_indice_pairs_2d = _no_2d
 get_indice_pairs_grid_2d = _no_2d
 
 
+class LazyPairs(object):
+    """Stand-in for the reference-format pair tensor [K, 2, n_in] of a rulebook that so far only
+    exists as a neighbour table.  The CUDA kernels never need the pair lists, so the layers of
+    this package build rulebooks without them; anything that does ask for tensor behaviour
+    (indexing, .cpu(), arithmetic ...) gets the real tensor, built on first use by
+    ssc_pairs_from_nbr."""
+
+    def __init__(self, nbr, n_in):
+        self._ssc_nbr = nbr
+        self._n_in = int(n_in)
+        self._tensor = None
+        self.shape = torch.Size((nbr.shape[0], 2, self._n_in))
+        self.device = nbr.device
+        self.dtype = torch.int32
+
+    def to(self, *args, **kwargs):
+        return self
+
+    def materialize(self):
+        if self._tensor is None:
+            nbr = self._ssc_nbr
+            K, n_out = nbr.shape
+            pairs = torch.empty((K, 2, self._n_in), dtype=torch.int32, device=nbr.device)
+            num = torch.empty(K, dtype=torch.int32, device=nbr.device)
+            nbytes = int(lib().ssc_pairs_from_nbr_scratch_bytes(K, n_out))
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=nbr.device)
+            _check(lib().ssc_pairs_from_nbr(_p(nbr), K, n_out, self._n_in, _p(pairs), _p(num), _p(scratch), nbytes,
+                                            _stream()))
+            pairs._ssc_nbr = nbr
+            self._tensor = pairs
+        return self._tensor
+
+    def __getattr__(self, name):  # only reached for attributes this class does not define
+        return getattr(self.materialize(), name)
+
+    def __getitem__(self, item):
+        return self.materialize()[item]
+
+    def __len__(self):
+        return self.shape[0]
+
+
 def neighbour_table(pairs, num, n_out, inverse=False):
     """nbr [K, n_out] for a reference-format rulebook (cached on the pair tensor when possible)."""
+    if isinstance(pairs, LazyPairs):
+        if not inverse and pairs._ssc_nbr.shape[1] == n_out:
+            return pairs._ssc_nbr
+        pairs = pairs.materialize()
     nbr = getattr(pairs, "_ssc_nbr", None)
     if nbr is not None and not inverse and nbr.shape[1] == n_out and nbr.device == pairs.device:
         return nbr

@@ -84,7 +84,7 @@ class SparseConvolution(nn.Module):
         else:
             outids, indice_pairs, indice_pair_num = get_indice_pairs(
                 indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
-                self.output_padding, self.subm, self.transposed, grid=input.grid)
+                self.output_padding, self.subm, self.transposed, grid=input.grid, lazy=True)
             input.indice_dict[self.indice_key] = (outids, indices, indice_pairs, indice_pair_num, spatial_shape)
 
         op = indice_subm_conv if self.subm else (indice_inverse_conv if self.inverse else indice_conv)

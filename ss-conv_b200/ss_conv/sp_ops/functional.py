@@ -13,17 +13,24 @@ from .. import _ext
 from . import ops
 
 
+def _save(ctx, pairs, *tensors):
+    """Pair lists may be a lazy handle (not a tensor): keep them as a plain attribute."""
+    ctx.indice_pairs = pairs
+    ctx.save_for_backward(*tensors)
+
+
 def _conv_function(inverse, subm):
     class _Conv(Function):
         @staticmethod
         def forward(ctx, features, filters, indice_pairs, indice_pair_num, num_activate_out):
-            ctx.save_for_backward(indice_pairs, indice_pair_num, features, filters)
+            _save(ctx, indice_pairs, indice_pair_num, features, filters)
             return ops.indice_conv_forward(features, filters, indice_pairs, indice_pair_num, num_activate_out,
                                            inverse, subm)
 
         @staticmethod
         def backward(ctx, grad_output):
-            indice_pairs, indice_pair_num, features, filters = ctx.saved_tensors
+            indice_pair_num, features, filters = ctx.saved_tensors
+            indice_pairs = ctx.indice_pairs
             d_in, d_flt = ops.indice_conv_backward(features, filters, grad_output.contiguous(), indice_pairs,
                                                    indice_pair_num, inverse, subm)
             return d_in, d_flt, None, None, None
@@ -40,12 +47,13 @@ class SparseMaxPoolFunction(Function):
     @staticmethod
     def forward(ctx, features, indice_pairs, indice_pair_num, num_activate_out):
         out = ops.indice_maxpool_forward(features, indice_pairs, indice_pair_num, num_activate_out)
-        ctx.save_for_backward(indice_pairs, indice_pair_num, features, out)
+        _save(ctx, indice_pairs, indice_pair_num, features, out)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        indice_pairs, indice_pair_num, features, out = ctx.saved_tensors
+        indice_pair_num, features, out = ctx.saved_tensors
+        indice_pairs = ctx.indice_pairs
         return ops.indice_maxpool_backward(features, out, grad_output.contiguous(), indice_pairs,
                                            indice_pair_num), None, None, None
 
@@ -56,14 +64,20 @@ class SparseAvgPoolFunction(Function):
         # use_gs: divide by the kernel volume; otherwise by the number of present inputs
         summaryrf = None if use_gs else _ext.indiceSummaryRF(indice_pairs, indice_pair_num, num_activate_out)
         out = ops.indice_avgpool_forward(features, indice_pairs, indice_pair_num, num_activate_out, summaryrf)
+        ctx.kernel_volume = int(indice_pairs.shape[0])
         if summaryrf is None:
-            summaryrf = indice_pairs.new_full((num_activate_out,), int(indice_pairs.shape[0]))
-        ctx.save_for_backward(indice_pairs, indice_pair_num, features, out, summaryrf)
+            _save(ctx, indice_pairs, indice_pair_num, features, out)
+        else:
+            _save(ctx, indice_pairs, indice_pair_num, features, out, summaryrf)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        indice_pairs, indice_pair_num, features, out, summaryrf = ctx.saved_tensors
+        saved = ctx.saved_tensors
+        indice_pair_num, features, out = saved[:3]
+        summaryrf = saved[3] if len(saved) > 3 else torch.full((out.shape[0],), ctx.kernel_volume, dtype=torch.int32,
+                                                               device=out.device)
+        indice_pairs = ctx.indice_pairs
         return ops.indice_avgpool_backward(features, out, grad_output.contiguous(), indice_pairs, indice_pair_num,
                                            summaryrf), None, None, None, None
 

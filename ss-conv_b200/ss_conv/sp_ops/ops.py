@@ -25,8 +25,10 @@ def get_deconv_output_size(input_size, kernel_size, stride, padding, dilation, o
 
 
 def get_indice_pairs(indices, batch_size, spatial_shape, ksize=3, stride=1, padding=0, dilation=1, out_padding=0,
-                     subm=False, transpose=False, grid=None):
-    """(outids, indice_pairs [K,2,N], indice_pair_num [K]) for a 3-D sparse tensor."""
+                     subm=False, transpose=False, grid=None, lazy=False):
+    """(outids, indice_pairs [K,2,N], indice_pair_num [K]) for a 3-D sparse tensor.
+    lazy=True returns the pair lists as a handle that builds the tensor only when it is looked
+    at (the layers of this package use that: the CUDA kernels work on the neighbour table)."""
     ndim = indices.shape[1] - 1
     ksize, stride, padding = _per_dim(ksize, ndim), _per_dim(stride, ndim), _per_dim(padding, ndim)
     dilation, out_padding = _per_dim(dilation, ndim), _per_dim(out_padding, ndim)
@@ -40,6 +42,9 @@ def get_indice_pairs(indices, batch_size, spatial_shape, ksize=3, stride=1, padd
         out_shape = get_conv_output_size(spatial_shape, ksize, stride, padding, dilation)
     if ndim != 3:
         raise NotImplementedError
+    if lazy:
+        return _ext.get_indice_pairs_lazy(indices, batch_size, out_shape, list(spatial_shape), ksize, stride, padding,
+                                          dilation, int(subm), int(transpose))
     if grid is None:
         return _ext.get_indice_pairs_3d(indices, batch_size, out_shape, list(spatial_shape), ksize, stride, padding,
                                         dilation, out_padding, int(subm), int(transpose))

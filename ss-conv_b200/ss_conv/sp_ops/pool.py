@@ -25,7 +25,7 @@ class _SparsePool(nn.Module):
         out_shape = shape if self.subm else get_conv_output_size(shape, self.kernel_size, self.stride, self.padding,
                                                                  self.dilation)
         outids, pairs, pair_num = get_indice_pairs(input.indices, input.batch_size, shape, self.kernel_size,
-                                                   self.stride, self.padding, self.dilation, 0, self.subm)
+                                                   self.stride, self.padding, self.dilation, 0, self.subm, lazy=True)
         feats = type(self)._op(input.features, pairs, pair_num, outids.shape[0])
         out = SparseTensor(feats, outids, out_shape, input.batch_size)
         out.indice_dict = input.indice_dict

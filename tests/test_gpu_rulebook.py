@@ -140,3 +140,17 @@ def test_transposed_rulebook(cuda, golden):
     big = random_voxels(rng, 2, 12, 300)
     got = gpu_rulebook(big, 2, [12] * 3, 3, 2, 1, 1, False, cuda, transpose=True)
     assert_rulebook_equal(got, O.get_indice_pairs(big, 2, [12] * 3, 3, 2, 1, 1, False, True, 0))
+
+
+def test_lazy_pairs_materialise_to_the_same_lists(cuda):
+    """Layers build rulebooks without pair lists; the handle must turn into exactly the lists
+    the eager entry point produces."""
+    from ss_conv.sp_ops.ops import get_indice_pairs
+    rng = np.random.RandomState(17)
+    ind = random_voxels(rng, 2, 12, 280)
+    for subm, s in ((False, 2), (True, 1)):
+        eager = get_indice_pairs(dev(ind, cuda), 2, [12] * 3, 3, s, 1, 1, 0, subm)
+        lazy = get_indice_pairs(dev(ind, cuda), 2, [12] * 3, 3, s, 1, 1, 0, subm, lazy=True)
+        assert lazy[1].shape == eager[1].shape and torch.equal(lazy[0], eager[0]) and torch.equal(lazy[2], eager[2])
+        assert torch.equal(lazy[1].materialize(), eager[1])
+        assert torch.equal(lazy[1][3], eager[1][3])          # tensor behaviour on demand
