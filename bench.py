@@ -25,7 +25,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -57,37 +56,40 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs: ONE
+    nvidia-smi process in loop mode (started before the region, stopped after it), so that the
+    sampling costs the benchmarked process nothing."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index, enabled=True):
-        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
-        self.enabled = enabled  # only rank 0 samples: N polling subprocesses would compete for host cores
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                f = [x.strip() for x in out.strip().split(",")]
-                if len(f) >= 7:
-                    self.samples.append(f)
-            except Exception:
-                pass
-            self._stop.wait(0.25)
+        self.index, self.samples, self.proc, self.enabled = index, [], None, enabled
 
     def __enter__(self):
         if self.enabled:
-            self._t = threading.Thread(target=self._run, daemon=True)
-            self._t.start()
+            try:
+                self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                              "--format=csv,noheader,nounits", "-lms", "100"],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                time.sleep(0.25)  # let the first samples come in before the timed region starts
+            except Exception:
+                self.proc = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        if self._t is not None:
-            self._t.join(timeout=6)
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                self.proc.kill()
+                out = ""
+            for line in out.strip().splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) >= 7:
+                    self.samples.append(f)
 
     def summary(self):
         if not self.samples:

@@ -125,18 +125,27 @@ def _p(t, dtype=None):
         raise TypeError("expected dtype %s, got %s" % (dtype, t.dtype))
     if not t.is_contiguous():
         raise ValueError("tensor must be contiguous")
-    return c_void_p(t.data_ptr())
+    return t.data_ptr()  # ctypes turns the int into a void* (NULL must be passed as None)
 
 
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return torch.cuda.current_stream().cuda_stream or None
+
+
+_i3_cache = {}
 
 
 def _i3(v):
-    return _I3(*[int(x) for x in v])
+    """ctypes int[3] for a geometry triple (cached: the same few triples recur every call)."""
+    key = (int(v[0]), int(v[1]), int(v[2]))
+    arr = _i3_cache.get(key)
+    if arr is None:
+        arr = _i3_cache[key] = _I3(*key)
+    return arr
 
 
 _status = {}
+_scratch_cache = {}
 
 
 def status_word(device):
@@ -175,9 +184,15 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
             raise ValueError("ssconv_b200: batch*volume does not fit the int32 flat index")
     if K > 256:
         raise ValueError("ssconv_b200: kernel volume %d > 256" % K)
-    sbytes = L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(grid), K)
-    scratch = torch.empty(max(int(sbytes), 256), dtype=torch.uint8, device=dev)
-    num = torch.empty(K, dtype=torch.int32, device=dev)
+    skey = (n_in, int(batch_size), int(grid[0]), int(grid[1]), int(grid[2]), K)
+    sbytes = _scratch_cache.get(skey)
+    if sbytes is None:
+        if len(_scratch_cache) > 4096:
+            _scratch_cache.clear()
+        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(grid), K)), 256)
+    scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+    small = torch.empty(K + 1, dtype=torch.int32, device=dev)   # [indice_num (K) | n_out]
+    num = small[:K]
     pairs = torch.empty((K, 2, n_in), dtype=torch.int32, device=dev) if want_pairs else None
     st = status_word(dev)
     if subm:
@@ -185,7 +200,7 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
         _check(L.ssc_rulebook_subm(_p(indices), n_in, int(batch_size), _i3(spatial_shape), _i3(ksize), _i3(dilation),
                                    _p(nbr), _p(pairs), _p(num), _p(st), _p(scratch), scratch.numel(), _stream()))
         return indices, nbr, pairs, num
-    n_out_dev = torch.empty(1, dtype=torch.int32, device=dev)
+    n_out_dev = small[K:]
     geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
     _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
                                      scratch.numel(), _stream()))
