@@ -253,27 +253,41 @@ def run_ours(args):
     _ext.check_status(dev)
     n_out_conv = None
 
-    # ---- end to end from pinned host buffers through the public API
-    def e2e_step(s):
-        f, i = pinned[s % ROTATE]
-        fd = f.to(dev, non_blocking=True)
-        idd = i.to(dev, non_blocking=True)
-        o = layer.step(fd, idd)
-        return o.features.cpu(), o.indices.cpu()
+    # ---- end to end from pinned host buffers through the public API: every step uploads its own
+    # indices + features from pinned host memory and downloads its pooled result; HostStream
+    # overlaps the upload of step s+1 and the download of step s-1 with the compute of step s.
+    from ss_conv.pipeline import HostStream
 
-    for w in range(min(args.warmup, 3)):
-        e2e_step(w)
+    def dev_step(fd, idd):
+        o = layer.step(fd, idd)
+        return o.features, o.indices
+
+    feed = HostStream(dev_step, dev, max_rows=max(n_in))
+    for _ in feed.run(pinned[w % ROTATE] for w in range(3)):
+        pass
     barrier()
     t0 = time.perf_counter()
-    vox_e2e = 0
     d2h = 0
-    for s in range(args.steps):
-        of, oi = e2e_step(s)
-        vox_e2e += n_in[s % ROTATE]
+    for of, oi in feed.run(pinned[s % ROTATE] for s in range(args.steps)):
         d2h = of.numel() * 4 + oi.numel() * 4
     barrier()
     e2e_s = time.perf_counter() - t0
+    vox_e2e = sum(n_in[s % ROTATE] for s in range(args.steps))
     h2d = int(np.mean([f.numel() * 4 + i.numel() * 4 for f, i in pinned]))
+
+    # the same without overlap (upload, compute, download one after the other), for comparison
+    def serial_step(s):
+        f, i = pinned[s % ROTATE]
+        o = layer.step(f.to(dev, non_blocking=True), i.to(dev, non_blocking=True))
+        return o.features.cpu(), o.indices.cpu()
+
+    serial_step(0)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        serial_step(s)
+    barrier()
+    serial_s = time.perf_counter() - t0
 
     # ---- dominant kernel alone: conv_fwd_tf32_kernel, CUDA events on the launching stream
     from ss_conv.sp_ops.ops import get_indice_pairs
@@ -304,13 +318,13 @@ def run_ours(args):
     _ext.set_precision("tf32")
 
     # ---- reduce over ranks
-    stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches)], dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches), serial_s], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms, e2e_s = float(mx[0]), float(mx[1])
+        ms, e2e_s, serial_s = float(mx[0]), float(mx[1]), float(mx[5])
         voxels, vox_e2e, launches = float(sm[2]), float(sm[3]), float(sm[4])
     if rank == 0:
         line = {
@@ -323,7 +337,9 @@ def run_ours(args):
                        "l2": "rotating %d distinct input batches (> 126 MB working set) between timed steps" % ROTATE,
                        "step": "rulebook + materialise + pack + conv + pool rulebook + maxpool",
                        "parallelism": "sample-sharded x%d, no data-path collective" % world},
-            "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h)},
+            "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h),
+                    "how": "ss_conv.pipeline.HostStream: upload / compute / download of consecutive steps overlap on 3 streams",
+                    "serial_value": vox_e2e / serial_s},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
             "roofline": {"bound": "hbm", "kernel": "conv_fwd_tf32_kernel", "achieved": achieved, "peak": peak,
@@ -350,6 +366,13 @@ def run_only(args):
     layer = Layer(cfg, dev)
     f, i = make_inputs(cfg, 0, 1)[0]
     f, i = torch.from_numpy(f).to(dev), torch.from_numpy(i).to(dev)
+    if args.only == "step":
+        for _ in range(max(1, args.steps)):
+            out = layer.step(f, i)
+        torch.cuda.synchronize()
+        _ext.check_status(dev)
+        print("only=step done, n_in=%d n_pooled=%d" % (i.shape[0], out.indices.shape[0]))
+        return
     with torch.no_grad():
         flt = layer.conv.kernel.filters().reshape(-1, layer.conv.in_channels, layer.conv.out_channels)
         for _ in range(max(1, args.steps)):
@@ -454,8 +477,8 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["conv", "rulebook"],
-                    help="run just one kernel group of the cfg2 step a few times (for ncu captures)")
+    ap.add_argument("--only", default=None, choices=["conv", "rulebook", "step"],
+                    help="run just one kernel group of the cfg2 step (or the whole step) a few times (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

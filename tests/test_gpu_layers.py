@@ -116,3 +116,37 @@ def test_backbone_forward_matches_oracle_chain(cuda):
     counts = np.bincount(cur_idx[:, 0], minlength=4)
     ref = O.global_avgpool(cur_feat, np.concatenate([[0], np.cumsum(counts)]))
     assert rel_err(pooled, ref) <= 5e-5
+
+
+def test_host_stream_gives_the_same_results_as_direct_calls(cuda):
+    """Batches of different sizes fed from pinned host memory through the overlapped
+    upload / compute / download pipeline come back in order and bit-equal to the results of
+    calling the step directly on device tensors."""
+    from ss_conv import _ext
+    from ss_conv.pipeline import HostStream
+    from ss_conv.pool import MaxPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    pool = MaxPool(2, stride=2)
+
+    def step(f, i):
+        y = pool(SparseTensor(f, i, [16] * 3, 2))
+        return y.features, y.indices
+
+    batches = []
+    for r, n in enumerate((300, 120, 511, 64, 300)):
+        ind = S.bernoulli_voxels(range(2), 16, n / (2 * 16 ** 3), base_seed=40 + 2 * r)
+        feats = S.features(ind.shape[0], 5, 90 + r)
+        batches.append((torch.from_numpy(feats).pin_memory(), torch.from_numpy(ind).pin_memory()))
+    want = []
+    for f, i in batches:
+        of, oi = step(f.to(cuda), i.to(cuda))
+        want.append((of.cpu().numpy(), oi.cpu().numpy()))
+    feed = HostStream(step, cuda, max_rows=max(i.shape[0] for _, i in batches))
+    got = [(of.numpy().copy(), oi.numpy().copy()) for of, oi in feed.run(iter(batches))]
+    assert len(got) == len(want)
+    for (gf, gi), (wf, wi) in zip(got, want):
+        np.testing.assert_array_equal(gi, wi)
+        np.testing.assert_array_equal(gf, wf)
+    assert list(feed.run(iter([]))) == []
+    _ext.check_status(cuda)
