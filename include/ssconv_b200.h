@@ -153,12 +153,18 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  * precision: SSC_PREC_FP32 = exact fp32 FMA on CUDA cores (filters = [K,Cin,Cout] fp32);
  *            SSC_PREC_TF32 = tcgen05 tensor cores, TF32 operands (filters = packed image).
  * status: device int32 that receives a non-zero value if a bounded wait inside the kernel
- * ran out (may be NULL). */
+ * ran out (may be NULL).
+ * scratch: optional device buffer of ssc_conv_scratch_bytes() bytes, 128-byte aligned.  With it
+ * the TF32 path of a large layer stages a TF32-rounded copy of the feature rows there and
+ * gathers them with the TMA unit (cp.async.bulk.tensor tile::gather4) in a persistent kernel;
+ * without it (NULL / too small) the rows are gathered by the SM's load-store units.  The
+ * result is the same up to the summation order inside the tensor core. */
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
+size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision);
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                  const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
-                 void *stream);
+                 void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------- sparse pools
  * Replace indiceMaxPool / indiceAvgPool (SS_Conv_lib/src/pool/indice_maxpool.h:15-50,

@@ -31,6 +31,10 @@ namespace ssc {
 
 int conv_fwd_tf32_ts(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                      const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st);
+int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st);
+int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
+                          const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch,
+                          size_t scratch_bytes, cudaStream_t st);
 
 constexpr int TC_M = 128;
 constexpr int TC_SLAB = 32;            // tf32 elements per 128-byte operand row
@@ -83,6 +87,17 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
   return true;
 }
 
+// Geometry of the packed filter image, for the other kernels that consume it.
+bool tc_operand_layout(int c_in, int c_out, int *k_slabs, int *n_pad, int *tile_n, int *n_tiles) {
+  TcParams p;
+  if (!tc_params(c_in, c_out, p)) return false;
+  *k_slabs = p.k_slabs;
+  *n_pad = p.n_pad;
+  *tile_n = p.tile_n;
+  *n_tiles = p.n_tiles;
+  return true;
+}
+
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -130,6 +145,7 @@ __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int 
 
 // Warps 0 .. n_prod-1 are producers (warp w <-> ring slot w; with fewer than four slots the
 // spare warps only help in the prologue and epilogue), the last warp issues the MMAs.
+template <bool STAGED>
 __global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
@@ -295,10 +311,11 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       dirty = present;
       cp_async_commit();
       cp_async_wait(0);
+      if (STAGED) fence_needed = fence_needed || present != 0;  // rows were rounded when they were staged
       // copies landed: round the gathered rows to TF32 in place
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        if (present & (1u << q)) {
+        if (!STAGED && (present & (1u << q))) {
           uint8_t *row = slot_ptr + row_off[q];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -401,24 +418,49 @@ static size_t tc_smem_bytes(const TcParams &p) {
   return (size_t)p.stages * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES;
 }
 
+// Smallest problem (in 128-row tiles) the persistent gather4 kernel is used for by default: below
+// this the one-tile-per-CTA kernel spreads the work over more SMs.
+constexpr int kGather4MinTiles = 296;
+// Smallest problem for which the extra staging launch pays for itself.
+constexpr int kStagingMinTiles = 64;
+
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
-                  const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st) {
+                  const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
+                  cudaStream_t st) {
   TcParams p;
-  if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
-  // Two variants share the packed filter image: the gathered operand in shared memory
-  // (default) or in tensor memory (SSC_TC_VARIANT=tmem, where the shape allows).
+  // Three variants share the packed filter image.  SSC_TC_VARIANT = gather4 | smem | tmem forces
+  // one (where the shape allows); by default large problems take the persistent TMA-gather
+  // kernel when the caller supplied its staging buffer, the others the shared-memory kernel.
   const char *variant = getenv("SSC_TC_VARIANT");
+  const bool force_g4 = variant != nullptr && strcmp(variant, "gather4") == 0;
+  if (force_g4) {
+    int rc = conv_fwd_tf32_gather4(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, scratch,
+                                   scratch_bytes, st);
+    if (rc >= 0) return rc;
+  }
+  if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
   if (variant != nullptr && strcmp(variant, "tmem") == 0) {
     int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
     if (rc >= 0) return rc;
   }
   if (!tc_params(c_in, c_out, p)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
   size_t smem = tc_smem_bytes(p);
-  cudaError_t e = cudaFuncSetAttribute(conv_fwd_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
   int grid = ceil_div(n_out, TC_M);
-  { conv_fwd_tf32_kernel<<<grid, p.threads, smem, st>>>(features, c_in, (const uint4 *)packed, K, c_out, nbr, n_out,
-                                                      out, status, p); note_launches(1); }
+  // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
+  // every gather (a row is gathered about K/2 times).
+  const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_in * sizeof(float);
+  const char *no_stage = getenv("SSC_TC_NO_STAGING");
+  const bool staged = scratch != nullptr && scratch_bytes >= stage_need && (c_in & 3) == 0 && ((uintptr_t)scratch & 15u) == 0 &&
+                      ((uintptr_t)features & 15u) == 0 && grid >= kStagingMinTiles && no_stage == nullptr;
+  if (staged) {
+    int rc = stage_features(features, n_in, c_in, scratch, st);
+    if (rc != SSC_OK) return rc;
+  }
+  auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
+  { kernel<<<grid, p.threads, smem, st>>>(staged ? (const float *)scratch : features, c_in, (const uint4 *)packed, K, c_out,
+                                        nbr, n_out, out, status, p); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;
 }

@@ -45,8 +45,9 @@ SIGNATURES = {
                                 c_void_p, c_void_p]),
     "ssc_conv_packed_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_pack_filters": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_conv_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-                             c_void_p, c_void_p]),
+                             c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -341,6 +342,12 @@ def _resolve_precision(c_in, c_out, precision=None):
     return mode
 
 
+# Layers with fewer output rows do not stage a TF32-rounded copy of their input rows (the extra
+# launch would cost more than it saves), so no staging buffer is allocated for them
+# (SSC_TC_VARIANT=gather4 forces the TMA-gather kernel, which always needs it).
+STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") == "gather4" else 64 * 128
+
+
 def conv_forward(features, filters, nbr, n_out, precision=None):
     """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch)."""
     if filters.dim() != 3:
@@ -361,12 +368,16 @@ def conv_forward(features, filters, nbr, n_out, precision=None):
                 filters._ssc_packed_version = filters._version
             except Exception:
                 pass
+        nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, PREC_TF32) if n_out >= STAGING_MIN_ROWS else 0
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
-                                  _p(nbr, torch.int32), int(n_out), PREC_TF32, _p(out), _p(st), _stream()))
+                                  _p(nbr, torch.int32), int(n_out), PREC_TF32, _p(out), _p(st), _p(scratch), nbytes,
+                                  _stream()))
     else:
         filters = filters.contiguous()
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(filters, torch.float32), K,
-                                  c_out, _p(nbr, torch.int32), int(n_out), PREC_FP32, _p(out), _p(st), _stream()))
+                                  c_out, _p(nbr, torch.int32), int(n_out), PREC_FP32, _p(out), _p(st), None, 0,
+                                  _stream()))
     return out
 
 
