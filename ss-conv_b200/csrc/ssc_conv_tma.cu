@@ -13,8 +13,9 @@
 //                   tile), skips offsets without any neighbour, and for every (offset, slab,
 //                   tile) arms one ring slot: each lane issues ONE gather4 that drops four
 //                   128-byte row slabs into the K-major 128-byte-swizzled operand layout.
-//                   Rows without a neighbour point at an all-zero row.  No thread touches the
-//                   gathered data: the copy engine writes shared memory, the tensor core reads it.
+//                   Rows without a neighbour use an out-of-range row index, which the copy
+//                   engine zero-fills.  No thread touches the gathered data: the copy engine
+//                   writes shared memory, the tensor core reads it.
 //   MMA thread    : consumes ring slots in order; a slot's tag says which accumulator it feeds
 //                   and whether it opens / closes the use of a filter slot.
 //   epilogue warps: tcgen05.ld the accumulators of a finished pass and store each output row
@@ -23,6 +24,11 @@
 // The gathered operand must already be TF32-representable: stage_features_kernel makes a
 // round-to-nearest copy of the feature rows (plus the zero row) once per call, so that a row
 // gathered ~K/2 times is rounded once.
+//
+// Measured on B200 (64 -> 76 channels, 3^3 offsets, 130 k output rows): the copy engine retires
+// one gather4 (4 x 128 bytes) about every 58 cycles per SM, which makes this kernel ~2.4x slower
+// than gathering with the load-store units (ssc_conv_tc.cu); it is kept as an option
+// (SSC_TC_VARIANT=gather4) for wider rows and as the reference point for that measurement.
 //
 // Every wait is bounded; on expiry the waiting thread raises the CTA's abort flag, every other
 // role leaves its loop at its next wait, the kernel releases its tensor memory and reports
@@ -59,7 +65,6 @@ struct G4Params {
   int T;              // tiles per pass
   int halves;         // 2: passes alternate between TMEM columns [0,256) and [256,512)
   int zero_row;       // row index of the all-zero row in the staged feature image
-  int dbg_lanes, dbg_nomma;
 };
 
 __device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int r0, int r1, int r2,
@@ -205,12 +210,12 @@ conv_fwd_tf32_gather4_kernel(const __grid_constant__ CUtensorMap feat_map, const
             const uint32_t bar = smem_u32(full_a + sa);
             if (lane == 0) {
               tags[sa] = (uint32_t)t | (t == first_t ? TAG_OPEN_B : 0u) | (t == last_t ? TAG_CLOSE_B : 0u);
-              mbar_expect_tx(bar, (uint32_t)p.dbg_lanes * 512u);
+              mbar_expect_tx(bar, (uint32_t)G4_A_BYTES);
             }
             int r[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) r[q] = cur[t][q] < 0 ? p.zero_row : cur[t][q];
-            if (lane < p.dbg_lanes) tma_gather4(smem_base + sa * (uint32_t)G4_A_BYTES + (uint32_t)lane * 512u, &feat_map, bar, slab * 32, r[0], r[1],
+            tma_gather4(smem_base + sa * (uint32_t)G4_A_BYTES + (uint32_t)lane * 512u, &feat_map, bar, slab * 32, r[0], r[1],
                         r[2], r[3]);
             next_a();
           }
@@ -259,12 +264,10 @@ conv_fwd_tf32_gather4_kernel(const __grid_constant__ CUtensorMap feat_map, const
         const uint32_t d = tmem_base + half * 256u + t * (uint32_t)p.n_pad;
         const uint32_t a_lo = desc_lo(smem_base + sa * (uint32_t)G4_A_BYTES);
         const uint32_t b_lo = desc_lo(b_base + sb * (uint32_t)p.b_bytes);
-        if (!p.dbg_nomma) {
         mma_tf32_ss(d, a_lo, b_lo, idesc, (began >> t) & 1u);
         mma_tf32_ss(d, a_lo + 2u, b_lo + 2u, idesc, 1u);
         mma_tf32_ss(d, a_lo + 4u, b_lo + 4u, idesc, 1u);
         mma_tf32_ss(d, a_lo + 6u, b_lo + 6u, idesc, 1u);
-        }
         began |= 1u << t;
         mma_commit(smem_u32(empty_a + sa));
         if (tag & TAG_CLOSE_B) {
@@ -407,9 +410,10 @@ int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void 
   if (rc != SSC_OK) return rc;
 
   CUtensorMap map;
-  const char *oob = getenv("SSC_G4_OOB");
-  const bool use_oob = oob != nullptr && oob[0] == '1';
-  const cuuint64_t dims[2] = {(cuuint64_t)c_in, (cuuint64_t)n_in + (use_oob ? 0 : 1)};
+  // The map covers the n_in real rows only: index n_in (used for "no neighbour") is out of
+  // bounds, so the copy engine fills zeros without touching memory.  The staged image still holds
+  // a zero row there, which keeps the result right on a device that would fetch it instead.
+  const cuuint64_t dims[2] = {(cuuint64_t)c_in, (cuuint64_t)(n_in > 0 ? n_in : 1)};
   const cuuint64_t strides[1] = {(cuuint64_t)c_in * sizeof(float)};
   const cuuint32_t box[2] = {32u, 1u};  // gather4 takes one row per index
   const cuuint32_t estr[2] = {1u, 1u};
@@ -418,8 +422,6 @@ int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void 
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): tensor map encode failed (%d)", (int)cr);
   p.zero_row = n_in;
-  p.dbg_lanes = getenv("SSC_DBG_LANES") ? atoi(getenv("SSC_DBG_LANES")) : 32;
-  p.dbg_nomma = getenv("SSC_DBG_NOMMA") ? 1 : 0;
 
   const size_t smem = (size_t)p.a_slots * G4_A_BYTES + (size_t)p.b_slots * p.b_bytes + G4_CTRL_BYTES + 1024;
   cudaError_t e = cudaFuncSetAttribute(conv_fwd_tf32_gather4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -176,3 +176,34 @@ def test_conv_tensor_memory_operand_variant(cuda, c_in, c_out, k, subm):
     finally:
         os.environ.pop("SSC_TC_VARIANT", None)
     assert rel_err(y, ref) <= TOL["tf32"]
+
+
+@pytest.mark.parametrize("c_in,c_out,k,subm", [(64, 76, 3, False), (32, 38, 3, True), (20, 8, 3, False), (128, 256, 3, False),
+                                                 (16, 16, 5, True)])
+def test_conv_tma_gather_variant(cuda, c_in, c_out, k, subm, monkeypatch):
+    """The persistent kernel whose rows are gathered by the copy engine (tile::gather4) from the
+    staged TF32 image (SSC_TC_VARIANT=gather4), several passes per CTA included."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(c_in * 5 + c_out)
+    ind = random_voxels(rng, 3, 14, 900)
+    monkeypatch.setenv("SSC_TC_VARIANT", "gather4")
+    monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 0)
+    l0 = _ext.kernel_launches()
+    y, ref = _run(cuda, ind, 3, 14, k, 1, k // 2, subm, c_in, c_out, "tf32")
+    assert rel_err(y, ref) <= TOL["tf32"]
+    assert _ext.kernel_launches() - l0 >= 3        # staging + conv (+ packing, + rulebook)
+
+
+def test_conv_staged_rows_give_the_same_bits(cuda, monkeypatch):
+    """Rounding the feature rows to TF32 once in a staging buffer, or after every gather,
+    feeds the tensor core the same operands: the results are bit-identical."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(77)
+    ind = random_voxels(rng, 4, 16, 2500)
+    monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 1 << 30)
+    plain, _ = _run(cuda, ind, 4, 16, 3, 1, 1, True, 64, 76, "tf32")
+    monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 0)
+    staged, ref = _run(cuda, ind, 4, 16, 3, 1, 1, True, 64, 76, "tf32")
+    assert ind.shape[0] >= 64 * 128                # large enough for the library to stage
+    np.testing.assert_array_equal(plain, staged)
+    assert rel_err(staged, ref) <= TOL["tf32"]
