@@ -164,6 +164,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   int *n_act_s = (int *)(ctrl + 208);
   uint8_t *act_flag = ctrl + 256;                          // [256]
   uint8_t *act_list = ctrl + 512;                          // [256]
+  uint32_t *slot_masks = (uint32_t *)(ctrl + 768);         // [stages][4] rows of the step WITHOUT a neighbour
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_warps = blockDim.x >> 5;
@@ -205,24 +206,33 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         if (lane == 0 && k0 + i < K) act_flag[k0 + i] = b != 0;
       }
     }
-    // every A row of every slot starts as zero
-    for (int sl = warp; sl < S; sl += mma_warp) {
-      uint4 *slot = (uint4 *)(smem + (size_t)sl * stage_bytes);
-      for (int i = lane; i < TC_A_BYTES / 16; i += 32) slot[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    fence_async_smem();  // publish the zero-fill to the tensor core's view of shared memory
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (warp < TC_EPI_WARPS) {
+    // Clear the accumulators.  Every MMA below accumulates, and rows without a neighbour at a
+    // step are switched off through the MMA's disable-output-lane mask, so the gathered operand
+    // never has to hold zero rows (stale rows of an earlier step are simply not written back).
+    for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr),
+          "r"(0u)
+          : "memory");
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
   if (tid == 0) {
     int n = 0;
     for (int kappa = 0; kappa < K; ++kappa)
       if (act_flag[kappa]) act_list[n++] = (uint8_t)kappa;
     *n_act_s = n;
   }
+  tc_fence_before();
   __syncthreads();
-  const uint32_t tmem_base = *tmem_slot;
+  tc_fence_after();
   const int n_act = *n_act_s;
   const int n_iter = n_act * p.k_slabs;
   const uint32_t smem_base = smem_u32(smem);
@@ -240,13 +250,12 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     const bool vec_ok = (c_in & 3) == 0;
     const uint32_t slot_addr = smem_base + (uint32_t)slot * (uint32_t)stage_bytes;
     uint8_t *slot_ptr = smem + (size_t)slot * stage_bytes;
+    (void)slot_ptr;
     const uint32_t sw = (uint32_t)(lane & 7);
     // row q*32+lane of the slot: 8-row group (q*4 + lane/8), row-in-group lane%8
     uint32_t row_off[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) row_off[q] = (uint32_t)(q * 4 + (lane >> 3)) * 1024u + sw * 128u;
-    uint32_t dirty = 0;        // bit q: row q*32+lane of the slot currently holds gathered data
-    bool fence_needed = false;
     uint32_t par = 0;          // parity of the slot's current use
     int src[4], nxt[4];
     auto load_rows = [&](int j, int *dst) {
@@ -280,6 +289,11 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       const int ch0 = slab * TC_SLAB;
       uint32_t present = 0;
 #pragma unroll
+      for (int q = 0; q < 4; ++q) {  // rows of this step that the MMA must leave alone
+        const unsigned have = __ballot_sync(0xffffffffu, src[q] >= 0);
+        if (lane == 0 && q >= q0 && q < q0 + q_per) slot_masks[slot * 4 + q] = ~have;
+      }
+#pragma unroll
       for (int q = 0; q < 4; ++q) {
         if (src[q] >= 0 && ch0 < c_in) {
           const float *fp = features + (size_t)src[q] * c_in + ch0;
@@ -301,17 +315,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
               }
           }
           present |= 1u << q;
-        } else if (dirty & (1u << q)) {
-          uint8_t *row = slot_ptr + row_off[q];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) *(uint4 *)(row + ((c ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);  // swizzled order: no bank conflicts
-          fence_needed = true;
         }
       }
-      dirty = present;
       cp_async_commit();
       cp_async_wait(0);
-      if (STAGED) fence_needed = fence_needed || present != 0;  // rows were rounded when they were staged
       // copies landed: round the gathered rows to TF32 in place
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -327,13 +334,9 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
             v.w = to_tf32(__uint_as_float(v.w));
             *ptr = v;
           }
-          fence_needed = true;
         }
       }
-      if (fence_needed) {  // make this lane's writes visible to the tensor core
-        fence_async_smem();
-        fence_needed = false;
-      }
+      if (present) fence_async_smem();  // make this lane's rows visible to the tensor core
       mbar_arrive(smem_u32(fulla_bars + slot));
       par ^= 1u;
     }
@@ -349,13 +352,13 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       if (!mbar_wait(fulla0 + s * 8u, par, abort_flag)) break;
       if (!mbar_wait(fullb0 + s * 8u, par, abort_flag)) break;
       tc_fence_after();
-      const uint32_t fresh = it > 0 ? 1u : 0u;  // the very first MMA overwrites the accumulators
+      const uint4 off = *(const uint4 *)(slot_masks + s * 4u);  // rows to leave untouched
       for (int nt = 0; nt < p.n_tiles; ++nt) {
         const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n), bn = a_lo + (TC_A_BYTES >> 4) + (uint32_t)nt * n_step;
-        mma_tf32_ss(dn, a_lo, bn, idesc, fresh);
-        mma_tf32_ss(dn, a_lo + 2u, bn + 2u, idesc, 1u);
-        mma_tf32_ss(dn, a_lo + 4u, bn + 4u, idesc, 1u);
-        mma_tf32_ss(dn, a_lo + 6u, bn + 6u, idesc, 1u);
+        mma_tf32_ss_masked(dn, a_lo, bn, idesc, off);
+        mma_tf32_ss_masked(dn, a_lo + 2u, bn + 2u, idesc, off);
+        mma_tf32_ss_masked(dn, a_lo + 4u, bn + 4u, idesc, off);
+        mma_tf32_ss_masked(dn, a_lo + 6u, bn + 6u, idesc, off);
       }
       mma_commit(empty0 + s * 8u);
       a_lo += slot_step;

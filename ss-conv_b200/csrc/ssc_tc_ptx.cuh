@@ -95,6 +95,19 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_c, uint32_t a_lo, uint
       : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "r"(0u)
       : "memory");
 }
+// D[tmem] += A * B for the rows whose bit in `off` (x = rows 0-31 ... w = rows 96-127) is clear;
+// rows whose bit is set keep their accumulator value (disable-output-lane mask).
+__device__ __forceinline__ void mma_tf32_ss_masked(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint4 off) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, {%6, %7, %8, %9}, p;\n\t}"
+      :
+      : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(1u), "r"(kDescHi), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
+      : "memory");
+}
 // Same with the A operand read from tensor memory (lane = row, one 32-bit column per element).
 __device__ __forceinline__ void mma_tf32_ts_lo(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
