@@ -101,6 +101,9 @@ bool tc_operand_layout(int c_in, int c_out, int *k_slabs, int *n_pad, int *tile_
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async16_cg(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -302,7 +305,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
             for (int c = 0; c < 8; ++c) {  // chunks past the last channel are zero-filled
               bool ok = ch0 + c * 4 < c_in;
-              cp_async16(a_row + ((c ^ sw) << 4), ok ? (const void *)(fp + c * 4) : (const void *)features, ok ? 16u : 0u);
+              if (STAGED) cp_async16_cg(a_row + ((c ^ sw) << 4), ok ? (const void *)(fp + c * 4) : (const void *)features, ok ? 16u : 0u);
+              else cp_async16(a_row + ((c ^ sw) << 4), ok ? (const void *)(fp + c * 4) : (const void *)features, ok ? 16u : 0u);
             }
           } else {
 #pragma unroll
