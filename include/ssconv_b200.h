@@ -105,13 +105,23 @@ int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int batch, const i
                             size_t scratch_bytes, void *stream);
 
 /* Phase 2 (same arguments and the SAME untouched scratch as phase 1): writes
- * out_indices [n_out,4], nbr [K,n_out], pairs [K,2,n_in] (may be NULL), indice_num [K]. */
+ * out_indices [n_out,4], nbr [K,n_out], pairs [K,2,n_in] (may be NULL), indice_num [K].
+ *
+ * Running ahead of the count.  n_out_dev (may be NULL) is the device word phase 1 wrote.  When
+ * it is given, n_out is only a CAPACITY chosen by the caller (>= the true count, <= the bound
+ * min(n_in*K, batch*out cells)): it sizes the launches and is the row stride of nbr, the exact
+ * count is read on the device, and table rows between the count and the capacity are -1.  A
+ * caller can then queue phase 2 and the layer that consumes the table (ssc_conv_fwd and the
+ * pools accept the same pair n_out / n_out_dev) without waiting for the 4-byte read-back of
+ * phase 1, and check afterwards that the count did fit (if not, repeat with the exact count).
+ * pairs must be NULL in that mode (indice_num is still produced).  No counterpart in the
+ * reference. */
 int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batch, const int in_shape[3],
                            const int out_shape[3], const int ksize[3], const int stride[3],
                            const int padding[3], const int dilation[3], int transpose, int n_out,
                            int32_t *out_indices, int32_t *nbr, int32_t *pairs,
                            int32_t *indice_num, int32_t *status, void *scratch,
-                           size_t scratch_bytes, void *stream);
+                           size_t scratch_bytes, const int32_t *n_out_dev, void *stream);
 
 /* Neighbour table from a reference-format rulebook (indicePairs [K,2,n_cols], indiceNum [K]):
  * nbr[kappa][pairs[kappa][1-swap][i]] = pairs[kappa][swap][i].  swap = 1 is the "inverse"
@@ -158,24 +168,27 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  * the TF32 path of a large layer stages a TF32-rounded copy of the feature rows there and
  * gathers them with the TMA unit (cp.async.bulk.tensor tile::gather4) in a persistent kernel;
  * without it (NULL / too small) the rows are gathered by the SM's load-store units.  The
- * result is the same up to the summation order inside the tensor core. */
+ * result is the same up to the summation order inside the tensor core.
+ * n_out_dev: NULL, or the device word holding the exact number of output rows when n_out is a
+ * capacity (see ssc_rulebook_conv_fill); rows past the exact count are not written. */
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
 size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision);
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                  const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
-                 void *scratch, size_t scratch_bytes, void *stream);
+                 void *scratch, size_t scratch_bytes, const int32_t *n_out_dev, void *stream);
 
 /* ---------------------------------------------------------------------------- sparse pools
  * Replace indiceMaxPool / indiceAvgPool (SS_Conv_lib/src/pool/indice_maxpool.h:15-50,
  * SS_Conv_lib/src/pool/indice_avgpool.h:17-52) and their K-launch kernels.  Max: output starts
  * at zero (indice_maxpool.h:24) so the result is max(0, max_i x_i).  Avg: out = sum_i x_i /
  * summaryrf[o] accumulated in ascending offset order (indice_avgpool_cuda_functor.cu:43);
- * summaryrf NULL means "divide by K" (SS_Conv_lib/ss_conv/sp_ops/functional.py:171-176). */
+ * summaryrf NULL means "divide by K" (SS_Conv_lib/ss_conv/sp_ops/functional.py:171-176).
+ * n_out_dev as in ssc_conv_fwd. */
 int ssc_maxpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out, float *out,
-                    void *stream);
+                    const int32_t *n_out_dev, void *stream);
 int ssc_avgpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out,
-                    const int32_t *summaryrf, float *out, void *stream);
+                    const int32_t *summaryrf, float *out, const int32_t *n_out_dev, void *stream);
 /* Replaces indiceSummaryRF (SS_Conv_lib/src/pool/indiceSummaryRF.cu:21-63). */
 int ssc_summary_rf(const int32_t *nbr, int K, int n_out, int32_t *rf, void *stream);
 

@@ -30,6 +30,14 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
     if (!(cond)) return ssc::fail(SSC_ERR_INVALID, __VA_ARGS__);                   \
   } while (0)
 
+// Number of valid rows of a launch whose row count may still be on the device: `cap` is the
+// host-side bound (and the row stride of the tables), `n_dev` (may be null) the exact count.
+__device__ __forceinline__ int live_rows(int cap, const int32_t *n_dev) {
+  if (n_dev == nullptr) return cap;
+  const int v = *n_dev;
+  return v < 0 ? 0 : (v < cap ? v : cap);
+}
+
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

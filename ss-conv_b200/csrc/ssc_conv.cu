@@ -6,7 +6,7 @@ namespace ssc {
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  cudaStream_t st);
+                  const int32_t *n_out_dev, cudaStream_t st);
 size_t conv_gather4_scratch_bytes(int n_in, int c_in, int c_out);
 
 // filters[kappa][cin][cout] = sum_b w[u,v,b] * basis[b,a,c,kappa]; one thread per element,
@@ -46,13 +46,16 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 __global__ void __launch_bounds__(256)
 conv_fwd_fp32_kernel(const float *__restrict__ features, int c_in, const float *__restrict__ filters, int K,
-                     int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out) {
+                     int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
+                     const int32_t *__restrict__ n_out_dev) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   __shared__ int rows[BM];
   int tid = threadIdx.x;
   int tx = tid & 15, ty = tid >> 4;
   int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int n_rows = live_rows(n_out, n_out_dev);
+  if (m0 >= n_rows) return;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -61,7 +64,7 @@ conv_fwd_fp32_kernel(const float *__restrict__ features, int c_in, const float *
 
   for (int kappa = 0; kappa < K; ++kappa) {
     int r = -1;
-    if (tid < BM && m0 + tid < n_out) r = nbr[(size_t)kappa * n_out + m0 + tid];
+    if (tid < BM && m0 + tid < n_rows) r = nbr[(size_t)kappa * n_out + m0 + tid];
     __syncthreads();  // previous iteration finished reading rows/As/Bs
     if (tid < BM) rows[tid] = r;
     if (!__syncthreads_or(r >= 0)) continue;
@@ -111,7 +114,7 @@ conv_fwd_fp32_kernel(const float *__restrict__ features, int c_in, const float *
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     int m = m0 + ty * 4 + i;
-    if (m >= n_out) continue;
+    if (m >= n_rows) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int n = n0 + tx * 4 + j;
@@ -143,17 +146,17 @@ extern "C" size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int prec
 
 extern "C" int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                             const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
-                            void *scratch, size_t scratch_bytes, void *stream) {
+                            void *scratch, size_t scratch_bytes, const int32_t *n_out_dev, void *stream) {
   SSC_REQUIRE(c_in > 0 && c_out > 0 && K > 0 && n_in >= 0 && n_out >= 0, "conv_fwd: bad sizes");
   if (n_out == 0) return SSC_OK;
   SSC_REQUIRE(filters && nbr && out && (n_in == 0 || features), "conv_fwd: null pointer");
   cudaStream_t st = as_stream(stream);
   if (precision == SSC_PREC_FP32) {
     dim3 grid(ceil_div(n_out, BM), ceil_div(c_out, BN));
-    { conv_fwd_fp32_kernel<<<grid, 256, 0, st>>>(features, c_in, (const float *)filters, K, c_out, nbr, n_out, out); note_launches(1); }
+    { conv_fwd_fp32_kernel<<<grid, 256, 0, st>>>(features, c_in, (const float *)filters, K, c_out, nbr, n_out, out, n_out_dev); note_launches(1); }
     SSC_CHECK_LAUNCH("conv_fwd_fp32");
     return SSC_OK;
   }
-  if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, st);
+  if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, st);
   return fail(SSC_ERR_INVALID, "conv_fwd: unknown precision %d", precision);
 }

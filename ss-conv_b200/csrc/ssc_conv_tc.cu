@@ -152,7 +152,11 @@ template <bool STAGED>
 __global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
-                     int32_t *status, TcParams p) {
+                     int32_t *status, TcParams p, const int32_t *__restrict__ n_out_dev) {
+  // n_out is the row stride of nbr and the launch bound; the exact row count may still be on the
+  // device (a rulebook sized optimistically): CTAs past it have nothing to do.
+  const int n_rows = live_rows(n_out, n_out_dev);
+  if ((int)blockIdx.x * TC_M >= n_rows) return;
   extern __shared__ uint8_t smem_raw[];
   // operand stages need 1024-byte alignment for the 128-byte swizzle
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -200,7 +204,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           int r = m0 + q * 32 + lane;
-          v[i][q] = (k0 + i < K && r < n_out) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
+          v[i][q] = (k0 + i < K && r < n_rows) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
         }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -266,7 +270,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         int r = m0 + q * 32 + lane;
-        dst[q] = (q >= q0 && q < q0 + q_per && r < n_out) ? __ldg(nbr + (size_t)kap * n_out + r) : -1;
+        dst[q] = (q >= q0 && q < q0 + q_per && r < n_rows) ? __ldg(nbr + (size_t)kap * n_out + r) : -1;
       }
     };
     if (slot < n_iter) load_rows(slot, nxt);
@@ -396,7 +400,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
         for (int q = 0; q < 16; ++q) r[q] = 0u;
       }
-      if (m < n_out) {
+      if (m < n_rows) {
         float *op = out + (size_t)m * c_out + c0;
         if ((c_out & 3) == 0) {
 #pragma unroll
@@ -433,20 +437,20 @@ constexpr int kStagingMinTiles = 64;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  cudaStream_t st) {
+                  const int32_t *n_out_dev, cudaStream_t st) {
   TcParams p;
   // Three variants share the packed filter image.  SSC_TC_VARIANT = gather4 | smem | tmem forces
   // one (where the shape allows); by default large problems take the persistent TMA-gather
   // kernel when the caller supplied its staging buffer, the others the shared-memory kernel.
   const char *variant = getenv("SSC_TC_VARIANT");
   const bool force_g4 = variant != nullptr && strcmp(variant, "gather4") == 0;
-  if (force_g4) {
+  if (force_g4 && n_out_dev == nullptr) {
     int rc = conv_fwd_tf32_gather4(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, scratch,
                                    scratch_bytes, st);
     if (rc >= 0) return rc;
   }
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
-  if (variant != nullptr && strcmp(variant, "tmem") == 0) {
+  if (variant != nullptr && strcmp(variant, "tmem") == 0 && n_out_dev == nullptr) {
     int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
     if (rc >= 0) return rc;
   }
@@ -467,7 +471,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
   { kernel<<<grid, p.threads, smem, st>>>(staged ? (const float *)scratch : features, c_in, (const uint4 *)packed, K, c_out,
-                                        nbr, n_out, out, status, p); note_launches(1); }
+                                        nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;
 }

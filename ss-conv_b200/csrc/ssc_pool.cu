@@ -8,10 +8,11 @@ namespace ssc {
 // One thread per (output row, 4 channels).
 template <int MODE, bool VEC>
 __global__ void pool_fwd_kernel(const float *__restrict__ features, int c, const int32_t *__restrict__ nbr, int K,
-                                int n_out, const int32_t *__restrict__ summaryrf, float *__restrict__ out) {
+                                int n_out, const int32_t *__restrict__ summaryrf, float *__restrict__ out,
+                                const int32_t *__restrict__ n_out_dev) {
   int cg = (c + 3) >> 2;
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= (long long)n_out * cg) return;
+  if (t >= (long long)live_rows(n_out, n_out_dev) * cg) return;  // n_out stays the row stride of nbr
   int o = (int)(t / cg);
   int c0 = (int)(t - (long long)o * cg) * 4;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -128,28 +129,28 @@ using namespace ssc;
 
 template <int MODE>
 static int launch_pool(const float *features, int c, const int32_t *nbr, int K, int n_out, const int32_t *rf,
-                       float *out, void *stream, const char *name) {
+                       float *out, const int32_t *n_out_dev, void *stream, const char *name) {
   SSC_REQUIRE(c > 0 && K > 0 && n_out >= 0, "%s: bad sizes", name);
   if (n_out == 0) return SSC_OK;
   SSC_REQUIRE(features && nbr && out, "%s: null pointer", name);
   long long threads = (long long)n_out * ((c + 3) / 4);
   bool vec = (c % 4 == 0) && (((uintptr_t)features | (uintptr_t)out) % 16 == 0);
   if (vec)
-    { pool_fwd_kernel<MODE, true><<<ceil_div(threads, 256), 256, 0, as_stream(stream)>>>(features, c, nbr, K, n_out, rf, out); note_launches(1); }
+    { pool_fwd_kernel<MODE, true><<<ceil_div(threads, 256), 256, 0, as_stream(stream)>>>(features, c, nbr, K, n_out, rf, out, n_out_dev); note_launches(1); }
   else
-    { pool_fwd_kernel<MODE, false><<<ceil_div(threads, 256), 256, 0, as_stream(stream)>>>(features, c, nbr, K, n_out, rf, out); note_launches(1); }
+    { pool_fwd_kernel<MODE, false><<<ceil_div(threads, 256), 256, 0, as_stream(stream)>>>(features, c, nbr, K, n_out, rf, out, n_out_dev); note_launches(1); }
   SSC_CHECK_LAUNCH(name);
   return SSC_OK;
 }
 
 extern "C" int ssc_maxpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out, float *out,
-                               void *stream) {
-  return launch_pool<0>(features, c, nbr, K, n_out, nullptr, out, stream, "maxpool_fwd");
+                               const int32_t *n_out_dev, void *stream) {
+  return launch_pool<0>(features, c, nbr, K, n_out, nullptr, out, n_out_dev, stream, "maxpool_fwd");
 }
 
 extern "C" int ssc_avgpool_fwd(const float *features, int c, const int32_t *nbr, int K, int n_out,
-                               const int32_t *summaryrf, float *out, void *stream) {
-  return launch_pool<1>(features, c, nbr, K, n_out, summaryrf, out, stream, "avgpool_fwd");
+                               const int32_t *summaryrf, float *out, const int32_t *n_out_dev, void *stream) {
+  return launch_pool<1>(features, c, nbr, K, n_out, summaryrf, out, n_out_dev, stream, "avgpool_fwd");
 }
 
 extern "C" int ssc_summary_rf(const int32_t *nbr, int K, int n_out, int32_t *rf, void *stream) {

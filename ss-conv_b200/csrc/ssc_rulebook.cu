@@ -206,12 +206,14 @@ __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
 __global__ void __launch_bounds__(kChunk)
 lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, Geometry g,
                          const unsigned long long *__restrict__ table, uint32_t mask,
-                         int32_t *__restrict__ nbr, int32_t *__restrict__ chunk_counts, int n_chunks) {
+                         int32_t *__restrict__ nbr, int32_t *__restrict__ chunk_counts, int n_chunks,
+                         const int32_t *__restrict__ n_out_dev) {
   const unsigned full = 0xffffffffu;
   int kappa = blockIdx.y;
   int o = blockIdx.x * kChunk + threadIdx.x;
   uint32_t key = 0xFFFFFFFFu;
-  if (o < n_out) {
+  const int n_rows = live_rows(n_out, n_out_dev);  // rows past it (up to the capacity n_out) get -1
+  if (o < n_rows) {
     int4 c = out_indices[o];
     int kk[3] = {kappa / (g.ksize[1] * g.ksize[2]), (kappa / g.ksize[2]) % g.ksize[1], kappa % g.ksize[2]};
     int oc[3] = {c.y, c.z, c.w};
@@ -377,13 +379,13 @@ static int build_hash(const int32_t *indices, int n_in, int batch, const Geometr
 
 static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, int batch, const Geometry &g,
                               RulebookScratch &s, int32_t *nbr, int32_t *pairs, int32_t *indice_num,
-                              cudaStream_t st) {
+                              cudaStream_t st, const int32_t *n_out_dev = nullptr) {
   int K = g.K;
   int n_chunks = ceil_div(n_out > 0 ? n_out : 1, kChunk);
   if (n_chunks > s.n_chunks_cap) return fail(SSC_ERR_SCRATCH, "rulebook: n_out exceeds the scratch capacity");
   dim3 grid(n_chunks, K);
   { lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
-                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks); note_launches(1); }
+                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks, n_out_dev); note_launches(1); }
   SSC_CHECK_LAUNCH("lookup_neighbours");
   if (indice_num == nullptr) return 0;
   { scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num); note_launches(1); }
@@ -554,9 +556,12 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
                                       const int out_shape[3], const int ksize[3], const int stride[3],
                                       const int padding[3], const int dilation[3], int transpose, int n_out,
                                       int32_t *out_indices, int32_t *nbr, int32_t *pairs, int32_t *indice_num,
-                                      int32_t *status, void *scratch, size_t scratch_bytes, void *stream) {
+                                      int32_t *status, void *scratch, size_t scratch_bytes,
+                                      const int32_t *n_out_dev, void *stream) {
   SSC_REQUIRE(n_in >= 0 && n_out >= 0 && in_shape && out_shape && ksize && stride && padding && dilation,
               "rulebook_conv_fill: bad arguments");
+  SSC_REQUIRE(n_out_dev == nullptr || pairs == nullptr,
+              "rulebook_conv_fill: pair lists need the exact output count on the host");
   SSC_REQUIRE(n_out == 0 || (out_indices && nbr), "rulebook_conv_fill: null pointer");
   Geometry g;
   SSC_REQUIRE(fill_geometry(g, in_shape, out_shape, ksize, stride, padding, dilation, transpose) == 0,
@@ -572,7 +577,7 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
                                                                    (int4 *)out_indices); note_launches(1); }
     SSC_CHECK_LAUNCH("decode_outputs");
   }
-  if (int e = lookup_and_compact(out_indices, n_out, n_in, batch, g, s, nbr, pairs, indice_num, st)) return e;
+  if (int e = lookup_and_compact(out_indices, n_out, n_in, batch, g, s, nbr, pairs, indice_num, st, n_out_dev)) return e;
   SSC_CHECK_LAUNCH("rulebook_conv_fill");
   return SSC_OK;
 }

@@ -47,9 +47,9 @@ SIGNATURES = {
     "ssc_conv_pack_filters": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_conv_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-                             c_void_p, c_void_p, c_size_t, c_void_p]),
-    "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
-    "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+                             c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_global_avgpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_global_maxpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -209,8 +209,76 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
     outids = torch.empty((n_out, 4), dtype=torch.int32, device=dev)
     nbr = torch.empty((K, n_out), dtype=torch.int32, device=dev)
     _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, n_out, _p(outids), _p(nbr), _p(pairs),
-                                    _p(num), _p(st), _p(scratch), scratch.numel(), _stream()))
+                                    _p(num), _p(st), _p(scratch), scratch.numel(), None, _stream()))
+    _note_ratio(_geometry_key(spatial_shape, ksize, stride, padding, dilation, transpose), n_in, n_out)
     return outids, nbr, pairs, num
+
+
+# ------------------------------------------------------------------ rulebooks that run ahead
+# The number of active outputs of a regular (strided) rulebook is only known on the device after
+# its counting phase.  Waiting for it on the host stalls the GPU twice per layer (the wait itself,
+# then the launches that follow).  A layer can instead size the second phase and its own kernel
+# by a CAPACITY guessed from the output/input ratio this geometry produced before, queue
+# everything, and read the count back once at the end; the count is then checked against the
+# capacity and, if it did not fit, the layer is redone the slow way.  Off unless SSCONV_AHEAD=1.
+AHEAD = os.environ.get("SSCONV_AHEAD", "0") == "1"
+AHEAD_MARGIN = 1.10
+_ratio_hint = {}
+
+
+def _geometry_key(spatial_shape, ksize, stride, padding, dilation, transpose):
+    return (tuple(int(v) for v in spatial_shape), tuple(int(v) for v in ksize), tuple(int(v) for v in stride),
+            tuple(int(v) for v in padding), tuple(int(v) for v in dilation), int(bool(transpose)))
+
+
+def _note_ratio(key, n_in, n_out):
+    if n_in > 0:
+        r = float(n_out) / float(n_in)
+        if r > _ratio_hint.get(key, 0.0):
+            if len(_ratio_hint) > 4096:
+                _ratio_hint.clear()
+            _ratio_hint[key] = r
+
+
+def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation, transpose):
+    """Regular rulebook whose output count stays on the device: returns [outids_cap [cap,4],
+    LazyPairs (pending, capacity cap), indice_num] or None when no capacity can be guessed yet
+    (first call for this geometry) or the feature is off.  The caller runs its kernel with
+    n_out = pairs.capacity, then calls pairs.resolve()."""
+    if not AHEAD:
+        return None
+    key = _geometry_key(spatial_shape, ksize, stride, padding, dilation, transpose)
+    ratio = _ratio_hint.get(key)
+    if ratio is None:
+        return None
+    L = lib()
+    if indices.dtype != torch.int32:
+        raise TypeError("indices must be int32")
+    indices = indices.contiguous()
+    dev = indices.device
+    n_in = indices.shape[0]
+    K = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
+    cells = int(batch_size) * int(out_shape[0]) * int(out_shape[1]) * int(out_shape[2])
+    if K > 256 or n_in == 0 or cells >= 2 ** 31 - 1:
+        return None
+    bound = min(n_in * K, cells)
+    cap = min(bound, int(n_in * ratio * AHEAD_MARGIN) + 1024)
+    skey = (n_in, int(batch_size), int(out_shape[0]), int(out_shape[1]), int(out_shape[2]), K)
+    sbytes = _scratch_cache.get(skey)
+    if sbytes is None:
+        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(out_shape), K)), 256)
+    scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+    small = torch.empty(K + 1, dtype=torch.int32, device=dev)
+    num, n_out_dev = small[:K], small[K:]
+    st = status_word(dev)
+    geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
+    _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
+                                     sbytes, _stream()))
+    outids = torch.empty((cap, 4), dtype=torch.int32, device=dev)
+    nbr = torch.empty((K, cap), dtype=torch.int32, device=dev)
+    _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, cap, _p(outids), _p(nbr), None, _p(num),
+                                    _p(st), _p(scratch), sbytes, _p(n_out_dev), _stream()))
+    return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=key), num]
 
 
 def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
@@ -255,13 +323,44 @@ class LazyPairs(object):
     (indexing, .cpu(), arithmetic ...) gets the real tensor, built on first use by
     ssc_pairs_from_nbr."""
 
-    def __init__(self, nbr, n_in):
-        self._ssc_nbr = nbr
+    def __init__(self, nbr, n_in, n_out_dev=None, ratio_key=None):
+        self._nbr_cap = nbr                  # [K, capacity]; capacity == n_out unless built ahead
+        self.capacity = int(nbr.shape[1])
+        self._n_out_dev = n_out_dev          # device count of a rulebook built ahead, until resolved
+        self._n_out = None if n_out_dev is not None else self.capacity
+        self._ratio_key = ratio_key
         self._n_in = int(n_in)
         self._tensor = None
         self.shape = torch.Size((nbr.shape[0], 2, self._n_in))
         self.device = nbr.device
         self.dtype = torch.int32
+
+    def pending(self):
+        return self._n_out is None
+
+    def resolve(self):
+        """Reads the output count of a rulebook built ahead (one host sync).  Returns it, or None
+        when it exceeded the capacity (everything computed from this handle is then invalid)."""
+        if self._n_out is None:
+            n = int(self._n_out_dev.item())
+            if self._ratio_key is not None:
+                _note_ratio(self._ratio_key, self._n_in, n)
+            if n > self.capacity:
+                return None
+            self._n_out = n
+            self._n_out_dev = None
+        return self._n_out
+
+    @property
+    def _ssc_nbr(self):
+        """The exact table [K, n_out], contiguous (compacted on first use if the capacity was larger)."""
+        n = self.resolve()
+        if n is None:
+            raise RuntimeError("rulebook built ahead overflowed its capacity and was not rebuilt")
+        if self.capacity != n:
+            self._nbr_cap = self._nbr_cap[:, :n].contiguous()
+            self.capacity = n
+        return self._nbr_cap
 
     def to(self, *args, **kwargs):
         return self
@@ -288,6 +387,15 @@ class LazyPairs(object):
 
     def __len__(self):
         return self.shape[0]
+
+
+def _table_for(pairs, num, n_out, inverse=False):
+    """(nbr, n_out_dev): the table a kernel launch with bound n_out should use.  n_out_dev is the
+    device row count when the rulebook was built ahead, is still pending, and n_out is its
+    capacity; otherwise None and the table is exact."""
+    if isinstance(pairs, LazyPairs) and not inverse and pairs.pending() and pairs.capacity == n_out:
+        return pairs._nbr_cap, pairs._n_out_dev
+    return neighbour_table(pairs, num, n_out, inverse), None
 
 
 def neighbour_table(pairs, num, n_out, inverse=False):
@@ -348,8 +456,9 @@ def _resolve_precision(c_in, c_out, precision=None):
 STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") == "gather4" else 64 * 128
 
 
-def conv_forward(features, filters, nbr, n_out, precision=None):
-    """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch)."""
+def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None):
+    """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch).
+    n_out_dev: device word with the exact row count when n_out is only a capacity."""
     if filters.dim() != 3:
         filters = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
     K, c_in, c_out = filters.shape
@@ -372,12 +481,12 @@ def conv_forward(features, filters, nbr, n_out, precision=None):
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
                                   _p(nbr, torch.int32), int(n_out), PREC_TF32, _p(out), _p(st), _p(scratch), nbytes,
-                                  _stream()))
+                                  _p(n_out_dev), _stream()))
     else:
         filters = filters.contiguous()
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(filters, torch.float32), K,
                                   c_out, _p(nbr, torch.int32), int(n_out), PREC_FP32, _p(out), _p(st), None, 0,
-                                  _stream()))
+                                  _p(n_out_dev), _stream()))
     return out
 
 
@@ -396,8 +505,8 @@ def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, i
             filters._ssc_flat = (filters._version, flt)
         except Exception:
             pass
-    nbr = neighbour_table(indice_pairs, indice_num, int(num_act_out), bool(inverse))
-    return conv_forward(features, flt, nbr, int(num_act_out))
+    nbr, n_out_dev = _table_for(indice_pairs, indice_num, int(num_act_out), bool(inverse))
+    return conv_forward(features, flt, nbr, int(num_act_out), n_out_dev=n_out_dev)
 
 
 def _not_built(name):
@@ -416,20 +525,20 @@ indice_conv_backward_half = _not_built("indice_conv_backward_half")
 # ================================================================================== pools
 def indice_maxpool_fp32(features, indice_pairs, indice_num, num_act):
     features = features.contiguous()
-    nbr = neighbour_table(indice_pairs, indice_num, int(num_act))
+    nbr, n_out_dev = _table_for(indice_pairs, indice_num, int(num_act))
     out = torch.empty((int(num_act), features.shape[1]), dtype=torch.float32, device=features.device)
     _check(lib().ssc_maxpool_fwd(_p(features, torch.float32), features.shape[1], _p(nbr), nbr.shape[0], int(num_act),
-                                 _p(out), _stream()))
+                                 _p(out), _p(n_out_dev), _stream()))
     return out
 
 
 def indice_avgpool_fp32(features, indice_pairs, indice_num, num_act, summaryrf):
     features = features.contiguous()
-    nbr = neighbour_table(indice_pairs, indice_num, int(num_act))
+    nbr, n_out_dev = _table_for(indice_pairs, indice_num, int(num_act))
     out = torch.empty((int(num_act), features.shape[1]), dtype=torch.float32, device=features.device)
     rf = None if summaryrf is None else summaryrf.to(torch.int32).contiguous()
     _check(lib().ssc_avgpool_fwd(_p(features, torch.float32), features.shape[1], _p(nbr), nbr.shape[0], int(num_act),
-                                 _p(rf), _p(out), _stream()))
+                                 _p(rf), _p(out), _p(n_out_dev), _stream()))
     return out
 
 

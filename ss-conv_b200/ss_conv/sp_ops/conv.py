@@ -8,6 +8,7 @@ from torch.nn.parameter import Parameter
 
 from .tensor import SparseTensor
 from .ops import get_conv_output_size, get_deconv_output_size, get_indice_pairs, _per_dim
+from .. import _ext
 from .functional import indice_conv, indice_inverse_conv, indice_subm_conv
 
 
@@ -82,13 +83,33 @@ class SparseConvolution(nn.Module):
         elif self.indice_key is not None and cached is not None:
             outids, _, indice_pairs, indice_pair_num, _ = cached
         else:
-            outids, indice_pairs, indice_pair_num = get_indice_pairs(
-                indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
-                self.output_padding, self.subm, self.transposed, grid=input.grid, lazy=True)
+            out_features = None
+            ahead = None
+            if not self.subm and features.dtype == torch.float32:
+                ahead = _ext.get_indice_pairs_ahead(indices, batch_size, out_spatial_shape, list(spatial_shape),
+                                                    self.kernel_size, self.stride, self.padding, self.dilation,
+                                                    int(self.transposed))
+            if ahead is not None:
+                # rulebook and convolution are queued with a guessed capacity; the output count is
+                # read back once, after the convolution has been launched
+                outids_cap, indice_pairs, indice_pair_num = ahead
+                out_cap = indice_conv(features, weight, indice_pairs, indice_pair_num, indice_pairs.capacity)
+                n_out = indice_pairs.resolve()
+                if n_out is not None:
+                    outids, out_features = outids_cap[:n_out], out_cap[:n_out]
+            if out_features is None:
+                outids, indice_pairs, indice_pair_num = get_indice_pairs(
+                    indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
+                    self.output_padding, self.subm, self.transposed, grid=input.grid, lazy=True)
             input.indice_dict[self.indice_key] = (outids, indices, indice_pairs, indice_pair_num, spatial_shape)
+            if out_features is not None:
+                return self._finish(input, out_features, outids, out_spatial_shape, batch_size)
 
         op = indice_subm_conv if self.subm else (indice_inverse_conv if self.inverse else indice_conv)
         out_features = op(features, weight, indice_pairs, indice_pair_num, outids.shape[0])
+        return self._finish(input, out_features, outids, out_spatial_shape, batch_size)
+
+    def _finish(self, input, out_features, outids, out_spatial_shape, batch_size):
         if self.bias is not None:
             out_features += self.bias
         out = SparseTensor(out_features, outids, out_spatial_shape, batch_size)

@@ -1,6 +1,7 @@
 """Sparse average / max pooling modules (interface of SS_Conv_lib/ss_conv/sp_ops/pool.py)."""
 import torch.nn as nn
 
+from .. import _ext
 from .tensor import SparseTensor
 from .ops import get_conv_output_size, get_indice_pairs, _per_dim
 from .functional import indice_avgpool, indice_maxpool
@@ -24,9 +25,20 @@ class _SparsePool(nn.Module):
         shape = input.spatial_shape
         out_shape = shape if self.subm else get_conv_output_size(shape, self.kernel_size, self.stride, self.padding,
                                                                  self.dilation)
-        outids, pairs, pair_num = get_indice_pairs(input.indices, input.batch_size, shape, self.kernel_size,
-                                                   self.stride, self.padding, self.dilation, 0, self.subm, lazy=True)
-        feats = type(self)._op(input.features, pairs, pair_num, outids.shape[0])
+        feats = None
+        ahead = None if self.subm else _ext.get_indice_pairs_ahead(input.indices, input.batch_size, out_shape, list(shape),
+                                                                   self.kernel_size, self.stride, self.padding,
+                                                                   self.dilation, 0)
+        if ahead is not None:  # rulebook and pooling queued with a guessed capacity, count read back last
+            outids_cap, pairs, pair_num = ahead
+            feats_cap = type(self)._op(input.features, pairs, pair_num, pairs.capacity)
+            n_out = pairs.resolve()
+            if n_out is not None:
+                outids, feats = outids_cap[:n_out], feats_cap[:n_out]
+        if feats is None:
+            outids, pairs, pair_num = get_indice_pairs(input.indices, input.batch_size, shape, self.kernel_size,
+                                                       self.stride, self.padding, self.dilation, 0, self.subm, lazy=True)
+            feats = type(self)._op(input.features, pairs, pair_num, outids.shape[0])
         out = SparseTensor(feats, outids, out_shape, input.batch_size)
         out.indice_dict = input.indice_dict
         out.grid = input.grid

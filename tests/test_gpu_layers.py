@@ -150,3 +150,49 @@ def test_host_stream_gives_the_same_results_as_direct_calls(cuda):
         np.testing.assert_array_equal(gf, wf)
     assert list(feed.run(iter([]))) == []
     _ext.check_status(cuda)
+
+
+def test_layers_that_run_ahead_of_the_output_count(cuda, monkeypatch):
+    """A strided convolution + max pool whose rulebooks are sized by a guessed capacity (output
+    count read back after the kernels were queued) give bit-identical results to the exact
+    path, also when the guess was too small and the layer has to be redone."""
+    from ss_conv import _ext
+    from ss_conv.pool import MaxPool
+    from ss_conv.sp_ops.conv import SparseConvolution
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(3)
+    conv = SparseConvolution(3, 16, 24, 3, stride=2, padding=1, bias=True).to(cuda)
+    pool = MaxPool(2, stride=2)
+    ind = S.bernoulli_voxels(range(3), 20, 0.15, base_seed=11)
+    feats = S.features(ind.shape[0], 16, 5)
+
+    def run():
+        with torch.no_grad():
+            y = pool(conv(SparseTensor(dev(feats, cuda), dev(ind, cuda), [20] * 3, 3)))
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+        return y.features.cpu().numpy(), y.indices.cpu().numpy()
+
+    _ext.set_precision("fp32")
+    try:
+        monkeypatch.setattr(_ext, "AHEAD", False)
+        exact = run()
+        monkeypatch.setattr(_ext, "AHEAD", True)
+        _ext._ratio_hint.clear()
+        first = run()                       # no hint yet: exact path, records the ratios
+        assert len(_ext._ratio_hint) == 2
+        l0 = _ext.kernel_launches()
+        ahead = run()                       # capacities guessed from the recorded ratios
+        n_ahead = _ext.kernel_launches() - l0
+        for k in list(_ext._ratio_hint):
+            _ext._ratio_hint[k] = 1e-3      # far too small: both layers overflow and are redone
+        l0 = _ext.kernel_launches()
+        redone = run()
+        assert _ext.kernel_launches() - l0 > n_ahead
+        again = run()                       # the overflow raised the hints again
+    finally:
+        _ext.set_precision("auto")
+    for got in (first, ahead, redone, again):
+        np.testing.assert_array_equal(got[1], exact[1])
+        np.testing.assert_array_equal(got[0], exact[0])

@@ -38,7 +38,7 @@ def test_argument_errors_without_gpu():
     assert L.ssc_rulebook_scratch_bytes(1000, 2, I3(16, 16, 16), 27) > 1000 * 2 * 8
     assert L.ssc_conv_packed_bytes(27, 64, 76, _ext.PREC_TF32) == 27 * 2 * 80 * 128
     assert L.ssc_conv_packed_bytes(27, 64, 600, _ext.PREC_TF32) == 0
-    rc = L.ssc_maxpool_fwd(None, 0, None, 27, 5, None, None)
+    rc = L.ssc_maxpool_fwd(None, 0, None, 27, 5, None, None, None)
     assert rc == 1 and b"bad sizes" in L.ssc_last_error()
     with pytest.raises(RuntimeError):
         _ext.indice_maxpool_fp32(torch.zeros(4, 4), torch.zeros(1, 2, 4, dtype=torch.int32),
