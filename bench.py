@@ -10,8 +10,10 @@ gather-GEMM (tcgen05, TF32 operands, fp32 accumulate) + pool rulebook + max pool
 metric  : active input voxels per second through the layer (whole job, all ranks)
 value   : inputs resident in HBM, CUDA-event timed, max over ranks
 e2e     : the same step through the public ss_conv API starting from pinned HOST buffers
-          (H2D of indices+features and D2H of the pooled features inside the timed region)
-roofline: dominant kernel (conv_fwd_tf32_kernel) algorithmic bytes / its CUDA-event time
+          (H2D of indices+features and D2H of the pooled features of every step inside the timed
+          region; ss_conv.pipeline.HostStream overlaps the copies of neighbouring steps)
+roofline: dominant kernel (conv_fwd_tf32_kernel, with the TF32 staging pass that precedes it)
+          algorithmic bytes / its CUDA-event time
 cpu_baseline / --impl reference: the reference's own C++ CPU path (oracle/_ref, built from the
           reference sources) on the box's host cores.
 
@@ -37,6 +39,7 @@ import torch  # noqa: E402
 
 CFG2 = dict(name="cfg2: SS-Conv (4,4,4,4)->(4,4,4,4)+12 gates, k3 s2 p1, batch 32, 64^3, 16384 pts/sample, + MaxPool k2 s2",
             batch=32, V=64, n_pts=16384, irreps=(4, 4, 4, 4), k=3, stride=2, pad=1, pool_k=2, pool_s=2)
+CONV_DRAM_TRAFFIC = 81.0e6  # bytes per launch, from the ncu capture summarised under profiles/
 ROTATE = 4  # distinct input batches cycled through so the working set exceeds the 126 MB L2
 
 
@@ -342,8 +345,11 @@ def run_ours(args):
                     "serial_value": vox_e2e / serial_s},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
-            "roofline": {"bound": "hbm", "kernel": "conv_fwd_tf32_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+            "roofline": {"bound": "hbm", "kernel": "stage_features_kernel + conv_fwd_tf32_kernel", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": CONV_DRAM_TRAFFIC,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of conv_fwd_tf32_kernel on the "
+                                           "cfg2 inputs (profiles/conv_fwd_tf32_cfg2.md)",
+                         "peak_source": peak_src,
                          "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
                          "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
         }
