@@ -239,7 +239,7 @@ def run_ours(args):
 
     # ---- device-resident throughput
     for w in range(args.warmup):
-        layer.step(*dev_sets[w % ROTATE])
+        layer.step(*dev_sets[w % ROTATE]).resolve()
     barrier()
     l0 = _ext.kernel_launches()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -248,6 +248,7 @@ def run_ours(args):
         voxels = 0
         for s in range(args.steps):
             out = layer.step(*dev_sets[s % ROTATE])
+            out.resolve()        # the step is complete (row counts on the host) before the next one
             voxels += n_in[s % ROTATE]
         ev1.record()
         barrier()

@@ -97,12 +97,14 @@ int ssc_rulebook_subm_static(const int32_t *indices, int n_in, int batch, const 
  * getValidOutPosTranspose geometry.h:82-138) rulebook, phase 1: build the input coordinate
  * hash, mark every reachable output cell and count them.  n_out_dev: device int32 that
  * receives the number of active outputs; the caller reads it back (one 4-byte copy, the
- * counterpart of the host sync inside torch::_unique, indice_conv.h:120) to size phase 2. */
+ * counterpart of the host sync inside torch::_unique, indice_conv.h:120) to size phase 2.
+ * n_in_dev: NULL, or a device word with the exact number of input rows when n_in is only the
+ * capacity of `indices` (the output of a layer whose own count has not been read back yet). */
 int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int batch, const int in_shape[3],
                             const int out_shape[3], const int ksize[3], const int stride[3],
                             const int padding[3], const int dilation[3], int transpose,
                             int32_t *n_out_dev, int32_t *status, void *scratch,
-                            size_t scratch_bytes, void *stream);
+                            size_t scratch_bytes, const int32_t *n_in_dev, void *stream);
 
 /* Phase 2 (same arguments and the SAME untouched scratch as phase 1): writes
  * out_indices [n_out,4], nbr [K,n_out], pairs [K,2,n_in] (may be NULL), indice_num [K].
@@ -201,8 +203,10 @@ int ssc_global_avgpool_fwd(const float *feats, const int32_t *offsets, int n_sam
 int ssc_global_maxpool_fwd(const float *feats, const int32_t *offsets, int n_samples, int c,
                            float *out, int32_t *maxidx, void *stream);
 /* Row offsets [B+1] of a batch-sorted indices [N,4] tensor; replaces the B host syncs of
- * SparseTensor.get_offsets (SS_Conv_lib/ss_conv/sp_ops/tensor.py:59-65). */
-int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, void *stream);
+ * SparseTensor.get_offsets (SS_Conv_lib/ss_conv/sp_ops/tensor.py:59-65).  n_dev: NULL, or the
+ * device word with the exact row count when n is a capacity. */
+int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, const int32_t *n_dev,
+                      void *stream);
 
 /* ---------------------------------------------------------------------------- voxelization
  * ssc_voxel2point_map replaces voxel2point_fp (SS_Conv_lib/src/voxelize/voxel2point_cuda_kernel.cu:16-42):

@@ -100,9 +100,10 @@ __global__ void global_pool_kernel(const float *__restrict__ feats, const int32_
 }
 
 // offsets[b+1] = number of rows with batch id <= b: histogram, then an in-place scan by one warp.
-__global__ void batch_count_kernel(const int4 *__restrict__ indices, int n, int batch, int32_t *offsets) {
+__global__ void batch_count_kernel(const int4 *__restrict__ indices, int n, int batch, int32_t *offsets,
+                                   const int32_t *__restrict__ n_dev) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  if (i >= live_rows(n, n_dev)) return;
   int b = indices[i].x;
   if ((unsigned)b < (unsigned)batch) atomicAdd(offsets + b + 1, 1);
 }
@@ -184,11 +185,12 @@ extern "C" int ssc_global_maxpool_fwd(const float *feats, const int32_t *offsets
   return SSC_OK;
 }
 
-extern "C" int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, void *stream) {
+extern "C" int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, const int32_t *n_dev,
+                                 void *stream) {
   SSC_REQUIRE(n >= 0 && batch >= 1 && offsets, "batch_offsets: bad arguments");
   cudaStream_t st = as_stream(stream);
   cudaMemsetAsync(offsets, 0, (size_t)(batch + 1) * 4, st);
-  if (n > 0) { batch_count_kernel<<<ceil_div(n, 256), 256, 0, st>>>((const int4 *)indices, n, batch, offsets); note_launches(1); }
+  if (n > 0) { batch_count_kernel<<<ceil_div(n, 256), 256, 0, st>>>((const int4 *)indices, n, batch, offsets, n_dev); note_launches(1); }
   { batch_scan_kernel<<<1, 32, 0, st>>>(offsets, batch); note_launches(1); }
   SSC_CHECK_LAUNCH("batch_offsets");
   return SSC_OK;

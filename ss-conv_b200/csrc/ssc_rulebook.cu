@@ -68,9 +68,9 @@ __device__ __forceinline__ bool in_range3(int x, int y, int z, const int *shape)
 
 __global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int batch,
                                    Geometry g, unsigned long long *table, uint32_t mask,
-                                   int32_t *status) {
+                                   int32_t *status, const int32_t *__restrict__ n_dev) {
   int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+  if (j >= live_rows(n, n_dev)) return;
   int4 c = indices[j];
   if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) {
     atomicOr(status, 1);
@@ -101,9 +101,9 @@ __global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int 
 constexpr int kMarkMaxK = 8;
 
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
-                                    uint32_t *bitmap) {
+                                    uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
   int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+  if (j >= live_rows(n, n_dev)) return;
   int4 c = indices[j];
   if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
   const int in[3] = {c.y, c.z, c.w};
@@ -152,9 +152,9 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
 
 // General fallback (a kernel extent above kMarkMaxK): one thread per (input row, kernel offset).
 __global__ void mark_outputs_generic_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
-                                            uint32_t *bitmap) {
+                                            uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= (long long)n * g.K) return;
+  if (t >= (long long)live_rows(n, n_dev) * g.K) return;
   int j = (int)(t / g.K);
   int kappa = (int)(t - (long long)j * g.K);
   int4 c = indices[j];
@@ -366,12 +366,12 @@ static int check_volume(int batch, const int shape[3], const char *what) {
 }
 
 static int build_hash(const int32_t *indices, int n_in, int batch, const Geometry &g, RulebookScratch &s,
-                      int32_t *status, cudaStream_t st) {
+                      int32_t *status, cudaStream_t st, const int32_t *n_in_dev = nullptr) {
   cudaMemsetAsync(s.table, 0xFF, (size_t)s.n_buckets * kBucketSlots * 8, st);
   cudaMemsetAsync(s.misc, 0, 256, st);
   if (n_in > 0) {
     { hash_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.table,
-                                                           s.n_buckets - 1, status ? status : s.misc + 1); note_launches(1); }
+                                                           s.n_buckets - 1, status ? status : s.misc + 1, n_in_dev); note_launches(1); }
   }
   SSC_CHECK_LAUNCH("hash_insert");
   return 0;
@@ -524,7 +524,7 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
                                        const int out_shape[3], const int ksize[3], const int stride[3],
                                        const int padding[3], const int dilation[3], int transpose,
                                        int32_t *n_out_dev, int32_t *status, void *scratch,
-                                       size_t scratch_bytes, void *stream) {
+                                       size_t scratch_bytes, const int32_t *n_in_dev, void *stream) {
   SSC_REQUIRE(n_in >= 0 && in_shape && out_shape && ksize && stride && padding && dilation && n_out_dev,
               "rulebook_conv_count: bad arguments");
   Geometry g;
@@ -537,13 +537,13 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_conv_count: scratch %zu < %zu bytes", scratch_bytes, s.total);
   cudaStream_t st = as_stream(stream);
-  if (int e = build_hash(indices, n_in, batch, g, s, status, st)) return e;
+  if (int e = build_hash(indices, n_in, batch, g, s, status, st, n_in_dev)) return e;
   cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
   if (n_in > 0) {
     if (g.ksize[0] <= kMarkMaxK && g.ksize[1] <= kMarkMaxK && g.ksize[2] <= kMarkMaxK) {
-      { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+      { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
     } else {
-      { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap); note_launches(1); }
+      { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
     }
     SSC_CHECK_LAUNCH("mark_outputs");
   }

@@ -35,7 +35,7 @@ SIGNATURES = {
     "ssc_rulebook_subm_static": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
     "ssc_rulebook_conv_count": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_void_p,
-                                        c_void_p, c_void_p, c_size_t, c_void_p]),
+                                        c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ssc_rulebook_conv_fill": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_pairs_to_nbr": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -53,7 +53,7 @@ SIGNATURES = {
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_global_avgpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_global_maxpool_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "ssc_batch_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_batch_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_voxel2point_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "ssc_voxelize_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "ssc_p2v_scratch_bytes": (c_size_t, [c_int, c_int, _I3]),
@@ -130,7 +130,9 @@ def _p(t, dtype=None):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream or None
+    """Raw handle of torch's current stream on the current device (None = the default stream);
+    the C-level getters cost a fraction of a microsecond, torch.cuda.current_stream() ~15."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()) or None
 
 
 _i3_cache = {}
@@ -204,7 +206,7 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
     n_out_dev = small[K:]
     geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
     _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
-                                     scratch.numel(), _stream()))
+                                     scratch.numel(), None, _stream()))
     n_out = int(n_out_dev.item())  # the one host sync of a regular rulebook
     outids = torch.empty((n_out, 4), dtype=torch.int32, device=dev)
     nbr = torch.empty((K, n_out), dtype=torch.int32, device=dev)
@@ -220,15 +222,16 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
 # then the launches that follow).  A layer can instead size the second phase and its own kernel
 # by a CAPACITY guessed from the output/input ratio this geometry produced before, queue
 # everything, and read the count back once at the end; the count is then checked against the
-# capacity and, if it did not fit, the layer is redone the slow way.  Off unless SSCONV_AHEAD=1.
-AHEAD = os.environ.get("SSCONV_AHEAD", "0") == "1"
+# capacity and, if it did not fit, the layer is redone the slow way.  The layers chain this: a
+# tensor with a pending count can feed the next layer (sp_ops/tensor.py), so the host reads counts
+# back only where somebody looks at a result.  SSCONV_AHEAD=0 turns it off.
+AHEAD = os.environ.get("SSCONV_AHEAD", "1") != "0"
 AHEAD_MARGIN = 1.10
 _ratio_hint = {}
 
 
 def _geometry_key(spatial_shape, ksize, stride, padding, dilation, transpose):
-    return (tuple(int(v) for v in spatial_shape), tuple(int(v) for v in ksize), tuple(int(v) for v in stride),
-            tuple(int(v) for v in padding), tuple(int(v) for v in dilation), int(bool(transpose)))
+    return (tuple(spatial_shape), tuple(ksize), tuple(stride), tuple(padding), tuple(dilation), bool(transpose))
 
 
 def _note_ratio(key, n_in, n_out):
@@ -240,11 +243,14 @@ def _note_ratio(key, n_in, n_out):
             _ratio_hint[key] = r
 
 
-def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation, transpose):
+def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation, transpose,
+                           n_in_dev=None):
     """Regular rulebook whose output count stays on the device: returns [outids_cap [cap,4],
     LazyPairs (pending, capacity cap), indice_num] or None when no capacity can be guessed yet
     (first call for this geometry) or the feature is off.  The caller runs its kernel with
-    n_out = pairs.capacity, then calls pairs.resolve()."""
+    n_out = pairs.capacity and reads the count back later (pairs.resolve()).  n_in_dev: device
+    word with the exact number of input rows when `indices` itself is only filled up to a count
+    that has not been read back yet (its length is then a capacity)."""
     if not AHEAD:
         return None
     key = _geometry_key(spatial_shape, ksize, stride, padding, dilation, transpose)
@@ -273,12 +279,12 @@ def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize,
     st = status_word(dev)
     geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
     _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
-                                     sbytes, _stream()))
+                                     sbytes, _p(n_in_dev), _stream()))
     outids = torch.empty((cap, 4), dtype=torch.int32, device=dev)
     nbr = torch.empty((K, cap), dtype=torch.int32, device=dev)
     _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, cap, _p(outids), _p(nbr), None, _p(num),
                                     _p(st), _p(scratch), sbytes, _p(n_out_dev), _stream()))
-    return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=key), num]
+    return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=None if n_in_dev is not None else key), num]
 
 
 def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
@@ -573,11 +579,12 @@ global_avgpool_bp = _not_built("global_avgpool_bp")
 global_maxpool_bp = _not_built("global_maxpool_bp")
 
 
-def batch_offsets(indices, batch_size):
-    """Row offsets [B+1] (int32, on device) of the samples of an indices tensor, no host sync."""
+def batch_offsets(indices, batch_size, n_dev=None):
+    """Row offsets [B+1] (int32, on device) of the samples of an indices tensor, no host sync.
+    n_dev: device word with the exact row count when the tensor's length is only a capacity."""
     off = torch.empty(int(batch_size) + 1, dtype=torch.int32, device=indices.device)
     _check(lib().ssc_batch_offsets(_p(indices.contiguous(), torch.int32), indices.shape[0], int(batch_size), _p(off),
-                                   _stream()))
+                                   _p(n_dev), _stream()))
     return off
 
 

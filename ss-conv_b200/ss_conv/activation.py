@@ -102,7 +102,9 @@ class Activation(nn.Module):
     def forward(self, input):
         if self.scalar_act is None and self.gate_act is None:
             return input
-        input.features = self._gate(input.features)
+        input.features = self._gate(input.raw()[0])   # row-wise: fine on a pending row count
+        if input.pending():
+            input._rows.post.append(self._gate)
         return input
 
     def _gate(self, y, scale=None, shift=None):

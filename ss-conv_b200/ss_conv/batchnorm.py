@@ -72,7 +72,8 @@ class BatchNorm(nn.Module):
         return _ext.bn_fold(mean, var, w, b, field, scalar, self.eps)
 
     def forward(self, input):
-        x = input.features
+        # eval mode works row by row, so it can run on a tensor whose row count is still pending
+        x = input.features if self.training else input.raw()[0]
         field, scalar = self._device_tables(x.device)
         if field.numel() != x.size(1):
             raise AssertionError("`ix` should have reached features.size(1) ({}), but it ended at {}".format(
@@ -87,5 +88,11 @@ class BatchNorm(nn.Module):
                 self.running_var.mul_(1 - self.momentum).add_(self.momentum * var)
         else:
             scale, shift = self.folded_affine(x.device)
-        input.features = _ext.bn_gate_forward(x, scale, shift, None, x.size(1), 0, 0, 0, None, None)
+
+        def apply(f):
+            return _ext.bn_gate_forward(f, scale, shift, None, f.size(1), 0, 0, 0, None, None)
+
+        input.features = apply(x)
+        if input.pending():
+            input._rows.post.append(apply)
         return input

@@ -46,7 +46,7 @@ class Convolution(SparseConvolution):
 
     def forward(self, input):
         assert isinstance(input, SparseTensor)
-        device = input.features.device
+        device = input.raw()[0].device
         if self.kernel.weight.device != device:
             self.kernel.to(device)
         if self.training:

@@ -23,6 +23,12 @@ class _GlobalPool(nn.Module):
 
     def forward(self, inputs, offsets=None):
         if isinstance(inputs, SparseTensor):
+            if inputs.pending() and offsets is None:
+                # queue the pooling on the rows as they are, then read the pending counts back;
+                # only a tensor that had to be recomputed is pooled again
+                out = type(self).func(inputs.raw()[0], inputs.get_offsets().detach())
+                if not inputs.resolve():
+                    return out
             feats = inputs.features
             offsets = inputs.get_offsets() if offsets is None else offsets
         else:

@@ -6,7 +6,7 @@ import torch
 import torch.nn as nn
 from torch.nn.parameter import Parameter
 
-from .tensor import SparseTensor
+from .tensor import PendingRows, SparseTensor
 from .ops import get_conv_output_size, get_deconv_output_size, get_indice_pairs, _per_dim
 from .. import _ext
 from .functional import indice_conv, indice_inverse_conv, indice_subm_conv
@@ -62,8 +62,41 @@ class SparseConvolution(nn.Module):
     def _sparse_conv(self, input, weight):
         """weight: [kx, ky, kz, Cin, Cout].  Rulebooks are cached in input.indice_dict under
         indice_key; an inverse convolution reuses its partner's rulebook with the pair roles
-        exchanged."""
+        exchanged.
+
+        A regular (strided / transposed) convolution without an indice_key can run ahead of its
+        output count: rulebook and convolution are queued with a guessed row capacity (also on
+        an input whose own count is still pending) and the result is a SparseTensor with pending
+        rows; see sp_ops/tensor.py."""
         assert isinstance(input, SparseTensor)
+        out_spatial_shape = self._output_shape(input.spatial_shape)
+        feats_raw, inds_raw, n_in_dev = input.raw()
+        if (_ext.AHEAD and not self.conv1x1 and not self.subm and not self.inverse and self.indice_key is None
+                and feats_raw.is_cuda and feats_raw.dtype == torch.float32):
+            ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_spatial_shape,
+                                                list(input.spatial_shape), self.kernel_size, self.stride,
+                                                self.padding, self.dilation, int(self.transposed), n_in_dev=n_in_dev)
+            if ahead is not None:
+                outids_cap, pairs, pair_num = ahead
+                out_cap = indice_conv(feats_raw, weight, pairs, pair_num, pairs.capacity)
+                if self.bias is not None:
+                    out_cap += self.bias
+                out = SparseTensor(out_cap, outids_cap, out_spatial_shape, input.batch_size)
+                out.indice_dict = input.indice_dict
+                out.grid = input.grid
+                key = _ext._geometry_key(input.spatial_shape, self.kernel_size, self.stride, self.padding,
+                                         self.dilation, self.transposed)
+
+                def redo():
+                    t = self._sparse_conv_exact(input, weight)
+                    return t.features, t.indices
+
+                out._rows = PendingRows(pairs._n_out_dev, pairs.capacity, input if input.pending() else None, redo,
+                                        lambda n: _ext._note_ratio(key, input.features.shape[0], n))
+                return out
+        return self._sparse_conv_exact(input, weight)
+
+    def _sparse_conv_exact(self, input, weight):
         features, indices = input.features, input.indices
         spatial_shape, batch_size = input.spatial_shape, input.batch_size
         out_spatial_shape = self._output_shape(spatial_shape)
@@ -83,33 +116,13 @@ class SparseConvolution(nn.Module):
         elif self.indice_key is not None and cached is not None:
             outids, _, indice_pairs, indice_pair_num, _ = cached
         else:
-            out_features = None
-            ahead = None
-            if not self.subm and features.dtype == torch.float32:
-                ahead = _ext.get_indice_pairs_ahead(indices, batch_size, out_spatial_shape, list(spatial_shape),
-                                                    self.kernel_size, self.stride, self.padding, self.dilation,
-                                                    int(self.transposed))
-            if ahead is not None:
-                # rulebook and convolution are queued with a guessed capacity; the output count is
-                # read back once, after the convolution has been launched
-                outids_cap, indice_pairs, indice_pair_num = ahead
-                out_cap = indice_conv(features, weight, indice_pairs, indice_pair_num, indice_pairs.capacity)
-                n_out = indice_pairs.resolve()
-                if n_out is not None:
-                    outids, out_features = outids_cap[:n_out], out_cap[:n_out]
-            if out_features is None:
-                outids, indice_pairs, indice_pair_num = get_indice_pairs(
-                    indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
-                    self.output_padding, self.subm, self.transposed, grid=input.grid, lazy=True)
+            outids, indice_pairs, indice_pair_num = get_indice_pairs(
+                indices, batch_size, spatial_shape, self.kernel_size, self.stride, self.padding, self.dilation,
+                self.output_padding, self.subm, self.transposed, grid=input.grid, lazy=True)
             input.indice_dict[self.indice_key] = (outids, indices, indice_pairs, indice_pair_num, spatial_shape)
-            if out_features is not None:
-                return self._finish(input, out_features, outids, out_spatial_shape, batch_size)
 
         op = indice_subm_conv if self.subm else (indice_inverse_conv if self.inverse else indice_conv)
         out_features = op(features, weight, indice_pairs, indice_pair_num, outids.shape[0])
-        return self._finish(input, out_features, outids, out_spatial_shape, batch_size)
-
-    def _finish(self, input, out_features, outids, out_spatial_shape, batch_size):
         if self.bias is not None:
             out_features += self.bias
         out = SparseTensor(out_features, outids, out_spatial_shape, batch_size)

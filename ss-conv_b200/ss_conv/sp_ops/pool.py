@@ -1,8 +1,9 @@
 """Sparse average / max pooling modules (interface of SS_Conv_lib/ss_conv/sp_ops/pool.py)."""
+import torch
 import torch.nn as nn
 
 from .. import _ext
-from .tensor import SparseTensor
+from .tensor import PendingRows, SparseTensor
 from .ops import get_conv_output_size, get_indice_pairs, _per_dim
 from .functional import indice_avgpool, indice_maxpool
 
@@ -20,25 +21,38 @@ class _SparsePool(nn.Module):
         self.subm = subm
 
     def forward(self, input):
-        """A fresh (never cached) regular-convolution rulebook, then one pooling launch."""
+        """A fresh (never cached) regular-convolution rulebook, then one pooling launch.  Like a
+        strided convolution it can run ahead of its output count (sp_ops/tensor.py)."""
         assert isinstance(input, SparseTensor)
         shape = input.spatial_shape
         out_shape = shape if self.subm else get_conv_output_size(shape, self.kernel_size, self.stride, self.padding,
                                                                  self.dilation)
-        feats = None
-        ahead = None if self.subm else _ext.get_indice_pairs_ahead(input.indices, input.batch_size, out_shape, list(shape),
-                                                                   self.kernel_size, self.stride, self.padding,
-                                                                   self.dilation, 0)
-        if ahead is not None:  # rulebook and pooling queued with a guessed capacity, count read back last
-            outids_cap, pairs, pair_num = ahead
-            feats_cap = type(self)._op(input.features, pairs, pair_num, pairs.capacity)
-            n_out = pairs.resolve()
-            if n_out is not None:
-                outids, feats = outids_cap[:n_out], feats_cap[:n_out]
-        if feats is None:
-            outids, pairs, pair_num = get_indice_pairs(input.indices, input.batch_size, shape, self.kernel_size,
-                                                       self.stride, self.padding, self.dilation, 0, self.subm, lazy=True)
-            feats = type(self)._op(input.features, pairs, pair_num, outids.shape[0])
+        feats_raw, inds_raw, n_in_dev = input.raw()
+        if _ext.AHEAD and not self.subm and feats_raw.is_cuda and feats_raw.dtype == torch.float32:
+            ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_shape, list(shape), self.kernel_size,
+                                                self.stride, self.padding, self.dilation, 0, n_in_dev=n_in_dev)
+            if ahead is not None:
+                outids_cap, pairs, pair_num = ahead
+                feats_cap = type(self)._op(feats_raw, pairs, pair_num, pairs.capacity)
+                out = SparseTensor(feats_cap, outids_cap, out_shape, input.batch_size)
+                out.indice_dict = input.indice_dict
+                out.grid = input.grid
+                key = _ext._geometry_key(shape, self.kernel_size, self.stride, self.padding, self.dilation, 0)
+
+                def redo():
+                    t = self._forward_exact(input, out_shape)
+                    return t.features, t.indices
+
+                out._rows = PendingRows(pairs._n_out_dev, pairs.capacity, input if input.pending() else None, redo,
+                                        lambda n: _ext._note_ratio(key, input.features.shape[0], n))
+                return out
+        return self._forward_exact(input, out_shape)
+
+    def _forward_exact(self, input, out_shape):
+        outids, pairs, pair_num = get_indice_pairs(input.indices, input.batch_size, input.spatial_shape,
+                                                   self.kernel_size, self.stride, self.padding, self.dilation, 0,
+                                                   self.subm, lazy=True)
+        feats = type(self)._op(input.features, pairs, pair_num, outids.shape[0])
         out = SparseTensor(feats, outids, out_shape, input.batch_size)
         out.indice_dict = input.indice_dict
         out.grid = input.grid

@@ -14,18 +14,88 @@ def scatter_nd(indices, updates, shape):
     return ret
 
 
+class PendingRows(object):
+    """Row set of a SparseTensor whose size is still on the device.
+
+    A layer that ran ahead of its output count (see _ext.get_indice_pairs_ahead) hands out tensors
+    whose `features` / `indices` buffers have `capacity` rows of which only the first n are
+    meaningful, n being the device word `n_dev`.  Layers that understand this keep queueing
+    kernels on the buffers (`SparseTensor.raw()`); anything else that looks at `.features` or
+    `.indices` triggers `SparseTensor.resolve()`: the chain of counts is read back (parents
+    first), and a tensor whose guessed capacity was too small, or whose parent had to be
+    recomputed, is recomputed exactly by `redo` (its producer's exact path) followed by the
+    row-wise operations applied to it since (`post`)."""
+
+    __slots__ = ("n_dev", "capacity", "parent", "redo", "post", "note", "grad")
+
+    def __init__(self, n_dev, capacity, parent, redo, note=None):
+        self.n_dev, self.capacity, self.parent, self.redo, self.note = n_dev, int(capacity), parent, redo, note
+        self.post = []
+        self.grad = torch.is_grad_enabled()   # a recomputation runs in the mode the layer was called in
+
+
 class SparseTensor(object):
     """features [N,C] float32, indices [N,4] int32 rows (batch,x,y,z), the dense spatial shape,
     the batch size, and `indice_dict`, the per-key rulebook cache shared along a network:
     key -> (outids, indices, indice_pairs, indice_pair_num, spatial_shape)."""
 
     def __init__(self, features, indices, spatial_shape, batch_size, grid=None):
-        self.features = features
-        self.indices = indices if indices.dtype == torch.int32 else indices.int()
+        self._features = features
+        self._indices = indices if indices.dtype == torch.int32 else indices.int()
+        self._rows = None
         self.spatial_shape = spatial_shape
         self.batch_size = batch_size
         self.indice_dict = {}
         self.grid = grid
+
+    # -- features / indices resolve a pending row count on first access ---------------------
+    @property
+    def features(self):
+        if self._rows is not None:
+            self.resolve()
+        return self._features
+
+    @features.setter
+    def features(self, value):
+        self._features = value
+
+    @property
+    def indices(self):
+        if self._rows is not None:
+            self.resolve()
+        return self._indices
+
+    @indices.setter
+    def indices(self, value):
+        self._indices = value if value.dtype == torch.int32 else value.int()
+
+    def pending(self):
+        return self._rows is not None
+
+    def raw(self):
+        """(features, indices, n_dev): the buffers as they are; n_dev is None for an exact tensor,
+        else the device word with the number of meaningful rows."""
+        return self._features, self._indices, (self._rows.n_dev if self._rows is not None else None)
+
+    def resolve(self):
+        """Make the tensor exact.  Returns True when its contents had to be recomputed."""
+        r = self._rows
+        if r is None:
+            return False
+        parent_changed = r.parent.resolve() if r.parent is not None else False
+        n = int(r.n_dev.item())
+        if r.note is not None:
+            r.note(n)
+        self._rows = None
+        if not parent_changed and n <= r.capacity:
+            self._features, self._indices = self._features[:n], self._indices[:n]
+            return False
+        with torch.set_grad_enabled(r.grad):
+            feats, inds = r.redo()
+            for fn in r.post:
+                feats = fn(feats)
+        self._features, self._indices = feats, inds
+        return True
 
     @property
     def spatial_size(self):
@@ -47,8 +117,9 @@ class SparseTensor(object):
     def get_offsets(self):
         """Row offsets [B+1] (int32) of the samples, computed on the device without host syncs
         (the reference loops over the batch with .item(), tensor.py:59-65)."""
-        if self.indices.is_cuda:
-            return _ext.batch_offsets(self.indices, self.batch_size)
+        if self._indices.is_cuda:
+            _, inds, n_dev = self.raw()
+            return _ext.batch_offsets(inds, self.batch_size, n_dev)
         counts = torch.bincount(self.indices[:, 0].long(), minlength=self.batch_size)
         return torch.cat([counts.new_zeros(1), counts.cumsum(0)]).int()
 

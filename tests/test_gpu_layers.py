@@ -196,3 +196,64 @@ def test_layers_that_run_ahead_of_the_output_count(cuda, monkeypatch):
     for got in (first, ahead, redone, again):
         np.testing.assert_array_equal(got[1], exact[1])
         np.testing.assert_array_equal(got[0], exact[0])
+
+
+def test_pending_row_counts_chain_through_a_network(cuda, monkeypatch):
+    """conv -> BN -> gate -> conv -> BN -> gate -> max pool -> global pool with every row count left
+    on the device until the end equals the same network run layer by layer with exact counts,
+    also after a capacity overflow in the middle of the chain."""
+    from ss_conv import _ext
+    from ss_conv.activation import Activation
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.convolution import Convolution
+    from ss_conv.pool import GlobalAvgPool, MaxPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(9)
+    Rs = [[(2, 0), (1, 1)], [(4, 0), (2, 1)], [(4, 0), (2, 1), (1, 2)]]
+
+    def gated(rs):
+        return rs + [(sum(m for m, l in rs if l > 0), 0)]
+
+    layers = []
+    for a, b in zip(Rs[:-1], Rs[1:]):
+        conv = Convolution(a, gated(b), 3, stride=2, padding=1).to(cuda).eval()
+        bn = BatchNorm(gated(b)).to(cuda).eval()
+        with torch.no_grad():
+            bn.running_var.uniform_(0.5, 1.5)
+            bn.running_mean.normal_(0, 0.1)
+        layers.append((conv, bn, Activation(b, (torch.relu, torch.sigmoid), bias=False, checkpoint=False)))
+    pool, gpool = MaxPool(2, stride=2), GlobalAvgPool()
+    ind = S.bernoulli_voxels(range(4), 24, 0.2, base_seed=21)
+    feats = S.features(ind.shape[0], 5, 8)
+
+    def run(check_pending):
+        with torch.no_grad():
+            x = SparseTensor(dev(feats, cuda), dev(ind, cuda), [24] * 3, 4)
+            for conv, bn, act in layers:
+                x = act(bn(conv(x)))
+            x = pool(x)
+            assert x.pending() == check_pending
+            pooled = gpool(x)
+            assert not x.pending()
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+        return pooled.cpu().numpy(), x.features.cpu().numpy(), x.indices.cpu().numpy()
+
+    _ext.set_precision("fp32")
+    try:
+        monkeypatch.setattr(_ext, "AHEAD", False)
+        exact = run(False)
+        monkeypatch.setattr(_ext, "AHEAD", True)
+        _ext._ratio_hint.clear()
+        first = run(False)                 # records the ratios layer by layer
+        chained = run(True)
+        keys = sorted(_ext._ratio_hint)
+        _ext._ratio_hint[keys[1]] = 1e-3   # one layer in the middle will overflow
+        overflowed = run(True)
+        again = run(True)
+    finally:
+        _ext.set_precision("auto")
+    for got in (first, chained, overflowed, again):
+        for g, e in zip(got, exact):
+            np.testing.assert_array_equal(g, e)
