@@ -207,6 +207,34 @@ def indice_conv_f64(features, filters, pairs, num, num_act_out, inverse=False):
     return out
 
 
+def indice_conv_backward(features, filters, out_grad, pairs, num, inverse=False, subm=False, dtype=np.float32):
+    """SS_Conv_lib/src/conv/indice_conv.h:344-426 (indiceConvBackward<float>): per kernel offset
+    filtersGrad[kappa] = gathered(features)^T . gathered(outGrad) (:411) and the rows
+    gathered(outGrad) . filters[kappa]^T are scatter-added into inputGrad (:412-424); the
+    submanifold centre is two dense products (:373-377).  dtype=np.float64 gives the error-free
+    yardstick for tolerance tests.  Returns (inputGrad [N,Cin], filtersGrad [K,Cin,Cout])."""
+    features = np.asarray(features, dtype=dtype)
+    out_grad = np.asarray(out_grad, dtype=dtype)
+    flt = np.asarray(filters, dtype=dtype).reshape(-1, features.shape[1], np.shape(filters)[-1])
+    K = pairs.shape[0]
+    d_in = np.zeros_like(features)
+    d_flt = np.zeros_like(flt)
+    centre = int(np.argmax(num)) if K else 0
+    if subm:
+        d_flt[centre] = features.T @ out_grad
+        d_in += out_grad @ flt[centre].T
+    a, b = (1, 0) if inverse else (0, 1)
+    for kappa in range(K):
+        c = int(num[kappa])
+        if c <= 0 or (subm and kappa == centre):
+            continue
+        fin = features[pairs[kappa, a, :c]]
+        gout = out_grad[pairs[kappa, b, :c]]
+        d_flt[kappa] = fin.T @ gout
+        np.add.at(d_in, pairs[kappa, a, :c], gout @ flt[kappa].T)
+    return d_in, d_flt
+
+
 # ------------------------------------------------------------------------------- pooling
 def indice_maxpool(features, pairs, num, num_act):
     """SS_Conv_lib/src/pool/indice_maxpool.h:15-50 + indice_maxpool_cpp_functor.cpp:16-40:
@@ -218,6 +246,58 @@ def indice_maxpool(features, pairs, num, num_act):
         if c > 0:
             np.maximum.at(out, pairs[kappa, 1, :c], features[pairs[kappa, 0, :c]])
     return out
+
+
+def indice_maxpool_backward(features, out_features, out_grad, pairs, num):
+    """SS_Conv_lib/src/pool/indice_maxpool_cpp_functor.cpp:65-86: for every pair and channel,
+    din[i] += dout[o] where the input value equals the pooled value (ties all receive it)."""
+    features = np.asarray(features, dtype=np.float32)
+    d_in = np.zeros_like(features)
+    for kappa in range(pairs.shape[0]):
+        c = int(num[kappa])
+        if c <= 0:
+            continue
+        i, o = pairs[kappa, 0, :c], pairs[kappa, 1, :c]
+        np.add.at(d_in, i, np.where(out_features[o] == features[i], out_grad[o], np.float32(0)).astype(np.float32))
+    return d_in
+
+
+def indice_avgpool_backward(features, out_grad, pairs, num, summaryrf):
+    """SS_Conv_lib/src/pool/indice_avgpool_cuda_functor.cu:175-205 (the reference has no CPU
+    path, indice_avgpool.h:70-79): din[i] += dout[o] / rf[o] per pair, offsets ascending."""
+    features = np.asarray(features, dtype=np.float32)
+    d_in = np.zeros_like(features)
+    rf = np.asarray(summaryrf).astype(np.float32)
+    for kappa in range(pairs.shape[0]):
+        c = int(num[kappa])
+        if c <= 0:
+            continue
+        i, o = pairs[kappa, 0, :c], pairs[kappa, 1, :c]
+        np.add.at(d_in, i, (out_grad[o] / rf[o][:, None]).astype(np.float32))
+    return d_in
+
+
+def global_avgpool_backward(d_out, offsets, n):
+    """SS_Conv_lib/src/pool/global_avgpool_cuda_kernel.cu:45-59: every row of sample s receives
+    d_out[s] / len(s)."""
+    d_out = np.asarray(d_out, dtype=np.float32)
+    d = np.zeros((n, d_out.shape[1]), dtype=np.float32)
+    for s in range(len(offsets) - 1):
+        lo, hi = int(offsets[s]), int(offsets[s + 1])
+        if hi > lo:
+            d[lo:hi] = d_out[s] / np.float32(hi - lo)
+    return d
+
+
+def global_maxpool_backward(d_out, maxidx, n):
+    """SS_Conv_lib/src/pool/global_maxpool_cuda_kernel.cu:46-55: d_feats[argmax row, c] += d_out[s, c]."""
+    d_out = np.asarray(d_out, dtype=np.float32)
+    d = np.zeros((n, d_out.shape[1]), dtype=np.float32)
+    for s in range(d_out.shape[0]):
+        for c in range(d_out.shape[1]):
+            if maxidx[s, c] >= 0:
+                d[maxidx[s, c], c] += d_out[s, c]
+    return d
 
 
 def summary_rf(pairs, num, num_act):

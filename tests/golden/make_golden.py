@@ -197,6 +197,33 @@ def main():
             out["maxpool_out_features"] = z.features.numpy().copy()
             out["maxpool_out_indices"] = z.indices.numpy().copy()
 
+    # ---- backward of the C++ CPU path: indiceConvBackward (indice_conv.h:344-426) and
+    #      indiceMaxPoolBackward (indice_maxpool.h:94-127) on a strided and a submanifold rulebook
+    brng = np.random.RandomState(4711)
+    bind = surface_indices(brng, 2, 10, 150)
+    out["bw_indices"] = bind
+    for tag, (k, s, p, subm) in (("bw_strided", (3, 2, 1, 0)), ("bw_subm", (3, 1, 1, 1))):
+        V, ci, co = 10, 6, 5
+        osz = [V] * 3 if subm else [(V + 2 * p - (k - 1) - 1) // s + 1] * 3
+        o, pr, nm = ext.get_indice_pairs_3d(torch.from_numpy(bind), 2, osz, [V] * 3, [k] * 3, [s] * 3, [p] * 3,
+                                            [1] * 3, [0] * 3, subm, 0)
+        feats = brng.randn(bind.shape[0], ci).astype(np.float32)
+        W = (brng.randn(k, k, k, ci, co) / np.sqrt(ci * k ** 3)).astype(np.float32)
+        dout = brng.randn(o.shape[0], co).astype(np.float32)
+        din, dW = ext.indice_conv_backward_fp32(torch.from_numpy(feats), torch.from_numpy(W), torch.from_numpy(dout),
+                                                pr, nm, 0, subm)
+        out[tag + "_geom"] = np.array([k, s, p, subm], dtype=np.int32)
+        out[tag + "_features"], out[tag + "_filters"], out[tag + "_dout"] = feats, W, dout
+        out[tag + "_din"], out[tag + "_dfilters"] = din.numpy().copy(), dW.numpy().copy()
+        out[tag + "_outids"], out[tag + "_pairs"], out[tag + "_num"] = o.numpy().copy(), pr.numpy().copy(), nm.numpy().copy()
+        if not subm:
+            pf = np.maximum(feats, 0).round(1)          # ties between inputs and a zero floor are exercised
+            y = ext.indice_maxpool_fp32(torch.from_numpy(pf), pr, nm, o.shape[0])
+            dy = brng.randn(o.shape[0], ci).astype(np.float32)
+            dp = ext.indice_maxpool_backward_fp32(torch.from_numpy(pf), y, torch.from_numpy(dy), pr, nm)
+            out["bw_pool_features"], out["bw_pool_out"], out["bw_pool_dout"] = pf, y.numpy().copy(), dy
+            out["bw_pool_din"] = dp.numpy().copy()
+
     # ---- Wigner-D / Q_J values the basis is built from (stand-in convention)
     out["irr_repr_l2"] = SO3.irr_repr(2, 0.3, 1.1, -2.0, dtype=torch.float64).numpy()
     out["Q_J_1_1_1"] = kernel.basis_transformation_Q_J(1, 1, 1).numpy() if hasattr(kernel, "basis_transformation_Q_J") \

@@ -2,6 +2,7 @@
 (tests/golden/make_golden.py): rulebooks bit-exact including order, floating point within
 the tolerance written at each check."""
 import numpy as np
+import pytest
 
 import ssconv_oracle as O
 
@@ -133,3 +134,26 @@ def test_transposed_rulebook_matches_reference(golden):
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[2], b[2])
         for x, y in zip(a[1], b[1]):
             assert np.array_equal(x, y)
+
+
+@pytest.mark.parametrize("tag", ["bw_strided", "bw_subm"])
+def test_conv_backward_matches_reference(golden, tag):
+    """indiceConvBackward<float> of the compiled reference (CPU) vs the restatement."""
+    k, s, p, subm = (int(v) for v in golden[tag + "_geom"])
+    d_in, d_flt = O.indice_conv_backward(golden[tag + "_features"], golden[tag + "_filters"], golden[tag + "_dout"],
+                                         golden[tag + "_pairs"], golden[tag + "_num"], False, bool(subm))
+    ref_in, ref_flt = golden[tag + "_din"], golden[tag + "_dfilters"].reshape(d_flt.shape)
+    assert np.abs(d_in - ref_in).max() <= 2e-6 * max(1.0, np.abs(ref_in).max())
+    assert np.abs(d_flt - ref_flt).max() <= 2e-6 * max(1.0, np.abs(ref_flt).max())
+    # and the rulebook the fixture was made with is the one the oracle builds
+    o, pr, nm = O.get_indice_pairs(golden["bw_indices"], 2, [10] * 3, k, s, p, 1, bool(subm))
+    np.testing.assert_array_equal(nm, golden[tag + "_num"])
+
+
+def test_maxpool_backward_matches_reference(golden):
+    d = O.indice_maxpool_backward(golden["bw_pool_features"], golden["bw_pool_out"], golden["bw_pool_dout"],
+                                  golden["bw_strided_pairs"], golden["bw_strided_num"])
+    np.testing.assert_array_equal(d, golden["bw_pool_din"])
+    y = O.indice_maxpool(golden["bw_pool_features"], golden["bw_strided_pairs"], golden["bw_strided_num"],
+                         golden["bw_pool_out"].shape[0])
+    np.testing.assert_array_equal(y, golden["bw_pool_out"])
