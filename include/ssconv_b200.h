@@ -208,6 +208,37 @@ int ssc_global_maxpool_fwd(const float *feats, const int32_t *offsets, int n_sam
 int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets, const int32_t *n_dev,
                       void *stream);
 
+/* ------------------------------------------------------------------------------- backward
+ * Replace indiceConvBackward<float> (SS_Conv_lib/src/conv/indice_conv.h:344-426),
+ * indiceMaxPoolBackward / indiceAvgPoolBackward (SS_Conv_lib/src/pool/indice_maxpool.h:94-127,
+ * SS_Conv_lib/src/pool/indice_avgpool.h:54-90) and global_avgpool_bp / global_maxpool_bp
+ * (SS_Conv_lib/src/pool/global_avgpool_cuda_kernel.cu:45-65,
+ *  SS_Conv_lib/src/pool/global_maxpool_cuda_kernel.cu:46-61).
+ *
+ * ssc_nbr_transpose: input-major table nbr_in[kappa][i] = o from the output-major nbr[kappa][o] = i
+ * (each (offset, input row) has at most one output row).  With it
+ *   input gradient  = ssc_conv_fwd(out_grad, filters transposed to [K,Cout,Cin], nbr_in, n_in)
+ * (the reference's gather -> mm(filters^T) -> scatter-add loop, :412-424), and the pool
+ * gradients below need no atomics.
+ * ssc_conv_wgrad: d_filters[kappa] = sum_o features[nbr[kappa][o]]^T . out_grad[o]  ([K,Cin,Cout],
+ * the reference's mm(inputBuffer^T, outputBuffer), :411), exact fp32, bitwise repeatable.
+ * ssc_maxpool_bwd: d_in[i,c] = sum over outputs o of i with out[o,c] == in[i,c] of out_grad[o,c]
+ * (indice_maxpool_cpp_functor.cpp:78-84); ssc_avgpool_bwd: d_in[i] = sum_o out_grad[o] / rf[o]
+ * (rf NULL: / K; indice_avgpool_cuda_functor.cu:195-205), both in ascending offset order. */
+int ssc_nbr_transpose(const int32_t *nbr, int K, int n_out, int n_in, int32_t *nbr_in, void *stream);
+size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n_out);
+int ssc_conv_wgrad(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr,
+                   int K, int n_out, float *d_filters, void *scratch, size_t scratch_bytes, void *stream);
+int ssc_maxpool_bwd(const float *features, const float *out_features, const float *out_grad, int c,
+                    const int32_t *nbr_in, int K, int n_in, float *d_in, void *stream);
+int ssc_avgpool_bwd(const float *out_grad, int c, const int32_t *nbr_in, int K, int n_in,
+                    const int32_t *summaryrf, float *d_in, void *stream);
+/* d_feats [n_rows, C] is written completely (rows outside every sample range get zero). */
+int ssc_global_avgpool_bwd(const float *d_out, const int32_t *offsets, int n_samples, int c, int n_rows,
+                           float *d_feats, void *stream);
+int ssc_global_maxpool_bwd(const float *d_out, const int32_t *maxidx, int n_samples, int c, int n_rows,
+                           float *d_feats, void *stream);
+
 /* ---------------------------------------------------------------------------- voxelization
  * ssc_voxel2point_map replaces voxel2point_fp (SS_Conv_lib/src/voxelize/voxel2point_cuda_kernel.cu:16-42):
  * maps [M, max_active+1] pre-initialised by the caller as in

@@ -48,6 +48,14 @@ SIGNATURES = {
     "ssc_conv_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                              c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ssc_nbr_transpose": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_conv_wgrad_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "ssc_conv_wgrad": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t,
+                               c_void_p]),
+    "ssc_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_avgpool_bwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ssc_global_avgpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_global_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -517,14 +525,51 @@ def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, i
 
 def _not_built(name):
     def f(*a, **k):
-        raise NotImplementedError(name + " is not built: this library covers the forward (inference) path; "
-                                  "fp16 storage and the backward kernels are listed as next steps")
+        raise NotImplementedError(name + " is not built: this library covers the fp32 forward and backward path; "
+                                  "fp16 storage, the field max pool and the voxelizer's backward are not part of it")
     f.__name__ = name
     return f
 
 
+def input_major_table(nbr, n_in):
+    """nbr_in [K, n_in]: for every (offset, input row) the output row it contributes to, or -1."""
+    K, n_out = nbr.shape
+    nbr_in = torch.empty((K, int(n_in)), dtype=torch.int32, device=nbr.device)
+    _check(lib().ssc_nbr_transpose(_p(nbr, torch.int32), K, n_out, int(n_in), _p(nbr_in), _stream()))
+    return nbr_in
+
+
+def conv_wgrad(features, out_grad, nbr):
+    """d_filters [K, Cin, Cout] = sum over output rows of gathered input rows (outer) out_grad rows."""
+    K, n_out = nbr.shape
+    c_in, c_out = features.shape[1], out_grad.shape[1]
+    d_flt = torch.empty((K, c_in, c_out), dtype=torch.float32, device=features.device)
+    nbytes = int(lib().ssc_conv_wgrad_scratch_bytes(K, c_in, c_out, n_out))
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=features.device)
+    _check(lib().ssc_conv_wgrad(_p(features, torch.float32), c_in, _p(out_grad, torch.float32), c_out,
+                                _p(nbr, torch.int32), K, n_out, _p(d_flt), _p(scratch), nbytes, _stream()))
+    return d_flt
+
+
+def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_num, inverse, subm):
+    """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:46-48): [input_grad, filters_grad].
+    The input gradient is the forward gather-GEMM over the input-major table with the filters
+    transposed (operand precision as set for the forward pass); the filter gradient is exact
+    fp32.  The submanifold centre needs no special case."""
+    if features.dtype != torch.float32:
+        raise TypeError("indice_conv_backward_fp32 expects float32 features")
+    features, out_bp = features.contiguous(), out_bp.contiguous()
+    c_in, c_out = filters.shape[-2], filters.shape[-1]
+    flt = filters.reshape(-1, c_in, c_out)
+    n_in, n_out = features.shape[0], out_bp.shape[0]
+    nbr = neighbour_table(indice_pairs, indice_num, n_out, bool(inverse))
+    nbr_in = input_major_table(nbr, n_in)
+    d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in)
+    d_flt = conv_wgrad(features, out_bp, nbr)
+    return [d_in, d_flt.reshape(filters.shape)]
+
+
 indice_conv_half = _not_built("indice_conv_half")
-indice_conv_backward_fp32 = _not_built("indice_conv_backward_fp32")
 indice_conv_backward_half = _not_built("indice_conv_backward_half")
 
 
@@ -557,9 +602,28 @@ def indiceSummaryRF(indice_pairs, indice_num, num_act):
 
 indice_maxpool_half = _not_built("indice_maxpool_half")
 indice_avgpool_half = _not_built("indice_avgpool_half")
-indice_maxpool_backward_fp32 = _not_built("indice_maxpool_backward_fp32")
+def indice_maxpool_backward_fp32(features, out_features, out_bp, indice_pairs, indice_num):
+    """(SS_Conv_lib/src/ss_conv_ops.h:58-59) gradient to every input that equals its pooled value."""
+    features, out_features, out_bp = features.contiguous(), out_features.contiguous(), out_bp.contiguous()
+    nbr_in = input_major_table(neighbour_table(indice_pairs, indice_num, out_features.shape[0]), features.shape[0])
+    d_in = torch.empty_like(features)
+    _check(lib().ssc_maxpool_bwd(_p(features, torch.float32), _p(out_features, torch.float32), _p(out_bp, torch.float32),
+                                 features.shape[1], _p(nbr_in), nbr_in.shape[0], features.shape[0], _p(d_in), _stream()))
+    return d_in
+
+
+def indice_avgpool_backward_fp32(features, out_features, out_bp, indice_pairs, indice_num, summaryrf):
+    """(SS_Conv_lib/src/ss_conv_ops.h:62-63) d_in[i] = sum of out_bp[o] / summaryrf[o]."""
+    features, out_bp = features.contiguous(), out_bp.contiguous()
+    nbr_in = input_major_table(neighbour_table(indice_pairs, indice_num, out_bp.shape[0]), features.shape[0])
+    rf = None if summaryrf is None else summaryrf.to(torch.int32).contiguous()
+    d_in = torch.empty_like(features)
+    _check(lib().ssc_avgpool_bwd(_p(out_bp, torch.float32), features.shape[1], _p(nbr_in), nbr_in.shape[0],
+                                 features.shape[0], _p(rf), _p(d_in), _stream()))
+    return d_in
+
+
 indice_maxpool_backward_half = _not_built("indice_maxpool_backward_half")
-indice_avgpool_backward_fp32 = _not_built("indice_avgpool_backward_fp32")
 indice_avgpool_backward_half = _not_built("indice_avgpool_backward_half")
 indice_field_maxpool_fp32 = _not_built("indice_field_maxpool_fp32")
 indice_field_maxpool_half = _not_built("indice_field_maxpool_half")
@@ -575,8 +639,15 @@ def global_maxpool_fp(feats, offsets, out, maxidx, n_proposal, c):
                                         _p(out, torch.float32), _p(maxidx, torch.int32), _stream()))
 
 
-global_avgpool_bp = _not_built("global_avgpool_bp")
-global_maxpool_bp = _not_built("global_maxpool_bp")
+def global_avgpool_bp(d_feats, offsets, maxidx, d_out, n_proposal, c):
+    """(SS_Conv_lib/src/pool/global_avgpool.h:25) writes d_feats [N, C] in place."""
+    _check(lib().ssc_global_avgpool_bwd(_p(d_out, torch.float32), _p(offsets, torch.int32), int(n_proposal), int(c),
+                                        d_feats.shape[0], _p(d_feats, torch.float32), _stream()))
+
+
+def global_maxpool_bp(d_feats, offsets, maxidx, d_out, n_proposal, c):
+    _check(lib().ssc_global_maxpool_bwd(_p(d_out, torch.float32), _p(maxidx, torch.int32), int(n_proposal), int(c),
+                                        d_feats.shape[0], _p(d_feats, torch.float32), _stream()))
 
 
 def batch_offsets(indices, batch_size, n_dev=None):

@@ -72,7 +72,8 @@ class SparseConvolution(nn.Module):
         out_spatial_shape = self._output_shape(input.spatial_shape)
         feats_raw, inds_raw, n_in_dev = input.raw()
         if (_ext.AHEAD and not self.conv1x1 and not self.subm and not self.inverse and self.indice_key is None
-                and feats_raw.is_cuda and feats_raw.dtype == torch.float32):
+                and feats_raw.is_cuda and feats_raw.dtype == torch.float32
+                and not (torch.is_grad_enabled() and (feats_raw.requires_grad or weight.requires_grad))):
             ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_spatial_shape,
                                                 list(input.spatial_shape), self.kernel_size, self.stride,
                                                 self.padding, self.dilation, int(self.transposed), n_in_dev=n_in_dev)

@@ -3,8 +3,8 @@ SS_Conv_lib/ss_conv/sp_ops/functional.py:441-453: indice_conv, indice_subm_conv,
 indice_inverse_conv, indice_maxpool, indice_avgpool, global_avgpool, global_maxpool,
 voxelization, voxel2point_mapping, three_nn, three_interpolate).
 
-Forward passes call the CUDA library.  The backward kernels are not built yet: calling
-.backward() through one of these ops raises NotImplementedError (via the native module).
+Forward and backward passes of the convolution and the pools call the CUDA library; the
+backward of the voxelizer / interpolation ops is not built (raises NotImplementedError).
 """
 import torch
 from torch.autograd import Function

@@ -28,7 +28,8 @@ class _SparsePool(nn.Module):
         out_shape = shape if self.subm else get_conv_output_size(shape, self.kernel_size, self.stride, self.padding,
                                                                  self.dilation)
         feats_raw, inds_raw, n_in_dev = input.raw()
-        if _ext.AHEAD and not self.subm and feats_raw.is_cuda and feats_raw.dtype == torch.float32:
+        if (_ext.AHEAD and not self.subm and feats_raw.is_cuda and feats_raw.dtype == torch.float32
+                and not (torch.is_grad_enabled() and feats_raw.requires_grad)):
             ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_shape, list(shape), self.kernel_size,
                                                 self.stride, self.padding, self.dilation, 0, n_in_dev=n_in_dev)
             if ahead is not None:

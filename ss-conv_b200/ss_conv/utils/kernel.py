@@ -107,6 +107,19 @@ def _orthogonal_(tensor, gain=1):
     return tensor
 
 
+class _Materialize(torch.autograd.Function):
+    """filters = M(weight) by the CUDA kernel; the backward applies M^T with torch ops."""
+
+    @staticmethod
+    def forward(ctx, weight, kernel):
+        ctx.kernel = kernel
+        return kernel._materialize(weight)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.kernel._weight_grad(g.contiguous()), None
+
+
 class SE3Kernel(torch.nn.Module):
     def __init__(self, Rs_in, Rs_out, size, radial_window=gaussian_window_wrapper, dyn_iso=False, verbose=False):
         super().__init__()
@@ -183,13 +196,39 @@ class SE3Kernel(torch.nn.Module):
         return super()._apply(fn, *args, **kwargs)
 
     def filters(self, weight=None):
-        """Convolution filters [k, k, k, Cin, Cout] (contiguous, fp32) on the weight's device."""
+        """Convolution filters [k, k, k, Cin, Cout] (contiguous, fp32) on the weight's device.
+        Differentiable with respect to the weights when autograd is recording."""
         weight = self.weight if weight is None else weight
+        if torch.is_grad_enabled() and weight.requires_grad:
+            return _Materialize.apply(weight, self)
+        return self._materialize(weight)
+
+    def _materialize(self, weight):
         blob, table, out_field, in_field = self._tables(weight.device)
         K = self.size ** 3
         flt = _ext.materialize(weight.detach().contiguous(), blob, table, len(self.Rs_in), out_field, in_field,
                                self.n_out, self.n_in, K)
         return flt.view(self.size, self.size, self.size, self.n_in, self.n_out)
+
+    def _weight_grad(self, g):
+        """Adjoint of the (linear) materialisation: g [k,k,k,Cin,Cout] -> gradient of the flat
+        weight vector, block by block (weights of block (i,j) are laid out [m_out, m_in, n_basis])."""
+        k = self.size
+        grads = []
+        out_off = 0
+        for i, (m_out, _) in enumerate(self.Rs_out):
+            do = self.dims_out[i]
+            in_off = 0
+            for j, (m_in, _) in enumerate(self.Rs_in):
+                di = self.dims_in[j]
+                b = getattr(self, "kernel_{}_{}".format(i, j))
+                if b is not None:
+                    blk = g[:, :, :, in_off:in_off + m_in * di, out_off:out_off + m_out * do]
+                    blk = blk.reshape(k, k, k, m_in, di, m_out, do)
+                    grads.append(torch.einsum("xyzvcua,bacxyz->uvb", blk, b.to(g.dtype)).reshape(-1))
+                in_off += m_in * di
+            out_off += m_out * do
+        return torch.cat(grads) if grads else g.new_zeros(0)
 
     def combination(self, weight):
         """[Cout, Cin, k, k, k] kernel (a permuted view of `filters`)."""

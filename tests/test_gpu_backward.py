@@ -1,0 +1,140 @@
+"""Backward kernels vs the reference's own CPU outputs (golden fixtures) and the oracle.
+Tolerances as for the forward pass: exact-fp32 2e-5, TF32 operands 1e-3 (max|diff|/max|ref|
+against the float64 evaluation); pool gradients are bit-exact (same accumulation order)."""
+import numpy as np
+import pytest
+import torch
+
+import ssconv_oracle as O
+from gpu_helpers import dev, gpu_rulebook, random_voxels, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = {"fp32": 2e-5, "tf32": 1e-3}
+
+
+@pytest.mark.parametrize("tag", ["bw_strided", "bw_subm"])
+def test_conv_backward_matches_reference_outputs(cuda, golden, tag):
+    from ss_conv import _ext
+    subm = int(golden[tag + "_geom"][3])
+    _ext.set_precision("fp32")
+    try:
+        d_in, d_flt = _ext.indice_conv_backward_fp32(dev(golden[tag + "_features"], cuda), dev(golden[tag + "_filters"], cuda),
+                                                     dev(golden[tag + "_dout"], cuda), dev(golden[tag + "_pairs"], cuda),
+                                                     dev(golden[tag + "_num"], cuda), 0, subm)
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+    assert d_flt.shape == golden[tag + "_filters"].shape
+    assert rel_err(d_in.cpu().numpy(), golden[tag + "_din"]) <= TOL["fp32"]
+    assert rel_err(d_flt.cpu().numpy(), golden[tag + "_dfilters"]) <= TOL["fp32"]
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+@pytest.mark.parametrize("c_in,c_out,k,s,p,subm", [(32, 38, 3, 2, 1, False), (64, 76, 3, 1, 1, True), (20, 70, 2, 2, 0, False),
+                                                     (130, 40, 3, 1, 1, False)])
+def test_conv_backward_vs_float64_oracle(cuda, precision, c_in, c_out, k, s, p, subm):
+    from ss_conv import _ext
+    rng = np.random.RandomState(c_in + 7 * c_out)
+    ind = random_voxels(rng, 2, 12, 400)
+    outids, pairs, num = gpu_rulebook(ind, 2, [12] * 3, k, s, p, 1, subm, cuda)
+    n_out = outids.shape[0]
+    feats = rng.randn(ind.shape[0], c_in).astype(np.float32)
+    W = (rng.randn(k, k, k, c_in, c_out) / np.sqrt(c_in * k ** 3)).astype(np.float32)
+    dout = rng.randn(n_out, c_out).astype(np.float32)
+    _ext.set_precision(precision)
+    try:
+        d_in, d_flt = _ext.indice_conv_backward_fp32(dev(feats, cuda), dev(W, cuda), dev(dout, cuda), pairs, num, 0, int(subm))
+        again = _ext.indice_conv_backward_fp32(dev(feats, cuda), dev(W, cuda), dev(dout, cuda), pairs, num, 0, int(subm))
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+    ref_in, ref_flt = O.indice_conv_backward(feats, W, dout, pairs.cpu().numpy(), num.cpu().numpy(), False, False,
+                                             dtype=np.float64)
+    assert rel_err(d_in.cpu().numpy(), ref_in) <= TOL[precision]
+    assert rel_err(d_flt.cpu().numpy().reshape(ref_flt.shape), ref_flt) <= TOL["fp32"]      # filter gradient is always fp32
+    assert torch.equal(d_in, again[0]) and torch.equal(d_flt, again[1])                        # bitwise repeatable
+
+
+def test_pool_backward_bit_exact(cuda, golden):
+    from ss_conv import _ext
+    pairs, num = dev(golden["bw_strided_pairs"], cuda), dev(golden["bw_strided_num"], cuda)
+    d = _ext.indice_maxpool_backward_fp32(dev(golden["bw_pool_features"], cuda), dev(golden["bw_pool_out"], cuda),
+                                          dev(golden["bw_pool_dout"], cuda), pairs, num)
+    np.testing.assert_array_equal(d.cpu().numpy(), golden["bw_pool_din"])
+    # average pool: divisor = kernel volume (use_gs) and = number of present inputs
+    n_out = golden["bw_pool_out"].shape[0]
+    for rf in (None, O.summary_rf(golden["bw_strided_pairs"], golden["bw_strided_num"], n_out)):
+        want = O.indice_avgpool_backward(golden["bw_pool_features"], golden["bw_pool_dout"], golden["bw_strided_pairs"],
+                                         golden["bw_strided_num"], np.full(n_out, 27, np.int32) if rf is None else rf)
+        got = _ext.indice_avgpool_backward_fp32(dev(golden["bw_pool_features"], cuda), dev(golden["bw_pool_out"], cuda),
+                                                dev(golden["bw_pool_dout"], cuda), pairs, num,
+                                                None if rf is None else dev(rf, cuda))
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_global_pool_backward(cuda):
+    from ss_conv.sp_ops.functional import global_avgpool, global_maxpool
+    rng = np.random.RandomState(5)
+    offsets = np.array([0, 7, 7, 40, 100], dtype=np.int32)      # one empty sample
+    feats = rng.randn(100, 37).astype(np.float32)
+    g = rng.randn(4, 37).astype(np.float32)
+    for fn, name in ((global_avgpool, "avg"), (global_maxpool, "max")):
+        x = dev(feats, cuda).requires_grad_(True)
+        y = fn(x, dev(offsets, cuda))
+        y.backward(dev(g, cuda))
+        if name == "avg":
+            want = O.global_avgpool_backward(g, offsets, 100)
+        else:
+            _, maxidx = O.global_maxpool(feats, offsets)
+            want = O.global_maxpool_backward(g, maxidx, 100)
+        np.testing.assert_allclose(x.grad.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+
+
+def test_training_step_through_a_steerable_layer(cuda):
+    """loss.backward() through Convolution (training mode) + MaxPool: gradients reach the input
+    features and the steerable weights; the weight gradient passes the adjoint identity
+    <M v, G> = <v, M^T G> of the linear materialisation, and the feature gradient matches the
+    oracle evaluated with the layer's own filters."""
+    from ss_conv import _ext
+    from ss_conv.convolution import Convolution
+    from ss_conv.pool import MaxPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    torch.manual_seed(12)
+    rng = np.random.RandomState(12)
+    conv = Convolution([(2, 0), (2, 1)], [(3, 0), (1, 1), (1, 2)], 3, stride=2, padding=1).to(cuda).train()
+    pool = MaxPool(2, stride=2)
+    ind = random_voxels(rng, 2, 12, 300)
+    feats = rng.randn(ind.shape[0], conv.in_channels).astype(np.float32)
+    _ext.set_precision("fp32")
+    try:
+        x = dev(feats, cuda).requires_grad_(True)
+        y = pool(conv(SparseTensor(x, dev(ind, cuda), [12] * 3, 2)))
+        G = torch.randn_like(y.features)
+        (y.features * G).sum().backward()
+        torch.cuda.synchronize()
+        assert x.grad is not None and conv.kernel.weight.grad is not None
+        # oracle chain with the layer's filters
+        W = conv.kernel.filters().detach().cpu().numpy()
+        o1, p1, n1 = O.get_indice_pairs(ind, 2, [12] * 3, 3, 2, 1, 1, False)
+        y1 = O.indice_conv(feats, W, p1, n1, o1.shape[0])
+        o2, p2, n2 = O.get_indice_pairs(o1, 2, [6] * 3, 2, 2, 0, 1, False)
+        y2 = O.indice_maxpool(y1, p2, n2, o2.shape[0])
+        # row orders: GPU ascending flat index, oracle first-seen -> compare through canonical order
+        perm1 = np.lexsort((o1[:, 3], o1[:, 2], o1[:, 1], o1[:, 0]))
+        perm2 = np.lexsort((o2[:, 3], o2[:, 2], o2[:, 1], o2[:, 0]))
+        Gn = np.zeros_like(y2)
+        Gn[perm2] = G.cpu().numpy()
+        d1 = O.indice_maxpool_backward(y1, y2, Gn, p2, n2)
+        d_x, d_W = O.indice_conv_backward(feats, W, d1, p1, n1, False, False, dtype=np.float64)
+        assert rel_err(x.grad.cpu().numpy(), d_x) <= 1e-4
+        # adjoint identity for the weights
+        v = torch.randn_like(conv.kernel.weight)
+        Mv = conv.kernel.filters(v.detach()).detach().cpu().numpy().astype(np.float64).reshape(d_W.shape)
+        lhs = float((Mv * d_W).sum())
+        rhs = float((v.double() * conv.kernel.weight.grad.double()).sum())
+        assert abs(lhs - rhs) <= 1e-4 * max(1.0, abs(lhs))
+        assert perm1.shape[0] == o1.shape[0]
+    finally:
+        _ext.set_precision("auto")
