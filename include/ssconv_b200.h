@@ -238,6 +238,15 @@ int ssc_global_avgpool_bwd(const float *d_out, const int32_t *offsets, int n_sam
                            float *d_feats, void *stream);
 int ssc_global_maxpool_bwd(const float *d_out, const int32_t *maxidx, int n_samples, int c, int n_rows,
                            float *d_feats, void *stream);
+/* Replace voxelize_bp (SS_Conv_lib/src/voxelize/voxelize_cuda_kernel.h:44-62: every point listed in
+ * a voxel's rule row receives the voxel's gradient, divided by the count in mean mode 4) and
+ * three_interpolate_grad (SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:123-165).  Both write
+ * their whole output (zero where nothing arrives); the interpolation gradient uses float atomics
+ * like the reference, so its low-order bits depend on the order of arrival. */
+int ssc_voxelize_bwd(const float *d_out, const int32_t *rules, int mode, int n_voxel, int max_active, int c,
+                     int n_point, float *d_feats, void *stream);
+int ssc_three_interpolate_bwd(int c, int n, int m, const float *grad_out, const int32_t *idx,
+                              const float *weight, float *grad_points, void *stream);
 
 /* ---------------------------------------------------------------------------- voxelization
  * ssc_voxel2point_map replaces voxel2point_fp (SS_Conv_lib/src/voxelize/voxel2point_cuda_kernel.cu:16-42):

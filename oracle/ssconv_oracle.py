@@ -607,3 +607,26 @@ def combination(weight, bases, Rs_in, Rs_out, size):
 def filters_from_kernel(W):
     """SS_Conv_lib/ss_conv/convolution.py:56: [Cout,Cin,kx,ky,kz] -> [kx,ky,kz,Cin,Cout]."""
     return np.ascontiguousarray(np.transpose(W, (2, 3, 4, 1, 0)))
+
+
+# ----------------------------------------------------------------- voxelizer gradients
+def voxelize_bp(d_out, maps, mode, n_point):
+    """SS_Conv_lib/src/voxelize/voxelize_cuda_kernel.h:44-57: every point listed in a voxel's
+    rule row [count, ids...] receives the voxel's gradient, times 1/count in mean mode 4."""
+    d_out = np.asarray(d_out, dtype=np.float32)
+    d = np.zeros((n_point, d_out.shape[1]), dtype=np.float32)
+    for v in range(maps.shape[0]):
+        n_act = int(maps[v, 0])
+        mult = np.float32(1.0 / n_act) if (mode == 4 and n_act > 0) else np.float32(1.0)
+        for p in maps[v, 1:1 + n_act]:
+            d[p] += mult * d_out[v]
+    return d
+
+
+def three_interpolate_bp(grad_out, idx, weight, m):
+    """SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:123-145:
+    grad_points[idx[p, j]] += grad_out[p] * weight[p, j] (float64 accumulation here)."""
+    g = np.zeros((m, grad_out.shape[1]), dtype=np.float64)
+    for j in range(3):
+        np.add.at(g, idx[:, j], grad_out.astype(np.float64) * weight[:, j:j + 1].astype(np.float64))
+    return g

@@ -150,9 +150,70 @@ __global__ void global_maxpool_bwd_kernel(const float *__restrict__ d_out, const
   if (row >= 0 && row < n_rows) d_feats[(size_t)row * c + (e % c)] = d_out[e];  // one writer per (row, channel) of a sample
 }
 
+// One thread per (voxel, channel): hands the voxel's gradient to the points listed in its rule
+// row [count, point ids...].  A point is listed by one voxel only, so plain stores suffice.
+__global__ void voxelize_bwd_kernel(const float *__restrict__ d_out, const int32_t *__restrict__ rules, int n_voxel,
+                                    int max_active, int c, int average, float *__restrict__ d_feats) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long long)n_voxel * c) return;
+  const int v = (int)(t / c), ch = (int)(t - (long long)v * c);
+  const int32_t *r = rules + (size_t)v * (max_active + 1);
+  int n_act = r[0];
+  if (n_act > max_active) n_act = max_active;
+  const float g = d_out[t] * ((average && n_act > 0) ? 1.f / (float)n_act : 1.f);
+  for (int i = 1; i <= n_act; ++i) d_feats[(size_t)r[i] * c + ch] = g;
+}
+
+// One thread per (point, channel): adds weight * gradient to each of the point's three voxels.
+__global__ void three_interpolate_bwd_kernel(int c, int n, const float *__restrict__ grad_out,
+                                             const int32_t *__restrict__ idx, const float *__restrict__ weight,
+                                             float *__restrict__ grad_points) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long long)n * c) return;
+  const int p = (int)(t / c), ch = (int)(t - (long long)p * c);
+  const float g = grad_out[t];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int v = idx[p * 3 + j];
+    if (v >= 0) atomicAdd(grad_points + (size_t)v * c + ch, g * weight[p * 3 + j]);
+  }
+}
+
 }  // namespace ssc
 
 using namespace ssc;
+
+extern "C" int ssc_voxelize_bwd(const float *d_out, const int32_t *rules, int mode, int n_voxel, int max_active, int c,
+                                int n_point, float *d_feats, void *stream) {
+  SSC_REQUIRE(n_voxel >= 0 && max_active >= 0 && c > 0 && n_point >= 0, "voxelize_bwd: bad sizes");
+  cudaStream_t st = as_stream(stream);
+  if (n_point > 0) {
+    SSC_REQUIRE(d_feats, "voxelize_bwd: null pointer");
+    cudaMemsetAsync(d_feats, 0, (size_t)n_point * c * 4, st);
+  }
+  if (n_voxel == 0 || n_point == 0) return SSC_OK;
+  SSC_REQUIRE(d_out && rules, "voxelize_bwd: null pointer");
+  long long total = (long long)n_voxel * c;
+  { voxelize_bwd_kernel<<<ceil_div(total, 256), 256, 0, st>>>(d_out, rules, n_voxel, max_active, c, mode == 4, d_feats); note_launches(1); }
+  SSC_CHECK_LAUNCH("voxelize_bwd");
+  return SSC_OK;
+}
+
+extern "C" int ssc_three_interpolate_bwd(int c, int n, int m, const float *grad_out, const int32_t *idx,
+                                         const float *weight, float *grad_points, void *stream) {
+  SSC_REQUIRE(c > 0 && n >= 0 && m >= 0, "three_interpolate_bwd: bad sizes");
+  cudaStream_t st = as_stream(stream);
+  if (m > 0) {
+    SSC_REQUIRE(grad_points, "three_interpolate_bwd: null pointer");
+    cudaMemsetAsync(grad_points, 0, (size_t)m * c * 4, st);
+  }
+  if (n == 0 || m == 0) return SSC_OK;
+  SSC_REQUIRE(grad_out && idx && weight, "three_interpolate_bwd: null pointer");
+  long long total = (long long)n * c;
+  { three_interpolate_bwd_kernel<<<ceil_div(total, 256), 256, 0, st>>>(c, n, grad_out, idx, weight, grad_points); note_launches(1); }
+  SSC_CHECK_LAUNCH("three_interpolate_bwd");
+  return SSC_OK;
+}
 
 extern "C" int ssc_nbr_transpose(const int32_t *nbr, int K, int n_out, int n_in, int32_t *nbr_in, void *stream) {
   SSC_REQUIRE(K >= 1 && n_out >= 0 && n_in >= 0, "nbr_transpose: bad sizes");

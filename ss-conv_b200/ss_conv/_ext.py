@@ -56,6 +56,8 @@ SIGNATURES = {
     "ssc_avgpool_bwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_global_avgpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_global_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_voxelize_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_three_interpolate_bwd": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -670,7 +672,11 @@ def voxelize_fp(feats, output_feats, map_rule, mode, n_voxel, max_active, c):
                                   int(mode), int(n_voxel), int(max_active), int(c), _stream()))
 
 
-voxelize_bp = _not_built("voxelize_bp")
+def voxelize_bp(d_output_feats, d_feats, map_rule, mode, n_voxel, max_active, c):
+    """(SS_Conv_lib/src/ss_conv_ops.h:71-72) writes d_feats [N, C] in place."""
+    _check(lib().ssc_voxelize_bwd(_p(d_output_feats, torch.float32), _p(map_rule, torch.int32), int(mode), int(n_voxel),
+                                  int(max_active), int(c), d_feats.shape[0], _p(d_feats, torch.float32), _stream()))
+
 voxelize_idx = _not_built("voxelize_idx")
 point_recover_fp = _not_built("point_recover_fp")
 point_recover_bp = _not_built("point_recover_bp")
@@ -714,7 +720,10 @@ def three_interpolate_fp(c, m, n, points, idx, weight, out):
                                            _p(weight, torch.float32), _p(out, torch.float32), _stream()))
 
 
-three_interpolate_bp = _not_built("three_interpolate_bp")
+def three_interpolate_bp(c, n, m, grad_out, idx, weight, grad_points):
+    """(SS_Conv_lib/src/voxelize/interpolate.h:23-25) writes grad_points [M, C] in place."""
+    _check(lib().ssc_three_interpolate_bwd(int(c), int(n), int(m), _p(grad_out, torch.float32), _p(idx, torch.int32),
+                                           _p(weight, torch.float32), _p(grad_points, torch.float32), _stream()))
 
 
 # ================================================================ BatchNorm / activation

@@ -8,6 +8,35 @@ from .tensor import SparseTensor
 from .functional import three_nn, three_interpolate
 
 
+class _VoxelFeatures(torch.autograd.Function):
+    """Attaches the gradient of the fused voxelizer to its (already computed) voxel features:
+    every point receives its voxel's gradient (sum mode 3), divided by the number of points of
+    the voxel (mean mode 4), or only the first / last point of the voxel does (modes 1 / 2) —
+    voxelize_bp of the reference (SS_Conv_lib/src/voxelize/voxelize_cuda_kernel.h:44-57)."""
+
+    @staticmethod
+    def forward(ctx, point_feats, voxel_feats, inverse, mode):
+        ctx.save_for_backward(inverse)
+        ctx.mode, ctx.n_voxel = int(mode), voxel_feats.shape[0]
+        return voxel_feats.view_as(voxel_feats)
+
+    @staticmethod
+    def backward(ctx, g):
+        (inverse,) = ctx.saved_tensors
+        inv = inverse.long()
+        d = g[inv]
+        if ctx.mode == 4:
+            counts = torch.bincount(inv, minlength=ctx.n_voxel).clamp_(min=1)
+            d = d / counts[inv].unsqueeze(1).to(d.dtype)
+        elif ctx.mode in (1, 2):
+            ids = torch.arange(inv.numel(), device=inv.device)
+            fill = inv.numel() if ctx.mode == 1 else -1
+            chosen = torch.full((ctx.n_voxel,), fill, dtype=torch.long, device=inv.device)
+            chosen.scatter_reduce_(0, inv, ids, "amin" if ctx.mode == 1 else "amax")
+            d = d * (chosen[inv] == ids).unsqueeze(1).to(d.dtype)
+        return d, None, None, None
+
+
 class Point2Voxel(nn.Module):
     """Bins points of a batch into a voxel grid centred at the origin.
 
@@ -61,6 +90,8 @@ class Point2Voxel(nn.Module):
         vox, _inverse, vfeat = _ext.point2voxel(pts.float(), fts.float(), ids, max(batch_span, B1),
                                                 [int(v) for v in self.voxel_num_limit],
                                                 [float(u) for u in self.unit_voxel_extent], self.voxelization_mode)
+        if torch.is_grad_enabled() and fts.requires_grad:
+            vfeat = _VoxelFeatures.apply(fts, vfeat, _inverse, self.voxelization_mode)
         sparse = SparseTensor(vfeat, vox, self.voxel_num_limit.astype(np.int64), B1)
         return pts, sparse, ids, flag
 

@@ -138,3 +138,46 @@ def test_training_step_through_a_steerable_layer(cuda):
         assert perm1.shape[0] == o1.shape[0]
     finally:
         _ext.set_precision("auto")
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3, 4])
+def test_voxelizer_gradients(cuda, mode):
+    """voxelize_bp on explicit rule rows vs the oracle, and the gradient the fused Point2Voxel
+    attaches to its voxel features vs the same oracle on the equivalent rule rows."""
+    from ss_conv import _ext
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    from ss_conv.utils import synthetic as S
+    rng = np.random.RandomState(mode)
+    pts, fts, ids = S.object_points(range(3), 400, base_seed=30)
+    p2v = Point2Voxel([8] * 3, [1.0 / 8] * 3, mode)
+    x = dev(fts, cuda).requires_grad_(True)
+    _, sp, _, _ = p2v(dev(pts, cuda), x, dev(ids, cuda))
+    G = rng.randn(*sp.features.shape).astype(np.float32)
+    sp.features.backward(dev(G, cuda))
+    # equivalent rule rows from the oracle's voxelizer on the same points
+    kept, _, vox, _, inverse = O.point2voxel(pts, fts, ids, [8] * 3, [1.0 / 8] * 3, mode)
+    assert kept.shape[0] == pts.shape[0]                       # every synthetic point is in range
+    np.testing.assert_array_equal(vox, sp.indices.cpu().numpy())
+    max_active = 1 if mode in (1, 2) else int(np.bincount(inverse).max())
+    maps = O.voxel2point_map(inverse, vox.shape[0], max_active, mode)
+    want = O.voxelize_bp(G, maps, mode, pts.shape[0])
+    np.testing.assert_allclose(x.grad.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+    d_feats = torch.empty((pts.shape[0], fts.shape[1]), dtype=torch.float32, device=cuda)
+    _ext.voxelize_bp(dev(G, cuda), d_feats, dev(maps.astype(np.int32), cuda), mode, vox.shape[0], max_active, fts.shape[1])
+    np.testing.assert_allclose(d_feats.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+
+
+def test_interpolation_gradient(cuda):
+    from ss_conv.sp_ops.functional import three_interpolate
+    rng = np.random.RandomState(3)
+    m, n, c = 50, 400, 9
+    feats = rng.randn(m, c).astype(np.float32)
+    idx = rng.randint(0, m, size=(n, 3)).astype(np.int32)
+    w = rng.rand(n, 3).astype(np.float32)
+    w /= w.sum(1, keepdims=True)
+    g = rng.randn(n, c).astype(np.float32)
+    x = dev(feats, cuda).requires_grad_(True)
+    y = three_interpolate(x, dev(idx, cuda), dev(w, cuda))
+    y.backward(dev(g, cuda))
+    want = O.three_interpolate_bp(g, idx, w, m)
+    assert rel_err(x.grad.cpu().numpy(), want) <= 1e-5
