@@ -109,7 +109,9 @@ class Activation(nn.Module):
 
     def _gate(self, y, scale=None, shift=None):
         C = Rs2dim(self.Rs)
-        if self.fusable() and y.is_cuda:
+        recording = torch.is_grad_enabled() and (y.requires_grad or
+                                                 (self.training and any(p.requires_grad for p in self.parameters())))
+        if self.fusable() and y.is_cuda and not recording:
             s_code = _act_code(self._scalar_fn) if self.scalar_act is not None else 0
             g_code = _act_code(self._gate_fn) if self.gate_act is not None else 0
             s_bias = None

@@ -71,7 +71,54 @@ class BatchNorm(nn.Module):
             b = None
         return _ext.bn_fold(mean, var, w, b, field, scalar, self.eps)
 
+    def _differentiable(self, x):
+        """The layer as a composite of torch ops, used while autograd is recording so that
+        gradients reach the input, the affine parameters and (training mode) the batch
+        statistics; same arithmetic as the fused path."""
+        parts = []
+        new_mean, new_var = [], []
+        ix = irm = irv = 0
+        for m, l in self.Rs:
+            d = 2 * l + 1
+            f = x[:, ix:ix + m * d].reshape(-1, m, d)
+            if d == 1:
+                if self.training:
+                    mu = f.mean(0).reshape(m)
+                    new_mean.append(mu.detach())
+                else:
+                    mu = self.running_mean[irm:irm + m]
+                f = f - mu.reshape(1, m, 1)
+            if self.training:
+                norm = f.pow(2).sum(2).mean(0)
+                new_var.append(norm.detach())
+            else:
+                norm = self.running_var[irv:irv + m]
+            scale = (norm + self.eps).pow(-0.5)
+            if self.affine:
+                scale = scale * self.weight[irv:irv + m]
+            f = f * scale.reshape(1, m, 1)
+            if d == 1 and self.affine:
+                f = f + self.bias[irm:irm + m].reshape(1, m, 1)
+            parts.append(f.reshape(-1, m * d))
+            if d == 1:
+                irm += m
+            irv += m
+            ix += m * d
+        if self.training:
+            with torch.no_grad():
+                if new_mean:
+                    self.running_mean.mul_(1 - self.momentum).add_(self.momentum * torch.cat(new_mean))
+                self.running_var.mul_(1 - self.momentum).add_(self.momentum * torch.cat(new_var))
+        return torch.cat(parts, dim=1)
+
     def forward(self, input):
+        # inference without no_grad() (nothing upstream asks for a gradient) keeps the fused kernels
+        if torch.is_grad_enabled() and (input.raw()[0].requires_grad or
+                                        (self.training and self.affine and self.weight.requires_grad)):
+            if self.training and self.reduce != 'mean':
+                raise ValueError("Invalid reduce option {}".format(self.reduce))
+            input.features = self._differentiable(input.features)
+            return input
         # eval mode works row by row, so it can run on a tensor whose row count is still pending
         x = input.features if self.training else input.raw()[0]
         field, scalar = self._device_tables(x.device)

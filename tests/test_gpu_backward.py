@@ -181,3 +181,44 @@ def test_interpolation_gradient(cuda):
     y.backward(dev(g, cuda))
     want = O.three_interpolate_bp(g, idx, w, m)
     assert rel_err(x.grad.cpu().numpy(), want) <= 1e-5
+
+
+def test_training_step_through_conv_bn_gate(cuda):
+    """One optimiser-style step through Convolution -> BatchNorm(train) -> gated Activation ->
+    GlobalAvgPool: every parameter receives a finite, non-zero gradient, the running statistics
+    move, and the differentiable composite equals the fused inference path in eval mode."""
+    from ss_conv import _ext
+    from ss_conv.activation import Activation
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.convolution import Convolution
+    from ss_conv.pool import GlobalAvgPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    torch.manual_seed(2)
+    rng = np.random.RandomState(2)
+    Rs_in, Rs_mid = [(3, 0)], [(4, 0), (2, 1), (1, 2)]
+    gated = Rs_mid + [(3, 0)]
+    conv = Convolution(Rs_in, gated, 3, stride=2, padding=1).to(cuda)
+    bn = BatchNorm(gated).to(cuda)
+    act = Activation(Rs_mid, (torch.relu, torch.sigmoid), bias=True, checkpoint=False).to(cuda)
+    gp = GlobalAvgPool()
+    ind = random_voxels(rng, 3, 10, 200)
+    feats = dev(rng.randn(ind.shape[0], 3).astype(np.float32), cuda)
+    _ext.set_precision("fp32")
+    try:
+        for m in (conv, bn, act):
+            m.train()
+        rv0 = bn.running_var.clone()
+        y = gp(act(bn(conv(SparseTensor(feats, dev(ind, cuda), [10] * 3, 3)))))
+        y.pow(2).sum().backward()
+        params = [conv.kernel.weight, bn.weight, bn.bias] + list(act.parameters())
+        for p in params:
+            assert p.grad is not None and torch.isfinite(p.grad).all() and float(p.grad.abs().sum()) > 0
+        assert not torch.equal(rv0, bn.running_var)
+        for m in (conv, bn, act):
+            m.eval()
+        x1 = act(bn(conv(SparseTensor(feats, dev(ind, cuda), [10] * 3, 3)))).features        # composite (grad on)
+        with torch.no_grad():
+            x2 = act(bn(conv(SparseTensor(feats, dev(ind, cuda), [10] * 3, 3)))).features    # fused kernels
+        assert rel_err(x1.detach().cpu().numpy(), x2.cpu().numpy()) <= 1e-5
+    finally:
+        _ext.set_precision("auto")

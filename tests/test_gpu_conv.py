@@ -122,10 +122,10 @@ def test_materialize_and_pack(cuda, golden):
                 state["kernel_%d_%d" % (i, j)] = torch.from_numpy(b)
     k.load_state_dict(state)
     k.to(cuda)
-    flt = k.filters().cpu().numpy()
+    flt = k.filters().detach().cpu().numpy()
     assert flt.shape == golden["conv_filters"].shape
     assert np.abs(flt - golden["conv_filters"]).max() <= 1e-6
-    W = k().cpu().numpy()                                          # [Cout, Cin, k, k, k] view
+    W = k().detach().cpu().numpy()                                          # [Cout, Cin, k, k, k] view
     assert np.abs(W - np.transpose(golden["conv_filters"], (4, 3, 0, 1, 2))).max() <= 1e-6
 
 

@@ -158,14 +158,22 @@ def test_batchnorm_activation_golden(cuda, golden):
     y = bn(SparseTensor(x.clone(), ind, [10] * 3, 2)).features.cpu().numpy()
     assert np.abs(y - golden["bn_eval_out"]).max() <= 3e-6 * max(1.0, np.abs(y).max())
     bn.train()
-    yt = bn(SparseTensor(x.clone(), ind, [10] * 3, 2)).features.cpu().numpy()
-    assert np.abs(yt - golden["bn_train_out"]).max() <= 2e-5 * max(1.0, np.abs(yt).max())
-    assert np.allclose(bn.running_mean.cpu().numpy(), golden["bn_train_running_mean"], rtol=1e-5, atol=1e-6)
-    assert np.allclose(bn.running_var.cpu().numpy(), golden["bn_train_running_var"], rtol=1e-5, atol=1e-6)
+    stats0 = (bn.running_mean.clone(), bn.running_var.clone())
+    for fused in (True, False):          # statistics kernels (no autograd) / differentiable composite
+        with torch.no_grad():
+            bn.running_mean.copy_(stats0[0])
+            bn.running_var.copy_(stats0[1])
+        with torch.set_grad_enabled(not fused):
+            yt = bn(SparseTensor(x.clone(), ind, [10] * 3, 2)).features.detach().cpu().numpy()
+        assert np.abs(yt - golden["bn_train_out"]).max() <= 2e-5 * max(1.0, np.abs(yt).max())
+        assert np.allclose(bn.running_mean.cpu().numpy(), golden["bn_train_running_mean"], rtol=1e-5, atol=1e-6)
+        assert np.allclose(bn.running_var.cpu().numpy(), golden["bn_train_running_var"], rtol=1e-5, atol=1e-6)
+    bn.eval()
     act = Activation(Rs_out[:-1], (torch.relu, torch.sigmoid), bias=True, checkpoint=False).to(cuda)
     with torch.no_grad():
         act.scalar_act.bias.copy_(dev(golden["act_scalar_bias"], cuda))
         act.gate_act.bias.copy_(dev(golden["act_gate_bias"], cuda))
+    act.eval()
     z = act(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
     assert z.shape == golden["act_out"].shape
     assert np.abs(z - golden["act_out"]).max() <= 3e-6
