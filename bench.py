@@ -315,6 +315,25 @@ def run_ours(args):
                 alg_bytes.append(4 * (f.shape[0] * ci + n_out * co + K * ci * co) + 8 * P)
                 flops.append(2.0 * P * ci * co)
     n_out_conv = prepared[0][2]
+    # ---- backward of the same layer (input gradient through the tcgen05 kernel on the input-major
+    #      table, exact-fp32 filter gradient), CUDA events, the rulebook of the forward pass reused
+    bwd_ms = []
+    with torch.no_grad():
+        grads = [torch.randn(n_out, flt.shape[2], device=dev) for _, _, n_out, _ in prepared]
+        tables = []
+        for (f, i), (_, nbr, n_out, _) in zip(dev_sets, prepared):
+            tables.append((nbr, _ext.input_major_table(nbr, f.shape[0])))
+        fltT = flt.transpose(1, 2).contiguous()
+        for it in range(2 + 6):
+            f, (nbr, nbr_in), g = prepared[it % ROTATE][0], tables[it % ROTATE], grads[it % ROTATE]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32")
+            _ext.conv_wgrad(f, g, nbr)
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 2:
+                bwd_ms.append(a.elapsed_time(b))
     peak, peak_src = peaks()
     achieved = float(np.mean(alg_bytes)) / (float(np.mean(kern_ms)) * 1e-3) / 1e9
 
@@ -354,6 +373,8 @@ def run_ours(args):
                          "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
                          "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
         }
+        line["backward"] = {"what": "input gradient (tcgen05, TF32 operands) + filter gradient (fp32) of the cfg2 convolution",
+                            "ms": float(np.mean(bwd_ms)), "voxels_per_s": float(np.mean(n_in)) / (float(np.mean(bwd_ms)) * 1e-3)}
         line["backbone"] = backbone
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, budget_s=12.0)
