@@ -60,8 +60,11 @@ int ssc_has_tcgen05(void);
  */
 
 /* Bytes of scratch the rulebook entry points need for n_in active inputs, a batch of
- * `batch` samples and an output grid of out_shape (use the input grid for submanifold). */
-size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int out_shape[3], int K);
+ * `batch` samples, an input grid of in_shape and an output grid of out_shape (the same grid
+ * twice for submanifold).  Input rows are found through a dense row map over the input grid when
+ * that grid is at most 64 cells per active voxel (and 2^26 cells), else through a hash table;
+ * SSC_RULEBOOK_TABLE=hash|dense overrides the choice. */
+size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int in_shape[3], const int out_shape[3], int K);
 
 /* Submanifold rulebook (stride 1, padding k/2 forced as in indice_conv.h:68-73; output rows
  * are the input rows, indice_conv.h:96).  Writes nbr [K,n_in]; pairs [K,2,n_in] and

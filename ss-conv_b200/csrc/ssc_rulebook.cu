@@ -17,8 +17,16 @@ namespace ssc {
 
 constexpr int kChunk = 1024;  // outputs per block in lookup / fill
 
+// Input coordinates are looked up either in a dense row map over the input grid (one int32 per
+// cell: a lookup is a single load) or, when the grid is large compared with the number of active
+// voxels, in the bucketed hash table.  Both live in the same scratch region.
+constexpr long long kDenseMaxCells = 1ll << 26;     // 256 MiB of row map at most
+constexpr long long kDenseCellsPerRow = 64;         // clearing the map must stay cheap per active voxel
+
 struct RulebookScratch {
   unsigned long long *table;
+  int32_t *row_map;      // non-null: dense map in use instead of the hash table
+  long long in_cells;
   uint32_t n_buckets;
   uint32_t *bitmap;
   uint32_t *word_prefix;
@@ -32,7 +40,15 @@ struct RulebookScratch {
   size_t total;
 };
 
-static RulebookScratch carve(void *base, int n_in, int batch, const int out_shape[3], int K) {
+static bool use_dense_map(int n_in, long long in_cells) {
+  const char *e = getenv("SSC_RULEBOOK_TABLE");
+  const int forced = e == nullptr ? 0 : (strcmp(e, "hash") == 0 ? 1 : (strcmp(e, "dense") == 0 ? 2 : 0));
+  if (forced == 1) return false;
+  if (in_cells > kDenseMaxCells) return false;
+  return forced == 2 || in_cells <= kDenseCellsPerRow * (long long)(n_in > 0 ? n_in : 1);
+}
+
+static RulebookScratch carve(void *base, int n_in, int batch, const int in_shape[3], const int out_shape[3], int K) {
   RulebookScratch s;
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -43,7 +59,14 @@ static RulebookScratch carve(void *base, int n_in, int batch, const int out_shap
   long long vol = (long long)out_shape[0] * out_shape[1] * out_shape[2];
   long long cells = vol * batch;
   s.n_buckets = hash_buckets_for(n_in);
-  s.table = (unsigned long long *)take((size_t)s.n_buckets * kBucketSlots * 8);
+  s.in_cells = (long long)in_shape[0] * in_shape[1] * in_shape[2] * batch;
+  if (use_dense_map(n_in, s.in_cells)) {
+    s.row_map = (int32_t *)take((size_t)s.in_cells * 4);
+    s.table = nullptr;
+  } else {
+    s.row_map = nullptr;
+    s.table = (unsigned long long *)take((size_t)s.n_buckets * kBucketSlots * 8);
+  }
   s.n_words = (cells + 31) / 32;
   s.bitmap = (uint32_t *)take((size_t)s.n_words * 4);
   s.word_prefix = (uint32_t *)take((size_t)s.n_words * 4);
@@ -92,6 +115,21 @@ __global__ void hash_insert_kernel(const int4 *__restrict__ indices, int n, int 
     b = (b + 1) & mask;
   }
   atomicOr(status, 2);  // table full (cannot happen at load factor <= 0.5)
+}
+
+// Dense alternative to hash_insert_kernel: row_map[flat input cell] = row (largest row wins on
+// duplicate coordinates, as in the hash table).
+__global__ void map_insert_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
+                                  int32_t *__restrict__ row_map, int32_t *status, const int32_t *__restrict__ n_dev) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= live_rows(n, n_dev)) return;
+  int4 c = indices[j];
+  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) {
+    atomicOr(status, 1);
+    return;
+  }
+  const long long cell = ((long long)(c.x * g.in_shape[0] + c.y) * g.in_shape[1] + c.z) * g.in_shape[2] + c.w;
+  atomicMax(row_map + cell, j);
 }
 
 // One thread per input row: mark every output cell the row reaches.  The per-dimension
@@ -207,7 +245,7 @@ __global__ void __launch_bounds__(kChunk)
 lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, Geometry g,
                          const unsigned long long *__restrict__ table, uint32_t mask,
                          int32_t *__restrict__ nbr, int32_t *__restrict__ chunk_counts, int n_chunks,
-                         const int32_t *__restrict__ n_out_dev) {
+                         const int32_t *__restrict__ n_out_dev, const int32_t *__restrict__ row_map) {
   const unsigned full = 0xffffffffu;
   int kappa = blockIdx.y;
   int o = blockIdx.x * kChunk + threadIdx.x;
@@ -231,6 +269,13 @@ lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int ba
       ok = ok && (unsigned)in[d] < (unsigned)g.in_shape[d];
     }
     if (ok) key = (uint32_t)(((c.x * g.in_shape[0] + in[0]) * g.in_shape[1] + in[1]) * g.in_shape[2] + in[2]);
+  }
+  if (row_map != nullptr) {  // dense row map: one load answers the query
+    const int found = key != 0xFFFFFFFFu ? __ldg(row_map + key) : -1;
+    if (o < n_out) nbr[(size_t)kappa * n_out + o] = found;
+    const int c = __syncthreads_count(o < n_out && found >= 0);
+    if (threadIdx.x == 0) chunk_counts[(size_t)kappa * n_chunks + blockIdx.x] = c;
+    return;
   }
   unsigned lane = threadIdx.x & 31u, sub = lane & 3u, gbase = lane & ~3u;
   unsigned gmask = 0xFu << gbase;
@@ -367,8 +412,17 @@ static int check_volume(int batch, const int shape[3], const char *what) {
 
 static int build_hash(const int32_t *indices, int n_in, int batch, const Geometry &g, RulebookScratch &s,
                       int32_t *status, cudaStream_t st, const int32_t *n_in_dev = nullptr) {
-  cudaMemsetAsync(s.table, 0xFF, (size_t)s.n_buckets * kBucketSlots * 8, st);
   cudaMemsetAsync(s.misc, 0, 256, st);
+  if (s.row_map != nullptr) {
+    cudaMemsetAsync(s.row_map, 0xFF, (size_t)s.in_cells * 4, st);
+    if (n_in > 0) {
+      { map_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.row_map,
+                                                            status ? status : s.misc + 1, n_in_dev); note_launches(1); }
+    }
+    SSC_CHECK_LAUNCH("map_insert");
+    return 0;
+  }
+  cudaMemsetAsync(s.table, 0xFF, (size_t)s.n_buckets * kBucketSlots * 8, st);
   if (n_in > 0) {
     { hash_insert_kernel<<<ceil_div(n_in, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.table,
                                                            s.n_buckets - 1, status ? status : s.misc + 1, n_in_dev); note_launches(1); }
@@ -385,7 +439,7 @@ static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, i
   if (n_chunks > s.n_chunks_cap) return fail(SSC_ERR_SCRATCH, "rulebook: n_out exceeds the scratch capacity");
   dim3 grid(n_chunks, K);
   { lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
-                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks, n_out_dev); note_launches(1); }
+                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks, n_out_dev, s.row_map); note_launches(1); }
   SSC_CHECK_LAUNCH("lookup_neighbours");
   if (indice_num == nullptr) return 0;
   { scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num); note_launches(1); }
@@ -493,9 +547,9 @@ namespace ssc {
 
 using namespace ssc;
 
-extern "C" size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int out_shape[3], int K) {
-  if (n_in < 0 || batch < 1 || K < 1) return 0;
-  return carve(nullptr, n_in, batch, out_shape, K).total;
+extern "C" size_t ssc_rulebook_scratch_bytes(int n_in, int batch, const int in_shape[3], const int out_shape[3], int K) {
+  if (n_in < 0 || batch < 1 || K < 1 || !in_shape || !out_shape) return 0;
+  return carve(nullptr, n_in, batch, in_shape, out_shape, K).total;
 }
 
 extern "C" int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, const int shape[3],
@@ -510,7 +564,7 @@ extern "C" int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, co
   SSC_REQUIRE(fill_geometry(g, shape, shape, ksize, one, pad, dilation, 0) == 0, "rulebook_subm: bad geometry");
   SSC_REQUIRE(g.K <= 256, "rulebook_subm: kernel volume %d > 256", g.K);
   if (int e = check_volume(batch, shape, "rulebook_subm")) return e;
-  RulebookScratch s = carve(scratch, n_in, batch, shape, g.K);
+  RulebookScratch s = carve(scratch, n_in, batch, shape, shape, g.K);
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_subm: scratch %zu < %zu bytes", scratch_bytes, s.total);
   cudaStream_t st = as_stream(stream);
@@ -533,7 +587,7 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   SSC_REQUIRE(g.K <= 256, "rulebook_conv_count: kernel volume %d > 256", g.K);
   if (int e = check_volume(batch, in_shape, "rulebook_conv_count(in)")) return e;
   if (int e = check_volume(batch, out_shape, "rulebook_conv_count(out)")) return e;
-  RulebookScratch s = carve(scratch, n_in, batch, out_shape, g.K);
+  RulebookScratch s = carve(scratch, n_in, batch, in_shape, out_shape, g.K);
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_conv_count: scratch %zu < %zu bytes", scratch_bytes, s.total);
   cudaStream_t st = as_stream(stream);
@@ -567,7 +621,7 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
   SSC_REQUIRE(fill_geometry(g, in_shape, out_shape, ksize, stride, padding, dilation, transpose) == 0,
               "rulebook_conv_fill: bad geometry");
   SSC_REQUIRE(g.K <= 256, "rulebook_conv_fill: kernel volume %d > 256", g.K);
-  RulebookScratch s = carve(scratch, n_in, batch, out_shape, g.K);
+  RulebookScratch s = carve(scratch, n_in, batch, in_shape, out_shape, g.K);
   if (scratch == nullptr || scratch_bytes < s.total)
     return fail(SSC_ERR_SCRATCH, "rulebook_conv_fill: scratch %zu < %zu bytes", scratch_bytes, s.total);
   SSC_REQUIRE((long long)n_out <= s.out_cap, "rulebook_conv_fill: n_out %d exceeds the possible maximum", n_out);

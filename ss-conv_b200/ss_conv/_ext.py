@@ -29,7 +29,7 @@ SIGNATURES = {
     "ssc_last_error": (ctypes.c_char_p, []),
     "ssc_has_tcgen05": (c_int, []),
     "ssc_kernel_launches": (ctypes.c_ulonglong, []),
-    "ssc_rulebook_scratch_bytes": (c_size_t, [c_int, c_int, _I3, c_int]),
+    "ssc_rulebook_scratch_bytes": (c_size_t, [c_int, c_int, _I3, _I3, c_int]),
     "ssc_rulebook_subm": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_size_t, c_void_p]),
     "ssc_rulebook_subm_static": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -197,12 +197,13 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
             raise ValueError("ssconv_b200: batch*volume does not fit the int32 flat index")
     if K > 256:
         raise ValueError("ssconv_b200: kernel volume %d > 256" % K)
-    skey = (n_in, int(batch_size), int(grid[0]), int(grid[1]), int(grid[2]), K)
+    skey = (n_in, int(batch_size), tuple(spatial_shape), tuple(grid), K)
     sbytes = _scratch_cache.get(skey)
     if sbytes is None:
         if len(_scratch_cache) > 4096:
             _scratch_cache.clear()
-        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(grid), K)), 256)
+        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(spatial_shape),
+                                                                             _i3(grid), K)), 256)
     scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
     small = torch.empty(K + 1, dtype=torch.int32, device=dev)   # [indice_num (K) | n_out]
     num = small[:K]
@@ -279,10 +280,13 @@ def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize,
         return None
     bound = min(n_in * K, cells)
     cap = min(bound, int(n_in * ratio * AHEAD_MARGIN) + 1024)
-    skey = (n_in, int(batch_size), int(out_shape[0]), int(out_shape[1]), int(out_shape[2]), K)
+    skey = (n_in, int(batch_size), tuple(spatial_shape), tuple(out_shape), K)
     sbytes = _scratch_cache.get(skey)
     if sbytes is None:
-        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(out_shape), K)), 256)
+        if len(_scratch_cache) > 4096:
+            _scratch_cache.clear()
+        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(spatial_shape),
+                                                                             _i3(out_shape), K)), 256)
     scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
     small = torch.empty(K + 1, dtype=torch.int32, device=dev)
     num, n_out_dev = small[:K], small[K:]

@@ -12,11 +12,19 @@ CASES = [(3, 1, 1, 1, False), (3, 2, 1, 1, False), (2, 2, 0, 1, False), (3, 1, 0
          (5, 1, 2, 1, True), (3, 3, 2, 1, False), (3, 1, 1, 2, True), (5, 2, 2, 1, False), (1, 1, 0, 1, False)]
 
 
+@pytest.mark.parametrize("table", ["dense", "hash"])
 @pytest.mark.parametrize("k,s,p,d,subm", CASES)
-def test_rulebook_matches_oracle(cuda, k, s, p, d, subm):
+def test_rulebook_matches_oracle(cuda, k, s, p, d, subm, table, monkeypatch):
+    """Both ways of finding an input row: the dense row map over the input grid and the hash table."""
+    from ss_conv import _ext
+    monkeypatch.setenv("SSC_RULEBOOK_TABLE", table)
+    _ext._scratch_cache.clear()            # scratch sizes depend on the table kind
     rng = np.random.RandomState(k * 100 + s * 10 + p + d)
     ind = random_voxels(rng, 3, 14, 300)
-    got = gpu_rulebook(ind, 3, [14] * 3, k, s, p, d, subm, cuda)
+    try:
+        got = gpu_rulebook(ind, 3, [14] * 3, k, s, p, d, subm, cuda)
+    finally:
+        _ext._scratch_cache.clear()
     ref = O.get_indice_pairs(ind, 3, [14] * 3, k, s, p, d, subm)
     assert_rulebook_equal(got, ref)
     from ss_conv import _ext

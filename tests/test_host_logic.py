@@ -35,7 +35,7 @@ def test_argument_errors_without_gpu():
     from ss_conv import _ext
     L = _ext.lib()
     I3 = ctypes.c_int * 3
-    assert L.ssc_rulebook_scratch_bytes(1000, 2, I3(16, 16, 16), 27) > 1000 * 2 * 8
+    assert L.ssc_rulebook_scratch_bytes(1000, 2, I3(16, 16, 16), I3(16, 16, 16), 27) > 1000 * 2 * 8
     assert L.ssc_conv_packed_bytes(27, 64, 76, _ext.PREC_TF32) == 27 * 2 * 80 * 128
     assert L.ssc_conv_packed_bytes(27, 64, 600, _ext.PREC_TF32) == 0
     rc = L.ssc_maxpool_fwd(None, 0, None, 27, 5, None, None, None)

@@ -38,7 +38,7 @@ def _both(L, ext, ind_np, batch, shape, ksize, dilation, dev):
             rc = L.ssc_rulebook_subm_static(ptr(ind), n, batch, I3(*shape), I3(*ksize), I3(*dilation), ptr(nbr),
                                             ptr(pairs), ptr(num), ptr(status), stream)
         else:
-            nbytes = L.ssc_rulebook_scratch_bytes(n, batch, I3(*shape), K)
+            nbytes = L.ssc_rulebook_scratch_bytes(n, batch, I3(*shape), I3(*shape), K)
             scratch = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
             rc = L.ssc_rulebook_subm(ptr(ind), n, batch, I3(*shape), I3(*ksize), I3(*dilation), ptr(nbr), ptr(pairs),
                                      ptr(num), ptr(status), ptr(scratch), scratch.numel(), stream)
