@@ -1,6 +1,7 @@
 """Pooling layers (interface of SS_Conv_lib/ss_conv/pool.py:15-92)."""
 import torch.nn as nn
 
+from ss_conv.sp_ops import tensor as tensor_mod
 from ss_conv.sp_ops.tensor import SparseTensor
 from ss_conv.sp_ops.pool import SparseAvgPool, SparseMaxPool
 from ss_conv.sp_ops.functional import global_avgpool, global_maxpool
@@ -27,8 +28,8 @@ class _GlobalPool(nn.Module):
                 # queue the pooling on the rows as they are, then read the pending counts back;
                 # only a tensor that had to be recomputed is pooled again
                 out = type(self).func(inputs.raw()[0], inputs.get_offsets().detach())
-                if not inputs.resolve():
-                    return out
+                if tensor_mod._capture_log is not None or not inputs.resolve():
+                    return out          # (while recording a CUDA graph the counts are checked by the replaying side)
             feats = inputs.features
             offsets = inputs.get_offsets() if offsets is None else offsets
         else:

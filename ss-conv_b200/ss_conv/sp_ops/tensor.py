@@ -14,6 +14,12 @@ def scatter_nd(indices, updates, shape):
     return ret
 
 
+# While a chain of layers is being recorded into a CUDA graph (ss_conv.graph) nothing may wait for
+# the device: resolving a pending count raises, and every PendingRows created is logged so that
+# the replaying side can check the counts against the capacities afterwards.
+_capture_log = None
+
+
 class PendingRows(object):
     """Row set of a SparseTensor whose size is still on the device.
 
@@ -32,6 +38,8 @@ class PendingRows(object):
         self.n_dev, self.capacity, self.parent, self.redo, self.note = n_dev, int(capacity), parent, redo, note
         self.post = []
         self.grad = torch.is_grad_enabled()   # a recomputation runs in the mode the layer was called in
+        if _capture_log is not None:
+            _capture_log.append(self)
 
 
 class SparseTensor(object):
@@ -82,6 +90,9 @@ class SparseTensor(object):
         r = self._rows
         if r is None:
             return False
+        if _capture_log is not None:
+            raise RuntimeError("a row count cannot be read back while a CUDA graph is being recorded: this layer "
+                               "needs exact row counts and cannot be part of a captured chain")
         parent_changed = r.parent.resolve() if r.parent is not None else False
         n = int(r.n_dev.item())
         if r.note is not None:

@@ -257,3 +257,64 @@ def test_pending_row_counts_chain_through_a_network(cuda, monkeypatch):
     for got in (first, chained, overflowed, again):
         for g, e in zip(got, exact):
             np.testing.assert_array_equal(g, e)
+
+
+def test_graphed_chain_replays_match_eager_results(cuda):
+    """conv -> BN -> gate -> max pool (-> global pool) recorded as one CUDA graph and replayed on
+    batches of different sizes equals the eager exact results; a batch that overflows a capacity
+    falls back to the exact path and the graph is recorded again."""
+    from ss_conv import _ext
+    from ss_conv.activation import Activation
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.convolution import Convolution
+    from ss_conv.graph import GraphedChain
+    from ss_conv.pool import GlobalAvgPool, MaxPool
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(4)
+    Rs_in, Rs_out = [(2, 0), (1, 1)], [(4, 0), (2, 1)]
+    gated = Rs_out + [(2, 0)]
+    conv = Convolution(Rs_in, gated, 3, stride=2, padding=1).to(cuda).eval()
+    bn = BatchNorm(gated).to(cuda).eval()
+    act = Activation(Rs_out, (torch.relu, torch.sigmoid), bias=False, checkpoint=False)
+    pool, gpool = MaxPool(2, stride=2), GlobalAvgPool()
+
+    def sparse_net(x):
+        return pool(act(bn(conv(x))))
+
+    def dense_net(x):
+        return gpool(sparse_net(x))
+
+    batches = []
+    for r, occ in enumerate((0.10, 0.06, 0.12, 0.10)):
+        ind = S.bernoulli_voxels(range(3), 20, occ, base_seed=50 + 3 * r)
+        batches.append((dev(S.features(ind.shape[0], 5, 60 + r), cuda), dev(ind, cuda)))
+    cap = max(i.shape[0] for _, i in batches)
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            want = []
+            for f, i in batches:
+                y = sparse_net(SparseTensor(f, i, [20] * 3, 3))
+                want.append((y.features.clone(), y.indices.clone(), dense_net(SparseTensor(f, i, [20] * 3, 3)).clone()))
+            g_sparse = GraphedChain(sparse_net, [20] * 3, 3, 5, cap, cuda)
+            g_dense = GraphedChain(dense_net, [20] * 3, 3, 5, cap, cuda)
+            for rep in range(2):
+                for (f, i), (wf, wi, wd) in zip(batches, want):
+                    y = g_sparse(f, i)
+                    assert torch.equal(y.indices, wi) and torch.equal(y.features, wf)
+                    assert torch.equal(g_dense(f, i), wd)
+            assert g_sparse.replays == 8 and g_sparse.launches > 10
+            # a much denser batch overflows the recorded capacities: exact fallback, then a new graph
+            ind = S.bernoulli_voxels(range(3), 20, 0.45, base_seed=99)
+            f, i = dev(S.features(ind.shape[0], 5, 7), cuda), dev(ind, cuda)
+            big = GraphedChain(sparse_net, [20] * 3, 3, 5, ind.shape[0], cuda)
+            big(*[t[:batches[1][1].shape[0]] for t in batches[1]])           # records with a sparse batch
+            ref = sparse_net(SparseTensor(f, i, [20] * 3, 3))
+            for _ in range(2):
+                y = big(f, i)
+                assert torch.equal(y.indices, ref.indices) and torch.equal(y.features, ref.features)
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
