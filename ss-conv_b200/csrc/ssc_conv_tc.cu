@@ -52,6 +52,8 @@ struct TcParams {
   int stages;     // operand ring depth = number of producer warps (>= 4)
   int threads;    // (stages + 1) * 32
   int b_bytes;    // n_pad * 128
+  int sps;        // 32-channel slabs per ring slot (a step covers sps slabs of one kernel offset)
+  int k_groups;   // ceil(k_slabs / sps) = steps per kernel offset
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
@@ -65,7 +67,16 @@ static bool tc_params(int c_in, int c_out, TcParams &p) {
   p.tmem_cols = 32;
   while (p.tmem_cols < p.n_pad) p.tmem_cols <<= 1;
   p.b_bytes = p.n_pad * 128;
-  int stage = TC_A_BYTES + p.b_bytes;
+  // Two slabs per step (SSC_TC_SPS=2) halve the per-step work that does not move data (neighbour
+  // look-ups, row masks, barrier hand-shakes) but also the resident CTAs; measured slower on the
+  // 64 -> 76 channel layer (0.21 vs 0.18 ms), so one slab per step is the default.
+  p.sps = 1;
+  if (const char *e = getenv("SSC_TC_SPS")) {
+    int v = atoi(e);
+    if (v == 1 || (v == 2 && p.k_slabs >= 2)) p.sps = v;
+  }
+  p.k_groups = (p.k_slabs + p.sps - 1) / p.sps;
+  int stage = p.sps * (TC_A_BYTES + p.b_bytes);
   int fixed = TC_CTRL_BYTES + 1024;
   // Resident CTAs hide each other's per-step latencies, so take as many per SM as tensor
   // memory (512 columns) and shared memory (two ring slots each at least) allow, up to four.
@@ -160,7 +171,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   extern __shared__ uint8_t smem_raw[];
   // operand stages need 1024-byte alignment for the 128-byte swizzle
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const int stage_bytes = TC_A_BYTES + p.b_bytes;
+  const int stage_bytes = p.sps * (TC_A_BYTES + p.b_bytes);   // [sps x gathered slab][sps x filter slab]
   uint8_t *ctrl = smem + (size_t)p.stages * stage_bytes;
   uint64_t *empty_bars = (uint64_t *)ctrl;                 // [stages] slot free (its MMAs retired)
   uint64_t *fulla_bars = (uint64_t *)(ctrl + 64);          // [stages] gathered rows ready
@@ -241,7 +252,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   __syncthreads();
   tc_fence_after();
   const int n_act = *n_act_s;
-  const int n_iter = n_act * p.k_slabs;
+  const int n_iter = n_act * p.k_groups;
   const uint32_t smem_base = smem_u32(smem);
 
   const int n_prod = S < TC_EPI_WARPS ? (TC_EPI_WARPS / S) * S : S;  // producer warps (2 slots -> 4 warps)
@@ -266,7 +277,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     uint32_t par = 0;          // parity of the slot's current use
     int src[4], nxt[4];
     auto load_rows = [&](int j, int *dst) {
-      const int kap = act_list[j / p.k_slabs];
+      const int kap = act_list[j / p.k_groups];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         int r = m0 + q * 32 + lane;
@@ -275,7 +286,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     };
     if (slot < n_iter) load_rows(slot, nxt);
     for (int j = slot; j < n_iter; j += S) {
-      const int act = j / p.k_slabs, slab = j - act * p.k_slabs;
+      const int act = j / p.k_groups, slab0 = (j - act * p.k_groups) * p.sps;
+      const int n_sub = min(p.sps, p.k_slabs - slab0);   // slabs of this step
       const int kappa = act_list[act];
 #pragma unroll
       for (int q = 0; q < 4; ++q) src[q] = nxt[q];
@@ -285,26 +297,27 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         tc_fence_after();
       }
       if (part == 0 && lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
-        const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
-        const uint32_t bar = smem_u32(fullb_bars + slot);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)p.b_bytes) : "memory");
+        const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab0) * (size_t)(p.n_pad * 8);
+        const uint32_t bar = smem_u32(fullb_bars + slot), nbytes = (uint32_t)(n_sub * p.b_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbytes) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                         slot_addr + TC_A_BYTES),
-                     "l"(bsrc), "r"((uint32_t)p.b_bytes), "r"(bar)
+                         slot_addr + (uint32_t)(p.sps * TC_A_BYTES)),
+                     "l"(bsrc), "r"(nbytes), "r"(bar)
                      : "memory");
       }
-      const int ch0 = slab * TC_SLAB;
       uint32_t present = 0;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {  // rows of this step that the MMA must leave alone
         const unsigned have = __ballot_sync(0xffffffffu, src[q] >= 0);
         if (lane == 0 && q >= q0 && q < q0 + q_per) slot_masks[slot * 4 + q] = ~have;
       }
+      for (int ss = 0; ss < n_sub; ++ss) {
+      const int ch0 = (slab0 + ss) * TC_SLAB;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         if (src[q] >= 0 && ch0 < c_in) {
           const float *fp = features + (size_t)src[q] * c_in + ch0;
-          const uint32_t a_row = slot_addr + row_off[q];
+          const uint32_t a_row = slot_addr + (uint32_t)(ss * TC_A_BYTES) + row_off[q];
           if (vec_ok) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {  // chunks past the last channel are zero-filled
@@ -325,13 +338,15 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
           present |= 1u << q;
         }
       }
+      }
       cp_async_commit();
       cp_async_wait(0);
       // copies landed: round the gathered rows to TF32 in place
+      for (int ss = 0; ss < (STAGED ? 0 : n_sub); ++ss)
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         if (!STAGED && (present & (1u << q))) {
-          uint8_t *row = slot_ptr + row_off[q];
+          uint8_t *row = slot_ptr + (size_t)ss * TC_A_BYTES + row_off[q];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             uint4 *ptr = (uint4 *)(row + ((c ^ sw) << 4));
@@ -356,18 +371,25 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     const uint32_t a_lo0 = desc_lo(smem_base), slot_step = (uint32_t)stage_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
     const uint32_t fulla0 = smem_u32(fulla_bars), fullb0 = smem_u32(fullb_bars), empty0 = smem_u32(empty_bars);
     uint32_t s = 0, par = 0, a_lo = a_lo0;
+    int grp = 0;  // which slab group of its kernel offset the current step is
     for (int it = 0; it < n_iter; ++it) {
       if (!mbar_wait(fulla0 + s * 8u, par, abort_flag)) break;
       if (!mbar_wait(fullb0 + s * 8u, par, abort_flag)) break;
       tc_fence_after();
       const uint4 off = *(const uint4 *)(slot_masks + s * 4u);  // rows to leave untouched
-      for (int nt = 0; nt < p.n_tiles; ++nt) {
-        const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n), bn = a_lo + (TC_A_BYTES >> 4) + (uint32_t)nt * n_step;
-        mma_tf32_ss_masked(dn, a_lo, bn, idesc, off);
-        mma_tf32_ss_masked(dn, a_lo + 2u, bn + 2u, idesc, off);
-        mma_tf32_ss_masked(dn, a_lo + 4u, bn + 4u, idesc, off);
-        mma_tf32_ss_masked(dn, a_lo + 6u, bn + 6u, idesc, off);
+      const int n_sub = min(p.sps, p.k_slabs - grp * p.sps);
+      for (int ss = 0; ss < n_sub; ++ss) {
+        const uint32_t an = a_lo + (uint32_t)ss * (TC_A_BYTES >> 4);
+        for (int nt = 0; nt < p.n_tiles; ++nt) {
+          const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n);
+          const uint32_t bn = a_lo + (uint32_t)(p.sps * TC_A_BYTES >> 4) + (uint32_t)ss * ((uint32_t)p.b_bytes >> 4) + (uint32_t)nt * n_step;
+          mma_tf32_ss_masked(dn, an, bn, idesc, off);
+          mma_tf32_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
+          mma_tf32_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
+          mma_tf32_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+        }
       }
+      if (++grp == p.k_groups) grp = 0;
       mma_commit(empty0 + s * 8u);
       a_lo += slot_step;
       if (++s == (uint32_t)S) { s = 0; par ^= 1u; a_lo = a_lo0; }
@@ -426,7 +448,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 }
 
 static size_t tc_smem_bytes(const TcParams &p) {
-  return (size_t)p.stages * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES;
+  return (size_t)p.stages * p.sps * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES;
 }
 
 // Smallest problem (in 128-row tiles) the persistent gather4 kernel is used for by default: below
