@@ -269,6 +269,13 @@ int ssc_voxelize_fwd(const float *feats, float *out, const int32_t *maps, int mo
  * ascending (b,x,y,z) order, inverse [N], and the voxel features (mode 1 first / 2 last /
  * 3 sum / 4 mean over points in ascending point id). */
 size_t ssc_p2v_scratch_bytes(int n_point, int batch, const int grid[3]);
+/* One pass over a point batch telling the host which path Point2Voxel can take
+ * (SS_Conv_lib/ss_conv/sp_ops/voxelize.py:38-84 answers the same questions with two torch.unique
+ * calls, a sort and three read-backs): stats_dev[0] = points outside the grid, [1] = places where
+ * batch_ids decreases, [2] = places where it changes (distinct samples - 1 when sorted), [3] = the
+ * last batch id. */
+int ssc_p2v_stats(const float *points, const int32_t *batch_ids, int n_point, const int grid[3],
+                  const float unit[3], int32_t *stats_dev, void *stream);
 int ssc_p2v_count(const float *points, const int32_t *batch_ids, int n_point, int batch,
                   const int grid[3], const float unit[3], int32_t *n_voxel_dev, int32_t *status,
                   void *scratch, size_t scratch_bytes, void *stream);

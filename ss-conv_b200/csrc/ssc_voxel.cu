@@ -123,6 +123,36 @@ __global__ void p2v_mark_kernel(const float *__restrict__ points, const int32_t 
   atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
 }
 
+// What the host needs to know about a point batch before voxelizing it, in one pass:
+// stats[0] points outside the grid (|p| > half extent or cell index out of range),
+// stats[1] positions where the batch id decreases, stats[2] positions where it changes,
+// stats[3] the last batch id.
+__global__ void p2v_stats_kernel(const float *__restrict__ points, const int32_t *__restrict__ batch_ids, int n,
+                                 VoxelGrid g, int32_t *stats) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool out = false, down = false, change = false;
+  if (i < n) {
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      const float p = points[i * 3 + d];
+      const int c = (int)__fdiv_rn(__fadd_rn(p, g.half[d]), g.unit[d]);
+      out = out || fabsf(p) > g.half[d] || (unsigned)c >= (unsigned)g.grid[d];
+    }
+    if (i > 0) {
+      const int a = batch_ids[i - 1], b = batch_ids[i];
+      down = b < a;
+      change = b != a;
+    }
+    if (i == n - 1) stats[3] = batch_ids[i];
+  }
+  const int n_out = __syncthreads_count(out), n_down = __syncthreads_count(down), n_change = __syncthreads_count(change);
+  if (threadIdx.x == 0) {
+    if (n_out) atomicAdd(stats + 0, n_out);
+    if (n_down) atomicAdd(stats + 1, n_down);
+    if (n_change) atomicAdd(stats + 2, n_change);
+  }
+}
+
 __global__ void p2v_inverse_kernel(const float *__restrict__ points, const int32_t *__restrict__ batch_ids, int n,
                                    int batch, VoxelGrid g, const uint32_t *__restrict__ bitmap,
                                    const uint32_t *__restrict__ word_prefix, int mode, int32_t *inverse,
@@ -337,6 +367,20 @@ extern "C" int ssc_voxelize_fwd(const float *feats, float *out, const int32_t *m
 extern "C" size_t ssc_p2v_scratch_bytes(int n_point, int batch, const int grid[3]) {
   if (n_point < 0 || batch < 1 || !grid) return 0;
   return carve_p2v(nullptr, n_point, batch, grid).total;
+}
+
+extern "C" int ssc_p2v_stats(const float *points, const int32_t *batch_ids, int n_point, const int grid[3],
+                             const float unit[3], int32_t *stats_dev, void *stream) {
+  SSC_REQUIRE(n_point >= 0 && grid && unit && stats_dev, "p2v_stats: bad arguments");
+  cudaStream_t st = as_stream(stream);
+  cudaMemsetAsync(stats_dev, 0, 4 * sizeof(int32_t), st);
+  if (n_point == 0) return SSC_OK;
+  SSC_REQUIRE(points && batch_ids, "p2v_stats: null pointer");
+  VoxelGrid g;
+  fill_grid(g, grid, unit);
+  { p2v_stats_kernel<<<ceil_div(n_point, 256), 256, 0, st>>>(points, batch_ids, n_point, g, stats_dev); note_launches(1); }
+  SSC_CHECK_LAUNCH("p2v_stats");
+  return SSC_OK;
 }
 
 extern "C" int ssc_p2v_count(const float *points, const int32_t *batch_ids, int n_point, int batch, const int grid[3],

@@ -58,6 +58,7 @@ SIGNATURES = {
     "ssc_global_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_voxelize_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_three_interpolate_bwd": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ssc_p2v_stats": (c_int, [c_void_p, c_void_p, c_int, _I3, _F3, c_void_p, c_void_p]),
     "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_summary_rf": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
@@ -684,6 +685,15 @@ def voxelize_bp(d_output_feats, d_feats, map_rule, mode, n_voxel, max_active, c)
 voxelize_idx = _not_built("voxelize_idx")
 point_recover_fp = _not_built("point_recover_fp")
 point_recover_bp = _not_built("point_recover_bp")
+
+
+def p2v_stats(points, batch_ids, grid, unit):
+    """[n outside the grid, n places where batch_ids decreases, n places where it changes, last id]
+    of a point batch (one kernel, one read-back)."""
+    stats = torch.empty(4, dtype=torch.int32, device=points.device)
+    _check(lib().ssc_p2v_stats(_p(points, torch.float32), _p(batch_ids, torch.int32), points.shape[0], _i3(grid),
+                               _F3(*[float(u) for u in unit]), _p(stats), _stream()))
+    return stats.tolist()
 
 
 def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode):

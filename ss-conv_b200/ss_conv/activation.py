@@ -102,7 +102,9 @@ class Activation(nn.Module):
     def forward(self, input):
         if self.scalar_act is None and self.gate_act is None:
             return input
-        input.features = self._gate(input.raw()[0])   # row-wise: fine on a pending row count
+        aff = input._take_affine()                    # a batch norm's scale / shift still to be applied
+        x = input.raw()[0]                            # row-wise: fine on a pending row count
+        input.features = self._gate(x) if aff is None else self._gate(x, aff[0], aff[1])
         if input.pending():
             input._rows.post.append(self._gate)
         return input

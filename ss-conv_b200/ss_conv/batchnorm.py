@@ -139,7 +139,10 @@ class BatchNorm(nn.Module):
         def apply(f):
             return _ext.bn_gate_forward(f, scale, shift, None, f.size(1), 0, 0, 0, None, None)
 
-        input.features = apply(x)
+        if self.training:
+            input.features = apply(x)
+        else:
+            input._affine = (scale, shift)   # applied by the next reader, fused into a gated Activation if that is next
         if input.pending():
             input._rows.post.append(apply)
         return input

@@ -51,20 +51,37 @@ class SparseTensor(object):
         self._features = features
         self._indices = indices if indices.dtype == torch.int32 else indices.int()
         self._rows = None
+        self._affine = None       # (scale, shift) of an eval-mode batch norm not applied yet, see _flush_affine
         self.spatial_shape = spatial_shape
         self.batch_size = batch_size
         self.indice_dict = {}
         self.grid = grid
 
     # -- features / indices resolve a pending row count on first access ---------------------
+    def _flush_affine(self):
+        """An eval-mode BatchNorm only records its per-channel scale / shift on the tensor so that a
+        gated Activation that follows can apply both in one pass; anybody else who looks at the
+        features gets them applied here first."""
+        if self._affine is not None:
+            scale, shift = self._affine
+            self._affine = None
+            self._features = _ext.bn_gate_forward(self._features, scale, shift, None, self._features.size(1), 0, 0, 0,
+                                                  None, None)
+
+    def _take_affine(self):
+        aff, self._affine = self._affine, None
+        return aff
+
     @property
     def features(self):
+        self._flush_affine()
         if self._rows is not None:
             self.resolve()
         return self._features
 
     @features.setter
     def features(self, value):
+        self._affine = None
         self._features = value
 
     @property
@@ -83,10 +100,12 @@ class SparseTensor(object):
     def raw(self):
         """(features, indices, n_dev): the buffers as they are; n_dev is None for an exact tensor,
         else the device word with the number of meaningful rows."""
+        self._flush_affine()
         return self._features, self._indices, (self._rows.n_dev if self._rows is not None else None)
 
     def resolve(self):
         """Make the tensor exact.  Returns True when its contents had to be recomputed."""
+        self._flush_affine()
         r = self._rows
         if r is None:
             return False

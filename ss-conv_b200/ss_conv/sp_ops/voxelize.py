@@ -58,6 +58,23 @@ class Point2Voxel(nn.Module):
         assert point_cloud.dim() == 2
         device = point_cloud.device
         C = feature.size(1)
+        grid_i = [int(v) for v in self.voxel_num_limit]
+        unit_f = [float(u) for u in self.unit_voxel_extent]
+        if (point_cloud.is_cuda and point_cloud.dtype == torch.float32 and point_cloud.shape[0] > 0
+                and batch_ids.dtype in (torch.int32, torch.int64) and point_cloud.is_contiguous()):
+            # the common case - every point inside the grid, batch ids already sorted - needs none of
+            # the filtering / unique / sort steps below: one kernel and one read-back find that out
+            ids32 = batch_ids.contiguous() if batch_ids.dtype == torch.int32 else batch_ids.int()
+            n_outside, n_down, n_change, last_id = _ext.p2v_stats(point_cloud, ids32, grid_i, unit_f)
+            if n_outside == 0 and n_down == 0 and last_id >= 0:
+                B1 = n_change + 1
+                fts = feature.float().contiguous()
+                vox, _inverse, vfeat = _ext.point2voxel(point_cloud, fts, ids32, max(last_id + 1, B1), grid_i, unit_f,
+                                                        self.voxelization_mode)
+                if torch.is_grad_enabled() and feature.requires_grad:
+                    vfeat = _VoxelFeatures.apply(fts, vfeat, _inverse, self.voxelization_mode)
+                sparse = SparseTensor(vfeat, vox, self.voxel_num_limit.astype(np.int64), B1)
+                return point_cloud, sparse, batch_ids, torch.ones(B1, dtype=torch.float32, device=device)
         origin_ids = torch.unique(batch_ids)
         B1 = origin_ids.size(0)
         unit = self.unit_voxel_extent.reshape(1, 3).to(device)
