@@ -481,10 +481,11 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   int grid = ceil_div(n_out, TC_M);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).
-  const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_in * sizeof(float);
+  const int c_pad = (c_in + 3) & ~3;  // row stride of the staged image (zero-padded channels)
+  const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_pad * sizeof(float);
   const char *no_stage = getenv("SSC_TC_NO_STAGING");
-  const bool staged = scratch != nullptr && scratch_bytes >= stage_need && (c_in & 3) == 0 && ((uintptr_t)scratch & 15u) == 0 &&
-                      ((uintptr_t)features & 15u) == 0 && grid >= kStagingMinTiles && no_stage == nullptr;
+  const bool staged = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0 &&
+                      grid >= kStagingMinTiles && no_stage == nullptr;
   if (staged) {
     int rc = stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
@@ -492,7 +493,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
-  { kernel<<<grid, p.threads, smem, st>>>(staged ? (const float *)scratch : features, c_in, (const uint4 *)packed, K, c_out,
+  { kernel<<<grid, p.threads, smem, st>>>(staged ? (const float *)scratch : features, staged ? c_pad : c_in, (const uint4 *)packed, K, c_out,
                                         nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;

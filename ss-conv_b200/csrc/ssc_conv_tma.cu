@@ -378,20 +378,40 @@ static bool g4_params(int c_in, int c_out, G4Params &p) {
   return p.a_slots >= 2;
 }
 
-// staged = TF32-rounded copy of features [n_in, c_in] plus one all-zero row.
+// Same for channel counts that are not a multiple of four: rows padded with zeros to c_pad floats.
+__global__ void stage_features_padded_kernel(const float *__restrict__ in, long long n_rows, int c_in, int c_pad,
+                                             long long total, uint32_t *__restrict__ out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const long long r = i / c_pad;
+    const int c = (int)(i - r * c_pad);
+    out[i] = (r < n_rows && c < c_in) ? to_tf32(__ldg(in + r * c_in + c)) : 0u;
+  }
+}
+
+// staged = TF32-rounded copy of features [n_in, c_in] plus one all-zero row; the row stride is
+// c_in rounded up to a multiple of four floats (16-byte copies in the convolution kernel).
 int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st) {
-  const long long n_vec = (long long)n_in * c_in / 4, total_vec = ((long long)n_in + 1) * c_in / 4;
-  int blocks = ceil_div(total_vec, 256 * 4);
-  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-  { stage_features_kernel<<<blocks, 256, 0, st>>>((const float4 *)features, n_vec, total_vec, (uint4 *)staged); note_launches(1); }
+  const int c_pad = (c_in + 3) & ~3;
+  if (c_pad == c_in && ((uintptr_t)features & 15u) == 0) {
+    const long long n_vec = (long long)n_in * c_in / 4, total_vec = ((long long)n_in + 1) * c_in / 4;
+    int blocks = ceil_div(total_vec, 256 * 4);
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    { stage_features_kernel<<<blocks, 256, 0, st>>>((const float4 *)features, n_vec, total_vec, (uint4 *)staged); note_launches(1); }
+  } else {
+    const long long total = ((long long)n_in + 1) * c_pad;
+    int blocks = ceil_div(total, 256 * 4);
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    { stage_features_padded_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, c_pad, total, (uint32_t *)staged); note_launches(1); }
+  }
   SSC_CHECK_LAUNCH("stage_features");
   return SSC_OK;
 }
 
 size_t conv_gather4_scratch_bytes(int n_in, int c_in, int c_out) {
   (void)c_out;
-  if ((c_in & 3) != 0) return 0;
-  return ((size_t)n_in + 1) * (size_t)c_in * sizeof(float);
+  return ((size_t)n_in + 1) * (size_t)((c_in + 3) & ~3) * sizeof(float);
 }
 
 // returns -1 when this variant does not apply (the caller then uses another kernel)
@@ -399,7 +419,7 @@ int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void 
                           const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch,
                           size_t scratch_bytes, cudaStream_t st) {
   G4Params p;
-  if (!g4_params(c_in, c_out, p)) return -1;
+  if (!g4_params(c_in, c_out, p)) return -1;   // (requires c_in % 4 == 0, so the staged row stride is c_in)
   const size_t need = ((size_t)n_in + 1) * (size_t)c_in * sizeof(float);
   if (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch & 127u) != 0) return -1;
   EncodeTiledFn encode = encode_tiled_fn();

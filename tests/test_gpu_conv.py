@@ -194,16 +194,18 @@ def test_conv_tma_gather_variant(cuda, c_in, c_out, k, subm, monkeypatch):
     assert _ext.kernel_launches() - l0 >= 3        # staging + conv (+ packing, + rulebook)
 
 
-def test_conv_staged_rows_give_the_same_bits(cuda, monkeypatch):
-    """Rounding the feature rows to TF32 once in a staging buffer, or after every gather,
-    feeds the tensor core the same operands: the results are bit-identical."""
+@pytest.mark.parametrize("c_in,c_out", [(64, 76), (3, 36), (30, 20)])
+def test_conv_staged_rows_give_the_same_bits(cuda, monkeypatch, c_in, c_out):
+    """Rounding the feature rows to TF32 once in a staging buffer (rows zero-padded to a multiple of
+    four channels), or after every gather, feeds the tensor core the same operands: the results
+    are bit-identical."""
     from ss_conv import _ext
     rng = np.random.RandomState(77)
     ind = random_voxels(rng, 4, 16, 2500)
     monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 1 << 30)
-    plain, _ = _run(cuda, ind, 4, 16, 3, 1, 1, True, 64, 76, "tf32")
+    plain, _ = _run(cuda, ind, 4, 16, 3, 1, 1, True, c_in, c_out, "tf32")
     monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 0)
-    staged, ref = _run(cuda, ind, 4, 16, 3, 1, 1, True, 64, 76, "tf32")
+    staged, ref = _run(cuda, ind, 4, 16, 3, 1, 1, True, c_in, c_out, "tf32")
     assert ind.shape[0] >= 64 * 128                # large enough for the library to stage
     np.testing.assert_array_equal(plain, staged)
     assert rel_err(staged, ref) <= TOL["tf32"]
