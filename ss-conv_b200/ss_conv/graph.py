@@ -32,6 +32,7 @@ class GraphedChain(object):
         self.graph = None
         self.launches = 0           # kernel launches recorded in the graph (= per replay)
         self.replays = 0
+        self.fallbacks = 0          # replays whose row counts overflowed a capacity (recomputed eagerly)
 
     def _eager(self, features, indices, ahead):
         old = _ext.AHEAD
@@ -81,6 +82,7 @@ class GraphedChain(object):
         counts = self.counts.tolist()                # the one read-back of the batch
         if any(c > cap for c, cap in zip(counts, self.caps)):
             self.graph = None                        # record again (with the raised hints) next time
+            self.fallbacks += 1
             return self._eager(features, indices, False)
         out = self.out
         if isinstance(out, SparseTensor):
