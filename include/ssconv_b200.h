@@ -269,6 +269,17 @@ int ssc_voxelize_fwd(const float *feats, float *out, const int32_t *maps, int mo
  * ascending (b,x,y,z) order, inverse [N], and the voxel features (mode 1 first / 2 last /
  * 3 sum / 4 mean over points in ascending point id). */
 size_t ssc_p2v_scratch_bytes(int n_point, int batch, const int grid[3]);
+/* Feature steering (Feature_Steering_Module._transform_points / _transform_feats,
+ * Common_utils/ss_conv_modules.py:198-224): new_points[p] = (points[p] - trans[b]) . rot[b]
+ * (divided by scale[b] + 1e-8 when scale is given), new_feats[p, block] = feats[p, block] . D_b for
+ * every irrep block, b = ids[p].  rot [B,3,3], trans [B,3], scale [B] or NULL; dmats [B, d_stride]
+ * holds the sample's D^l matrices (row-major, one per order l) back to back; chan [C,3] gives per
+ * channel (first channel of its block, block width 2l+1, offset of D^l inside a dmats row). */
+int ssc_steer_fwd(const float *points, const float *feats, const int32_t *ids, const float *rot,
+                  const float *trans, const float *scale, const float *dmats, int d_stride,
+                  const int32_t *chan, int n, int c, int n_sample, float *new_points, float *new_feats,
+                  void *stream);
+
 /* One pass over a point batch telling the host which path Point2Voxel can take
  * (SS_Conv_lib/ss_conv/sp_ops/voxelize.py:38-84 answers the same questions with two torch.unique
  * calls, a sort and three read-backs): stats_dev[0] = points outside the grid, [1] = places where

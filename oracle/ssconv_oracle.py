@@ -630,3 +630,31 @@ def three_interpolate_bp(grad_out, idx, weight, m):
     for j in range(3):
         np.add.at(g, idx[:, j], grad_out.astype(np.float64) * weight[:, j:j + 1].astype(np.float64))
     return g
+
+
+# ------------------------------------------------------------------------ feature steering
+def steer_points(points, ids, rot, trans, scale=None):
+    """Common_utils/ss_conv_modules.py:198-208 (_transform_points): (p - t_b) @ R_b, divided by
+    (s_b + 1e-8) when a scale is given."""
+    p = (np.asarray(points, np.float32) - trans[ids])[:, None, :] @ rot[ids]
+    p = p[:, 0, :]
+    if scale is not None:
+        p = p / (np.asarray(scale, np.float32)[ids].reshape(-1, 1) + np.float32(1e-8))
+    return p.astype(np.float32)
+
+
+def steer_feats(feats, ids, d_mats, irrep):
+    """Common_utils/ss_conv_modules.py:210-224 (_transform_feats): every copy of every order-l
+    block of a feature row is multiplied from the right by D^l of the row's sample
+    (d_mats[l]: [B, 2l+1, 2l+1])."""
+    f = np.asarray(feats, np.float32)
+    out = np.empty_like(f)
+    dim = 0
+    for l, m in enumerate(irrep):
+        D = np.asarray(d_mats[l], np.float32)[ids]
+        for _ in range(int(m)):
+            w = 2 * l + 1
+            out[:, dim:dim + w] = (f[:, None, dim:dim + w] @ D)[:, 0, :]
+            dim += w
+    assert dim == f.shape[1]
+    return out

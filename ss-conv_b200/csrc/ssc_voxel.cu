@@ -369,6 +369,55 @@ extern "C" size_t ssc_p2v_scratch_bytes(int n_point, int batch, const int grid[3
   return carve_p2v(nullptr, n_point, batch, grid).total;
 }
 
+// Feature steering: every point is moved into the frame of its sample, new_p = (p - t_b) . R_b
+// (/ (s_b + 1e-8)), and every irrep block of its feature row is multiplied from the right by the
+// sample's representation matrix D^l_b.  One thread per (point, output channel or coordinate).
+__global__ void steer_kernel(const float *__restrict__ points, const float *__restrict__ feats,
+                             const int32_t *__restrict__ ids, const float *__restrict__ rot, const float *__restrict__ trans,
+                             const float *__restrict__ scale, const float *__restrict__ dmats, int d_stride,
+                             const int32_t *__restrict__ chan, int n, int c, int n_sample, float *__restrict__ new_points,
+                             float *__restrict__ new_feats) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int width = c + 3;
+  if (t >= (long long)n * width) return;
+  const int p = (int)(t / width), k = (int)(t - (long long)p * width);
+  const int b = ids[p];
+  if ((unsigned)b >= (unsigned)n_sample) {  // foreign batch id: leave a defined value
+    if (k < c) new_feats[(size_t)p * c + k] = 0.f;
+    else new_points[(size_t)p * 3 + (k - c)] = 0.f;
+    return;
+  }
+  if (k >= c) {
+    const int j = k - c;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) acc += (points[(size_t)p * 3 + i] - trans[b * 3 + i]) * rot[b * 9 + i * 3 + j];
+    if (scale) acc = acc / (scale[b] + 1e-8f);
+    new_points[(size_t)p * 3 + j] = acc;
+    return;
+  }
+  const int start = chan[k * 3 + 0], d = chan[k * 3 + 1], off = chan[k * 3 + 2];
+  const int j = k - start;
+  const float *D = dmats + (size_t)b * d_stride + off;
+  float acc = 0.f;
+  for (int i = 0; i < d; ++i) acc += feats[(size_t)p * c + start + i] * D[i * d + j];
+  new_feats[(size_t)p * c + k] = acc;
+}
+
+extern "C" int ssc_steer_fwd(const float *points, const float *feats, const int32_t *ids, const float *rot,
+                             const float *trans, const float *scale, const float *dmats, int d_stride,
+                             const int32_t *chan, int n, int c, int n_sample, float *new_points, float *new_feats,
+                             void *stream) {
+  SSC_REQUIRE(n >= 0 && c >= 1 && n_sample >= 1 && d_stride >= 1, "steer_fwd: bad sizes");
+  if (n == 0) return SSC_OK;
+  SSC_REQUIRE(points && feats && ids && rot && trans && dmats && chan && new_points && new_feats, "steer_fwd: null pointer");
+  long long total = (long long)n * (c + 3);
+  { steer_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(points, feats, ids, rot, trans, scale, dmats, d_stride,
+                                                                    chan, n, c, n_sample, new_points, new_feats); note_launches(1); }
+  SSC_CHECK_LAUNCH("steer_fwd");
+  return SSC_OK;
+}
+
 extern "C" int ssc_p2v_stats(const float *points, const int32_t *batch_ids, int n_point, const int grid[3],
                              const float unit[3], int32_t *stats_dev, void *stream) {
   SSC_REQUIRE(n_point >= 0 && grid && unit && stats_dev, "p2v_stats: bad arguments");

@@ -58,6 +58,8 @@ SIGNATURES = {
     "ssc_global_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_voxelize_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_three_interpolate_bwd": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ssc_steer_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                              c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_p2v_stats": (c_int, [c_void_p, c_void_p, c_int, _I3, _F3, c_void_p, c_void_p]),
     "ssc_maxpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_avgpool_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -685,6 +687,18 @@ def voxelize_bp(d_output_feats, d_feats, map_rule, mode, n_voxel, max_active, c)
 voxelize_idx = _not_built("voxelize_idx")
 point_recover_fp = _not_built("point_recover_fp")
 point_recover_bp = _not_built("point_recover_bp")
+
+
+def steer(points, feats, ids, rot, trans, scale, dmats, chan):
+    """(new_points [N,3], new_feats [N,C]) of the feature-steering change of frame (one launch)."""
+    n, c = feats.shape
+    new_points = torch.empty((n, 3), dtype=torch.float32, device=feats.device)
+    new_feats = torch.empty((n, c), dtype=torch.float32, device=feats.device)
+    _check(lib().ssc_steer_fwd(_p(points, torch.float32), _p(feats, torch.float32), _p(ids, torch.int32),
+                               _p(rot, torch.float32), _p(trans, torch.float32), _p(scale), _p(dmats, torch.float32),
+                               dmats.shape[1], _p(chan, torch.int32), n, c, rot.shape[0], _p(new_points), _p(new_feats),
+                               _stream()))
+    return new_points, new_feats
 
 
 def p2v_stats(points, batch_ids, grid, unit):

@@ -128,6 +128,42 @@ def irr_repr(order, alpha, beta, gamma, dtype=None):
     return torch.tensor(D, dtype=torch.get_default_dtype() if dtype is None else dtype)
 
 
+def irr_repr_of_matrix(order, R):
+    """Real Wigner-D matrix of the proper rotation R (3x3) in the basis of `spherical_harmonics`:
+    Y(R x) = D Y(x), obtained by projection on sample directions (no Euler angles needed)."""
+    v, pinvY = _sample_dirs(order)
+    w = v @ np.asarray(R, dtype=np.float64).T
+    a = np.arctan2(w[:, 1], w[:, 0])
+    b = np.arccos(np.clip(w[:, 2], -1, 1))
+    return _real_sh(order, a, b) @ pinvY
+
+
+# Axis relabelling between the frame the feature-steering code describes rotations in (polar axis
+# y; Common_utils/rotation_utils.py:334-372 builds D from Y-X-Y angles) and the frame of
+# `spherical_harmonics` here (polar axis z): D_steer(R) = irr_repr_of_matrix(S R S^T).
+_STEER_AXES = np.array([[0.0, 0.0, 1.0], [1.0, 0.0, 0.0], [0.0, 1.0, 0.0]])
+
+
+def D_from_matrix(R, l, frame="reference"):
+    """Representation matrices D^l [..., 2l+1, 2l+1] of rotation matrices R [..., 3, 3], the
+    function of the same name in the reference (Common_utils/rotation_utils.py:424-447): an
+    improper R is first multiplied by -1 (its parity factor is 1 there).
+    frame="reference" reproduces that function (rotations described in a frame whose polar axis
+    is y); frame="kernel" is the representation in the frame of the filter basis
+    (`spherical_harmonics`, polar axis z, axes = voxel axes), the one under which the steerable
+    convolution of this package commutes with rotations of the voxel grid."""
+    Rn = np.asarray(R.detach().cpu().double() if torch.is_tensor(R) else R, dtype=np.float64)
+    flat = Rn.reshape(-1, 3, 3)
+    out = np.empty((flat.shape[0], 2 * l + 1, 2 * l + 1), dtype=np.float64)
+    for i, Ri in enumerate(flat):
+        Ri = Ri * np.sign(np.linalg.det(Ri))
+        out[i] = irr_repr_of_matrix(l, Ri if frame == "kernel" else _STEER_AXES @ Ri @ _STEER_AXES.T)
+    out = out.reshape(Rn.shape[:-2] + (2 * l + 1, 2 * l + 1))
+    if torch.is_tensor(R):
+        return torch.as_tensor(out, dtype=R.dtype, device=R.device)
+    return out
+
+
 def kron(x, y):
     return torch.einsum("ij,kl->ikjl", x, y).reshape(x.size(0) * y.size(0), x.size(1) * y.size(1))
 

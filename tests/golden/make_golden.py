@@ -224,6 +224,32 @@ def main():
             out["bw_pool_features"], out["bw_pool_out"], out["bw_pool_dout"] = pf, y.numpy().copy(), dy
             out["bw_pool_din"] = dp.numpy().copy()
 
+    # ---- feature steering (Common_utils/ss_conv_modules.py:173-224, rotation_utils.py:424-447): the
+    #      per-point change of frame of points and irrep features, and the D matrices it uses
+    sys.path.insert(0, os.path.join(ref_root, "Common_utils"))
+    modules = importlib.import_module("ss_conv_modules")
+    rot_utils = importlib.import_module("rotation_utils")
+    frng = np.random.RandomState(99)
+    Bf, Nf, irrep = 3, 40, (2, 2, 1, 1)
+    q = frng.randn(Bf, 4)
+    q /= np.linalg.norm(q, axis=1, keepdims=True)
+    Rf = rot_utils.quaternion_to_matrix(torch.from_numpy(q)).float()
+    tf = torch.from_numpy(frng.randn(Bf, 3).astype(np.float32) * 0.1)
+    sf = torch.from_numpy(frng.uniform(0.8, 1.2, Bf).astype(np.float32))
+    idf = torch.from_numpy(np.sort(frng.randint(0, Bf, Nf)).astype(np.int64))
+    pf = torch.from_numpy(frng.randn(Nf, 3).astype(np.float32) * 0.3)
+    Cf = sum(m * (2 * l + 1) for l, m in enumerate(irrep))
+    ff = torch.from_numpy(frng.randn(Nf, Cf).astype(np.float32))
+    holder = type("H", (), {"irrep": irrep})()
+    out["fsm_R"], out["fsm_t"], out["fsm_s"] = Rf.numpy(), tf.numpy(), sf.numpy()
+    out["fsm_ids"], out["fsm_points"], out["fsm_feats"] = idf.numpy().astype(np.int32), pf.numpy(), ff.numpy()
+    out["fsm_irrep"] = np.array(irrep, dtype=np.int32)
+    out["fsm_new_points"] = modules.Feature_Steering_Module._transform_points(holder, pf, Rf[idf], tf[idf], sf[idf]).numpy()
+    out["fsm_new_points_noscale"] = modules.Feature_Steering_Module._transform_points(holder, pf, Rf[idf], tf[idf]).squeeze(1).numpy()
+    out["fsm_new_feats"] = modules.Feature_Steering_Module._transform_feats(holder, ff, Rf[idf]).numpy()
+    for l in range(len(irrep)):
+        out["fsm_D%d" % l] = rot_utils.D_from_matrix(Rf.double(), l).numpy()
+
     # ---- Wigner-D / Q_J values the basis is built from (stand-in convention)
     out["irr_repr_l2"] = SO3.irr_repr(2, 0.3, 1.1, -2.0, dtype=torch.float64).numpy()
     out["Q_J_1_1_1"] = kernel.basis_transformation_Q_J(1, 1, 1).numpy() if hasattr(kernel, "basis_transformation_Q_J") \

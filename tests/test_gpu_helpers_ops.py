@@ -183,3 +183,105 @@ def test_batchnorm_activation_golden(cuda, golden):
     with torch.no_grad():
         z2 = act2(SparseTensor(dev(golden["bn_eval_out"], cuda), ind, [10] * 3, 2)).features.cpu().numpy()
     assert np.abs(z2 - z).max() <= 2e-6
+
+
+def test_feature_steering_kernel_and_module(cuda, golden):
+    """ssc_steer_fwd vs the reference's own outputs; then Feature_Steering_Module end to end with
+    the identity pose = plain voxelize + two SS_Conv blocks."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", "ss-conv_b200"))
+    from ss_conv_modules import Feature_Steering_Module, SS_Conv
+    from ss_conv import _ext
+    from ss_conv.sp_ops.tensor import SparseTensor
+    irrep = tuple(int(v) for v in golden["fsm_irrep"])
+    torch.manual_seed(5)
+    fsm = Feature_Steering_Module(irrep, kernel_size=3, dropout_p=0.0, voxel_num_limit=[8] * 3,
+                                  unit_voxel_extent=[0.25] * 3).to(cuda).eval()
+    pts, fts = dev(golden["fsm_points"], cuda), dev(golden["fsm_feats"], cuda)
+    ids = dev(golden["fsm_ids"], cuda)
+    R, t, s = dev(golden["fsm_R"], cuda), dev(golden["fsm_t"], cuda), dev(golden["fsm_s"], cuda)
+    new_p, new_f = fsm.steer(pts, fts, ids, R, t, s)
+    assert np.abs(new_p.cpu().numpy() - golden["fsm_new_points"]).max() <= 2e-6
+    assert np.abs(new_f.cpu().numpy() - golden["fsm_new_feats"]).max() <= 5e-6
+    new_p2, _ = fsm.steer(pts, fts, ids, R, t)
+    assert np.abs(new_p2.cpu().numpy() - golden["fsm_new_points_noscale"]).max() <= 2e-6
+    # whole module, identity pose
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            B = 3
+            eye = torch.eye(3, device=cuda).repeat(B, 1, 1)
+            zero = torch.zeros(B, 3, device=cuda)
+            vp, vf, vi, flag = fsm(pts, fts, ids, eye, zero)
+            assert isinstance(vf, SparseTensor) and float(flag.sum()) == B
+            _, sp, _, _ = fsm.p2v(pts, fts, ids)
+            want = fsm.conv2(fsm.conv1(sp))
+            assert torch.equal(vf.indices, want.indices)
+            assert rel_err(vf.features.cpu().numpy(), want.features.cpu().numpy()) <= 1e-5
+            assert isinstance(fsm.conv1, SS_Conv)
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+
+
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_steerable_convolution_is_equivariant_under_grid_rotations(cuda, axis):
+    """Steering the input by a rotation that maps the voxel grid onto itself (90 degrees about a
+    coordinate axis) and convolving equals convolving and steering the output, through
+    convolution + batch norm + gated activation, when the features are rotated by the
+    representation in the frame of the filter basis (frame="kernel")."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", "ss-conv_b200"))
+    from ss_conv_modules import Feature_Steering_Module
+    from ss_conv import _ext
+    torch.manual_seed(11 + axis)
+    rng = np.random.RandomState(11 + axis)
+    irrep = (2, 2, 1)
+    V, unit = 8, 0.25
+    fsm = Feature_Steering_Module(irrep, kernel_size=3, dropout_p=0.0, voxel_num_limit=[V] * 3,
+                                  unit_voxel_extent=[unit] * 3, voxelization_mode=4, frame="kernel").to(cuda).eval()
+    with torch.no_grad():
+        fsm.conv1.bn.running_var.uniform_(0.5, 1.5)
+        fsm.conv1.bn.running_mean.normal_(0, 0.1)
+    # one point per occupied voxel, at the voxel centre
+    occ = np.argwhere(rng.rand(2, V, V, V) < 0.15)
+    pts = ((occ[:, 1:] + 0.5) * unit - 0.5 * V * unit).astype(np.float32)
+    ids = occ[:, 0].astype(np.int32)
+    C = sum(m * (2 * l + 1) for l, m in enumerate(irrep))
+    fts = rng.randn(pts.shape[0], C).astype(np.float32)
+    c, s = 0.0, 1.0
+    R1 = np.eye(3, dtype=np.float32)
+    i, j = [(1, 2), (2, 0), (0, 1)][axis]
+    R1[i, i], R1[i, j], R1[j, i], R1[j, j] = c, -s, s, c
+    R = dev(np.stack([R1, R1]), cuda)
+    zero = torch.zeros(2, 3, device=cuda)
+    P, Fe, I = dev(pts, cuda), dev(fts, cuda), dev(ids, cuda)
+
+    def centres(sp):
+        return ((sp.indices[:, 1:].float() + 0.5) * unit - 0.5 * V * unit), sp.indices[:, 0].contiguous()
+
+    def keyed(sp):
+        k = ((sp.indices[:, 0] * V + sp.indices[:, 1]) * V + sp.indices[:, 2]) * V + sp.indices[:, 3]
+        order = torch.argsort(k)
+        return k[order].cpu().numpy(), sp.features[order].cpu().numpy()
+
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            # A: steer, voxelize, convolve
+            p1, f1 = fsm.steer(P, Fe, I, R, zero)
+            a = fsm.conv1(fsm.p2v(p1, f1, I)[1])
+            # B: voxelize, convolve, then steer the output voxels
+            b0 = fsm.conv1(fsm.p2v(P, Fe, I)[1])
+            cp, cid = centres(b0)
+            order = torch.argsort(cid, stable=True)
+            p2, f2 = fsm.steer(cp[order].contiguous(), b0.features[order].contiguous(), cid[order].contiguous(), R, zero)
+            b = fsm.p2v(p2, f2, cid[order].contiguous())[1]
+        ka, fa = keyed(a)
+        kb, fb = keyed(b)
+        np.testing.assert_array_equal(ka, kb)
+        assert rel_err(fa, fb) <= 1e-4
+    finally:
+        _ext.set_precision("auto")

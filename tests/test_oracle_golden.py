@@ -157,3 +157,21 @@ def test_maxpool_backward_matches_reference(golden):
     y = O.indice_maxpool(golden["bw_pool_features"], golden["bw_strided_pairs"], golden["bw_strided_num"],
                          golden["bw_pool_out"].shape[0])
     np.testing.assert_array_equal(y, golden["bw_pool_out"])
+
+
+def test_feature_steering_matches_reference(golden):
+    """Point / feature change of frame of Feature_Steering_Module and the representation matrices
+    of rotation_utils.D_from_matrix (reference outputs) vs the restatement and this package's
+    own Wigner-D construction (no constants file)."""
+    import sys
+    import os
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "..", "ss-conv_b200"))
+    from ss_conv.utils import SO3
+    irrep = [int(v) for v in golden["fsm_irrep"]]
+    R, t, s, ids = golden["fsm_R"], golden["fsm_t"], golden["fsm_s"], golden["fsm_ids"]
+    d_ref = [golden["fsm_D%d" % l] for l in range(len(irrep))]
+    for l in range(len(irrep)):
+        assert np.abs(SO3.D_from_matrix(R.astype(np.float64), l) - d_ref[l]).max() <= 1e-6     # R is stored in fp32
+    assert np.abs(O.steer_points(golden["fsm_points"], ids, R, t, s) - golden["fsm_new_points"]).max() <= 2e-6
+    assert np.abs(O.steer_points(golden["fsm_points"], ids, R, t) - golden["fsm_new_points_noscale"]).max() <= 2e-6
+    assert np.abs(O.steer_feats(golden["fsm_feats"], ids, d_ref, irrep) - golden["fsm_new_feats"]).max() <= 5e-6
