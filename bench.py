@@ -351,7 +351,7 @@ def run_ours(args):
                 flops.append(2.0 * P * ci * co)
     n_out_conv = prepared[0][2]
     # ---- backward of the same layer (input gradient through the tcgen05 kernel on the input-major
-    #      table, exact-fp32 filter gradient), CUDA events, the rulebook of the forward pass reused
+    #      table, tensor-core filter gradient), CUDA events, the rulebook of the forward pass reused
     bwd_ms = []
     with torch.no_grad():
         grads = [torch.randn(n_out, flt.shape[2], device=dev) for _, _, n_out, _ in prepared]
@@ -411,7 +411,7 @@ def run_ours(args):
                          "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
                          "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
         }
-        line["backward"] = {"what": "input gradient (tcgen05, TF32 operands) + filter gradient (fp32) of the cfg2 convolution",
+        line["backward"] = {"what": "input gradient + filter gradient of the cfg2 convolution, both tcgen05 with TF32 operands",
                             "ms": float(np.mean(bwd_ms)), "voxels_per_s": float(np.mean(n_in)) / (float(np.mean(bwd_ms)) * 1e-3)}
         line["backbone"] = backbone
         if world == 1:

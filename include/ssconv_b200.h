@@ -224,14 +224,17 @@ int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets
  * (the reference's gather -> mm(filters^T) -> scatter-add loop, :412-424), and the pool
  * gradients below need no atomics.
  * ssc_conv_wgrad: d_filters[kappa] = sum_o features[nbr[kappa][o]]^T . out_grad[o]  ([K,Cin,Cout],
- * the reference's mm(inputBuffer^T, outputBuffer), :411), exact fp32, bitwise repeatable.
+ * the reference's mm(inputBuffer^T, outputBuffer), :411), bitwise repeatable; precision
+ * SSC_PREC_FP32 = exact fp32 FMA, SSC_PREC_TF32 = tcgen05 with TF32 operands (both operands are
+ * transposed into K-major shared-memory tiles on the fly; up to 256 input channels, else fp32).
  * ssc_maxpool_bwd: d_in[i,c] = sum over outputs o of i with out[o,c] == in[i,c] of out_grad[o,c]
  * (indice_maxpool_cpp_functor.cpp:78-84); ssc_avgpool_bwd: d_in[i] = sum_o out_grad[o] / rf[o]
  * (rf NULL: / K; indice_avgpool_cuda_functor.cu:195-205), both in ascending offset order. */
 int ssc_nbr_transpose(const int32_t *nbr, int K, int n_out, int n_in, int32_t *nbr_in, void *stream);
 size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n_out);
 int ssc_conv_wgrad(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr,
-                   int K, int n_out, float *d_filters, void *scratch, size_t scratch_bytes, void *stream);
+                   int K, int n_out, int precision, float *d_filters, int32_t *status, void *scratch,
+                   size_t scratch_bytes, void *stream);
 int ssc_maxpool_bwd(const float *features, const float *out_features, const float *out_grad, int c,
                     const int32_t *nbr_in, int K, int n_in, float *d_in, void *stream);
 int ssc_avgpool_bwd(const float *out_grad, int c, const int32_t *nbr_in, int K, int n_in,

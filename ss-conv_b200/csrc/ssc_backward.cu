@@ -244,8 +244,14 @@ extern "C" size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n
   return (size_t)wgrad_splits(K, c_in, c_out, n_out) * K * c_in * c_out * sizeof(float);
 }
 
+namespace ssc {
+int conv_wgrad_tc(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr, int K, int n_out,
+                  int max_splits, int *splits_used, float *partial, int32_t *status, cudaStream_t st);
+}
+
 extern "C" int ssc_conv_wgrad(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr, int K,
-                              int n_out, float *d_filters, void *scratch, size_t scratch_bytes, void *stream) {
+                              int n_out, int precision, float *d_filters, int32_t *status, void *scratch,
+                              size_t scratch_bytes, void *stream) {
   SSC_REQUIRE(K >= 1 && c_in >= 1 && c_out >= 1 && n_out >= 0 && d_filters, "conv_wgrad: bad arguments");
   cudaStream_t st = as_stream(stream);
   const long long elems = (long long)K * c_in * c_out;
@@ -260,12 +266,19 @@ extern "C" int ssc_conv_wgrad(const float *features, int c_in, const float *out_
     return fail(SSC_ERR_SCRATCH, "conv_wgrad: scratch %zu < %zu bytes", scratch_bytes, need);
   int rows_per_split = ceil_div(n_out, splits);
   rows_per_split = ceil_div(rows_per_split, WG_ROWS) * WG_ROWS;
-  const int tiles_co = ceil_div(c_out, WG_T);
-  dim3 grid(splits, K, ceil_div(c_in, WG_T) * tiles_co);
-  { conv_wgrad_partial_kernel<<<grid, 256, 0, st>>>(features, c_in, out_grad, c_out, nbr, n_out, rows_per_split, tiles_co,
-                                                   (float *)scratch); note_launches(1); }
-  SSC_CHECK_LAUNCH("conv_wgrad_partial");
-  { wgrad_reduce_kernel<<<ceil_div(elems, 256), 256, 0, st>>>((const float *)scratch, splits, elems, d_filters); note_launches(1); }
+  int rc = -1, used = splits;
+  if (precision == SSC_PREC_TF32)  // tensor cores where the shape allows, else the exact kernel below
+    rc = conv_wgrad_tc(features, c_in, out_grad, c_out, nbr, K, n_out, splits, &used, (float *)scratch, status, st);
+  if (rc > 0) return rc;
+  if (rc < 0) {
+    const int tiles_co = ceil_div(c_out, WG_T);
+    dim3 grid(splits, K, ceil_div(c_in, WG_T) * tiles_co);
+    { conv_wgrad_partial_kernel<<<grid, 256, 0, st>>>(features, c_in, out_grad, c_out, nbr, n_out, rows_per_split, tiles_co,
+                                                     (float *)scratch); note_launches(1); }
+    SSC_CHECK_LAUNCH("conv_wgrad_partial");
+    used = splits;
+  }
+  { wgrad_reduce_kernel<<<ceil_div(elems, 256), 256, 0, st>>>((const float *)scratch, used, elems, d_filters); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_wgrad_reduce");
   return SSC_OK;
 }

@@ -50,8 +50,8 @@ SIGNATURES = {
                              c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ssc_nbr_transpose": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_conv_wgrad_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
-    "ssc_conv_wgrad": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t,
-                               c_void_p]),
+    "ssc_conv_wgrad": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                               c_void_p, c_size_t, c_void_p]),
     "ssc_maxpool_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ssc_avgpool_bwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "ssc_global_avgpool_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -548,23 +548,26 @@ def input_major_table(nbr, n_in):
     return nbr_in
 
 
-def conv_wgrad(features, out_grad, nbr):
-    """d_filters [K, Cin, Cout] = sum over output rows of gathered input rows (outer) out_grad rows."""
+def conv_wgrad(features, out_grad, nbr, precision=None):
+    """d_filters [K, Cin, Cout] = sum over output rows of gathered input rows (outer) out_grad rows
+    (tensor cores with TF32 operands or exact fp32, chosen like the forward pass)."""
     K, n_out = nbr.shape
     c_in, c_out = features.shape[1], out_grad.shape[1]
+    mode = PREC_TF32 if _resolve_precision(c_in, c_out, precision) == "tf32" else PREC_FP32
     d_flt = torch.empty((K, c_in, c_out), dtype=torch.float32, device=features.device)
     nbytes = int(lib().ssc_conv_wgrad_scratch_bytes(K, c_in, c_out, n_out))
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=features.device)
     _check(lib().ssc_conv_wgrad(_p(features, torch.float32), c_in, _p(out_grad, torch.float32), c_out,
-                                _p(nbr, torch.int32), K, n_out, _p(d_flt), _p(scratch), nbytes, _stream()))
+                                _p(nbr, torch.int32), K, n_out, mode, _p(d_flt), _p(status_word(features.device)),
+                                _p(scratch), nbytes, _stream()))
     return d_flt
 
 
 def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_num, inverse, subm):
     """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:46-48): [input_grad, filters_grad].
     The input gradient is the forward gather-GEMM over the input-major table with the filters
-    transposed (operand precision as set for the forward pass); the filter gradient is exact
-    fp32.  The submanifold centre needs no special case."""
+    transposed; both gradients use the operand precision set for the forward pass.  The
+    submanifold centre needs no special case."""
     if features.dtype != torch.float32:
         raise TypeError("indice_conv_backward_fp32 expects float32 features")
     features, out_bp = features.contiguous(), out_bp.contiguous()

@@ -53,7 +53,7 @@ def test_conv_backward_vs_float64_oracle(cuda, precision, c_in, c_out, k, s, p, 
     ref_in, ref_flt = O.indice_conv_backward(feats, W, dout, pairs.cpu().numpy(), num.cpu().numpy(), False, False,
                                              dtype=np.float64)
     assert rel_err(d_in.cpu().numpy(), ref_in) <= TOL[precision]
-    assert rel_err(d_flt.cpu().numpy().reshape(ref_flt.shape), ref_flt) <= TOL["fp32"]      # filter gradient is always fp32
+    assert rel_err(d_flt.cpu().numpy().reshape(ref_flt.shape), ref_flt) <= TOL[precision]
     assert torch.equal(d_in, again[0]) and torch.equal(d_flt, again[1])                        # bitwise repeatable
 
 
