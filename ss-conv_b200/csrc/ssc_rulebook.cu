@@ -239,13 +239,74 @@ __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
   }
 }
 
+// Dense-map lookup: one thread per output row walks all kernel offsets, so the row's coordinates
+// are decoded once; every offset costs a few integer operations, one load from the row map and
+// one coalesced store.
+// Block = kChunk rows; counts per (offset, chunk) are only produced when chunk_counts is given.
+__global__ void __launch_bounds__(256)
+lookup_dense_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, Geometry g,
+                    const int32_t *__restrict__ row_map, int32_t *__restrict__ nbr,
+                    int32_t *__restrict__ chunk_counts, int n_chunks, const int32_t *__restrict__ n_out_dev) {
+  extern __shared__ int32_t cnt[];  // [K] when counting
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n_rows = live_rows(n_out, n_out_dev);
+  const bool counting = chunk_counts != nullptr;
+  if (counting) {
+    for (int k = threadIdx.x; k < g.K; k += blockDim.x) cnt[k] = 0;
+    __syncthreads();
+  }
+  int base = -1;
+  int oc[3] = {0, 0, 0};
+  if (o < n_rows) {
+    const int4 c = out_indices[o];
+    oc[0] = c.y; oc[1] = c.z; oc[2] = c.w;
+    if ((unsigned)c.x < (unsigned)batch) base = c.x;
+  }
+  // input coordinate along dimension d for kernel index k, or -1
+  auto coord = [&](int d, int k) -> int {
+    int v;
+    if (g.transpose) {
+      const int num = oc[d] + g.padding[d] - k * g.dilation[d];
+      v = (num >= 0 && num % g.stride[d] == 0) ? num / g.stride[d] : -1;
+    } else {
+      v = oc[d] * g.stride[d] - g.padding[d] + k * g.dilation[d];
+    }
+    return (unsigned)v < (unsigned)g.in_shape[d] ? v : -1;
+  };
+  int kappa = 0;
+  for (int kx = 0; kx < g.ksize[0]; ++kx) {
+    const int x = coord(0, kx);
+    for (int ky = 0; ky < g.ksize[1]; ++ky) {
+      const int y = coord(1, ky);
+      const long long plane = ((long long)(base * g.in_shape[0] + x) * g.in_shape[1] + y) * g.in_shape[2];
+      for (int kz = 0; kz < g.ksize[2]; ++kz, ++kappa) {
+        const int z = coord(2, kz);
+        int found = -1;
+        if (base >= 0 && (x | y | z) >= 0) found = __ldg(row_map + plane + z);
+        if (o < n_out) nbr[(size_t)kappa * n_out + o] = found;
+        if (counting) {
+          const unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
+          if ((threadIdx.x & 31) == 0 && hits) atomicAdd(cnt + kappa, __popc(hits));
+        }
+      }
+    }
+  }
+  if (counting) {
+    __syncthreads();
+    // chunk = kChunk rows = (kChunk / blockDim.x) consecutive blocks: add this block's share
+    const int chunk = (int)(((long long)blockIdx.x * blockDim.x) / kChunk);
+    for (int k = threadIdx.x; k < g.K; k += blockDim.x)
+      if (cnt[k]) atomicAdd(chunk_counts + (size_t)k * n_chunks + chunk, cnt[k]);
+  }
+}
+
 // grid (chunks, K), block kChunk threads: thread <-> output row; the hash is probed by
 // groups of 4 lanes, each group reading one 32-byte bucket per probe.
 __global__ void __launch_bounds__(kChunk)
 lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, Geometry g,
                          const unsigned long long *__restrict__ table, uint32_t mask,
                          int32_t *__restrict__ nbr, int32_t *__restrict__ chunk_counts, int n_chunks,
-                         const int32_t *__restrict__ n_out_dev, const int32_t *__restrict__ row_map) {
+                         const int32_t *__restrict__ n_out_dev) {
   const unsigned full = 0xffffffffu;
   int kappa = blockIdx.y;
   int o = blockIdx.x * kChunk + threadIdx.x;
@@ -269,13 +330,6 @@ lookup_neighbours_kernel(const int4 *__restrict__ out_indices, int n_out, int ba
       ok = ok && (unsigned)in[d] < (unsigned)g.in_shape[d];
     }
     if (ok) key = (uint32_t)(((c.x * g.in_shape[0] + in[0]) * g.in_shape[1] + in[1]) * g.in_shape[2] + in[2]);
-  }
-  if (row_map != nullptr) {  // dense row map: one load answers the query
-    const int found = key != 0xFFFFFFFFu ? __ldg(row_map + key) : -1;
-    if (o < n_out) nbr[(size_t)kappa * n_out + o] = found;
-    const int c = __syncthreads_count(o < n_out && found >= 0);
-    if (threadIdx.x == 0) chunk_counts[(size_t)kappa * n_chunks + blockIdx.x] = c;
-    return;
   }
   unsigned lane = threadIdx.x & 31u, sub = lane & 3u, gbase = lane & ~3u;
   unsigned gmask = 0xFu << gbase;
@@ -437,9 +491,16 @@ static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, i
   int K = g.K;
   int n_chunks = ceil_div(n_out > 0 ? n_out : 1, kChunk);
   if (n_chunks > s.n_chunks_cap) return fail(SSC_ERR_SCRATCH, "rulebook: n_out exceeds the scratch capacity");
-  dim3 grid(n_chunks, K);
-  { lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
-                                                   s.n_buckets - 1, nbr, s.chunk_counts, n_chunks, n_out_dev, s.row_map); note_launches(1); }
+  if (s.row_map != nullptr) {
+    int32_t *counts = indice_num != nullptr ? s.chunk_counts : nullptr;
+    if (counts) cudaMemsetAsync(counts, 0, (size_t)n_chunks * K * 4, st);
+    { lookup_dense_kernel<<<ceil_div(n_out > 0 ? n_out : 1, 256), 256, K * sizeof(int32_t), st>>>(
+          (const int4 *)out_indices, n_out, batch, g, s.row_map, nbr, counts, n_chunks, n_out_dev); note_launches(1); }
+  } else {
+    dim3 grid(n_chunks, K);
+    { lookup_neighbours_kernel<<<grid, kChunk, 0, st>>>((const int4 *)out_indices, n_out, batch, g, s.table,
+                                                     s.n_buckets - 1, nbr, s.chunk_counts, n_chunks, n_out_dev); note_launches(1); }
+  }
   SSC_CHECK_LAUNCH("lookup_neighbours");
   if (indice_num == nullptr) return 0;
   { scan_chunks_kernel<<<K, 256, 0, st>>>(s.chunk_counts, n_chunks, indice_num); note_launches(1); }

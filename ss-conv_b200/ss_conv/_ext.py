@@ -291,17 +291,18 @@ def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize,
         sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(n_in, int(batch_size), _i3(spatial_shape),
                                                                              _i3(out_shape), K)), 256)
     scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
-    small = torch.empty(K + 1, dtype=torch.int32, device=dev)
-    num, n_out_dev = small[:K], small[K:]
+    n_out_dev = torch.empty(1, dtype=torch.int32, device=dev)
     st = status_word(dev)
     geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
     _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
                                      sbytes, _p(n_in_dev), _stream()))
     outids = torch.empty((cap, 4), dtype=torch.int32, device=dev)
     nbr = torch.empty((K, cap), dtype=torch.int32, device=dev)
-    _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, cap, _p(outids), _p(nbr), None, _p(num),
+    # the per-offset pair counts (indice_num) are not needed by the kernels that consume the table:
+    # they are computed only if somebody turns the handle into reference-format pair lists
+    _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, cap, _p(outids), _p(nbr), None, None,
                                     _p(st), _p(scratch), sbytes, _p(n_out_dev), _stream()))
-    return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=None if n_in_dev is not None else key), num]
+    return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=None if n_in_dev is not None else key), None]
 
 
 def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,
