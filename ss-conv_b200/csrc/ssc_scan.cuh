@@ -100,12 +100,44 @@ __global__ void word_prefix_kernel(const uint32_t *__restrict__ bitmap, long lon
 }
 
 
+// Small inputs (up to kSingleScanMax values): the whole exclusive scan in ONE block of 1024
+// threads, each thread owning a contiguous run of values — one launch instead of three when the
+// three would each be pure launch latency.
+constexpr long long kSingleScanMax = 1 << 13;
+template <bool POPC>
+__global__ void __launch_bounds__(1024)
+single_block_scan_kernel(const uint32_t *values, int n, uint32_t *prefix, int32_t *total_a, int32_t *total_b) {
+  // values and prefix may be the same array (in-place scan): every value is read before its slot is written
+  __shared__ uint32_t smem[33];
+  const int per = (n + 1023) / 1024;          // values per thread (<= 8)
+  const int begin = threadIdx.x * per, end = min(n, begin + per);
+  uint32_t s = 0;
+  for (int i = begin; i < end; ++i) s += POPC ? (uint32_t)__popc(values[i]) : values[i];
+  uint32_t tot;
+  uint32_t run = block_exclusive_scan(s, smem, &tot);
+  for (int i = begin; i < end; ++i) {
+    const uint32_t v = POPC ? (uint32_t)__popc(values[i]) : values[i];
+    prefix[i] = run;
+    run += v;
+  }
+  if (threadIdx.x == 0) {
+    if (total_a) *total_a = (int32_t)tot;
+    if (total_b) *total_b = (int32_t)tot;
+  }
+}
+
 // Exclusive scan of n values (popcounts of words if POPC, else the words themselves):
 // prefix[i] = sum of values before i; the grand total goes to total_a / total_b (may be NULL).
 // block_sums needs ceil(n/1024)+1 entries.
 template <bool POPC>
 static inline int exclusive_scan_u32(const uint32_t *values, long long n, uint32_t *prefix, uint32_t *block_sums,
                                      int32_t *total_a, int32_t *total_b, cudaStream_t st) {
+  if (n >= 1 && n <= kSingleScanMax) {
+    { single_block_scan_kernel<POPC><<<1, 1024, 0, st>>>(values, (int)n, prefix, total_a, total_b); note_launches(1); }
+    cudaError_t e1 = cudaGetLastError();
+    if (e1 != cudaSuccess) return fail(SSC_ERR_CUDA, "exclusive_scan: %s", cudaGetErrorString(e1));
+    return 0;
+  }
   int blocks = (int)((n + 1023) / 1024);
   if (blocks < 1) blocks = 1;
   { popc_block_sums_kernel<POPC><<<blocks, 256, 0, st>>>(values, n, block_sums); note_launches(1); }
