@@ -54,26 +54,32 @@ struct TcParams {
   int b_bytes;    // n_pad * 128
   int sps;        // 32-channel slabs per ring slot (a step covers sps slabs of one kernel offset)
   int k_groups;   // ceil(k_slabs / sps) = steps per kernel offset
+  int nt_cta;     // N tiles handled by one CTA: n_tiles, or 1 when the N tiles are spread over gridDim.y
+  int n_cta;      // nt_cta * tile_n: accumulator columns / filter-slab rows per CTA
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
-static bool tc_params(int c_in, int c_out, TcParams &p) {
+static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   int n16 = (c_out + 15) / 16 * 16;
   p.n_tiles = (n16 + 255) / 256;
   p.tile_n = ((n16 + p.n_tiles - 1) / p.n_tiles + 15) / 16 * 16;
   p.n_pad = p.n_tiles * p.tile_n;
   if (p.n_pad > 512) return false;
+  // A layer with few row tiles and more than one N tile gets one CTA per (row tile, N tile): more
+  // CTAs in flight, each with a smaller accumulator and filter slab (the rows are gathered twice).
+  p.nt_cta = (split_n && p.n_tiles > 1) ? 1 : p.n_tiles;
+  p.n_cta = p.nt_cta * p.tile_n;
   p.tmem_cols = 32;
-  while (p.tmem_cols < p.n_pad) p.tmem_cols <<= 1;
-  p.b_bytes = p.n_pad * 128;
+  while (p.tmem_cols < p.n_cta) p.tmem_cols <<= 1;
+  p.b_bytes = p.n_cta * 128;
   // Two slabs per step (SSC_TC_SPS=2) halve the per-step work that does not move data (neighbour
   // look-ups, row masks, barrier hand-shakes) but also the resident CTAs; measured slower on the
   // 64 -> 76 channel layer (0.21 vs 0.18 ms), so one slab per step is the default.
   p.sps = 1;
   if (const char *e = getenv("SSC_TC_SPS")) {
     int v = atoi(e);
-    if (v == 1 || (v == 2 && p.k_slabs >= 2)) p.sps = v;
+    if (v == 1 || (v == 2 && p.k_slabs >= 2 && p.nt_cta == p.n_tiles)) p.sps = v;
   }
   p.k_groups = (p.k_slabs + p.sps - 1) / p.sps;
   int stage = p.sps * (TC_A_BYTES + p.b_bytes);
@@ -188,6 +194,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int n_warps = blockDim.x >> 5;
   const int mma_warp = n_warps - 1;
   const int m0 = blockIdx.x * TC_M;
+  const int nt0 = (int)blockIdx.y * p.nt_cta;   // first N tile of this CTA
   const int S = p.stages;
 
   if (tid == 0) {
@@ -233,7 +240,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     // Clear the accumulators.  Every MMA below accumulates, and rows without a neighbour at a
     // step are switched off through the MMA's disable-output-lane mask, so the gathered operand
     // never has to hold zero rows (stale rows of an earlier step are simply not written back).
-    for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+    for (int c0 = 0; c0 < p.n_cta; c0 += 16) {
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr),
@@ -297,7 +304,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         tc_fence_after();
       }
       if (part == 0 && lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
-        const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab0) * (size_t)(p.n_pad * 8);
+        const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab0) * (size_t)(p.n_pad * 8) +
+                            (size_t)nt0 * (size_t)(p.tile_n * 8);
         const uint32_t bar = smem_u32(fullb_bars + slot), nbytes = (uint32_t)(n_sub * p.b_bytes);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbytes) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -380,7 +388,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       const int n_sub = min(p.sps, p.k_slabs - grp * p.sps);
       for (int ss = 0; ss < n_sub; ++ss) {
         const uint32_t an = a_lo + (uint32_t)ss * (TC_A_BYTES >> 4);
-        for (int nt = 0; nt < p.n_tiles; ++nt) {
+        for (int nt = 0; nt < p.nt_cta; ++nt) {
           const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n);
           const uint32_t bn = a_lo + (uint32_t)(p.sps * TC_A_BYTES >> 4) + (uint32_t)ss * ((uint32_t)p.b_bytes >> 4) + (uint32_t)nt * n_step;
           mma_tf32_ss_masked(dn, an, bn, idesc, off);
@@ -406,8 +414,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
     const int m = m0 + warp * 32 + lane;
-    const int n_cols = (c_out + 15) & ~15;
-    for (int c0 = 0; c0 < n_cols && c0 < p.n_pad; c0 += 16) {
+    const int col0 = nt0 * p.tile_n;   // first output channel of this CTA
+    for (int c0 = 0; c0 < p.n_cta && col0 + c0 < c_out; c0 += 16) {
       uint32_t r[16];
       if (ok && n_iter > 0) {
         uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
@@ -423,17 +431,17 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         for (int q = 0; q < 16; ++q) r[q] = 0u;
       }
       if (m < n_rows) {
-        float *op = out + (size_t)m * c_out + c0;
+        float *op = out + (size_t)m * c_out + col0 + c0;
         if ((c_out & 3) == 0) {
 #pragma unroll
           for (int q = 0; q < 16; q += 4)
-            if (c0 + q < c_out)
+            if (col0 + c0 + q < c_out)
               *(float4 *)(op + q) = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
                                                 __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
         } else {
 #pragma unroll
           for (int q = 0; q < 16; ++q)
-            if (c0 + q < c_out) op[q] = __uint_as_float(r[q]);
+            if (col0 + c0 + q < c_out) op[q] = __uint_as_float(r[q]);
         }
       }
     }
@@ -476,9 +484,13 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
     int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
     if (rc >= 0) return rc;
   }
-  if (!tc_params(c_in, c_out, p)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
-  size_t smem = tc_smem_bytes(p);
   int grid = ceil_div(n_out, TC_M);
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const char *no_split = getenv("SSC_TC_NO_NSPLIT");
+  const bool split_n = grid < 2 * sms && no_split == nullptr;   // few row tiles: spread the N tiles over CTAs too
+  if (!tc_params(c_in, c_out, p, split_n)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
+  size_t smem = tc_smem_bytes(p);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).
   const int c_pad = (c_in + 3) & ~3;  // row stride of the staged image (zero-padded channels)
@@ -493,7 +505,8 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
-  { kernel<<<grid, p.threads, smem, st>>>(staged ? (const float *)scratch : features, staged ? c_pad : c_in, (const uint4 *)packed, K, c_out,
+  const dim3 grid2(grid, p.n_tiles / p.nt_cta);
+  { kernel<<<grid2, p.threads, smem, st>>>(staged ? (const float *)scratch : features, staged ? c_pad : c_in, (const uint4 *)packed, K, c_out,
                                         nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;
@@ -507,7 +520,7 @@ extern "C" size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precisio
   if (precision != SSC_PREC_TF32 || K < 1 || c_in < 1 || c_out < 1) return 0;
   TcParams p;
   if (!tc_params(c_in, c_out, p)) return 0;
-  return (size_t)K * p.k_slabs * p.b_bytes;
+  return (size_t)K * p.k_slabs * p.n_pad * 128;
 }
 
 extern "C" int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision, void *packed,
