@@ -171,7 +171,7 @@ class Backbone:
             if self.graphed is None:
                 self.graphed = GraphedChain(self.stages_and_pool, x.spatial_shape, x.batch_size, x.features.shape[1],
                                             int(x.features.shape[0] * 1.05) + 64, x.features.device)
-            return self.graphed(x.features, x.indices)
+            return self.graphed(x)       # the voxel count stays on the device (checked after the replay)
 
 
 def run_backbone(args, dev, rank, world, dist):
@@ -298,10 +298,10 @@ def run_ours(args):
     from ss_conv.pipeline import HostStream
 
     def dev_step(fd, idd):
-        o = layer.step(fd, idd)
+        o = graphed(fd, idd)            # the recorded step (its buffers are reused by the next replay)
         return o.features, o.indices
 
-    feed = HostStream(dev_step, dev, max_rows=max(n_in))
+    feed = HostStream(dev_step, dev, max_rows=max(n_in), step_reuses_outputs=True)
     for _ in feed.run(pinned[w % ROTATE] for w in range(3)):
         pass
     barrier()
@@ -317,7 +317,7 @@ def run_ours(args):
     # the same without overlap (upload, compute, download one after the other), for comparison
     def serial_step(s):
         f, i = pinned[s % ROTATE]
-        o = layer.step(f.to(dev, non_blocking=True), i.to(dev, non_blocking=True))
+        o = graphed(f.to(dev, non_blocking=True), i.to(dev, non_blocking=True))
         return o.features.cpu(), o.indices.cpu()
 
     serial_step(0)
@@ -337,11 +337,21 @@ def run_ours(args):
         for f, i in dev_sets:
             outids, pairs, num = get_indice_pairs(i, cfg["batch"], [cfg["V"]] * 3, cfg["k"], cfg["stride"], cfg["pad"])
             prepared.append((f, _ext.neighbour_table(pairs, num, outids.shape[0]), outids.shape[0], int(num.sum().item())))
+        # the two launches of the convolution call (stage + conv) are recorded as a small CUDA graph per
+        # input batch, so that the CUDA events around a replay see device time only (no host gaps)
+        conv_graphs = []
+        for f, nbr, n_out, P in prepared:
+            _ext.conv_forward(f, flt, nbr, n_out, "tf32")
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                _ext.conv_forward(f, flt, nbr, n_out, "tf32")
+            conv_graphs.append(g)
         for it in range(3 + 12):
             f, nbr, n_out, P = prepared[it % ROTATE]
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            _ext.conv_forward(f, flt, nbr, n_out, "tf32")
+            conv_graphs[it % ROTATE].replay()
             b.record()
             torch.cuda.synchronize()
             if it >= 3:
@@ -359,12 +369,21 @@ def run_ours(args):
         for (f, i), (_, nbr, n_out, _) in zip(dev_sets, prepared):
             tables.append((nbr, _ext.input_major_table(nbr, f.shape[0])))
         fltT = flt.transpose(1, 2).contiguous()
-        for it in range(2 + 6):
-            f, (nbr, nbr_in), g = prepared[it % ROTATE][0], tables[it % ROTATE], grads[it % ROTATE]
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
+        bwd_graphs = []
+        for k in range(ROTATE):                       # recorded like the forward call: device time only
+            f, (nbr, nbr_in), g = prepared[k][0], tables[k], grads[k]
             _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32")
             _ext.conv_wgrad(f, g, nbr)
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32")
+                _ext.conv_wgrad(f, g, nbr)
+            bwd_graphs.append(cg)
+        for it in range(2 + 6):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            bwd_graphs[it % ROTATE].replay()
             b.record()
             torch.cuda.synchronize()
             if it >= 2:
@@ -399,7 +418,8 @@ def run_ours(args):
                        "eager_ms_per_step": eager_ms, "graph_fallbacks": graph_fallbacks,
                        "parallelism": "sample-sharded x%d, no data-path collective" % world},
             "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h),
-                    "how": "ss_conv.pipeline.HostStream: upload / compute / download of consecutive steps overlap on 3 streams",
+                    "how": "ss_conv.pipeline.HostStream (upload / compute / download of consecutive steps overlap on 3 streams) "
+                           "around the CUDA-graph replay of the step",
                     "serial_value": vox_e2e / serial_s},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),

@@ -714,9 +714,11 @@ def p2v_stats(points, batch_ids, grid, unit):
     return stats.tolist()
 
 
-def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode):
+def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode, ahead=False):
     """Fused voxelizer core: (voxel_indices [M,4] int32, inverse [N] int32, voxel_feats [M,C])
-    for batch-sorted, in-range points (one host sync for M)."""
+    for batch-sorted, in-range points (one host sync for M).  ahead=True skips that sync: the
+    outputs then have N rows (a voxel count can never exceed the point count), of which the first
+    M are meaningful, and a fourth value is returned, the device word holding M."""
     L = lib()
     dev = points.device
     points = points.contiguous().float()
@@ -730,12 +732,14 @@ def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode):
     unit3 = _F3(*[float(u) for u in unit])
     _check(L.ssc_p2v_count(_p(points), _p(batch_ids), n, int(batch_size), _i3(grid), unit3, _p(m_dev), _p(st),
                            _p(scratch), scratch.numel(), _stream()))
-    m = int(m_dev.item())
+    m = n if ahead else int(m_dev.item())
     vox = torch.empty((m, 4), dtype=torch.int32, device=dev)
     inverse = torch.empty(n, dtype=torch.int32, device=dev)
     vfeat = torch.empty((m, feats.shape[1]), dtype=torch.float32, device=dev)
     _check(L.ssc_p2v_fill(_p(points), _p(batch_ids), _p(feats), n, feats.shape[1], int(batch_size), _i3(grid), unit3,
                           int(mode), m, _p(vox), _p(inverse), _p(vfeat), _p(scratch), scratch.numel(), _stream()))
+    if ahead:
+        return vox, inverse, vfeat, m_dev
     return vox, inverse, vfeat
 
 

@@ -55,15 +55,26 @@ class GraphedChain(object):
         try:
             with torch.cuda.graph(graph):
                 out = self.fn(x)
-                counts = torch.cat([r.n_dev.reshape(1) for r in log]) if log else self.n.clone()
+                counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log])   # input count first
         finally:
             tensor_mod._capture_log = None
         self.launches = _ext.kernel_launches() - l0
-        self.graph, self.out, self.counts, self.caps = graph, out, counts, [r.capacity for r in log]
-        if len(self.caps) == 0 or (isinstance(out, SparseTensor) and not out.pending()):
+        self.graph, self.out, self.counts, self.caps = graph, out, counts, [self.cap] + [r.capacity for r in log]
+        if len(log) == 0 or (isinstance(out, SparseTensor) and not out.pending()):
             raise RuntimeError("nothing in this chain ran ahead of its row counts (no capacity hints yet?)")
 
-    def __call__(self, features, indices):
+    def __call__(self, features, indices=None):
+        """features [n, C] + indices [n, 4], or one SparseTensor.  A SparseTensor whose row count is
+        still pending (e.g. straight out of Point2Voxel) is taken as it is: its count joins the
+        counts that are checked after the replay, so nothing waits for it before."""
+        pending_in = None
+        if isinstance(features, SparseTensor):
+            if features.pending() and self.graph is not None:
+                pending_in = features
+            else:
+                features, indices = features.features, features.indices
+        if pending_in is not None:
+            return self._replay_pending(pending_in)
         n = int(features.shape[0])
         if n > self.cap:
             raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
@@ -77,13 +88,30 @@ class GraphedChain(object):
         self.feats[:n].copy_(features)
         self.inds[:n].copy_(indices)
         self.n.fill_(n)
+        return self._finish(lambda: (features, indices))
+
+    def _replay_pending(self, x):
+        f, i, n_dev = x.raw()
+        rows = min(self.cap, int(f.shape[0]))
+        self.feats[:rows].copy_(f[:rows])
+        self.inds[:rows].copy_(i[:rows])
+        self.n.copy_(n_dev.reshape(1))               # device to device: the host does not wait for the count
+
+        def exact():
+            x.resolve()
+            if x.features.shape[0] > self.cap:
+                raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (x.features.shape[0], self.cap))
+            return x.features, x.indices
+        return self._finish(exact)
+
+    def _finish(self, exact_inputs):
         self.graph.replay()
         self.replays += 1
         counts = self.counts.tolist()                # the one read-back of the batch
         if any(c > cap for c, cap in zip(counts, self.caps)):
             self.graph = None                        # record again (with the raised hints) next time
             self.fallbacks += 1
-            return self._eager(features, indices, False)
+            return self._eager(*exact_inputs(), False)
         out = self.out
         if isinstance(out, SparseTensor):
             f, i, _ = out.raw()

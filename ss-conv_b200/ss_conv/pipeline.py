@@ -19,8 +19,12 @@ class HostStream:
     of pinned CPU tensors (views into two rotating result buffers: consume or copy a result
     before asking for the result after next)."""
 
-    def __init__(self, step_fn, device, max_rows, depth=2):
+    def __init__(self, step_fn, device, max_rows, depth=2, step_reuses_outputs=False):
+        """step_reuses_outputs: the step writes its results into the same device buffers on every
+        call (a replayed CUDA graph does); the next step then waits until the previous result has
+        been downloaded."""
         self.fn, self.dev, self.cap, self.depth = step_fn, torch.device(device), int(max_rows), int(depth)
+        self.reuses = bool(step_reuses_outputs)
         self.up = torch.cuda.Stream(self.dev)
         self.down = torch.cuda.Stream(self.dev)
         self.stage_in, self.stage_out = [None] * depth, [None] * depth
@@ -77,6 +81,8 @@ class HostStream:
             except StopIteration:
                 nxt = None
             compute.wait_event(ready)
+            if self.reuses and pending is not None:
+                compute.wait_event(pending[1])       # the previous result has left the step's buffers
             outs = self.fn(*views)
             done = torch.cuda.Event()
             done.record(compute)

@@ -4,7 +4,7 @@ import torch
 import torch.nn as nn
 
 from .. import _ext
-from .tensor import SparseTensor
+from .tensor import PendingRows, SparseTensor
 from .functional import three_nn, three_interpolate
 
 
@@ -69,6 +69,13 @@ class Point2Voxel(nn.Module):
             if n_outside == 0 and n_down == 0 and last_id >= 0:
                 B1 = n_change + 1
                 fts = feature.float().contiguous()
+                if _ext.AHEAD and not (torch.is_grad_enabled() and feature.requires_grad):
+                    # the voxel count stays on the device too: buffers sized by the point count
+                    vox, _inverse, vfeat, m_dev = _ext.point2voxel(point_cloud, fts, ids32, max(last_id + 1, B1), grid_i,
+                                                                   unit_f, self.voxelization_mode, ahead=True)
+                    sparse = SparseTensor(vfeat, vox, self.voxel_num_limit.astype(np.int64), B1)
+                    sparse._rows = PendingRows(m_dev, vox.shape[0], None, None)
+                    return point_cloud, sparse, batch_ids, torch.ones(B1, dtype=torch.float32, device=device)
                 vox, _inverse, vfeat = _ext.point2voxel(point_cloud, fts, ids32, max(last_id + 1, B1), grid_i, unit_f,
                                                         self.voxelization_mode)
                 if torch.is_grad_enabled() and feature.requires_grad:

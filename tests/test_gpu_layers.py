@@ -305,6 +305,14 @@ def test_graphed_chain_replays_match_eager_results(cuda):
                     assert torch.equal(y.indices, wi) and torch.equal(y.features, wf)
                     assert torch.equal(g_dense(f, i), wd)
             assert g_sparse.replays == 8 and g_sparse.launches > 10
+            # the replayed step inside the overlapped host-fed loop (its output buffers are reused)
+            from ss_conv.pipeline import HostStream
+            host = [(f.cpu().pin_memory(), i.cpu().pin_memory()) for f, i in batches]
+            feed = HostStream(lambda f, i: (lambda y: (y.features, y.indices))(g_sparse(f, i)), cuda, cap,
+                              step_reuses_outputs=True)
+            got = [(of.clone(), oi.clone()) for of, oi in feed.run(iter(host * 2))]
+            for (of, oi), (wf, wi, _) in zip(got, want * 2):
+                assert torch.equal(oi, wi.cpu()) and torch.equal(of, wf.cpu())
             # a much denser batch overflows the recorded capacities: exact fallback, then a new graph
             ind = S.bernoulli_voxels(range(3), 20, 0.45, base_seed=99)
             f, i = dev(S.features(ind.shape[0], 5, 7), cuda), dev(ind, cuda)
@@ -315,6 +323,48 @@ def test_graphed_chain_replays_match_eager_results(cuda):
                 y = big(f, i)
                 assert torch.equal(y.indices, ref.indices) and torch.equal(y.features, ref.features)
         torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+
+
+def test_voxelizer_count_stays_on_the_device_into_a_graphed_chain(cuda):
+    """Point2Voxel hands out a tensor whose voxel count is still on the device; a GraphedChain
+    takes it as it is (the count is checked after the replay).  Results equal the exact path."""
+    from ss_conv import _ext
+    from ss_conv.convolution import Convolution
+    from ss_conv.graph import GraphedChain
+    from ss_conv.pool import GlobalAvgPool
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(6)
+    p2v = Point2Voxel([16] * 3, [1.0 / 16] * 3, 4)
+    conv = Convolution([(3, 0)], [(4, 0), (2, 1)], 3, stride=2, padding=1).to(cuda).eval()
+    gpool = GlobalAvgPool()
+
+    def net(x):
+        return gpool(conv(x))
+
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            g = None
+            for r in range(3):
+                pts, fts, ids = S.object_points(range(4), 600, base_seed=70 + 4 * r)
+                P, Fe, I = dev(pts, cuda), dev(fts, cuda), dev(ids, cuda)
+                x = p2v(P, Fe, I)[1]
+                assert x.pending()
+                if g is None:
+                    g = GraphedChain(net, x.spatial_shape, x.batch_size, 3, 4 * 600, cuda)
+                got = g(x).clone()
+                old = _ext.AHEAD
+                _ext.AHEAD = False
+                try:
+                    want = net(p2v(P, Fe, I)[1])
+                finally:
+                    _ext.AHEAD = old
+                assert torch.equal(got, want)
+            assert g.replays >= 2 and g.fallbacks == 0
         _ext.check_status(cuda)
     finally:
         _ext.set_precision("auto")
