@@ -132,11 +132,39 @@ __global__ void map_insert_kernel(const int4 *__restrict__ indices, int n, int b
   atomicMax(row_map + cell, j);
 }
 
-// One thread per input row: mark every output cell the row reaches.  The per-dimension
-// candidates (kernel index -> output coordinate, at most kMarkMaxK per dimension) are worked
-// out once, so the loop over the kernel volume has no division; bits that fall into the same
-// bitmap word (consecutive kz) are merged before the atomic.
-constexpr int kMarkMaxK = 8;
+// One thread per input row: mark every output cell the row reaches.  Bits that fall into the
+// same bitmap word (consecutive z) are merged before the atomic.
+// Output coordinates an input coordinate reaches along one dimension form an arithmetic
+// progression; this clips it to [0, limit) and returns its first element and length.
+struct Reach {
+  int first, step, n;
+};
+__device__ __forceinline__ Reach clip_progression(int lo, int step, int count, int limit) {
+  Reach r;
+  r.step = step;
+  const int i_min = lo < 0 ? (-lo + step - 1) / step : 0;
+  const int last = lo + (count - 1) * step;
+  int i_max = count - 1;
+  if (last > limit - 1) i_max = (limit - 1 - lo) >= 0 ? (limit - 1 - lo) / step : -1;
+  r.first = lo + i_min * step;
+  r.n = i_max - i_min + 1;
+  return r;
+}
+
+// Needs, per dimension, stride == 1 or dilation == 1 (or the transposed geometry): then the reached
+// outputs need no test of every kernel index and at most two divisions per dimension.
+__device__ __forceinline__ Reach reach_of(const Geometry &g, int d, int in) {
+  if (g.transpose)  // o = in*stride - pad + k*dil
+    return clip_progression(in * g.stride[d] - g.padding[d], g.dilation[d], g.ksize[d], g.out_shape[d]);
+  if (g.dilation[d] == 1) {  // o*stride = in + pad - k, k in [0, ksize): a contiguous range of o
+    const int hi_num = in + g.padding[d], lo_num = hi_num - g.ksize[d] + 1;
+    const int o_lo = lo_num <= 0 ? 0 : (lo_num + g.stride[d] - 1) / g.stride[d];
+    const int o_hi = hi_num / g.stride[d];
+    return clip_progression(o_lo, 1, o_hi - o_lo + 1, g.out_shape[d]);
+  }
+  // stride == 1: o = in + pad - k*dil
+  return clip_progression(in + g.padding[d] - (g.ksize[d] - 1) * g.dilation[d], g.dilation[d], g.ksize[d], g.out_shape[d]);
+}
 
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
                                     uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
@@ -144,38 +172,15 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
   if (j >= live_rows(n, n_dev)) return;
   int4 c = indices[j];
   if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
-  const int in[3] = {c.y, c.z, c.w};
-  int cand[3][kMarkMaxK];  // output coordinate for kernel index k along the dimension, or -1
-#pragma unroll
-  for (int d = 0; d < 3; ++d) {
-#pragma unroll
-    for (int k = 0; k < kMarkMaxK; ++k) {
-      int o = -1;
-      if (k < g.ksize[d]) {
-        if (g.transpose) {
-          o = in[d] * g.stride[d] - g.padding[d] + k * g.dilation[d];
-        } else {
-          int num = in[d] + g.padding[d] - k * g.dilation[d];
-          o = (num >= 0 && num % g.stride[d] == 0) ? num / g.stride[d] : -1;
-        }
-        if ((unsigned)o >= (unsigned)g.out_shape[d]) o = -1;
-      }
-      cand[d][k] = o;
-    }
-  }
+  const Reach rx = reach_of(g, 0, c.y), ry = reach_of(g, 1, c.z), rz = reach_of(g, 2, c.w);
+  if (rx.n <= 0 || ry.n <= 0 || rz.n <= 0) return;
   const int base_b = c.x * g.out_shape[0];
-#pragma unroll
-  for (int kx = 0; kx < kMarkMaxK; ++kx) {
-    if (cand[0][kx] < 0) continue;
-#pragma unroll
-    for (int ky = 0; ky < kMarkMaxK; ++ky) {
-      if (cand[1][ky] < 0) continue;
-      const uint32_t row = (uint32_t)((base_b + cand[0][kx]) * g.out_shape[1] + cand[1][ky]) * (uint32_t)g.out_shape[2];
+  for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
+    for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
+      const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
       uint32_t word = 0xFFFFFFFFu, bits = 0u;
-#pragma unroll
-      for (int kz = 0; kz < kMarkMaxK; ++kz) {
-        if (cand[2][kz] < 0) continue;
-        const uint32_t flat = row + (uint32_t)cand[2][kz];
+      for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
+        const uint32_t flat = row + (uint32_t)z;
         if ((flat >> 5) != word) {
           if (bits) atomicOr(bitmap + word, bits);
           word = flat >> 5;
@@ -185,10 +190,9 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
       }
       if (bits) atomicOr(bitmap + word, bits);
     }
-  }
 }
 
-// General fallback (a kernel extent above kMarkMaxK): one thread per (input row, kernel offset).
+// General fallback (stride and dilation both above one in some dimension): one thread per (input row, kernel offset).
 __global__ void mark_outputs_generic_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
                                             uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -656,7 +660,9 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (int e = build_hash(indices, n_in, batch, g, s, status, st, n_in_dev)) return e;
   cudaMemsetAsync(s.bitmap, 0, (size_t)s.n_words * 4, st);
   if (n_in > 0) {
-    if (g.ksize[0] <= kMarkMaxK && g.ksize[1] <= kMarkMaxK && g.ksize[2] <= kMarkMaxK) {
+    bool simple = true;
+    for (int d = 0; d < 3; ++d) simple = simple && (g.transpose || g.stride[d] == 1 || g.dilation[d] == 1);
+    if (simple) {
       { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
     } else {
       { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
