@@ -278,8 +278,10 @@ lookup_dense_kernel(const int4 *__restrict__ out_indices, int n_out, int batch, 
     }
     return (unsigned)v < (unsigned)g.in_shape[d] ? v : -1;
   };
-  int kappa = 0;
-  for (int kx = 0; kx < g.ksize[0]; ++kx) {
+  // gridDim.y = kernel extent along x: a block walks the offsets of one kx (more threads in flight)
+  int kappa = (int)blockIdx.y * g.ksize[1] * g.ksize[2];
+  {
+    const int kx = (int)blockIdx.y;
     const int x = coord(0, kx);
     for (int ky = 0; ky < g.ksize[1]; ++ky) {
       const int y = coord(1, ky);
@@ -499,7 +501,8 @@ static int lookup_and_compact(const int32_t *out_indices, int n_out, int n_in, i
   if (s.row_map != nullptr) {
     int32_t *counts = indice_num != nullptr ? s.chunk_counts : nullptr;
     if (counts) cudaMemsetAsync(counts, 0, (size_t)n_chunks * K * 4, st);
-    { lookup_dense_kernel<<<ceil_div(n_out > 0 ? n_out : 1, 256), 256, K * sizeof(int32_t), st>>>(
+    const dim3 lgrid(ceil_div(n_out > 0 ? n_out : 1, 256), g.ksize[0]);
+    { lookup_dense_kernel<<<lgrid, 256, K * sizeof(int32_t), st>>>(
           (const int4 *)out_indices, n_out, batch, g, s.row_map, nbr, counts, n_chunks, n_out_dev); note_launches(1); }
   } else {
     dim3 grid(n_chunks, K);
