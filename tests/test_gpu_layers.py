@@ -368,3 +368,44 @@ def test_voxelizer_count_stays_on_the_device_into_a_graphed_chain(cuda):
         _ext.check_status(cuda)
     finally:
         _ext.set_precision("auto")
+
+
+def test_ahead_path_edge_cases(cuda):
+    """Capacity-sized layers on awkward inputs: a transposed convolution, an anisotropic kernel with
+    dilation, a batch with an empty sample, a single voxel, and an empty tensor (which must take
+    the exact path) - all bit-equal to the exact results."""
+    from ss_conv import _ext
+    from ss_conv.pool import AvgPool
+    from ss_conv.sp_ops.conv import SparseConvolution
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    torch.manual_seed(8)
+    layers = [SparseConvolution(3, 8, 12, 3, stride=2, padding=1, transposed=True, bias=False).to(cuda),
+              SparseConvolution(3, 8, 12, (3, 1, 2), stride=1, padding=(2, 0, 1), dilation=(2, 1, 1), bias=True).to(cuda),
+              AvgPool(3, stride=2, padding=1)]
+    ind = S.bernoulli_voxels(range(3), 9, 0.2, base_seed=31)
+    ind = ind[ind[:, 0] != 1]                                   # sample 1 is empty
+    inputs = [(S.features(ind.shape[0], 8, 3), ind),
+              (S.features(1, 8, 4), np.array([[2, 4, 4, 4]], dtype=np.int32)),
+              (np.zeros((0, 8), np.float32), np.zeros((0, 4), np.int32))]
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            for layer in layers:
+                for feats, idx in inputs:
+                    def run():
+                        y = layer(SparseTensor(dev(feats, cuda), dev(idx, cuda), [9] * 3, 3))
+                        return y.features.cpu().numpy(), y.indices.cpu().numpy()
+                    old = _ext.AHEAD
+                    _ext.AHEAD = False
+                    try:
+                        want = run()
+                    finally:
+                        _ext.AHEAD = old
+                    run()                      # records the ratio (exact path)
+                    got = run()                # capacity-sized path where it applies
+                    np.testing.assert_array_equal(got[1], want[1])
+                    np.testing.assert_array_equal(got[0], want[0])
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
