@@ -32,6 +32,8 @@ namespace ssc {
 int conv_fwd_tf32_ts(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                      const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st);
 int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st);
+int conv_fwd_tf32_wide(const float *staged, int c_pad, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
+                       int n_out, float *out, int32_t *status, const int32_t *n_out_dev, cudaStream_t st);
 int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                           const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch,
                           size_t scratch_bytes, cudaStream_t st);
@@ -181,7 +183,6 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   uint8_t *ctrl = smem + (size_t)p.stages * stage_bytes;
   uint64_t *empty_bars = (uint64_t *)ctrl;                 // [stages] slot free (its MMAs retired)
   uint64_t *fulla_bars = (uint64_t *)(ctrl + 64);          // [stages] gathered rows ready
-  uint64_t *fullb_bars = (uint64_t *)(ctrl + 128);         // [stages] filter slab landed
   uint64_t *done_bar = (uint64_t *)(ctrl + 192);           // all MMAs of the tile retired
   uint32_t *tmem_slot = (uint32_t *)(ctrl + 200);
   volatile int *abort_flag = (volatile int *)(ctrl + 204);
@@ -200,8 +201,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(empty_bars + s), 1);
-      mbar_init(smem_u32(fulla_bars + s), 32u * (uint32_t)(S < TC_EPI_WARPS ? TC_EPI_WARPS / S : 1));
-      mbar_init(smem_u32(fullb_bars + s), 1);
+      // one barrier per slot for both operands: every producer lane arrives for its gathered rows,
+      // and the lane that starts the filter copy arrives once more with the copy's byte count
+      // (the issuing thread then pays one barrier round trip per step, not two)
+      mbar_init(smem_u32(fulla_bars + s), 32u * (uint32_t)(S < TC_EPI_WARPS ? TC_EPI_WARPS / S : 1) + 1u);
     }
     mbar_init(smem_u32(done_bar), 1);
     *abort_flag = 0;
@@ -306,7 +309,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       if (part == 0 && lane == 0) {  // the pre-packed filter slab of this step: one bulk copy
         const uint4 *bsrc = packed + ((size_t)kappa * p.k_slabs + slab0) * (size_t)(p.n_pad * 8) +
                             (size_t)nt0 * (size_t)(p.tile_n * 8);
-        const uint32_t bar = smem_u32(fullb_bars + slot), nbytes = (uint32_t)(n_sub * p.b_bytes);
+        const uint32_t bar = smem_u32(fulla_bars + slot), nbytes = (uint32_t)(n_sub * p.b_bytes);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbytes) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                          slot_addr + (uint32_t)(p.sps * TC_A_BYTES)),
@@ -377,12 +380,11 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     // handful of instructions: slot index, parity and descriptor halves are running values.
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t a_lo0 = desc_lo(smem_base), slot_step = (uint32_t)stage_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
-    const uint32_t fulla0 = smem_u32(fulla_bars), fullb0 = smem_u32(fullb_bars), empty0 = smem_u32(empty_bars);
+    const uint32_t fulla0 = smem_u32(fulla_bars), empty0 = smem_u32(empty_bars);
     uint32_t s = 0, par = 0, a_lo = a_lo0;
     int grp = 0;  // which slab group of its kernel offset the current step is
     for (int it = 0; it < n_iter; ++it) {
       if (!mbar_wait(fulla0 + s * 8u, par, abort_flag)) break;
-      if (!mbar_wait(fullb0 + s * 8u, par, abort_flag)) break;
       tc_fence_after();
       const uint4 off = *(const uint4 *)(slot_masks + s * 4u);  // rows to leave untouched
       const int n_sub = min(p.sps, p.k_slabs - grp * p.sps);
@@ -496,11 +498,17 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   const int c_pad = (c_in + 3) & ~3;  // row stride of the staged image (zero-padded channels)
   const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_pad * sizeof(float);
   const char *no_stage = getenv("SSC_TC_NO_STAGING");
+  const bool force_wide = variant != nullptr && strcmp(variant, "wide") == 0;
   const bool staged = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0 &&
-                      grid >= kStagingMinTiles && no_stage == nullptr;
+                      (grid >= kStagingMinTiles || force_wide) && no_stage == nullptr;
   if (staged) {
     int rc = stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
+    // persistent variant: several row tiles per pass share every filter slab
+    if (force_wide) {
+      rc = conv_fwd_tf32_wide((const float *)scratch, c_pad, c_in, packed, K, c_out, nbr, n_out, out, status, n_out_dev, st);
+      if (rc >= 0) return rc;
+    }
   }
   auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

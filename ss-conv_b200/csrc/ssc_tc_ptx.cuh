@@ -43,6 +43,24 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   ok = __shfl_sync(0xffffffffu, ok, 0);
   return ok != 0;
 }
+// Bounded waits for the roles that are NOT on the critical path: after a few polls the thread
+// sleeps `ns` between polls, which leaves the issue slots and the barrier unit to the threads
+// that are.  Same contract as mbar_wait / mbar_wait_warp.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t ns) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 4u) __nanosleep(ns);
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_warp_backoff(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t ns) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_backoff(bar, parity, abort_flag, ns) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -477,7 +477,7 @@ def _resolve_precision(c_in, c_out, precision=None):
 # Layers with fewer output rows do not stage a TF32-rounded copy of their input rows (the extra
 # launch would cost more than it saves), so no staging buffer is allocated for them
 # (SSC_TC_VARIANT=gather4 forces the TMA-gather kernel, which always needs it).
-STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") == "gather4" else 64 * 128
+STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") in ("gather4", "wide") else 64 * 128
 
 
 def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None):

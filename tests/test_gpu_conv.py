@@ -194,6 +194,25 @@ def test_conv_tma_gather_variant(cuda, c_in, c_out, k, subm, monkeypatch):
     assert _ext.kernel_launches() - l0 >= 3        # staging + conv (+ packing, + rulebook)
 
 
+@pytest.mark.parametrize("c_in,c_out,k,subm,batch,grid,per", [(64, 76, 3, False, 3, 14, 900), (32, 38, 3, True, 3, 14, 900),
+                                                              (20, 8, 3, False, 3, 14, 900), (128, 256, 3, False, 3, 14, 900),
+                                                              (16, 16, 5, True, 3, 14, 900), (64, 76, 3, True, 4, 40, 20000),
+                                                              (32, 16, 3, False, 4, 48, 40000)])
+def test_conv_wide_variant(cuda, c_in, c_out, k, subm, batch, grid, per, monkeypatch):
+    """The persistent one-CTA-per-SM kernel whose row tiles share each filter slab
+    (SSC_TC_VARIANT=wide); the two large cases give every CTA several passes.  It accumulates in
+    the same order as the default kernel, so the results are bit-identical."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(c_in * 7 + c_out)
+    ind = random_voxels(rng, batch, grid, per)
+    monkeypatch.setattr(_ext, "STAGING_MIN_ROWS", 0)
+    base, _ = _run(cuda, ind, batch, grid, k, 1, k // 2, subm, c_in, c_out, "tf32")
+    monkeypatch.setenv("SSC_TC_VARIANT", "wide")
+    y, ref = _run(cuda, ind, batch, grid, k, 1, k // 2, subm, c_in, c_out, "tf32")
+    assert rel_err(y, ref) <= TOL["tf32"]
+    np.testing.assert_array_equal(y, base)
+
+
 @pytest.mark.parametrize("c_in,c_out", [(64, 76), (3, 36), (30, 20)])
 def test_conv_staged_rows_give_the_same_bits(cuda, monkeypatch, c_in, c_out):
     """Rounding the feature rows to TF32 once in a staging buffer (rows zero-padded to a multiple of
