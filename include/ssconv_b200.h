@@ -154,7 +154,8 @@ int ssc_materialize(const float *weight, const float *basis, const int32_t *bloc
                     int c_in, int K, float *filters, void *stream);
 
 /* Pack filters [K,Cin,Cout] fp32 into the tensor-core operand image used by ssc_conv_fwd
- * with precision SSC_PREC_TF32 (round-to-nearest TF32, K-major, 128-byte swizzled, padded).
+ * with precision SSC_PREC_TF32 (round-to-nearest TF32, K-major, 128-byte swizzled, padded) or
+ * SSC_PREC_F16 (the same layout with fp16 elements, 64 input channels per 128-byte row).
  * ssc_conv_packed_bytes gives the size of `packed`. */
 size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision);
 int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision,
@@ -166,7 +167,12 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  *   out[o,:] = sum_kappa features[nbr[kappa][o],:] * filters[kappa]   (fp32 accumulate)
  * as ONE launch, output-stationary (no scatter atomics, deterministic).
  * precision: SSC_PREC_FP32 = exact fp32 FMA on CUDA cores (filters = [K,Cin,Cout] fp32);
- *            SSC_PREC_TF32 = tcgen05 tensor cores, TF32 operands (filters = packed image).
+ *            SSC_PREC_TF32 = tcgen05 tensor cores, TF32 operands (filters = packed image);
+ *            SSC_PREC_F16  = tcgen05 tensor cores, fp16 operands and fp32 accumulation (the
+ *            reference's half-precision entry point indice_conv_half, SS_Conv_lib/src/ss_conv_ops.h:49-51): the same
+ *            11-bit significand as TF32 within fp16's range (finite values beyond +-65504
+ *            saturate, magnitudes below 6e-5 lose bits), half the gathered bytes and half the
+ *            tensor-core instructions.  Needs `scratch` (the fp16 copy of the feature rows).
  * status: device int32 that receives a non-zero value if a bounded wait inside the kernel
  * ran out (may be NULL).
  * scratch: optional device buffer of ssc_conv_scratch_bytes() bytes, 128-byte aligned.  With it
@@ -178,6 +184,7 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  * capacity (see ssc_rulebook_conv_fill); rows past the exact count are not written. */
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
+#define SSC_PREC_F16 2
 size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision);
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                  const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,

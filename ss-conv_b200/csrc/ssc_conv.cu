@@ -8,6 +8,10 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
                   const int32_t *n_out_dev, cudaStream_t st);
 size_t conv_gather4_scratch_bytes(int n_in, int c_in, int c_out);
+size_t conv_f16_scratch_bytes(int n_in, int c_in);
+int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
+                 int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
+                 cudaStream_t st);
 
 // filters[kappa][cin][cout] = sum_b w[u,v,b] * basis[b,a,c,kappa]; one thread per element,
 // cout fastest so the (large) filter tensor is written coalesced; the basis blob is small
@@ -140,7 +144,9 @@ extern "C" int ssc_materialize(const float *weight, const float *basis, const in
 }
 
 extern "C" size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision) {
-  if (precision != SSC_PREC_TF32 || n_in < 0 || c_in < 1 || c_out < 1) return 0;
+  if (n_in < 0 || c_in < 1 || c_out < 1) return 0;
+  if (precision == SSC_PREC_F16) return conv_f16_scratch_bytes(n_in, c_in);
+  if (precision != SSC_PREC_TF32) return 0;
   return conv_gather4_scratch_bytes(n_in, c_in, c_out);
 }
 
@@ -158,5 +164,6 @@ extern "C" int ssc_conv_fwd(const float *features, int n_in, int c_in, const voi
     return SSC_OK;
   }
   if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, st);
+  if (precision == SSC_PREC_F16) return conv_fwd_f16(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, st);
   return fail(SSC_ERR_INVALID, "conv_fwd: unknown precision %d", precision);
 }

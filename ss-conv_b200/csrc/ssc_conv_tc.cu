@@ -167,7 +167,9 @@ __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int 
 
 // Warps 0 .. n_prod-1 are producers (warp w <-> ring slot w; with fewer than four slots the
 // spare warps only help in the prologue and epilogue), the last warp issues the MMAs.
-template <bool STAGED>
+// F16: the staged image and the filter slabs hold fp16 (64 channels per 128-byte row); the
+// gather is the same byte-for-byte, `c_in` is then the row length in 4-byte units.
+template <bool STAGED, bool F16 = false>
 __global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
@@ -378,7 +380,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     // ================================ MMA issuer ============================================
     // The issuing thread is the serial bottleneck of the pipeline, so its loop is kept to a
     // handful of instructions: slot index, parity and descriptor halves are running values.
-    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+    // fp32 accumulator; operand formats 2 = TF32, 0 = fp16
+    const uint32_t idesc = (1u << 4) | ((F16 ? 0u : 2u) << 7) | ((F16 ? 0u : 2u) << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t a_lo0 = desc_lo(smem_base), slot_step = (uint32_t)stage_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
     const uint32_t fulla0 = smem_u32(fulla_bars), empty0 = smem_u32(empty_bars);
     uint32_t s = 0, par = 0, a_lo = a_lo0;
@@ -393,10 +396,17 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         for (int nt = 0; nt < p.nt_cta; ++nt) {
           const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n);
           const uint32_t bn = a_lo + (uint32_t)(p.sps * TC_A_BYTES >> 4) + (uint32_t)ss * ((uint32_t)p.b_bytes >> 4) + (uint32_t)nt * n_step;
-          mma_tf32_ss_masked(dn, an, bn, idesc, off);
-          mma_tf32_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
-          mma_tf32_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
-          mma_tf32_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+          if (F16) {
+            mma_f16_ss_masked(dn, an, bn, idesc, off);
+            mma_f16_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
+            mma_f16_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
+            mma_f16_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+          } else {
+            mma_tf32_ss_masked(dn, an, bn, idesc, off);
+            mma_tf32_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
+            mma_tf32_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
+            mma_tf32_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+          }
         }
       }
       if (++grp == p.k_groups) grp = 0;
@@ -459,6 +469,88 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 
 static size_t tc_smem_bytes(const TcParams &p) {
   return (size_t)p.stages * p.sps * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES;
+}
+
+// fp16 operands: filters [K, c_in, c_out] fp32 -> [K][k_slabs][n_pad rows][64 fp16], same swizzle
+// (a 16-byte chunk holds 8 input channels).
+__global__ void pack_filters_f16_kernel(const float *__restrict__ filters, int K, int c_in, int c_out, TcParams p,
+                                        uint4 *__restrict__ packed) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = (long long)K * p.k_slabs * p.n_pad * 8;
+  if (t >= total) return;
+  int chunk = (int)(t & 7);
+  long long r = t >> 3;
+  int n = (int)(r % p.n_pad);
+  r /= p.n_pad;
+  int slab = (int)(r % p.k_slabs);
+  int kappa = (int)(r / p.k_slabs);
+  uint32_t v[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float f[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int ci = slab * 64 + chunk * 8 + q * 2 + h;
+      f[h] = (ci < c_in && n < c_out) ? filters[((size_t)kappa * c_in + ci) * c_out + n] : 0.f;
+    }
+    v[q] = pack_f16x2(f[0], f[1]);
+  }
+  size_t block = ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
+  size_t off = (size_t)(n >> 3) * 64 + (size_t)(n & 7) * 8 + (size_t)(chunk ^ (n & 7));
+  packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
+}
+
+// features [n_in, c_in] fp32 -> staged [n_in + 1, c_pad] fp16 (round to nearest, finite values
+// beyond the fp16 range saturate), c_pad = c_in rounded up to 8, padding and last row zero.
+__global__ void stage_features_f16_kernel(const float *__restrict__ in, long long n_rows, int c_in, int c_pad,
+                                          long long total_pairs, uint32_t *__restrict__ out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  const int pairs = c_pad >> 1;
+  for (; i < total_pairs; i += step) {
+    const long long r = i / pairs;
+    const int c = (int)(i - r * pairs) * 2;
+    float a = 0.f, b = 0.f;
+    if (r < n_rows) {
+      if (c < c_in) a = __ldg(in + r * c_in + c);
+      if (c + 1 < c_in) b = __ldg(in + r * c_in + c + 1);
+    }
+    out[i] = pack_f16x2(a, b);
+  }
+}
+
+// Width of an fp16 row in 4-byte units (rows are padded to 16 bytes): the kernel gathers it like
+// an fp32 image of that many channels.
+static inline int f16_row_words(int c_in) { return ((c_in + 7) & ~7) / 2; }
+
+size_t conv_f16_scratch_bytes(int n_in, int c_in) { return ((size_t)n_in + 1) * (size_t)f16_row_words(c_in) * 4; }
+
+int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
+                 int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
+                 cudaStream_t st) {
+  if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(fp16): kernel volume %d > 256", K);
+  const int words = f16_row_words(c_in);
+  if (scratch == nullptr || scratch_bytes < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
+    return fail(SSC_ERR_INVALID, "conv_fwd(fp16): needs the staging buffer of ssc_conv_scratch_bytes (16-byte aligned)");
+  int grid = ceil_div(n_out, TC_M);
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  TcParams p;
+  if (!tc_params(words, c_out, p, grid < 2 * sms))
+    return fail(SSC_ERR_INVALID, "conv_fwd(fp16): c_out %d / kernel volume %d not supported", c_out, K);
+  const long long total_pairs = ((long long)n_in + 1) * words;
+  int blocks = ceil_div(total_pairs, 256 * 4);
+  if (blocks > sms * 16) blocks = sms * 16;
+  { stage_features_f16_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, words * 2, total_pairs, (uint32_t *)scratch); note_launches(1); }
+  SSC_CHECK_LAUNCH("stage_features_f16");
+  const size_t smem = tc_smem_bytes(p);
+  auto kernel = conv_fwd_tf32_kernel<true, true>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(fp16): smem attribute: %s", cudaGetErrorString(e));
+  const dim3 grid2(grid, p.n_tiles / p.nt_cta);
+  { kernel<<<grid2, p.threads, smem, st>>>((const float *)scratch, words, (const uint4 *)packed, K, c_out, nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
+  SSC_CHECK_LAUNCH("conv_fwd_f16");
+  return SSC_OK;
 }
 
 // Smallest problem (in 128-row tiles) the persistent gather4 kernel is used for by default: below
@@ -525,19 +617,24 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
 using namespace ssc;
 
 extern "C" size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision) {
-  if (precision != SSC_PREC_TF32 || K < 1 || c_in < 1 || c_out < 1) return 0;
+  if ((precision != SSC_PREC_TF32 && precision != SSC_PREC_F16) || K < 1 || c_in < 1 || c_out < 1) return 0;
   TcParams p;
-  if (!tc_params(c_in, c_out, p)) return 0;
+  if (!tc_params(precision == SSC_PREC_F16 ? f16_row_words(c_in) : c_in, c_out, p)) return 0;
   return (size_t)K * p.k_slabs * p.n_pad * 128;
 }
 
 extern "C" int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision, void *packed,
                                      void *stream) {
-  SSC_REQUIRE(precision == SSC_PREC_TF32, "conv_pack_filters: only SSC_PREC_TF32 has a packed form");
+  SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16, "conv_pack_filters: only SSC_PREC_TF32 and SSC_PREC_F16 have a packed form");
   SSC_REQUIRE(filters && packed && K >= 1 && c_in >= 1 && c_out >= 1, "conv_pack_filters: bad arguments");
   TcParams p;
-  SSC_REQUIRE(tc_params(c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
+  SSC_REQUIRE(tc_params(precision == SSC_PREC_F16 ? f16_row_words(c_in) : c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
   long long total = (long long)K * p.k_slabs * p.n_pad * 8;
+  if (precision == SSC_PREC_F16) {
+    { pack_filters_f16_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
+    SSC_CHECK_LAUNCH("pack_filters_f16");
+    return SSC_OK;
+  }
   { pack_filters_tf32_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
   SSC_CHECK_LAUNCH("pack_filters_tf32");
   return SSC_OK;

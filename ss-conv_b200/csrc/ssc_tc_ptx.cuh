@@ -92,6 +92,12 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return r;
 }
+// Two floats -> two fp16 in one word (lo = a), round to nearest even, finite overflow saturates.
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
 // .ca: a lane fetches the eight 16-byte chunks of one 128-byte row with eight copies; letting
 // them allocate in L1 turns seven of the eight into L1 hits.
 
@@ -122,6 +128,18 @@ __device__ __forceinline__ void mma_tf32_ss_masked(uint32_t tmem_c, uint32_t a_l
       "mov.b64 da, {%1, %5};\n\t"
       "mov.b64 db, {%2, %5};\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, {%6, %7, %8, %9}, p;\n\t}"
+      :
+      : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(1u), "r"(kDescHi), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
+      : "memory");
+}
+// The same for fp16 operands (kind::f16, 16 elements = 32 bytes along K per instruction).
+__device__ __forceinline__ void mma_f16_ss_masked(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint4 off) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, {%6, %7, %8, %9}, p;\n\t}"
       :
       : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(1u), "r"(kDescHi), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
       : "memory");

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # SSCONV_B200_LIB selects another build of the same library (e.g. a debug build)
 LIB_PATH = os.environ.get("SSCONV_B200_LIB", os.path.join(_HERE, "libssconv_b200.so"))
 
-PREC_FP32, PREC_TF32 = 0, 1
+PREC_FP32, PREC_TF32, PREC_F16 = 0, 1, 2
 _precision = os.environ.get("SSCONV_PRECISION", "auto")
 
 c_int, c_size_t, c_void_p, c_float = ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_float
@@ -109,11 +109,13 @@ def kernel_launches():
 
 
 def set_precision(mode):
-    """'fp32' (exact CUDA-core path), 'tf32' (tcgen05 tensor cores) or 'auto'
+    """'fp32' (exact CUDA-core path), 'tf32' (tcgen05 tensor cores), 'fp16' (tcgen05 with
+    fp16 operands: the same 11-bit significand as TF32 but fp16's range, half the gathered
+    bytes and half the tensor-core instructions; opt-in only) or 'auto'
     (tf32 when the layer has at least 16 input channels)."""
     global _precision
-    if mode not in ("fp32", "tf32", "auto"):
-        raise ValueError("precision must be 'fp32', 'tf32' or 'auto'")
+    if mode not in ("fp32", "tf32", "fp16", "auto"):
+        raise ValueError("precision must be 'fp32', 'tf32', 'fp16' or 'auto'")
     _precision = mode
 
 
@@ -456,14 +458,14 @@ def materialize(weight, basis, block_table, n_blocks_in, out_field, in_field, c_
     return flt
 
 
-def pack_filters(filters_kio):
-    """TF32 tensor-core operand image of contiguous filters [K, Cin, Cout]."""
+def pack_filters(filters_kio, prec=PREC_TF32):
+    """Tensor-core operand image (TF32 or fp16) of contiguous filters [K, Cin, Cout]."""
     K, c_in, c_out = filters_kio.shape
-    nbytes = lib().ssc_conv_packed_bytes(K, c_in, c_out, PREC_TF32)
+    nbytes = lib().ssc_conv_packed_bytes(K, c_in, c_out, prec)
     if nbytes == 0:
         raise ValueError("channel count not supported by the tensor-core path")
     packed = torch.empty(int(nbytes), dtype=torch.uint8, device=filters_kio.device)
-    _check(lib().ssc_conv_pack_filters(_p(filters_kio, torch.float32), K, c_in, c_out, PREC_TF32, _p(packed), _stream()))
+    _check(lib().ssc_conv_pack_filters(_p(filters_kio, torch.float32), K, c_in, c_out, prec, _p(packed), _stream()))
     return packed
 
 
@@ -492,19 +494,25 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None):
     out = torch.empty((n_out, c_out), dtype=torch.float32, device=features.device)
     mode = _resolve_precision(c_in, c_out, precision)
     st = status_word(features.device)
-    if mode == "tf32":
+    if mode == "fp16" and c_out > 512:
+        mode = "fp32"
+    if mode in ("tf32", "fp16"):
+        prec = PREC_F16 if mode == "fp16" else PREC_TF32
+        tag = (prec, filters._version)
         packed = getattr(filters, "_ssc_packed", None)
-        if packed is None or getattr(filters, "_ssc_packed_version", None) != filters._version:
-            packed = pack_filters(filters.contiguous())
+        if packed is None or getattr(filters, "_ssc_packed_version", None) != tag:
+            packed = pack_filters(filters.contiguous(), prec)
             try:
                 filters._ssc_packed = packed
-                filters._ssc_packed_version = filters._version
+                filters._ssc_packed_version = tag
             except Exception:
                 pass
-        nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, PREC_TF32) if n_out >= STAGING_MIN_ROWS else 0
+        # the fp16 kernel always gathers from its staged fp16 image
+        stage = prec == PREC_F16 or n_out >= STAGING_MIN_ROWS
+        nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec) if stage else 0
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
-                                  _p(nbr, torch.int32), int(n_out), PREC_TF32, _p(out), _p(st), _p(scratch), nbytes,
+                                  _p(nbr, torch.int32), int(n_out), prec, _p(out), _p(st), _p(scratch), nbytes,
                                   _p(n_out_dev), _stream()))
     else:
         filters = filters.contiguous()
@@ -536,7 +544,7 @@ def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, i
 def _not_built(name):
     def f(*a, **k):
         raise NotImplementedError(name + " is not built: this library covers the fp32 forward and backward path; "
-                                  "fp16 storage, the field max pool and the voxelizer's backward are not part of it")
+                                  "fp16 pools and the field max pool are not part of it")
     f.__name__ = name
     return f
 
@@ -554,7 +562,8 @@ def conv_wgrad(features, out_grad, nbr, precision=None):
     (tensor cores with TF32 operands or exact fp32, chosen like the forward pass)."""
     K, n_out = nbr.shape
     c_in, c_out = features.shape[1], out_grad.shape[1]
-    mode = PREC_TF32 if _resolve_precision(c_in, c_out, precision) == "tf32" else PREC_FP32
+    # the filter gradient has no fp16 form: 'fp16' takes the TF32 kernel
+    mode = PREC_TF32 if _resolve_precision(c_in, c_out, precision) in ("tf32", "fp16") else PREC_FP32
     d_flt = torch.empty((K, c_in, c_out), dtype=torch.float32, device=features.device)
     nbytes = int(lib().ssc_conv_wgrad_scratch_bytes(K, c_in, c_out, n_out))
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=features.device)
@@ -582,8 +591,35 @@ def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_nu
     return [d_in, d_flt.reshape(filters.shape)]
 
 
-indice_conv_half = _not_built("indice_conv_half")
-indice_conv_backward_half = _not_built("indice_conv_backward_half")
+def indice_conv_half(features, filters, indice_pairs, indice_num, num_act_out, inverse, subm):
+    """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:49-51): half tensors in, half tensor out.
+    The tensor cores take the fp16 operands as they are and accumulate in fp32 (the reference's
+    cuBLAS half GEMM per kernel offset rounds every partial product sum to fp16); only the result
+    is rounded to fp16."""
+    if features.dtype != torch.half or filters.dtype != torch.half:
+        raise TypeError("indice_conv_half expects float16 features and filters")
+    c_in, c_out = filters.shape[-2], filters.shape[-1]
+    flt = filters.reshape(-1, c_in, c_out).float()
+    nbr, n_out_dev = _table_for(indice_pairs, indice_num, int(num_act_out), bool(inverse))
+    out = conv_forward(features.float(), flt, nbr, int(num_act_out), precision="fp16", n_out_dev=n_out_dev)
+    return out.half()
+
+
+def indice_conv_backward_half(features, filters, out_bp, indice_pairs, indice_num, inverse, subm):
+    """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:52-54): [input_grad, filters_grad] in half.
+    The input gradient runs on fp16 operands, the filter gradient on TF32 operands (the same
+    significand, fp32 range), both with fp32 accumulation."""
+    if features.dtype != torch.half or filters.dtype != torch.half:
+        raise TypeError("indice_conv_backward_half expects float16 features and filters")
+    c_in, c_out = filters.shape[-2], filters.shape[-1]
+    flt = filters.reshape(-1, c_in, c_out).float()
+    feats, grad = features.float().contiguous(), out_bp.float().contiguous()
+    n_in, n_out = feats.shape[0], grad.shape[0]
+    nbr = neighbour_table(indice_pairs, indice_num, n_out, bool(inverse))
+    nbr_in = input_major_table(nbr, n_in)
+    d_in = conv_forward(grad, flt.transpose(1, 2).contiguous(), nbr_in, n_in, precision="fp16")
+    d_flt = conv_wgrad(feats, grad, nbr, precision="tf32")
+    return [d_in.half(), d_flt.reshape(filters.shape).half()]
 
 
 # ================================================================================== pools

@@ -9,7 +9,8 @@ import ssconv_oracle as O
 from gpu_helpers import dev, gpu_rulebook, random_voxels, rel_err
 
 pytestmark = pytest.mark.gpu
-TOL = {"fp32": 2e-5, "tf32": 1e-3}
+# fp16 operands carry the same 11-bit significand as TF32
+TOL = {"fp32": 2e-5, "tf32": 1e-3, "fp16": 1e-3}
 
 
 def _run(cuda, ind, batch, V, k, s, p, subm, c_in, c_out, precision, seed=0):
@@ -211,6 +212,45 @@ def test_conv_wide_variant(cuda, c_in, c_out, k, subm, batch, grid, per, monkeyp
     y, ref = _run(cuda, ind, batch, grid, k, 1, k // 2, subm, c_in, c_out, "tf32")
     assert rel_err(y, ref) <= TOL["tf32"]
     np.testing.assert_array_equal(y, base)
+
+
+@pytest.mark.parametrize("c_in,c_out,k,subm,batch,grid,per", [(64, 76, 3, False, 3, 14, 900), (32, 38, 3, True, 3, 14, 900),
+                                                              (20, 8, 3, False, 3, 14, 900), (130, 270, 3, False, 2, 12, 330),
+                                                              (3, 36, 3, True, 2, 12, 330), (16, 16, 5, True, 3, 14, 900),
+                                                              (64, 76, 3, True, 4, 40, 20000), (200, 64, 2, False, 2, 16, 2000)])
+def test_conv_fp16_operands(cuda, c_in, c_out, k, subm, batch, grid, per):
+    """precision 'fp16': feature rows and filters rounded to fp16 (64 channels per 128-byte operand
+    row), fp32 accumulation.  Odd channel counts exercise the zero padding of rows and slabs."""
+    rng = np.random.RandomState(c_in * 3 + c_out)
+    ind = random_voxels(rng, batch, grid, per)
+    y, ref = _run(cuda, ind, batch, grid, k, 1 if subm else 2, k // 2 if subm else 0, subm, c_in, c_out, "fp16")
+    assert rel_err(y, ref) <= TOL["fp16"]
+
+
+def test_conv_half_entry_points(cuda):
+    """indice_conv_half / indice_conv_backward_half (half tensors in and out) against the fp64
+    oracle run on the same fp16-rounded inputs: only the final rounding to fp16 is left."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(5)
+    ind = random_voxels(rng, 2, 12, 500)
+    c_in, c_out, k = 32, 48, 3
+    feats = rng.randn(ind.shape[0], c_in).astype(np.float16)
+    W = (rng.randn(k, k, k, c_in, c_out) / np.sqrt(c_in * k ** 3)).astype(np.float16)
+    outids, pairs, num = gpu_rulebook(ind, 2, [12] * 3, k, 1, 1, 1, True, cuda)
+    n_out = outids.shape[0]
+    y = _ext.indice_conv_half(dev(feats, cuda), dev(W, cuda), pairs, num, n_out, 0, 1)
+    assert y.dtype == torch.half
+    ref = O.indice_conv_f64(feats.astype(np.float32), W.astype(np.float32), pairs.cpu().numpy(), num.cpu().numpy(), n_out)
+    assert rel_err(y.float().cpu().numpy(), ref) <= 1e-3
+    g = rng.randn(n_out, c_out).astype(np.float16)
+    d_in, d_w = _ext.indice_conv_backward_half(dev(feats, cuda), dev(W, cuda), dev(g, cuda), pairs, num, 0, 1)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    assert d_in.dtype == torch.half and d_w.dtype == torch.half and d_w.shape == W.shape
+    ref_in, ref_w = O.indice_conv_backward(feats.astype(np.float64), W.astype(np.float64), g.astype(np.float64),
+                                           pairs.cpu().numpy(), num.cpu().numpy(), subm=True, dtype=np.float64)
+    assert rel_err(d_in.float().cpu().numpy(), ref_in) <= 1e-3
+    assert rel_err(d_w.float().cpu().numpy().reshape(ref_w.shape), ref_w) <= 2e-3
 
 
 @pytest.mark.parametrize("c_in,c_out", [(64, 76), (3, 36), (30, 20)])

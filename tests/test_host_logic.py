@@ -44,7 +44,7 @@ def test_argument_errors_without_gpu():
         _ext.indice_maxpool_fp32(torch.zeros(4, 4), torch.zeros(1, 2, 4, dtype=torch.int32),
                                  torch.zeros(1, dtype=torch.int32), 4)
     with pytest.raises(NotImplementedError):
-        _ext.indice_conv_backward_half()
+        _ext.indice_field_maxpool_fp32()
 
 
 def test_output_size_and_shards():
