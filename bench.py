@@ -360,6 +360,26 @@ def run_ours(args):
                 alg_bytes.append(4 * (f.shape[0] * ci + n_out * co + K * ci * co) + 8 * P)
                 flops.append(2.0 * P * ci * co)
     n_out_conv = prepared[0][2]
+    # ---- the same call with fp16 operands (opt-in precision 'fp16'; not the headline configuration)
+    f16_ms = []
+    with torch.no_grad():
+        f16_graphs = []
+        for f, nbr, n_out, P in prepared:
+            _ext.conv_forward(f, flt, nbr, n_out, "fp16")
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                _ext.conv_forward(f, flt, nbr, n_out, "fp16")
+            f16_graphs.append(g)
+        for it in range(3 + 12):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            f16_graphs[it % ROTATE].replay()
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                f16_ms.append(a.elapsed_time(b))
+        del f16_graphs
     # ---- backward of the same layer (input gradient through the tcgen05 kernel on the input-major
     #      table, tensor-core filter gradient), CUDA events, the rulebook of the forward pass reused
     bwd_ms = []
@@ -433,6 +453,9 @@ def run_ours(args):
         }
         line["backward"] = {"what": "input gradient + filter gradient of the cfg2 convolution, both tcgen05 with TF32 operands",
                             "ms": float(np.mean(bwd_ms)), "voxels_per_s": float(np.mean(n_in)) / (float(np.mean(bwd_ms)) * 1e-3)}
+        line["fp16_operands"] = {"what": "the convolution call (stage + conv) of the same layer with precision 'fp16': fp16 "
+                                         "operands, f32 accumulate (opt-in; the headline numbers above use TF32 operands)",
+                                 "conv_call_ms": float(np.mean(f16_ms)), "tf32_conv_call_ms": float(np.mean(kern_ms))}
         line["backbone"] = backbone
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, budget_s=12.0)
