@@ -238,6 +238,23 @@ int ssc_batch_offsets(const int32_t *indices, int n, int batch, int32_t *offsets
  * (indice_maxpool_cpp_functor.cpp:78-84); ssc_avgpool_bwd: d_in[i] = sum_o out_grad[o] / rf[o]
  * (rf NULL: / K; indice_avgpool_cuda_functor.cu:195-205), both in ascending offset order. */
 int ssc_nbr_transpose(const int32_t *nbr, int K, int n_out, int n_in, int32_t *nbr_in, void *stream);
+
+/* Row order for ssc_conv_fwd_ordered.  order[0..n_rows) is a permutation of the rows of the table
+ * nbr[K][n_rows] that puts rows with the same first used kernel offset next to each other
+ * (ascending row number inside a group; rows without any neighbour last).  The convolution
+ * kernel works on tiles of 128 rows of that order and skips the offsets no row of a tile uses:
+ * on the input-major table of a strided convolution (the reference's input-gradient loop,
+ * SS_Conv_lib/src/conv/indice_conv.h:412-424, and the forward pass of a transposed convolution)
+ * a row uses only the offsets of its parity class, so grouped tiles skip 7/8 of the steps of a
+ * 3^3 stride-2 kernel.  The result of the convolution does not depend on the order, bit for bit.
+ * Kernel volumes up to 343. */
+size_t ssc_nbr_row_order_scratch_bytes(int K, int n_rows);
+int ssc_nbr_row_order(const int32_t *nbr, int K, int n_rows, int32_t *order, void *scratch,
+                      size_t scratch_bytes, void *stream);
+int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
+                         const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
+                         void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
+                         const int32_t *row_order, void *stream);
 size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n_out);
 int ssc_conv_wgrad(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr,
                    int K, int n_out, int precision, float *d_filters, int32_t *status, void *scratch,

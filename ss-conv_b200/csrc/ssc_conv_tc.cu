@@ -173,7 +173,11 @@ template <bool STAGED, bool F16 = false>
 __global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
-                     int32_t *status, TcParams p, const int32_t *__restrict__ n_out_dev) {
+                     int32_t *status, TcParams p, const int32_t *__restrict__ n_out_dev,
+                     const int32_t *__restrict__ order) {
+  // `order` (may be NULL): the rows of tile t are order[128 t .. 128 t + 127] instead of the same
+  // consecutive numbers; rows that use the same kernel offsets, put next to each other, make a
+  // tile skip the offsets none of them uses.
   // n_out is the row stride of nbr and the launch bound; the exact row count may still be on the
   // device (a rulebook sized optimistically): CTAs past it have nothing to do.
   const int n_rows = live_rows(n_out, n_out_dev);
@@ -220,14 +224,20 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   } else {
     // which kernel offsets touch this tile: four offsets per pass so that 16 loads are in
     // flight per lane before the first ballot
+    int scan_rows[4];  // this lane's four rows of the tile (-1 past the end)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = m0 + q * 32 + lane;
+      scan_rows[q] = r < n_rows ? (order ? __ldg(order + r) : r) : -1;
+    }
     for (int k0 = warp * 4; k0 < K; k0 += mma_warp * 4) {
       int v[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          int r = m0 + q * 32 + lane;
-          v[i][q] = (k0 + i < K && r < n_rows) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
+          const int r = scan_rows[q];
+          v[i][q] = (k0 + i < K && r >= 0) ? __ldg(nbr + (size_t)(k0 + i) * n_out + r) : -1;
         }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -288,13 +298,17 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     for (int q = 0; q < 4; ++q) row_off[q] = (uint32_t)(q * 4 + (lane >> 3)) * 1024u + sw * 128u;
     uint32_t par = 0;          // parity of the slot's current use
     int src[4], nxt[4];
+    int my_rows[4];            // this lane's four rows of the tile (-1 past the end)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = m0 + q * 32 + lane;
+      my_rows[q] = r < n_rows ? (order ? __ldg(order + r) : r) : -1;
+    }
     auto load_rows = [&](int j, int *dst) {
       const int kap = act_list[j / p.k_groups];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        int r = m0 + q * 32 + lane;
-        dst[q] = (q >= q0 && q < q0 + q_per && r < n_rows) ? __ldg(nbr + (size_t)kap * n_out + r) : -1;
-      }
+      for (int q = 0; q < 4; ++q)
+        dst[q] = (q >= q0 && q < q0 + q_per && my_rows[q] >= 0) ? __ldg(nbr + (size_t)kap * n_out + my_rows[q]) : -1;
     };
     if (slot < n_iter) load_rows(slot, nxt);
     for (int j = slot; j < n_iter; j += S) {
@@ -425,7 +439,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     if (ok && n_iter > 0) ok = mbar_wait_warp(smem_u32(done_bar), 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
     tc_fence_after();
-    const int m = m0 + warp * 32 + lane;
+    const int m_tile = m0 + warp * 32 + lane;
+    const int m = m_tile < n_rows ? (order ? __ldg(order + m_tile) : m_tile) : n_rows;
     const int col0 = nt0 * p.tile_n;   // first output channel of this CTA
     for (int c0 = 0; c0 < p.n_cta && col0 + c0 < c_out; c0 += 16) {
       uint32_t r[16];
@@ -527,7 +542,7 @@ size_t conv_f16_scratch_bytes(int n_in, int c_in) { return ((size_t)n_in + 1) * 
 
 int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
                  int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
-                 cudaStream_t st) {
+                 const int32_t *order, cudaStream_t st) {
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(fp16): kernel volume %d > 256", K);
   const int words = f16_row_words(c_in);
   if (scratch == nullptr || scratch_bytes < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
@@ -548,7 +563,7 @@ int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, 
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(fp16): smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid2(grid, p.n_tiles / p.nt_cta);
-  { kernel<<<grid2, p.threads, smem, st>>>((const float *)scratch, words, (const uint4 *)packed, K, c_out, nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
+  { kernel<<<grid2, p.threads, smem, st>>>((const float *)scratch, words, (const uint4 *)packed, K, c_out, nbr, n_out, out, status, p, n_out_dev, order); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_f16");
   return SSC_OK;
 }
@@ -561,20 +576,20 @@ constexpr int kStagingMinTiles = 64;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  const int32_t *n_out_dev, cudaStream_t st) {
+                  const int32_t *n_out_dev, const int32_t *order, cudaStream_t st) {
   TcParams p;
   // Three variants share the packed filter image.  SSC_TC_VARIANT = gather4 | smem | tmem forces
   // one (where the shape allows); by default large problems take the persistent TMA-gather
   // kernel when the caller supplied its staging buffer, the others the shared-memory kernel.
   const char *variant = getenv("SSC_TC_VARIANT");
   const bool force_g4 = variant != nullptr && strcmp(variant, "gather4") == 0;
-  if (force_g4 && n_out_dev == nullptr) {
+  if (force_g4 && n_out_dev == nullptr && order == nullptr) {
     int rc = conv_fwd_tf32_gather4(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, scratch,
                                    scratch_bytes, st);
     if (rc >= 0) return rc;
   }
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
-  if (variant != nullptr && strcmp(variant, "tmem") == 0 && n_out_dev == nullptr) {
+  if (variant != nullptr && strcmp(variant, "tmem") == 0 && n_out_dev == nullptr && order == nullptr) {
     int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
     if (rc >= 0) return rc;
   }
@@ -597,7 +612,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
     int rc = stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
     // persistent variant: several row tiles per pass share every filter slab
-    if (force_wide) {
+    if (force_wide && order == nullptr) {
       rc = conv_fwd_tf32_wide((const float *)scratch, c_pad, c_in, packed, K, c_out, nbr, n_out, out, status, n_out_dev, st);
       if (rc >= 0) return rc;
     }
@@ -607,7 +622,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid2(grid, p.n_tiles / p.nt_cta);
   { kernel<<<grid2, p.threads, smem, st>>>(staged ? (const float *)scratch : features, staged ? c_pad : c_in, (const uint4 *)packed, K, c_out,
-                                        nbr, n_out, out, status, p, n_out_dev); note_launches(1); }
+                                        nbr, n_out, out, status, p, n_out_dev, order); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_tf32");
   return SSC_OK;
 }

@@ -1,0 +1,104 @@
+// Row order for the gather-GEMM: rows that use the same kernel offsets next to each other.
+//
+// The convolution kernel works on tiles of 128 rows and skips, per tile, every kernel offset that
+// none of the tile's rows uses.  In the input-major table of a strided convolution (the table
+// the input gradient runs on, and the forward table of a transposed convolution) the offsets a
+// row uses depend on the parity of its coordinates: a row sees 1/8 of the 27 offsets of a 3^3
+// stride-2 kernel, but 128 consecutive rows see all of them, so nearly every (tile, offset) step
+// runs with 7/8 of its rows switched off.  Grouping the rows by the first offset they use (which
+// names the parity class) makes the tiles uniform: a tile then skips the other classes' offsets.
+//
+// A counting sort in three launches, stable (ascending row number inside a group), so the
+// order - and with it everything computed through it - is repeatable:
+//   1. key per row (first offset with a neighbour, K if none) + histogram per block of 1024 rows,
+//   2. exclusive scan of the histograms laid out group-major,
+//   3. scatter: position = scanned base of (group, block) + rank of the row inside its block.
+#include "ssc_common.cuh"
+#include "ssc_scan.cuh"
+
+namespace ssc {
+
+constexpr int ORD_BLOCK = 1024;
+constexpr int ORD_MAX_K = 343;   // 7^3: the scatter kernel keeps 32 x (K + 1) counters in shared memory
+
+__global__ void __launch_bounds__(ORD_BLOCK)
+row_key_hist_kernel(const int32_t *__restrict__ nbr, int K, int n_rows, uint16_t *__restrict__ keys,
+                    uint32_t *__restrict__ hist, int n_blocks) {
+  extern __shared__ uint32_t hist_s[];  // [K + 1]
+  const int B = K + 1;
+  for (int b = threadIdx.x; b < B; b += ORD_BLOCK) hist_s[b] = 0u;
+  __syncthreads();
+  const int row = blockIdx.x * ORD_BLOCK + threadIdx.x;
+  if (row < n_rows) {
+    int key = K;
+    for (int kappa = 0; kappa < K; ++kappa)
+      if (__ldg(nbr + (size_t)kappa * n_rows + row) >= 0) {
+        key = kappa;
+        break;
+      }
+    keys[row] = (uint16_t)key;
+    atomicAdd(&hist_s[key], 1u);  // a count: the order of the additions does not matter
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += ORD_BLOCK) hist[(size_t)b * n_blocks + blockIdx.x] = hist_s[b];
+}
+
+__global__ void __launch_bounds__(ORD_BLOCK)
+row_scatter_kernel(const uint16_t *__restrict__ keys, int K, int n_rows, const uint32_t *__restrict__ base, int n_blocks,
+                   int32_t *__restrict__ order) {
+  extern __shared__ uint32_t cnt[];  // [32 warps][K + 1] rows of each group in each warp
+  const int B = K + 1;
+  for (int i = threadIdx.x; i < 32 * B; i += ORD_BLOCK) cnt[i] = 0u;
+  __syncthreads();
+  const int row = blockIdx.x * ORD_BLOCK + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int key = row < n_rows ? (int)keys[row] : -1;
+  const unsigned peers = __match_any_sync(0xffffffffu, key);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  if (key >= 0 && rank == 0) cnt[warp * B + key] = (uint32_t)__popc(peers);
+  __syncthreads();
+  if (key >= 0) {
+    uint32_t before = 0;
+    for (int w = 0; w < warp; ++w) before += cnt[w * B + key];
+    order[base[(size_t)key * n_blocks + blockIdx.x] + before + (uint32_t)rank] = row;
+  }
+}
+
+}  // namespace ssc
+
+using namespace ssc;
+
+static size_t order_align(size_t x) { return (x + 255) & ~(size_t)255; }
+
+extern "C" size_t ssc_nbr_row_order_scratch_bytes(int K, int n_rows) {
+  if (K < 1 || K > ORD_MAX_K || n_rows < 0) return 0;
+  const size_t n_blocks = (size_t)ceil_div(n_rows > 0 ? n_rows : 1, ORD_BLOCK);
+  const size_t cells = (size_t)(K + 1) * n_blocks;
+  return order_align((size_t)n_rows * 2) + 2 * order_align(cells * 4) + order_align((cells / 1024 + 2) * 4);
+}
+
+extern "C" int ssc_nbr_row_order(const int32_t *nbr, int K, int n_rows, int32_t *order, void *scratch, size_t scratch_bytes,
+                                 void *stream) {
+  SSC_REQUIRE(K >= 1 && K <= ORD_MAX_K && n_rows >= 0, "nbr_row_order: kernel volume %d not in 1..%d or bad row count", K, ORD_MAX_K);
+  if (n_rows == 0) return SSC_OK;
+  SSC_REQUIRE(nbr && order && scratch, "nbr_row_order: null pointer");
+  SSC_REQUIRE(scratch_bytes >= ssc_nbr_row_order_scratch_bytes(K, n_rows), "nbr_row_order: scratch too small");
+  cudaStream_t st = as_stream(stream);
+  const int n_blocks = ceil_div(n_rows, ORD_BLOCK);
+  const size_t cells = (size_t)(K + 1) * n_blocks;
+  uint8_t *sp = (uint8_t *)scratch;
+  uint16_t *keys = (uint16_t *)sp;
+  sp += order_align((size_t)n_rows * 2);
+  uint32_t *hist = (uint32_t *)sp;
+  sp += order_align(cells * 4);
+  uint32_t *base = (uint32_t *)sp;
+  sp += order_align(cells * 4);
+  uint32_t *block_sums = (uint32_t *)sp;
+  { row_key_hist_kernel<<<n_blocks, ORD_BLOCK, (K + 1) * 4, st>>>(nbr, K, n_rows, keys, hist, n_blocks); note_launches(1); }
+  SSC_CHECK_LAUNCH("row_key_hist");
+  int rc = exclusive_scan_u32<false>(hist, (long long)cells, base, block_sums, nullptr, nullptr, st);
+  if (rc != 0) return rc;
+  { row_scatter_kernel<<<n_blocks, ORD_BLOCK, 32 * (K + 1) * 4, st>>>(keys, K, n_rows, base, n_blocks, order); note_launches(1); }
+  SSC_CHECK_LAUNCH("row_scatter");
+  return SSC_OK;
+}

@@ -49,6 +49,10 @@ SIGNATURES = {
     "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                              c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ssc_nbr_transpose": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_nbr_row_order_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "ssc_nbr_row_order": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_conv_fwd_ordered": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     "ssc_conv_wgrad_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_wgrad": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p]),
@@ -482,9 +486,10 @@ def _resolve_precision(c_in, c_out, precision=None):
 STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") in ("gather4", "wide") else 64 * 128
 
 
-def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None):
+def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None):
     """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch).
-    n_out_dev: device word with the exact row count when n_out is only a capacity."""
+    n_out_dev: device word with the exact row count when n_out is only a capacity.
+    row_order: permutation of the output rows from nbr_row_order (same result, fewer steps)."""
     if filters.dim() != 3:
         filters = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
     K, c_in, c_out = filters.shape
@@ -511,9 +516,9 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None):
         stage = prec == PREC_F16 or n_out >= STAGING_MIN_ROWS
         nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec) if stage else 0
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
-        _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
-                                  _p(nbr, torch.int32), int(n_out), prec, _p(out), _p(st), _p(scratch), nbytes,
-                                  _p(n_out_dev), _stream()))
+        _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
+                                          _p(nbr, torch.int32), int(n_out), prec, _p(out), _p(st), _p(scratch), nbytes,
+                                          _p(n_out_dev), _p(row_order), _stream()))
     else:
         filters = filters.contiguous()
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(filters, torch.float32), K,
@@ -557,6 +562,23 @@ def input_major_table(nbr, n_in):
     return nbr_in
 
 
+# Tables with fewer rows are not worth the three launches of the ordering.
+ROW_ORDER_MIN_ROWS = 64 * 128
+
+
+def nbr_row_order(nbr):
+    """Permutation of the rows of nbr [K, n] that groups rows by the first kernel offset they use
+    (for conv_forward(row_order=...)); None where the library has no ordering for this table."""
+    K, n = nbr.shape
+    nbytes = int(lib().ssc_nbr_row_order_scratch_bytes(K, n))
+    if nbytes == 0 or n == 0:
+        return None
+    order = torch.empty(n, dtype=torch.int32, device=nbr.device)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=nbr.device)
+    _check(lib().ssc_nbr_row_order(_p(nbr, torch.int32), K, n, _p(order), _p(scratch), nbytes, _stream()))
+    return order
+
+
 def conv_wgrad(features, out_grad, nbr, precision=None):
     """d_filters [K, Cin, Cout] = sum over output rows of gathered input rows (outer) out_grad rows
     (tensor cores with TF32 operands or exact fp32, chosen like the forward pass)."""
@@ -586,7 +608,10 @@ def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_nu
     n_in, n_out = features.shape[0], out_bp.shape[0]
     nbr = neighbour_table(indice_pairs, indice_num, n_out, bool(inverse))
     nbr_in = input_major_table(nbr, n_in)
-    d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in)
+    # rows of the input-major table use few of the offsets each (their parity class under a
+    # stride): grouped tiles skip the rest
+    order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
+    d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in, row_order=order)
     d_flt = conv_wgrad(features, out_bp, nbr)
     return [d_in, d_flt.reshape(filters.shape)]
 
@@ -617,7 +642,8 @@ def indice_conv_backward_half(features, filters, out_bp, indice_pairs, indice_nu
     n_in, n_out = feats.shape[0], grad.shape[0]
     nbr = neighbour_table(indice_pairs, indice_num, n_out, bool(inverse))
     nbr_in = input_major_table(nbr, n_in)
-    d_in = conv_forward(grad, flt.transpose(1, 2).contiguous(), nbr_in, n_in, precision="fp16")
+    order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
+    d_in = conv_forward(grad, flt.transpose(1, 2).contiguous(), nbr_in, n_in, precision="fp16", row_order=order)
     d_flt = conv_wgrad(feats, grad, nbr, precision="tf32")
     return [d_in.half(), d_flt.reshape(filters.shape).half()]
 

@@ -12,6 +12,37 @@ pytestmark = pytest.mark.gpu
 TOL = {"fp32": 2e-5, "tf32": 1e-3}
 
 
+@pytest.mark.parametrize("k,s,p,subm,precision", [(3, 2, 1, False, "tf32"), (3, 1, 1, True, "tf32"), (2, 2, 0, False, "fp16"),
+                                                  (5, 2, 2, False, "tf32")])
+def test_row_order_is_a_grouping_permutation_and_changes_no_bit(cuda, k, s, p, subm, precision):
+    """ssc_nbr_row_order: a permutation, groups = first used offset in ascending order, ascending
+    rows inside a group; the convolution run through it gives the same bits as without."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(k * 11 + s)
+    ind = random_voxels(rng, 3, 24, 4000)
+    outids, pairs, num = gpu_rulebook(ind, 3, [24] * 3, k, s, p, 1, subm, cuda)
+    n_in, n_out = ind.shape[0], outids.shape[0]
+    nbr = _ext.neighbour_table(pairs, num, n_out)
+    nbr_in = _ext.input_major_table(nbr, n_in)
+    order = _ext.nbr_row_order(nbr_in)
+    torch.cuda.synchronize()
+    o = order.cpu().numpy()
+    t = nbr_in.cpu().numpy()
+    assert np.array_equal(np.sort(o), np.arange(n_in))
+    has = t >= 0
+    key = np.where(has.any(0), has.argmax(0), t.shape[0])
+    want = np.lexsort((np.arange(n_in), key))       # by key, then by row number
+    assert np.array_equal(o, want)
+    c_out, c_in = 40, 24
+    g = torch.randn(n_out, c_out, device=cuda)
+    fT = torch.randn(k ** 3, c_out, c_in, device=cuda) / 30
+    plain = _ext.conv_forward(g, fT, nbr_in, n_in, precision)
+    ordered = _ext.conv_forward(g, fT, nbr_in, n_in, precision, row_order=order)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    assert torch.equal(plain, ordered)
+
+
 @pytest.mark.parametrize("tag", ["bw_strided", "bw_subm"])
 def test_conv_backward_matches_reference_outputs(cuda, golden, tag):
     from ss_conv import _ext
