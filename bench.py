@@ -387,17 +387,18 @@ def run_ours(args):
         grads = [torch.randn(n_out, flt.shape[2], device=dev) for _, _, n_out, _ in prepared]
         tables = []
         for (f, i), (_, nbr, n_out, _) in zip(dev_sets, prepared):
-            tables.append((nbr, _ext.input_major_table(nbr, f.shape[0])))
+            nbr_in = _ext.input_major_table(nbr, f.shape[0])
+            tables.append((nbr, nbr_in, _ext.nbr_row_order(nbr_in)))   # tables + row order: per rulebook, reused
         fltT = flt.transpose(1, 2).contiguous()
         bwd_graphs = []
         for k in range(ROTATE):                       # recorded like the forward call: device time only
-            f, (nbr, nbr_in), g = prepared[k][0], tables[k], grads[k]
-            _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32")
+            f, (nbr, nbr_in, order), g = prepared[k][0], tables[k], grads[k]
+            _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32", row_order=order)
             _ext.conv_wgrad(f, g, nbr)
             torch.cuda.synchronize()
             cg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(cg):
-                _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32")
+                _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32", row_order=order)
                 _ext.conv_wgrad(f, g, nbr)
             bwd_graphs.append(cg)
         for it in range(2 + 6):
@@ -451,7 +452,7 @@ def run_ours(args):
                          "kernel_ms": float(np.mean(kern_ms)), "algorithmic_bytes": float(np.mean(alg_bytes)),
                          "tensor_tflops": float(np.mean(flops)) / (float(np.mean(kern_ms)) * 1e-3) / 1e12},
         }
-        line["backward"] = {"what": "input gradient + filter gradient of the cfg2 convolution, both tcgen05 with TF32 operands",
+        line["backward"] = {"what": "input gradient (forward kernel on the input-major table, rows grouped by parity class) + filter gradient (pair lists compacted inside the call) of the cfg2 convolution, both tcgen05 with TF32 operands; input-major table and row order come with the rulebook",
                             "ms": float(np.mean(bwd_ms)), "voxels_per_s": float(np.mean(n_in)) / (float(np.mean(bwd_ms)) * 1e-3)}
         line["fp16_operands"] = {"what": "the convolution call (stage + conv) of the same layer with precision 'fp16': fp16 "
                                          "operands, f32 accumulate (opt-in; the headline numbers above use TF32 operands)",

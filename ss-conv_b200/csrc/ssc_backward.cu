@@ -239,14 +239,21 @@ static int wgrad_splits(int K, int c_in, int c_out, int n_out) {
   return splits;
 }
 
-extern "C" size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n_out) {
-  if (K < 1 || c_in < 1 || c_out < 1 || n_out < 0) return 0;
-  return (size_t)wgrad_splits(K, c_in, c_out, n_out) * K * c_in * c_out * sizeof(float);
-}
-
 namespace ssc {
 int conv_wgrad_tc(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr, int K, int n_out,
-                  int max_splits, int *splits_used, float *partial, int32_t *status, cudaStream_t st);
+                  int max_splits, int *splits_used, float *partial, void *lists, int32_t *status, cudaStream_t st);
+size_t conv_wgrad_tc_list_bytes(int K, int n_out);
+}
+
+// [partial tiles of the row ranges][pair lists of the tensor-core kernel]
+static size_t wgrad_partial_bytes(int K, int c_in, int c_out, int n_out) {
+  const size_t b = (size_t)wgrad_splits(K, c_in, c_out, n_out) * K * c_in * c_out * sizeof(float);
+  return (b + 255) & ~(size_t)255;
+}
+
+extern "C" size_t ssc_conv_wgrad_scratch_bytes(int K, int c_in, int c_out, int n_out) {
+  if (K < 1 || c_in < 1 || c_out < 1 || n_out < 0) return 0;
+  return wgrad_partial_bytes(K, c_in, c_out, n_out) + conv_wgrad_tc_list_bytes(K, n_out);
 }
 
 extern "C" int ssc_conv_wgrad(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr, int K,
@@ -261,14 +268,15 @@ extern "C" int ssc_conv_wgrad(const float *features, int c_in, const float *out_
   }
   SSC_REQUIRE(features && out_grad && nbr, "conv_wgrad: null pointer");
   const int splits = wgrad_splits(K, c_in, c_out, n_out);
-  const size_t need = (size_t)splits * elems * sizeof(float);
+  const size_t need = ssc_conv_wgrad_scratch_bytes(K, c_in, c_out, n_out);
   if (scratch == nullptr || scratch_bytes < need)
     return fail(SSC_ERR_SCRATCH, "conv_wgrad: scratch %zu < %zu bytes", scratch_bytes, need);
   int rows_per_split = ceil_div(n_out, splits);
   rows_per_split = ceil_div(rows_per_split, WG_ROWS) * WG_ROWS;
   int rc = -1, used = splits;
   if (precision == SSC_PREC_TF32)  // tensor cores where the shape allows, else the exact kernel below
-    rc = conv_wgrad_tc(features, c_in, out_grad, c_out, nbr, K, n_out, splits, &used, (float *)scratch, status, st);
+    rc = conv_wgrad_tc(features, c_in, out_grad, c_out, nbr, K, n_out, splits, &used, (float *)scratch,
+                       (uint8_t *)scratch + wgrad_partial_bytes(K, c_in, c_out, n_out), status, st);
   if (rc > 0) return rc;
   if (rc < 0) {
     const int tiles_co = ceil_div(c_out, WG_T);

@@ -2,13 +2,17 @@
 //
 //   dW[kappa][ci][co] = sum over output rows o with a neighbour i = nbr[kappa][o]:  x[i][ci] * dy[o][co]
 //
-// One CTA owns one kernel offset, one range of output rows and one block of 128 output channels,
-// and accumulates D[co][ci] (M = 128 rows = output channels, N = input channels) in tensor memory
-// over chunks of 32 output rows (the K dimension of the MMA).  Both operands have to be K-major,
+// The (output row, input row) pairs of every kernel offset are first compacted into lists (a
+// bitmap of the neighbour table, a popcount scan, a scatter: ascending output row inside an
+// offset, so the lists - and the sums below - are repeatable); rows without a neighbour, more
+// than half of the table of a strided convolution, then cost nothing.
+// One CTA owns one kernel offset, one range of that offset's pair list and one block of 128 output
+// channels, and accumulates D[co][ci] (M = 128 rows = output channels, N = input channels) in
+// tensor memory over chunks of 32 pairs (the K dimension of the MMA).  Both operands have to be K-major,
 // i.e. transposed with respect to how the rows lie in memory, so the producer warps transpose on
 // the way into shared memory: lane = row of the chunk; for every channel the 32 lanes store 32
 // consecutive K elements of that channel's operand row (one conflict-free 128-byte store, in the
-// 128-byte-swizzled layout), rounded to TF32; rows without a neighbour store zeros.  Operand
+// 128-byte-swizzled layout), rounded to TF32; the lanes past the end of the list store zeros.  Operand
 // rows of channels past c_out / c_in are zeroed once and never touched again.
 //
 // warps 0-3: producers (warp w prepares chunks w, w+4, ...), then the epilogue (each lane owns one
@@ -17,6 +21,7 @@
 // ranges are added by wgrad_reduce_kernel in a fixed order (bitwise repeatable).
 // Every wait is bounded (status bit 16 on expiry).
 #include "ssc_common.cuh"
+#include "ssc_scan.cuh"
 #include "ssc_tc_ptx.cuh"
 
 namespace ssc {
@@ -27,6 +32,34 @@ constexpr int WT_STAGES = 4;
 constexpr int WT_A_BYTES = WT_M * 128;
 constexpr int WT_THREADS = 160;
 
+// One warp per 32 output rows of one kernel offset: which of them have a neighbour.
+__global__ void pair_bitmap_kernel(const int32_t *__restrict__ nbr, int K, int n_out, int words_per_row,
+                                   uint32_t *__restrict__ bitmap) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (gw >= (long long)K * words_per_row) return;
+  const int kappa = (int)(gw / words_per_row), r = (int)(gw % words_per_row) * 32 + (int)(threadIdx.x & 31);
+  const bool have = r < n_out && __ldg(nbr + (size_t)kappa * n_out + r) >= 0;
+  const unsigned m = __ballot_sync(0xffffffffu, have);
+  if ((threadIdx.x & 31) == 0) bitmap[gw] = m;
+}
+// prefix[w] = number of pairs before word w (over all offsets): the lists of the offsets follow one
+// another in pair_out / pair_in, starts[kappa] is where the list of offset kappa begins.
+__global__ void pair_scatter_kernel(const int32_t *__restrict__ nbr, int K, int n_out, int words_per_row,
+                                    const uint32_t *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                                    int32_t *__restrict__ pair_out, int32_t *__restrict__ pair_in, int32_t *__restrict__ starts) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (gw >= (long long)K * words_per_row) return;
+  const int lane = threadIdx.x & 31;
+  const int kappa = (int)(gw / words_per_row), w = (int)(gw % words_per_row), r = w * 32 + lane;
+  const uint32_t m = bitmap[gw], base = prefix[gw];
+  if (w == 0 && lane == 0) starts[kappa] = (int32_t)base;
+  if ((m >> lane) & 1u) {
+    const uint32_t pos = base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+    pair_out[pos] = r;
+    pair_in[pos] = __ldg(nbr + (size_t)kappa * n_out + r);
+  }
+}
+
 __device__ __forceinline__ uint32_t wt_off(int row, int k) {  // byte offset of element (row, k) of a K-major SW128 tile
   return (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u + ((((uint32_t)k >> 2) ^ (uint32_t)(row & 7)) << 4) +
          ((uint32_t)k & 3u) * 4u;
@@ -34,8 +67,9 @@ __device__ __forceinline__ uint32_t wt_off(int row, int k) {  // byte offset of 
 
 __global__ void __launch_bounds__(WT_THREADS)
 conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *__restrict__ out_grad, int c_out,
-                     const int32_t *__restrict__ nbr, int n_out, int rows_per_split, int n_pad, uint32_t tmem_cols,
-                     float *__restrict__ partial, int32_t *status) {
+                     const int32_t *__restrict__ pair_out, const int32_t *__restrict__ pair_in,
+                     const int32_t *__restrict__ starts, int n_pad, uint32_t tmem_cols, float *__restrict__ partial,
+                     int32_t *status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int b_bytes = n_pad * 128;
@@ -49,8 +83,11 @@ conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kappa = blockIdx.y, co0 = blockIdx.z * WT_M;
+  // this CTA's share of the offset's pair list: equal ranges of whole chunks
+  const int list0 = starts[kappa], n_pairs = starts[kappa + 1] - list0;
+  const int rows_per_split = (((n_pairs + (int)gridDim.x - 1) / (int)gridDim.x + WT_K - 1) / WT_K) * WT_K;
   const int r_begin = split * rows_per_split;
-  const int r_end = min(n_out, r_begin + rows_per_split);
+  const int r_end = min(n_pairs, r_begin + rows_per_split);
   const int n_chunks = r_end > r_begin ? (r_end - r_begin + WT_K - 1) / WT_K : 0;
 
   if (tid == 0) {
@@ -91,8 +128,9 @@ conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *
     uint8_t *b_tile = a_tile + WT_A_BYTES;
     const bool vec = ((c_in | c_out) & 3) == 0 && (((uintptr_t)features | (uintptr_t)out_grad) & 15u) == 0;
     for (int ch = warp; ch < n_chunks; ch += 4) {
-      const int r = r_begin + ch * WT_K + lane;
-      const int src = r < r_end ? __ldg(nbr + (size_t)kappa * n_out + r) : -1;
+      const int j = r_begin + ch * WT_K + lane;   // position in the offset's pair list
+      const int r = j < r_end ? __ldg(pair_out + list0 + j) : 0;
+      const int src = j < r_end ? __ldg(pair_in + list0 + j) : -1;
       if (ch >= WT_STAGES) {
         if (!mbar_wait_warp(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
         tc_fence_after();
@@ -192,28 +230,56 @@ conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *
   }
 }
 
+size_t conv_wgrad_tc_list_bytes(int K, int n_out) {
+  const size_t wpr = (size_t)ceil_div(n_out > 0 ? n_out : 1, 32), words = (size_t)K * wpr;
+  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  return 2 * al(words * 4) + al((words / 1024 + 2) * 4) + 2 * al((size_t)K * n_out * 4) + al((size_t)(K + 1) * 4);
+}
+
 // returns -1 when the shape is not covered (the caller then uses the CUDA-core kernel)
 int conv_wgrad_tc(const float *features, int c_in, const float *out_grad, int c_out, const int32_t *nbr, int K, int n_out,
-                  int max_splits, int *splits_used, float *partial, int32_t *status, cudaStream_t st) {
+                  int max_splits, int *splits_used, float *partial, void *lists, int32_t *status, cudaStream_t st) {
   const int n_pad = (c_in + 15) & ~15;
   if (n_pad > 256) return -1;
-  // as many row ranges as fit one wave of two resident CTAs per SM (never more than the scratch holds)
+  // as many ranges per offset as fit one wave of two resident CTAs per SM (never more than the scratch holds)
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int splits = (2 * sms) / (K * ceil_div(c_out, WT_M));
   if (splits > max_splits) splits = max_splits;
+  const int most = ceil_div(n_out, WT_K);   // a range is at least one chunk
+  if (splits > most) splits = most;
   if (splits < 1) splits = 1;
-  int rows_per_split = ceil_div(ceil_div(n_out, splits), WT_K) * WT_K;
-  splits = ceil_div(n_out, rows_per_split);
   *splits_used = splits;
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < n_pad) tmem_cols <<= 1;
   const size_t smem = (size_t)WT_STAGES * (WT_A_BYTES + n_pad * 128) + 1024 + 256;
   if (smem > 227 * 1024) return -1;
+  // ---- pair lists
+  const int wpr = ceil_div(n_out, 32);
+  const long long words = (long long)K * wpr;
+  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  uint8_t *sp = (uint8_t *)lists;
+  uint32_t *bitmap = (uint32_t *)sp;
+  sp += al((size_t)words * 4);
+  uint32_t *prefix = (uint32_t *)sp;
+  sp += al((size_t)words * 4);
+  uint32_t *block_sums = (uint32_t *)sp;
+  sp += al(((size_t)words / 1024 + 2) * 4);
+  int32_t *pair_out = (int32_t *)sp;
+  sp += al((size_t)K * n_out * 4);
+  int32_t *pair_in = (int32_t *)sp;
+  sp += al((size_t)K * n_out * 4);
+  int32_t *starts = (int32_t *)sp;
+  { pair_bitmap_kernel<<<ceil_div(words * 32, 256), 256, 0, st>>>(nbr, K, n_out, wpr, bitmap); note_launches(1); }
+  SSC_CHECK_LAUNCH("pair_bitmap");
+  int rc = exclusive_scan_u32<true>(bitmap, words, prefix, block_sums, starts + K, nullptr, st);
+  if (rc != 0) return rc;
+  { pair_scatter_kernel<<<ceil_div(words * 32, 256), 256, 0, st>>>(nbr, K, n_out, wpr, bitmap, prefix, pair_out, pair_in, starts); note_launches(1); }
+  SSC_CHECK_LAUNCH("pair_scatter");
   cudaError_t e = cudaFuncSetAttribute(conv_wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_wgrad(tf32): smem attribute: %s", cudaGetErrorString(e));
   dim3 grid(splits, K, ceil_div(c_out, WT_M));
-  { conv_wgrad_tc_kernel<<<grid, WT_THREADS, smem, st>>>(features, c_in, out_grad, c_out, nbr, n_out, rows_per_split, n_pad,
+  { conv_wgrad_tc_kernel<<<grid, WT_THREADS, smem, st>>>(features, c_in, out_grad, c_out, pair_out, pair_in, starts, n_pad,
                                                       tmem_cols, partial, status); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_wgrad_tc");
   return SSC_OK;
