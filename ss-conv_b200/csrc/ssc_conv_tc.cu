@@ -52,7 +52,8 @@ struct TcParams {
   int tile_n;     // N of one MMA, multiple of 16, <= 256
   int tmem_cols;  // power of two >= max(32, n_pad)
   int stages;     // operand ring depth = number of producer warps (>= 4)
-  int threads;    // (stages + 1) * 32
+  int threads;    // (max(n_prod, 4) + 1) * 32
+  int n_prod;     // producer warps: a multiple of the slots (several warps share a slot's rows)
   int b_bytes;    // n_pad * 128
   int sps;        // 32-channel slabs per ring slot (a step covers sps slabs of one kernel offset)
   int k_groups;   // ceil(k_slabs / sps) = steps per kernel offset
@@ -102,7 +103,14 @@ static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
     if (v >= 2 && v <= p.stages) p.stages = v;
   }
   if (p.stages < 2) return false;
-  p.threads = ((p.stages > TC_EPI_WARPS ? p.stages : TC_EPI_WARPS) + 1) * 32;
+  // producer warps: one per slot with four or more slots, else the slots' rows are split over four
+  // warps (SSC_TC_PROD_WARPS=8: over eight)
+  p.n_prod = p.stages < TC_EPI_WARPS ? (TC_EPI_WARPS / p.stages) * p.stages : p.stages;
+  if (const char *e = getenv("SSC_TC_PROD_WARPS")) {
+    int v = atoi(e);
+    if (v == 8 && p.stages == 2) p.n_prod = 8;
+  }
+  p.threads = ((p.n_prod > TC_EPI_WARPS ? p.n_prod : TC_EPI_WARPS) + 1) * 32;
   return true;
 }
 
@@ -210,7 +218,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       // one barrier per slot for both operands: every producer lane arrives for its gathered rows,
       // and the lane that starts the filter copy arrives once more with the copy's byte count
       // (the issuing thread then pays one barrier round trip per step, not two)
-      mbar_init(smem_u32(fulla_bars + s), 32u * (uint32_t)(S < TC_EPI_WARPS ? TC_EPI_WARPS / S : 1) + 1u);
+      mbar_init(smem_u32(fulla_bars + s), 32u * (uint32_t)(p.n_prod / S) + 1u);
     }
     mbar_init(smem_u32(done_bar), 1);
     *abort_flag = 0;
@@ -277,7 +285,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   const int n_iter = n_act * p.k_groups;
   const uint32_t smem_base = smem_u32(smem);
 
-  const int n_prod = S < TC_EPI_WARPS ? (TC_EPI_WARPS / S) * S : S;  // producer warps (2 slots -> 4 warps)
+  const int n_prod = p.n_prod;  // producer warps (2 slots -> 4 warps)
   if (warp < n_prod) {
     // ====================== producer warp ====================================================
     // With S >= 4 ring slots, warp w owns slot w and prepares all 128 rows of the steps

@@ -13,7 +13,17 @@ Every call copies the batch into the graph's input buffers, replays, then reads 
 of the chain back in one copy and checks them against the capacities.  If a capacity was too
 small the batch is recomputed eagerly with exact counts (which also raises the capacity hints) and
 the graph is recorded again on the next call.  Results live in buffers owned by the graph: use or
-copy them before the next call.  The reference has no counterpart.
+copy them before the next call.
+
+With depth = 2 (or more) the chain is recorded that many times, each recording with buffers of its
+own, and batches can be queued without waiting for the one before:
+
+    a = net.submit(f0, i0)
+    b = net.submit(f1, i1)                # queued behind a; the device does not idle in between
+    ya = a.result()                       # valid until `depth` more batches have been submitted
+
+submit() returns at once; result() waits for that batch only (an event), checks its row counts
+and hands out the exact tensors.  net(f, i) is submit + result.  The reference has no counterpart.
 """
 import torch
 
@@ -22,17 +32,84 @@ from .sp_ops import tensor as tensor_mod
 from .sp_ops.tensor import PendingRows, SparseTensor
 
 
-class GraphedChain(object):
-    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device):
-        self.fn, self.shape, self.batch, self.dev = fn, spatial_shape, int(batch_size), torch.device(device)
-        self.cap = int(max_rows)
-        self.feats = torch.zeros((self.cap, int(channels)), dtype=torch.float32, device=self.dev)
-        self.inds = torch.zeros((self.cap, 4), dtype=torch.int32, device=self.dev)
-        self.n = torch.zeros(1, dtype=torch.int32, device=self.dev)
+class _Recording(object):
+    """One capture of the chain: the graph, its input buffers, its outputs and its row counts."""
+
+    def __init__(self, chain):
+        dev = chain.dev
+        self.feats = torch.zeros((chain.cap, chain.channels), dtype=torch.float32, device=dev)
+        self.inds = torch.zeros((chain.cap, 4), dtype=torch.int32, device=dev)
+        self.n = torch.zeros(1, dtype=torch.int32, device=dev)
         self.graph = None
+        self.out = self.counts = self.caps = self.host_counts = None
+        self.done = torch.cuda.Event()
+
+    def record(self, chain):
+        x = SparseTensor(self.feats, self.inds, chain.shape, chain.batch)
+        x._rows = PendingRows(self.n, chain.cap, None, None)
+        log = []
+        graph = torch.cuda.CUDAGraph()
+        l0 = _ext.kernel_launches()
+        tensor_mod._capture_log = log
+        try:
+            with torch.cuda.graph(graph):
+                out = chain.fn(x)
+                counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log])   # input count first
+        finally:
+            tensor_mod._capture_log = None
+        chain.launches = _ext.kernel_launches() - l0
+        self.graph, self.out, self.counts, self.caps = graph, out, counts, [chain.cap] + [r.capacity for r in log]
+        self.host_counts = torch.empty(counts.shape[0], dtype=torch.int32).pin_memory()
+        if len(log) == 0 or (isinstance(out, SparseTensor) and not out.pending()):
+            raise RuntimeError("nothing in this chain ran ahead of its row counts (no capacity hints yet?)")
+
+
+class _Queued(object):
+    """A batch that has been queued on one recording; result() finishes it."""
+
+    def __init__(self, chain, rec, exact_inputs):
+        self.chain, self.rec, self.exact_inputs = chain, rec, exact_inputs
+        self.value = None
+        self.finished = False
+
+    def result(self):
+        if self.finished:
+            return self.value
+        rec, chain = self.rec, self.chain
+        rec.done.synchronize()                       # this batch only
+        counts = rec.host_counts.tolist()
+        if any(c > cap for c, cap in zip(counts, rec.caps)):
+            chain.stale = True                       # record again (with the raised hints) next time
+            chain.fallbacks += 1
+            self.value = chain._eager(*self.exact_inputs(), False)
+        else:
+            out = rec.out
+            if isinstance(out, SparseTensor):
+                f, i, _ = out.raw()
+                res = SparseTensor(f[:counts[-1]], i[:counts[-1]], out.spatial_shape, out.batch_size)
+                res.indice_dict, res.grid = out.indice_dict, out.grid
+                out = res
+            self.value = out
+        self.finished = True
+        self.exact_inputs = None
+        return self.value
+
+
+class GraphedChain(object):
+    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device, depth=1):
+        self.fn, self.shape, self.batch, self.dev = fn, spatial_shape, int(batch_size), torch.device(device)
+        self.cap, self.channels, self.depth = int(max_rows), int(channels), max(1, int(depth))
+        self.recs = None            # `depth` recordings, made on first use
+        self.stale = False          # a capacity overflowed: record again before the next replay
+        self.turn = 0
+        self.queued = []            # per recording: the batch that occupies it (or None)
         self.launches = 0           # kernel launches recorded in the graph (= per replay)
         self.replays = 0
         self.fallbacks = 0          # replays whose row counts overflowed a capacity (recomputed eagerly)
+
+    @property
+    def graph(self):
+        return None if (self.recs is None or self.stale) else self.recs[0].graph
 
     def _eager(self, features, indices, ahead):
         old = _ext.AHEAD
@@ -45,77 +122,76 @@ class GraphedChain(object):
         finally:
             _ext.AHEAD = old
 
-    def _record(self):
-        x = SparseTensor(self.feats, self.inds, self.shape, self.batch)
-        x._rows = PendingRows(self.n, self.cap, None, None)
-        log = []
-        graph = torch.cuda.CUDAGraph()
-        l0 = _ext.kernel_launches()
-        tensor_mod._capture_log = log
-        try:
-            with torch.cuda.graph(graph):
-                out = self.fn(x)
-                counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log])   # input count first
-        finally:
-            tensor_mod._capture_log = None
-        self.launches = _ext.kernel_launches() - l0
-        self.graph, self.out, self.counts, self.caps = graph, out, counts, [self.cap] + [r.capacity for r in log]
-        if len(log) == 0 or (isinstance(out, SparseTensor) and not out.pending()):
-            raise RuntimeError("nothing in this chain ran ahead of its row counts (no capacity hints yet?)")
+    def _ready(self, features, indices):
+        """Recordings exist and are current; (features, indices) is an exact batch to warm up on."""
+        if self.recs is not None and not self.stale:
+            return
+        for q in self.queued:                        # nothing may still be running on the old recordings
+            if q is not None:
+                q.result()
+        # two eager passes: the first records the output/input ratios of every layer, the
+        # second runs the capacity-sized path once (allocations, cached filters)
+        self._eager(features, indices, False)
+        self._eager(features, indices, True)
+        torch.cuda.synchronize(self.dev)
+        self.recs = [_Recording(self) for _ in range(self.depth)]
+        for rec in self.recs:
+            rec.record(self)
+        self.queued = [None] * self.depth
+        self.stale = False
+        self.turn = 0
+
+    def _launch(self, rec, exact_inputs):
+        rec.graph.replay()
+        self.replays += 1
+        rec.host_counts.copy_(rec.counts, non_blocking=True)    # the one read-back of the batch
+        rec.done.record()
+        q = _Queued(self, rec, exact_inputs)
+        self.queued[self.recs.index(rec)] = q
+        return q
+
+    def _next(self):
+        k = self.turn
+        self.turn = (self.turn + 1) % self.depth
+        old = self.queued[k]
+        if old is not None and not old.finished:
+            old.result()                             # its buffers are about to be overwritten
+        return self.recs[k]
+
+    def submit(self, features, indices):
+        """Queue one batch (features [n, C], indices [n, 4]); returns an object whose result() gives
+        what the chain returns.  Does not wait for the device."""
+        n = int(features.shape[0])
+        if n > self.cap:
+            raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
+        self._ready(features, indices)
+        rec = self._next()
+        rec.feats[:n].copy_(features)
+        rec.inds[:n].copy_(indices)
+        rec.n.fill_(n)
+        return self._launch(rec, lambda: (features, indices))
 
     def __call__(self, features, indices=None):
         """features [n, C] + indices [n, 4], or one SparseTensor.  A SparseTensor whose row count is
         still pending (e.g. straight out of Point2Voxel) is taken as it is: its count joins the
         counts that are checked after the replay, so nothing waits for it before."""
-        pending_in = None
         if isinstance(features, SparseTensor):
             if features.pending() and self.graph is not None:
-                pending_in = features
-            else:
-                features, indices = features.features, features.indices
-        if pending_in is not None:
-            return self._replay_pending(pending_in)
-        n = int(features.shape[0])
-        if n > self.cap:
-            raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
-        if self.graph is None:
-            # two eager passes: the first records the output/input ratios of every layer, the
-            # second runs the capacity-sized path once (allocations, cached filters)
-            self._eager(features, indices, False)
-            self._eager(features, indices, True)
-            torch.cuda.synchronize(self.dev)
-            self._record()
-        self.feats[:n].copy_(features)
-        self.inds[:n].copy_(indices)
-        self.n.fill_(n)
-        return self._finish(lambda: (features, indices))
+                return self._replay_pending(features).result()
+            features, indices = features.features, features.indices
+        return self.submit(features, indices).result()
 
     def _replay_pending(self, x):
         f, i, n_dev = x.raw()
+        rec = self._next()
         rows = min(self.cap, int(f.shape[0]))
-        self.feats[:rows].copy_(f[:rows])
-        self.inds[:rows].copy_(i[:rows])
-        self.n.copy_(n_dev.reshape(1))               # device to device: the host does not wait for the count
+        rec.feats[:rows].copy_(f[:rows])
+        rec.inds[:rows].copy_(i[:rows])
+        rec.n.copy_(n_dev.reshape(1))                # device to device: the host does not wait for the count
 
         def exact():
             x.resolve()
             if x.features.shape[0] > self.cap:
                 raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (x.features.shape[0], self.cap))
             return x.features, x.indices
-        return self._finish(exact)
-
-    def _finish(self, exact_inputs):
-        self.graph.replay()
-        self.replays += 1
-        counts = self.counts.tolist()                # the one read-back of the batch
-        if any(c > cap for c, cap in zip(counts, self.caps)):
-            self.graph = None                        # record again (with the raised hints) next time
-            self.fallbacks += 1
-            return self._eager(*exact_inputs(), False)
-        out = self.out
-        if isinstance(out, SparseTensor):
-            f, i, _ = out.raw()
-            res = SparseTensor(f[:counts[-1]], i[:counts[-1]], out.spatial_shape, out.batch_size)
-            res.indice_dict, res.grid = out.indice_dict, out.grid
-            return res
-        return out
+        return self._launch(rec, exact)

@@ -313,6 +313,20 @@ def test_graphed_chain_replays_match_eager_results(cuda):
             got = [(of.clone(), oi.clone()) for of, oi in feed.run(iter(host * 2))]
             for (of, oi), (wf, wi, _) in zip(got, want * 2):
                 assert torch.equal(oi, wi.cpu()) and torch.equal(of, wf.cpu())
+            # two recordings: batches queued back to back, results read one batch late; the result of
+            # a batch stays valid while the next one runs
+            two = GraphedChain(sparse_net, [20] * 3, 3, 5, cap, cuda, depth=2)
+            queued, seen = [], []
+            for f, i in batches * 2:
+                queued.append(two.submit(f, i))
+                if len(queued) >= 2:
+                    y = queued[-2].result()
+                    seen.append((y.features.clone(), y.indices.clone()))
+            y = queued[-1].result()
+            seen.append((y.features.clone(), y.indices.clone()))
+            for (gf, gi), (wf, wi, _) in zip(seen, want * 2):
+                assert torch.equal(gi, wi) and torch.equal(gf, wf)
+            assert two.replays == 8 and two.fallbacks == 0
             # a much denser batch overflows the recorded capacities: exact fallback, then a new graph
             ind = S.bernoulli_voxels(range(3), 20, 0.45, base_seed=99)
             f, i = dev(S.features(ind.shape[0], 5, 7), cuda), dev(ind, cuda)
@@ -322,6 +336,16 @@ def test_graphed_chain_replays_match_eager_results(cuda):
             for _ in range(2):
                 y = big(f, i)
                 assert torch.equal(y.indices, ref.indices) and torch.equal(y.features, ref.features)
+            # the same with two recordings and a queue: the overflowing batch is recomputed exactly,
+            # the one queued behind it is not disturbed
+            big2 = GraphedChain(sparse_net, [20] * 3, 3, 5, ind.shape[0], cuda, depth=2)
+            small = [t[:batches[1][1].shape[0]] for t in batches[1]]
+            big2(*small)
+            qa, qb = big2.submit(f, i), big2.submit(*small)
+            ya, yb = qa.result(), qb.result()
+            assert torch.equal(ya.indices, ref.indices) and torch.equal(ya.features, ref.features)
+            assert torch.equal(yb.indices, want[1][1]) and torch.equal(yb.features, want[1][0])
+            assert big2.fallbacks <= 1        # 0 when the capacity hints raised by `big` above already cover the dense batch
         torch.cuda.synchronize()
         _ext.check_status(cuda)
     finally:
