@@ -273,7 +273,7 @@ def run_ours(args):
         voxels = 0
         queued = None
         for s in range(args.steps):
-            nxt = graphed.submit(*dev_sets[s % ROTATE])
+            nxt = graphed.submit(*dev_sets[s % ROTATE], inputs_ready=True)   # the rotating batches are long resident
             if queued is not None:
                 out = queued.result()           # step s-1: wait, check the row counts, exact tensors
             queued = nxt
