@@ -23,7 +23,12 @@ own, and batches can be queued without waiting for the one before:
     ya = a.result()                       # valid until `depth` more batches have been submitted
 
 submit() returns at once; result() waits for that batch only (an event), checks its row counts
-and hands out the exact tensors.  net(f, i) is submit + result.  The reference has no counterpart.
+and hands out the exact tensors.  net(f, i) is submit + result.
+
+A producer that can write where it is told needs no copy at all: load(k, f, i) puts a batch into
+the input buffers of recording k once, and submit_loaded(k) replays recording k on what its
+buffers hold, as often as wanted.
+The reference has no counterpart.
 """
 import torch
 
@@ -103,6 +108,7 @@ class GraphedChain(object):
         self.stale = False          # a capacity overflowed: record again before the next replay
         self.turn = 0
         self.copy_stream = None     # side stream of submit(inputs_ready=True)
+        self.loaded = {}            # recording -> (features, indices) put there by load()
         self.queued = []            # per recording: the batch that occupies it (or None)
         self.launches = 0           # kernel launches recorded in the graph (= per replay)
         self.replays = 0
@@ -141,6 +147,39 @@ class GraphedChain(object):
         self.queued = [None] * self.depth
         self.stale = False
         self.turn = 0
+        for k, (f, i) in self.loaded.items():        # batches that lived in the old recordings' buffers
+            self._fill(self.recs[k], f, i)
+
+    def _fill(self, rec, features, indices):
+        n = int(features.shape[0])
+        rec.feats[:n].copy_(features)
+        rec.inds[:n].copy_(indices)
+        rec.n.fill_(n)
+
+    def _free(self, k):
+        old = self.queued[k]
+        if old is not None and not old.finished:
+            old.result()                             # its buffers are about to be overwritten
+        return self.recs[k]
+
+    def load(self, k, features, indices):
+        """Copy a batch into the input buffers of recording k (0 <= k < depth) for submit_loaded(k)."""
+        n = int(features.shape[0])
+        if n > self.cap:
+            raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
+        self._ready(features, indices)
+        self._fill(self._free(k), features, indices)
+        self.loaded[k] = (features, indices)
+
+    def submit_loaded(self, k):
+        """Replay recording k on the batch that load(k, ...) left in its input buffers: no copy.  The
+        previous result of recording k must have been used by now (its buffers are overwritten)."""
+        if self.recs is None or self.stale:
+            if k not in self.loaded:
+                raise RuntimeError("recording %d holds no batch: call load() first" % k)
+            self._ready(*self.loaded[k])
+        rec = self._free(k)
+        return self._launch(rec, lambda: self.loaded[k])
 
     def _launch(self, rec, exact_inputs):
         rec.graph.replay()
@@ -154,10 +193,8 @@ class GraphedChain(object):
     def _next(self):
         k = self.turn
         self.turn = (self.turn + 1) % self.depth
-        old = self.queued[k]
-        if old is not None and not old.finished:
-            old.result()                             # its buffers are about to be overwritten
-        return self.recs[k]
+        self.loaded.pop(k, None)                     # whatever load() left there is overwritten
+        return self._free(k)
 
     def submit(self, features, indices, inputs_ready=False):
         """Queue one batch (features [n, C], indices [n, 4]); returns an object whose result() gives

@@ -327,6 +327,18 @@ def test_graphed_chain_replays_match_eager_results(cuda):
             for (gf, gi), (wf, wi, _) in zip(seen, want * 2):
                 assert torch.equal(gi, wi) and torch.equal(gf, wf)
             assert two.replays == 8 and two.fallbacks == 0
+            # batches loaded once into the recordings' own input buffers and replayed in place
+            two.load(0, *batches[2])
+            two.load(1, *batches[0])
+            for _ in range(2):
+                qa, qb = two.submit_loaded(0), two.submit_loaded(1)
+                ya, yb = qa.result(), qb.result()
+                assert torch.equal(ya.indices, want[2][1]) and torch.equal(ya.features, want[2][0])
+                assert torch.equal(yb.indices, want[0][1]) and torch.equal(yb.features, want[0][0])
+            y = two(*batches[3])          # an ordinary call takes over recording 0 ...
+            assert torch.equal(y.indices, want[3][1]) and torch.equal(y.features, want[3][0])
+            yb = two.submit_loaded(1).result()   # ... and leaves the batch of recording 1 alone
+            assert torch.equal(yb.indices, want[0][1]) and torch.equal(yb.features, want[0][0])
             # a much denser batch overflows the recorded capacities: exact fallback, then a new graph
             ind = S.bernoulli_voxels(range(3), 20, 0.45, base_seed=99)
             f, i = dev(S.features(ind.shape[0], 5, 7), cuda), dev(ind, cuda)
