@@ -185,6 +185,12 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
 #define SSC_PREC_F16 2
+/* OR'ed into `precision` of ssc_conv_fwd / ssc_conv_fwd_ordered: `scratch` already holds the staged
+ * copy of the feature rows, written by ssc_conv_stage (e.g. on another stream, next to the
+ * rulebook kernels, which do not depend on the features); the call then skips its staging launch. */
+#define SSC_CONV_PRESTAGED 0x100
+int ssc_conv_stage(const float *features, int n_in, int c_in, int precision, void *scratch,
+                   size_t scratch_bytes, void *stream);
 size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision);
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                  const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,

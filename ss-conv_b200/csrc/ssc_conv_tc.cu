@@ -548,9 +548,21 @@ static inline int f16_row_words(int c_in) { return ((c_in + 7) & ~7) / 2; }
 
 size_t conv_f16_scratch_bytes(int n_in, int c_in) { return ((size_t)n_in + 1) * (size_t)f16_row_words(c_in) * 4; }
 
+int stage_features_f16(const float *features, int n_in, int c_in, void *staged, cudaStream_t st) {
+  const int words = f16_row_words(c_in);
+  const long long total_pairs = ((long long)n_in + 1) * words;
+  int blocks = ceil_div(total_pairs, 256 * 4);
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (blocks > sms * 16) blocks = sms * 16;
+  { stage_features_f16_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, words * 2, total_pairs, (uint32_t *)staged); note_launches(1); }
+  SSC_CHECK_LAUNCH("stage_features_f16");
+  return SSC_OK;
+}
+
 int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
                  int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
-                 const int32_t *order, cudaStream_t st) {
+                 const int32_t *order, bool prestaged, cudaStream_t st) {
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(fp16): kernel volume %d > 256", K);
   const int words = f16_row_words(c_in);
   if (scratch == nullptr || scratch_bytes < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
@@ -561,11 +573,10 @@ int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, 
   TcParams p;
   if (!tc_params(words, c_out, p, grid < 2 * sms))
     return fail(SSC_ERR_INVALID, "conv_fwd(fp16): c_out %d / kernel volume %d not supported", c_out, K);
-  const long long total_pairs = ((long long)n_in + 1) * words;
-  int blocks = ceil_div(total_pairs, 256 * 4);
-  if (blocks > sms * 16) blocks = sms * 16;
-  { stage_features_f16_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, words * 2, total_pairs, (uint32_t *)scratch); note_launches(1); }
-  SSC_CHECK_LAUNCH("stage_features_f16");
+  if (!prestaged) {
+    int rc = stage_features_f16(features, n_in, c_in, scratch, st);
+    if (rc != SSC_OK) return rc;
+  }
   const size_t smem = tc_smem_bytes(p);
   auto kernel = conv_fwd_tf32_kernel<true, true>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -584,14 +595,14 @@ constexpr int kStagingMinTiles = 64;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  const int32_t *n_out_dev, const int32_t *order, cudaStream_t st) {
+                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
   TcParams p;
   // Three variants share the packed filter image.  SSC_TC_VARIANT = gather4 | smem | tmem forces
   // one (where the shape allows); by default large problems take the persistent TMA-gather
   // kernel when the caller supplied its staging buffer, the others the shared-memory kernel.
   const char *variant = getenv("SSC_TC_VARIANT");
   const bool force_g4 = variant != nullptr && strcmp(variant, "gather4") == 0;
-  if (force_g4 && n_out_dev == nullptr && order == nullptr) {
+  if (force_g4 && n_out_dev == nullptr && order == nullptr && !prestaged) {
     int rc = conv_fwd_tf32_gather4(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, scratch,
                                    scratch_bytes, st);
     if (rc >= 0) return rc;
@@ -614,10 +625,11 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_pad * sizeof(float);
   const char *no_stage = getenv("SSC_TC_NO_STAGING");
   const bool force_wide = variant != nullptr && strcmp(variant, "wide") == 0;
-  const bool staged = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0 &&
-                      (grid >= kStagingMinTiles || force_wide) && no_stage == nullptr;
+  const bool fits = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0;
+  if (prestaged && !fits) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): SSC_CONV_PRESTAGED without the staged image in scratch");
+  const bool staged = fits && (prestaged || ((grid >= kStagingMinTiles || force_wide) && no_stage == nullptr));
   if (staged) {
-    int rc = stage_features(features, n_in, c_in, scratch, st);
+    int rc = prestaged ? SSC_OK : stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
     // persistent variant: several row tiles per pass share every filter slab
     if (force_wide && order == nullptr) {

@@ -51,6 +51,7 @@ SIGNATURES = {
     "ssc_nbr_transpose": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_nbr_row_order_scratch_bytes": (c_size_t, [c_int, c_int]),
     "ssc_nbr_row_order": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_conv_stage": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "ssc_conv_fwd_ordered": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     "ssc_conv_wgrad_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
@@ -486,6 +487,45 @@ def _resolve_precision(c_in, c_out, precision=None):
 STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") in ("gather4", "wide") else 64 * 128
 
 
+PRESTAGED = 0x100
+# (features.data_ptr(), filters.data_ptr()) -> (prec, packed, scratch, nbytes) left by conv_prepare for the
+# conv_forward call that follows on the same tensors
+_prepared = {}
+_side_streams = {}
+
+
+def side_stream(device):
+    """The stream on which work that does not depend on a layer's rulebook is queued next to it."""
+    key = torch.device(device).index
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device)
+    return _side_streams[key]
+
+
+def conv_prepare(features, filters, precision=None):
+    """Everything of a tensor-core convolution call that does not need the rulebook - the packed
+    filter image and the staged (TF32- or fp16-rounded) copy of the feature rows - queued on the
+    current stream (meant to be a side stream running next to the rulebook kernels).  The
+    conv_forward call on the same two tensors picks the result up.  Returns False when the call
+    would not use a staged image (exact fp32, small layers)."""
+    flt = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
+    if not (flt.is_contiguous() and features.is_contiguous() and features.dtype == torch.float32):
+        return False
+    K, c_in, c_out = flt.shape
+    mode = _resolve_precision(c_in, c_out, precision)
+    if mode not in ("tf32", "fp16") or (mode == "fp16" and c_out > 512):
+        return False
+    if mode == "tf32" and features.shape[0] < STAGING_MIN_ROWS:
+        return False
+    prec = PREC_F16 if mode == "fp16" else PREC_TF32
+    packed = pack_filters(flt, prec)
+    nbytes = int(lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device)
+    _check(lib().ssc_conv_stage(_p(features, torch.float32), features.shape[0], c_in, prec, _p(scratch), nbytes, _stream()))
+    _prepared[(features.data_ptr(), flt.data_ptr())] = (prec, packed, scratch, nbytes)
+    return True
+
+
 def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None):
     """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch).
     n_out_dev: device word with the exact row count when n_out is only a capacity.
@@ -501,7 +541,16 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
     st = status_word(features.device)
     if mode == "fp16" and c_out > 512:
         mode = "fp32"
-    if mode in ("tf32", "fp16"):
+    ready = None
+    if _prepared:   # only the call that directly follows conv_prepare may use what it left
+        ready = _prepared.pop((features.data_ptr(), filters.data_ptr()), None)
+        _prepared.clear()
+    if ready is not None and ready[0] == (PREC_F16 if mode == "fp16" else PREC_TF32 if mode == "tf32" else -1):
+        prec, packed, scratch, nbytes = ready
+        _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
+                                          _p(nbr, torch.int32), int(n_out), prec | PRESTAGED, _p(out), _p(st), _p(scratch),
+                                          nbytes, _p(n_out_dev), _p(row_order), _stream()))
+    elif mode in ("tf32", "fp16"):
         prec = PREC_F16 if mode == "fp16" else PREC_TF32
         tag = (prec, filters._version)
         packed = getattr(filters, "_ssc_packed", None)

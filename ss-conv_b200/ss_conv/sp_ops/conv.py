@@ -74,9 +74,22 @@ class SparseConvolution(nn.Module):
         if (_ext.AHEAD and not self.conv1x1 and not self.subm and not self.inverse and self.indice_key is None
                 and feats_raw.is_cuda and feats_raw.dtype == torch.float32
                 and not (torch.is_grad_enabled() and (feats_raw.requires_grad or weight.requires_grad))):
+            # While a CUDA graph is being recorded, the part of the convolution call that does not
+            # need the rulebook (filter packing, staging of the feature rows) goes to a side stream:
+            # the graph then runs it next to the rulebook kernels, which leave most of the GPU idle.
+            forked = None
+            if torch.cuda.is_current_stream_capturing():
+                cur, side = torch.cuda.current_stream(feats_raw.device), _ext.side_stream(feats_raw.device)
+                side.wait_stream(cur)
+                with torch.cuda.stream(side):
+                    forked = _ext.conv_prepare(feats_raw, weight)
             ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_spatial_shape,
                                                 list(input.spatial_shape), self.kernel_size, self.stride,
                                                 self.padding, self.dilation, int(self.transposed), n_in_dev=n_in_dev)
+            if forked is not None:
+                cur.wait_stream(side)
+                if ahead is None:
+                    _ext._prepared.clear()
             if ahead is not None:
                 outids_cap, pairs, pair_num = ahead
                 out_cap = indice_conv(feats_raw, weight, pairs, pair_num, pairs.capacity)
