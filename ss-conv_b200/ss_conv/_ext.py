@@ -494,12 +494,39 @@ _prepared = {}
 _side_streams = {}
 
 
-def side_stream(device):
-    """The stream on which work that does not depend on a layer's rulebook is queued next to it."""
-    key = torch.device(device).index
+def side_stream(device, which=0):
+    """Side streams used while a CUDA graph is recorded, to give the graph parallel branches:
+    0 - the part of a convolution call that does not need its rulebook (filter packing, staging);
+    1 - the rulebook of a layer, which needs the indices of its input but not the features, so it
+        can run next to the kernels that are still producing those features."""
+    key = (torch.device(device).index, which)
     if key not in _side_streams:
         _side_streams[key] = torch.cuda.Stream(device)
     return _side_streams[key]
+
+
+def rulebook_next_to_features(rows, build):
+    """build() queues a rulebook.  While a graph is recorded and the input's indices are known to be
+    complete at an event (rows.indices_ready, left by the layer that made them), it is queued on side
+    stream 1 behind that event only - not behind the feature kernels on the current stream - and the
+    current stream joins afterwards.  Returns (build(), event after the rulebook or None)."""
+    if not torch.cuda.is_current_stream_capturing():
+        return build(), None
+    dev = torch.cuda.current_device()
+    cur = torch.cuda.current_stream(dev)
+    ready = getattr(rows, "indices_ready", None) if rows is not None else None
+    after = torch.cuda.Event()
+    if ready is None:
+        out = build()
+        after.record(cur)
+        return out, after
+    rb = side_stream(dev, 1)
+    rb.wait_event(ready)
+    with torch.cuda.stream(rb):
+        out = build()
+        after.record(rb)
+    cur.wait_stream(rb)
+    return out, after
 
 
 def conv_prepare(features, filters, precision=None):

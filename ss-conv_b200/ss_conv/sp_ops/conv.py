@@ -83,9 +83,9 @@ class SparseConvolution(nn.Module):
                 side.wait_stream(cur)
                 with torch.cuda.stream(side):
                     forked = _ext.conv_prepare(feats_raw, weight)
-            ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_spatial_shape,
-                                                list(input.spatial_shape), self.kernel_size, self.stride,
-                                                self.padding, self.dilation, int(self.transposed), n_in_dev=n_in_dev)
+            ahead, indices_ready = _ext.rulebook_next_to_features(input._rows, lambda: _ext.get_indice_pairs_ahead(
+                inds_raw, input.batch_size, out_spatial_shape, list(input.spatial_shape), self.kernel_size, self.stride,
+                self.padding, self.dilation, int(self.transposed), n_in_dev=n_in_dev))
             if forked is not None:
                 cur.wait_stream(side)
                 if ahead is None:
@@ -107,6 +107,7 @@ class SparseConvolution(nn.Module):
 
                 out._rows = PendingRows(pairs._n_out_dev, pairs.capacity, input if input.pending() else None, redo,
                                         lambda n: _ext._note_ratio(key, input.features.shape[0], n))
+                out._rows.indices_ready = indices_ready   # the next layer's rulebook may start here
                 return out
         return self._sparse_conv_exact(input, weight)
 

@@ -30,8 +30,9 @@ class _SparsePool(nn.Module):
         feats_raw, inds_raw, n_in_dev = input.raw()
         if (_ext.AHEAD and not self.subm and feats_raw.is_cuda and feats_raw.dtype == torch.float32
                 and not (torch.is_grad_enabled() and feats_raw.requires_grad)):
-            ahead = _ext.get_indice_pairs_ahead(inds_raw, input.batch_size, out_shape, list(shape), self.kernel_size,
-                                                self.stride, self.padding, self.dilation, 0, n_in_dev=n_in_dev)
+            ahead, indices_ready = _ext.rulebook_next_to_features(input._rows, lambda: _ext.get_indice_pairs_ahead(
+                inds_raw, input.batch_size, out_shape, list(shape), self.kernel_size, self.stride, self.padding,
+                self.dilation, 0, n_in_dev=n_in_dev))
             if ahead is not None:
                 outids_cap, pairs, pair_num = ahead
                 feats_cap = type(self)._op(feats_raw, pairs, pair_num, pairs.capacity)
@@ -46,6 +47,7 @@ class _SparsePool(nn.Module):
 
                 out._rows = PendingRows(pairs._n_out_dev, pairs.capacity, input if input.pending() else None, redo,
                                         lambda n: _ext._note_ratio(key, input.features.shape[0], n))
+                out._rows.indices_ready = indices_ready
                 return out
         return self._forward_exact(input, out_shape)
 

@@ -32,11 +32,12 @@ class PendingRows(object):
     recomputed, is recomputed exactly by `redo` (its producer's exact path) followed by the
     row-wise operations applied to it since (`post`)."""
 
-    __slots__ = ("n_dev", "capacity", "parent", "redo", "post", "note", "grad")
+    __slots__ = ("n_dev", "capacity", "parent", "redo", "post", "note", "grad", "indices_ready")
 
     def __init__(self, n_dev, capacity, parent, redo, note=None):
         self.n_dev, self.capacity, self.parent, self.redo, self.note = n_dev, int(capacity), parent, redo, note
         self.post = []
+        self.indices_ready = None   # while a graph is recorded: event after which indices and n_dev are complete
         self.grad = torch.is_grad_enabled()   # a recomputation runs in the mode the layer was called in
         if _capture_log is not None:
             _capture_log.append(self)
