@@ -264,7 +264,7 @@ def run_ours(args):
         with torch.no_grad():
             return layer.pool(layer.conv(x))
 
-    graphed = GraphedChain(chain, [cfg["V"]] * 3, cfg["batch"], layer.conv.in_channels, max(n_in), dev, depth=ROTATE)
+    graphed = GraphedChain(chain, [cfg["V"]] * 3, cfg["batch"], layer.conv.in_channels, max(n_in), dev, depth=ROTATE, streams=2)
     for k in range(ROTATE):
         graphed.load(k, *dev_sets[k])
     for w in range(max(args.warmup, ROTATE)):

@@ -23,7 +23,9 @@ own, and batches can be queued without waiting for the one before:
     ya = a.result()                       # valid until `depth` more batches have been submitted
 
 submit() returns at once; result() waits for that batch only (an event), checks its row counts
-and hands out the exact tensors.  net(f, i) is submit + result.
+and hands out the exact tensors.  net(f, i) is submit + result.  With streams = 2 the recordings
+replay on alternating streams of the chain's own, so that queued batches also overlap on the device;
+result() makes the outputs safe to use from the caller's stream.
 
 A producer that can write where it is told needs no copy at all: load(k, f, i) puts a batch into
 the input buffers of recording k once, and submit_loaded(k) replays recording k on what its
@@ -101,9 +103,12 @@ class _Queued(object):
 
 
 class GraphedChain(object):
-    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device, depth=1):
+    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device, depth=1, streams=1):
         self.fn, self.shape, self.batch, self.dev = fn, spatial_shape, int(batch_size), torch.device(device)
         self.cap, self.channels, self.depth = int(max_rows), int(channels), max(1, int(depth))
+        # streams > 1: recording k replays on stream k % streams, so consecutive batches overlap on the
+        # device (the small rulebook kernels of one batch under the convolution of the one before)
+        self.exec_streams = [torch.cuda.Stream(self.dev) for _ in range(int(streams))] if int(streams) > 1 else None
         self.recs = None            # `depth` recordings, made on first use
         self.stale = False          # a capacity overflowed: record again before the next replay
         self.turn = 0
@@ -182,12 +187,21 @@ class GraphedChain(object):
         return self._launch(rec, lambda: self.loaded[k])
 
     def _launch(self, rec, exact_inputs):
-        rec.graph.replay()
+        k = self.recs.index(rec)
+        if self.exec_streams is None:
+            rec.graph.replay()
+            rec.host_counts.copy_(rec.counts, non_blocking=True)    # the one read-back of the batch
+            rec.done.record()
+        else:
+            stream = self.exec_streams[k % len(self.exec_streams)]
+            stream.wait_stream(torch.cuda.current_stream(self.dev))  # the batch's inputs (copies queued by the caller's stream)
+            with torch.cuda.stream(stream):
+                rec.graph.replay()
+                rec.host_counts.copy_(rec.counts, non_blocking=True)
+                rec.done.record()
         self.replays += 1
-        rec.host_counts.copy_(rec.counts, non_blocking=True)    # the one read-back of the batch
-        rec.done.record()
         q = _Queued(self, rec, exact_inputs)
-        self.queued[self.recs.index(rec)] = q
+        self.queued[k] = q
         return q
 
     def _next(self):

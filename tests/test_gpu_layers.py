@@ -315,7 +315,7 @@ def test_graphed_chain_replays_match_eager_results(cuda):
                 assert torch.equal(oi, wi.cpu()) and torch.equal(of, wf.cpu())
             # two recordings: batches queued back to back, results read one batch late; the result of
             # a batch stays valid while the next one runs
-            two = GraphedChain(sparse_net, [20] * 3, 3, 5, cap, cuda, depth=2)
+            two = GraphedChain(sparse_net, [20] * 3, 3, 5, cap, cuda, depth=2, streams=2)
             queued, seen = [], []
             for f, i in batches * 2:
                 queued.append(two.submit(f, i, inputs_ready=len(queued) % 2 == 1))   # side-stream copy every other batch
