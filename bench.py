@@ -447,7 +447,8 @@ def run_ours(args):
                        "step": "rulebook + materialise + pack + stage + conv + pool rulebook + maxpool, replayed as one "
                                "CUDA graph (device-side row counts, capacity-sized buffers), one recording per rotating batch "
                                "with the batch resident in its input buffers; a step = replay + read-back and check of the "
-                               "row counts, step s+1 queued before the host checks step s",
+                               "row counts, step s+1 queued before the host checks step s; the recordings replay on two "
+                               "alternating streams, so consecutive steps overlap on the device",
                        "eager_ms_per_step": eager_ms, "graph_fallbacks": graph_fallbacks,
                        "parallelism": "sample-sharded x%d, no data-path collective" % world},
             "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h),
