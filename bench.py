@@ -162,16 +162,20 @@ class Backbone:
                 x = act(bn(conv(x)))
             return self.pool(x)
 
-    def forward(self, points, feats, ids):
+    def submit(self, points, feats, ids):
         """Voxelise eagerly (its voxel count sizes the rest), then the four stages + global pool
-        replayed as one recorded CUDA graph."""
+        replayed as one recorded CUDA graph (two recordings on two streams: the next batch is queued
+        while this one runs).  Returns the queued batch; .result() is the pooled [B, C] tensor."""
         from ss_conv.graph import GraphedChain
         with torch.no_grad():
             x = self.p2v(points, feats, ids)[1]
             if self.graphed is None:
                 self.graphed = GraphedChain(self.stages_and_pool, x.spatial_shape, x.batch_size, x.features.shape[1],
-                                            int(x.features.shape[0] * 1.05) + 64, x.features.device)
-            return self.graphed(x)       # the voxel count stays on the device (checked after the replay)
+                                            int(x.features.shape[0] * 1.05) + 64, x.features.device, depth=2, streams=2)
+            return self.graphed.submit(x)   # the voxel count stays on the device (checked after the replay)
+
+    def forward(self, points, feats, ids):
+        return self.submit(points, feats, ids).result()
 
 
 def run_backbone(args, dev, rank, world, dist):
@@ -198,8 +202,13 @@ def run_backbone(args, dev, rank, world, dist):
         torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(steps):
-        out = step()
+    queued = None
+    for _ in range(steps):                     # batch s+1 is voxelised and queued before batch s is waited for
+        nxt = net.submit(pts, fts, ids)
+        if queued is not None:
+            out = parallel.all_gather_rows(queued.result(), cfg["global_batch"])
+        queued = nxt
+    out = parallel.all_gather_rows(queued.result(), cfg["global_batch"])
     b.record()
     torch.cuda.synchronize()
     ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
@@ -208,7 +217,7 @@ def run_backbone(args, dev, rank, world, dist):
     assert out.shape == (cfg["global_batch"], 240)
     return {"metric": "backbone samples/sec", "value": cfg["global_batch"] * steps / (float(ms) * 1e-3), "unit": "samples/s",
             "global_batch": cfg["global_batch"], "steps": steps, "ms_per_step": float(ms) / steps, "scaling": "strong",
-            "workload": cfg["name"] + "; stages + pool replayed as one CUDA graph after an eager Point2Voxel", "collective": "all_gather of pooled [B/G,240] fp32 rows" if world > 1 else "none"}
+            "workload": cfg["name"] + "; stages + pool replayed as one CUDA graph (two recordings on two streams) after an eager Point2Voxel, batch s+1 voxelised and queued before batch s is waited for", "collective": "all_gather of pooled [B/G,240] fp32 rows" if world > 1 else "none"}
 
 
 def make_inputs(cfg, sample_base, n_sets):

@@ -210,12 +210,17 @@ class GraphedChain(object):
         self.loaded.pop(k, None)                     # whatever load() left there is overwritten
         return self._free(k)
 
-    def submit(self, features, indices, inputs_ready=False):
+    def submit(self, features, indices=None, inputs_ready=False):
         """Queue one batch (features [n, C], indices [n, 4]); returns an object whose result() gives
         what the chain returns.  Does not wait for the device.
         inputs_ready: the caller states that both tensors are complete (nothing queued on the current
         stream still writes them).  With more than one recording the copy into the graph's input
-        buffers then runs on a side stream, next to the replay of the batch before."""
+        buffers then runs on a side stream, next to the replay of the batch before.
+        A SparseTensor (indices=None) is accepted too, also one whose row count is still pending."""
+        if isinstance(features, SparseTensor):
+            if features.pending() and self.graph is not None:
+                return self._replay_pending(features)
+            features, indices = features.features, features.indices
         n = int(features.shape[0])
         if n > self.cap:
             raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
@@ -239,10 +244,6 @@ class GraphedChain(object):
         """features [n, C] + indices [n, 4], or one SparseTensor.  A SparseTensor whose row count is
         still pending (e.g. straight out of Point2Voxel) is taken as it is: its count joins the
         counts that are checked after the replay, so nothing waits for it before."""
-        if isinstance(features, SparseTensor):
-            if features.pending() and self.graph is not None:
-                return self._replay_pending(features).result()
-            features, indices = features.features, features.indices
         return self.submit(features, indices).result()
 
     def _replay_pending(self, x):
