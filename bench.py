@@ -273,31 +273,43 @@ def run_ours(args):
         with torch.no_grad():
             return layer.pool(layer.conv(x))
 
-    graphed = GraphedChain(chain, [cfg["V"]] * 3, cfg["batch"], layer.conv.in_channels, max(n_in), dev, depth=ROTATE, streams=2)
-    for k in range(ROTATE):
-        graphed.load(k, *dev_sets[k])
-    for w in range(max(args.warmup, ROTATE)):
-        graphed.submit_loaded(w % ROTATE).result()
-    barrier()
-    r0, f0 = graphed.replays, graphed.fallbacks
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local, enabled=(rank == 0)) as clk:
-        ev0.record()
-        voxels = 0
-        queued = None
-        for s in range(args.steps):
-            nxt = graphed.submit_loaded(s % ROTATE)
-            if queued is not None:
-                out = queued.result()           # step s-1: wait, check the row counts, exact tensors
-            queued = nxt
-            voxels += n_in[s % ROTATE]
-        out = queued.result()
-        ev1.record()
+    def timed_steps(depth, streams, lag):
+        """steps/s of the recorded step: `depth` recordings (recording k holds rotating batch k % ROTATE),
+        replayed round-robin on `streams` streams, each result taken `lag` steps after its submission."""
+        g = GraphedChain(chain, [cfg["V"]] * 3, cfg["batch"], layer.conv.in_channels, max(n_in), dev, depth=depth, streams=streams)
+        for k in range(depth):
+            g.load(k, *dev_sets[k % ROTATE])
+        for w in range(max(args.warmup, depth)):
+            g.submit_loaded(w % depth).result()
         barrier()
-    launches = (graphed.replays - r0) * graphed.launches
-    ms = ev0.elapsed_time(ev1)
+        r0, f0 = g.replays, g.fallbacks
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        vox, waiting = 0, []
+        for s in range(args.steps):
+            waiting.append(g.submit_loaded(s % depth))
+            if len(waiting) > lag:
+                waiting.pop(0).result()         # an earlier step: wait, check the row counts, exact tensors
+            vox += n_in[(s % depth) % ROTATE]
+        for q in waiting:
+            q.result()
+        e1.record()
+        barrier()
+        return g, e0.elapsed_time(e1), vox, g.replays - r0, g.fallbacks - f0
+
+    DEPTH, STREAMS, LAG = 6, 3, 2
+    with ClockSampler(local, enabled=(rank == 0)) as clk:
+        graphed, ms, voxels, n_replays, graph_fallbacks = timed_steps(DEPTH, STREAMS, LAG)
+    launches = n_replays * graphed.launches
     _ext.check_status(dev)
-    graph_fallbacks = graphed.fallbacks - f0   # timed steps whose row counts overflowed a capacity (recomputed eagerly)
+    # the same loop with fp16 operands in the convolution (opt-in precision; reported beside the headline)
+    _ext.set_precision("fp16")
+    try:
+        g16, ms16, vox16, _, fb16 = timed_steps(DEPTH, STREAMS, LAG)
+    finally:
+        _ext.set_precision("tf32")
+    f16_step_ms = ms16 / args.steps
+    del g16
     # the same step launched kernel by kernel from Python, for comparison
     eager_steps = min(args.steps, 20)
     for w in range(3):
@@ -456,8 +468,8 @@ def run_ours(args):
                        "step": "rulebook + materialise + pack + stage + conv + pool rulebook + maxpool, replayed as one "
                                "CUDA graph (device-side row counts, capacity-sized buffers), one recording per rotating batch "
                                "with the batch resident in its input buffers; a step = replay + read-back and check of the "
-                               "row counts, step s+1 queued before the host checks step s; the recordings replay on two "
-                               "alternating streams, so consecutive steps overlap on the device",
+                               "row counts, step s+1 queued before the host checks step s; the recordings replay on three "
+                               "streams in turn (6 recordings, results taken two steps late), so consecutive steps overlap on the device",
                        "eager_ms_per_step": eager_ms, "graph_fallbacks": graph_fallbacks,
                        "parallelism": "sample-sharded x%d, no data-path collective" % world},
             "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h),
@@ -478,7 +490,8 @@ def run_ours(args):
                             "ms": float(np.mean(bwd_ms)), "voxels_per_s": float(np.mean(n_in)) / (float(np.mean(bwd_ms)) * 1e-3)}
         line["fp16_operands"] = {"what": "the convolution call (stage + conv) of the same layer with precision 'fp16': fp16 "
                                          "operands, f32 accumulate (opt-in; the headline numbers above use TF32 operands)",
-                                 "conv_call_ms": float(np.mean(f16_ms)), "tf32_conv_call_ms": float(np.mean(kern_ms))}
+                                 "conv_call_ms": float(np.mean(f16_ms)), "tf32_conv_call_ms": float(np.mean(kern_ms)),
+                                 "step_ms": f16_step_ms, "step_what": "the timed step loop above with precision 'fp16' (this rank)"}
         line["backbone"] = backbone
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, budget_s=12.0)
