@@ -619,7 +619,12 @@ def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, i
         except Exception:
             pass
     nbr, n_out_dev = _table_for(indice_pairs, indice_num, int(num_act_out), bool(inverse))
-    return conv_forward(features, flt, nbr, int(num_act_out), n_out_dev=n_out_dev)
+    order = None
+    if inverse and n_out_dev is None and int(num_act_out) >= ROW_ORDER_MIN_ROWS and nbr.shape[0] > 1:
+        # an inverse convolution gathers through its partner's table with the roles exchanged: like the
+        # input gradient, every output row uses only the offsets of its parity class
+        order = nbr_row_order(nbr)
+    return conv_forward(features, flt, nbr, int(num_act_out), n_out_dev=n_out_dev, row_order=order)
 
 
 def _not_built(name):

@@ -112,7 +112,6 @@ class GraphedChain(object):
         self.recs = None            # `depth` recordings, made on first use
         self.stale = False          # a capacity overflowed: record again before the next replay
         self.turn = 0
-        self.copy_stream = None     # side stream of submit(inputs_ready=True)
         self.loaded = {}            # recording -> (features, indices) put there by load()
         self.queued = []            # per recording: the batch that occupies it (or None)
         self.launches = 0           # kernel launches recorded in the graph (= per replay)
@@ -210,12 +209,9 @@ class GraphedChain(object):
         self.loaded.pop(k, None)                     # whatever load() left there is overwritten
         return self._free(k)
 
-    def submit(self, features, indices=None, inputs_ready=False):
+    def submit(self, features, indices=None):
         """Queue one batch (features [n, C], indices [n, 4]); returns an object whose result() gives
         what the chain returns.  Does not wait for the device.
-        inputs_ready: the caller states that both tensors are complete (nothing queued on the current
-        stream still writes them).  With more than one recording the copy into the graph's input
-        buffers then runs on a side stream, next to the replay of the batch before.
         A SparseTensor (indices=None) is accepted too, also one whose row count is still pending."""
         if isinstance(features, SparseTensor):
             if features.pending() and self.graph is not None:
@@ -226,18 +222,7 @@ class GraphedChain(object):
             raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (n, self.cap))
         self._ready(features, indices)
         rec = self._next()
-        if inputs_ready and self.depth > 1:
-            if self.copy_stream is None:
-                self.copy_stream = torch.cuda.Stream(self.dev)
-            with torch.cuda.stream(self.copy_stream):
-                rec.feats[:n].copy_(features)
-                rec.inds[:n].copy_(indices)
-                rec.n.fill_(n)
-            torch.cuda.current_stream(self.dev).wait_stream(self.copy_stream)
-        else:
-            rec.feats[:n].copy_(features)
-            rec.inds[:n].copy_(indices)
-            rec.n.fill_(n)
+        self._fill(rec, features, indices)
         return self._launch(rec, lambda: (features, indices))
 
     def __call__(self, features, indices=None):

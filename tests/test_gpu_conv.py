@@ -83,6 +83,32 @@ def test_inverse_conv(cuda):
         assert rel_err(y, ref) <= TOL[precision]
 
 
+def test_inverse_conv_with_grouped_rows_gives_the_same_bits(cuda, monkeypatch):
+    """A large inverse convolution runs through the row order of its table (rows grouped by parity
+    class); the result is the one of the plain order, bit for bit."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(3)
+    ind = random_voxels(rng, 3, 32, 6000)
+    outids, pairs, num = gpu_rulebook(ind, 3, [32] * 3, 3, 2, 1, 1, False, cuda)
+    assert ind.shape[0] >= _ext.ROW_ORDER_MIN_ROWS
+    feats = torch.randn(outids.shape[0], 32, device=cuda)
+    W = torch.randn(3, 3, 3, 32, 24, device=cuda) / 20
+    _ext.set_precision("tf32")
+    try:
+        l0 = _ext.kernel_launches()
+        grouped = _ext.indice_conv_fp32(feats, W, pairs, num, ind.shape[0], 1, 0)
+        l1 = _ext.kernel_launches()
+        monkeypatch.setattr(_ext, "ROW_ORDER_MIN_ROWS", 1 << 30)
+        plain = _ext.indice_conv_fp32(feats, W, pairs, num, ind.shape[0], 1, 0)
+        l2 = _ext.kernel_launches()
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+    finally:
+        _ext.set_precision("auto")
+    assert (l1 - l0) - (l2 - l1) >= 2                     # the ordering kernels ran in the first call only
+    assert torch.equal(grouped, plain)
+
+
 def test_conv_is_deterministic_and_linear(cuda):
     from ss_conv import _ext
     from ss_conv.utils import synthetic as S

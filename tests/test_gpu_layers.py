@@ -318,7 +318,7 @@ def test_graphed_chain_replays_match_eager_results(cuda):
             two = GraphedChain(sparse_net, [20] * 3, 3, 5, cap, cuda, depth=2, streams=2)
             queued, seen = [], []
             for f, i in batches * 2:
-                queued.append(two.submit(f, i, inputs_ready=len(queued) % 2 == 1))   # side-stream copy every other batch
+                queued.append(two.submit(f, i))
                 if len(queued) >= 2:
                     y = queued[-2].result()
                     seen.append((y.features.clone(), y.indices.clone()))
