@@ -526,6 +526,20 @@ def run_only(args):
                 nbr = _ext.neighbour_table(pairs, num, outids.shape[0])
                 for _ in range(4):
                     _ext.conv_forward(f, flt, nbr, outids.shape[0], "tf32")
+            elif args.only == "conv_fp16":
+                nbr = _ext.neighbour_table(pairs, num, outids.shape[0])
+                for _ in range(4):
+                    _ext.conv_forward(f, flt, nbr, outids.shape[0], "fp16")
+            elif args.only == "backward":     # input gradient (plain and grouped rows) + filter gradient
+                nbr = _ext.neighbour_table(pairs, num, outids.shape[0])
+                nbr_in = _ext.input_major_table(nbr, i.shape[0])
+                order = _ext.nbr_row_order(nbr_in)
+                g = torch.randn(outids.shape[0], flt.shape[2], device=dev)
+                fltT = flt.transpose(1, 2).contiguous()
+                for _ in range(2):
+                    _ext.conv_forward(g, fltT, nbr_in, i.shape[0], "tf32")
+                    _ext.conv_forward(g, fltT, nbr_in, i.shape[0], "tf32", row_order=order)
+                    _ext.conv_wgrad(f, g, nbr)
     torch.cuda.synchronize()
     _ext.check_status(dev)
     print("only=%s done, n_in=%d n_out=%d" % (args.only, i.shape[0], outids.shape[0]))
@@ -622,7 +636,7 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["conv", "rulebook", "step"],
+    ap.add_argument("--only", default=None, choices=["conv", "conv_fp16", "backward", "rulebook", "step"],
                     help="run just one kernel group of the cfg2 step (or the whole step) a few times (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
