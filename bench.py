@@ -425,18 +425,16 @@ def run_ours(args):
         bwd_graphs = []
         for k in range(ROTATE):                       # recorded like the forward call: device time only
             f, (nbr, nbr_in, order), g = prepared[k][0], tables[k], grads[k]
-            _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32", row_order=order)
-            _ext.conv_wgrad(f, g, nbr)
+            _ext.conv_backward(f, flt, g, nbr, nbr_in, order, "tf32")
             torch.cuda.synchronize()
             cg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(cg):
-                _ext.conv_forward(g, fltT, nbr_in, f.shape[0], "tf32", row_order=order)
-                _ext.conv_wgrad(f, g, nbr)
-            bwd_graphs.append(cg)
+                keep = _ext.conv_backward(f, flt, g, nbr, nbr_in, order, "tf32")   # the two gradients on parallel branches
+            bwd_graphs.append((cg, keep))
         for it in range(2 + 6):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            bwd_graphs[it % ROTATE].replay()
+            bwd_graphs[it % ROTATE][0].replay()
             b.record()
             torch.cuda.synchronize()
             if it >= 2:

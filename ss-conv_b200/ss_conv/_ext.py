@@ -676,6 +676,32 @@ def conv_wgrad(features, out_grad, nbr, precision=None):
     return d_flt
 
 
+def conv_backward(features, flt, out_bp, nbr, nbr_in=None, order=None, precision=None):
+    """(input gradient [n_in, Cin], filter gradient [K, Cin, Cout]) of out = conv(features, flt [K, Cin, Cout])
+    over the table nbr [K, n_out].  nbr_in / order: the input-major table and its row order when the
+    caller kept them with the rulebook (built here otherwise)."""
+    n_in = features.shape[0]
+    # the two gradients do not depend on each other: while a graph is recorded the filter gradient
+    # goes to a side stream, so the graph runs it next to the input gradient
+    forked = torch.cuda.is_current_stream_capturing()
+    if forked:
+        cur, side = torch.cuda.current_stream(features.device), side_stream(features.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            d_flt = conv_wgrad(features, out_bp, nbr, precision)
+    if nbr_in is None:
+        nbr_in = input_major_table(nbr, n_in)
+        # rows of the input-major table use few of the offsets each (their parity class under a
+        # stride): grouped tiles skip the rest
+        order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
+    d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in, precision, row_order=order)
+    if forked:
+        cur.wait_stream(side)
+    else:
+        d_flt = conv_wgrad(features, out_bp, nbr, precision)
+    return d_in, d_flt
+
+
 def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_num, inverse, subm):
     """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:46-48): [input_grad, filters_grad].
     The input gradient is the forward gather-GEMM over the input-major table with the filters
@@ -688,12 +714,7 @@ def indice_conv_backward_fp32(features, filters, out_bp, indice_pairs, indice_nu
     flt = filters.reshape(-1, c_in, c_out)
     n_in, n_out = features.shape[0], out_bp.shape[0]
     nbr = neighbour_table(indice_pairs, indice_num, n_out, bool(inverse))
-    nbr_in = input_major_table(nbr, n_in)
-    # rows of the input-major table use few of the offsets each (their parity class under a
-    # stride): grouped tiles skip the rest
-    order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
-    d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in, row_order=order)
-    d_flt = conv_wgrad(features, out_bp, nbr)
+    d_in, d_flt = conv_backward(features, flt, out_bp, nbr)
     return [d_in, d_flt.reshape(filters.shape)]
 
 
