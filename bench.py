@@ -462,7 +462,9 @@ def run_ours(args):
             "data": "synthetic (seeded ellipsoid-surface voxels, N(0,1) features, reference-style N(0,1) kernel weights)",
             "config": {"workload": cfg["name"], "n_in_per_batch": n_in[0], "n_out_conv": n_out_conv,
                        "c_in": layer.conv.in_channels, "c_out": layer.conv.out_channels,
-                       "l2": "rotating %d distinct input batches (> 126 MB working set) between timed steps" % ROTATE,
+                       "l2": "%d recordings with buffers of their own (inputs, tables, staging, outputs: > 1 GB working set) holding %d "
+                             "distinct input batches, replayed in turn: nothing a step reads is still in L2 from its last replay"
+                             % (DEPTH, ROTATE),
                        "step": "rulebook + materialise + pack + stage + conv + pool rulebook + maxpool, replayed as one "
                                "CUDA graph (device-side row counts, capacity-sized buffers), one recording per rotating batch "
                                "with the batch resident in its input buffers; a step = replay + read-back and check of the "
