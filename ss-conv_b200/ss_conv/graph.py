@@ -59,14 +59,19 @@ class _Recording(object):
         l0 = _ext.kernel_launches()
         tensor_mod._capture_log = log
         try:
+            pinned = torch.empty(256, dtype=torch.int32).pin_memory()
             with torch.cuda.graph(graph):
                 out = chain.fn(x)
                 counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log])   # input count first
+                if counts.shape[0] > pinned.shape[0]:
+                    raise RuntimeError("chain with more than %d pending row counts" % (pinned.shape[0] - 1))
+                host_counts = pinned[:counts.shape[0]]
+                host_counts.copy_(counts, non_blocking=True)    # the one read-back of the batch, part of the graph
         finally:
             tensor_mod._capture_log = None
         chain.launches = _ext.kernel_launches() - l0
         self.graph, self.out, self.counts, self.caps = graph, out, counts, [chain.cap] + [r.capacity for r in log]
-        self.host_counts = torch.empty(counts.shape[0], dtype=torch.int32).pin_memory()
+        self.host_counts = host_counts
         if len(log) == 0 or (isinstance(out, SparseTensor) and not out.pending()):
             raise RuntimeError("nothing in this chain ran ahead of its row counts (no capacity hints yet?)")
 
@@ -189,14 +194,12 @@ class GraphedChain(object):
         k = self.recs.index(rec)
         if self.exec_streams is None:
             rec.graph.replay()
-            rec.host_counts.copy_(rec.counts, non_blocking=True)    # the one read-back of the batch
             rec.done.record()
         else:
             stream = self.exec_streams[k % len(self.exec_streams)]
             stream.wait_stream(torch.cuda.current_stream(self.dev))  # the batch's inputs (copies queued by the caller's stream)
             with torch.cuda.stream(stream):
                 rec.graph.replay()
-                rec.host_counts.copy_(rec.counts, non_blocking=True)
                 rec.done.record()
         self.replays += 1
         q = _Queued(self, rec, exact_inputs)
