@@ -286,21 +286,31 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         vox, waiting = 0, []
+        t_submit = t_result = 0.0
         for s in range(args.steps):
+            t0 = time.perf_counter()
             waiting.append(g.submit_loaded(s % depth))
+            t1 = time.perf_counter()
             if len(waiting) > lag:
                 waiting.pop(0).result()         # an earlier step: wait, check the row counts, exact tensors
+            t2 = time.perf_counter()
+            t_submit += t1 - t0
+            t_result += t2 - t1
             vox += n_in[(s % depth) % ROTATE]
         for q in waiting:
             q.result()
         e1.record()
         barrier()
+        host_us[0], host_us[1] = t_submit / args.steps * 1e6, t_result / args.steps * 1e6
         return g, e0.elapsed_time(e1), vox, g.replays - r0, g.fallbacks - f0
+
+    host_us = [0.0, 0.0]    # host time per step of the last timed_steps call: queueing a step / waiting for and checking one
 
     DEPTH, STREAMS, LAG = 6, 3, 2
     with ClockSampler(local, enabled=(rank == 0)) as clk:
         graphed, ms, voxels, n_replays, graph_fallbacks = timed_steps(DEPTH, STREAMS, LAG)
     launches = n_replays * graphed.launches
+    host_submit_us, host_result_us = host_us
     _ext.check_status(dev)
     # the same loop with fp16 operands in the convolution (opt-in precision; reported beside the headline)
     _ext.set_precision("fp16")
@@ -446,13 +456,14 @@ def run_ours(args):
     _ext.set_precision("tf32")
 
     # ---- reduce over ranks
-    stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches), serial_s, eager_ms], dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms, e2e_s, float(voxels), float(vox_e2e), float(launches), serial_s, eager_ms, host_submit_us, host_result_us], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         ms, e2e_s, serial_s, eager_ms = float(mx[0]), float(mx[1]), float(mx[5]), float(mx[6])
+        host_submit_us, host_result_us = float(mx[7]), float(mx[8])
         voxels, vox_e2e, launches = float(sm[2]), float(sm[3]), float(sm[4])
     if rank == 0:
         line = {
@@ -471,6 +482,8 @@ def run_ours(args):
                                "row counts, step s+1 queued before the host checks step s; the recordings replay on three "
                                "streams in turn (6 recordings, results taken two steps late), so consecutive steps overlap on the device",
                        "eager_ms_per_step": eager_ms, "graph_fallbacks": graph_fallbacks,
+                       "host_us_per_step": {"queue_a_step": host_submit_us, "wait_for_and_check_a_step": host_result_us,
+                                            "note": "host time in the timed loop (max over ranks); the second includes waiting for the device"},
                        "parallelism": "sample-sharded x%d, no data-path collective" % world},
             "e2e": {"value": vox_e2e / e2e_s, "unit": "voxels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(d2h),
                     "how": "ss_conv.pipeline.HostStream (upload / compute / download of consecutive steps overlap on 3 streams) "

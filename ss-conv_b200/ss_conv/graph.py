@@ -50,6 +50,7 @@ class _Recording(object):
         self.graph = None
         self.out = self.counts = self.caps = self.host_counts = None
         self.done = torch.cuda.Event()
+        self.fence = torch.cuda.Event()     # what the caller's stream had queued when the batch was submitted
 
     def record(self, chain):
         x = SparseTensor(self.feats, self.inds, chain.shape, chain.batch)
@@ -197,10 +198,15 @@ class GraphedChain(object):
             rec.done.record()
         else:
             stream = self.exec_streams[k % len(self.exec_streams)]
-            stream.wait_stream(torch.cuda.current_stream(self.dev))  # the batch's inputs (copies queued by the caller's stream)
-            with torch.cuda.stream(stream):
+            cur = torch.cuda.current_stream(self.dev)
+            rec.fence.record(cur)                    # the batch's inputs (copies queued by the caller's stream) and
+            stream.wait_event(rec.fence)             # the caller's reads of this recording's previous output
+            torch.cuda.set_stream(stream)
+            try:
                 rec.graph.replay()
-                rec.done.record()
+            finally:
+                torch.cuda.set_stream(cur)
+            rec.done.record(stream)
         self.replays += 1
         q = _Queued(self, rec, exact_inputs)
         self.queued[k] = q
