@@ -43,6 +43,31 @@ def test_row_order_is_a_grouping_permutation_and_changes_no_bit(cuda, k, s, p, s
     assert torch.equal(plain, ordered)
 
 
+def test_conv_backward_recorded_with_parallel_branches(cuda):
+    """conv_backward recorded into a CUDA graph puts the filter gradient on a side stream (a
+    parallel branch of the graph); the replay gives the bits of the eager call."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(21)
+    ind = random_voxels(rng, 3, 24, 4000)
+    outids, pairs, num = gpu_rulebook(ind, 3, [24] * 3, 3, 2, 1, 1, False, cuda)
+    n_in, n_out = ind.shape[0], outids.shape[0]
+    nbr = _ext.neighbour_table(pairs, num, n_out)
+    f = torch.randn(n_in, 32, device=cuda)
+    g = torch.randn(n_out, 40, device=cuda)
+    flt = torch.randn(27, 32, 40, device=cuda) / 30
+    want_in, want_w = _ext.conv_backward(f, flt, g, nbr, precision="tf32")
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        got_in, got_w = _ext.conv_backward(f, flt, g, nbr, precision="tf32")
+    got_in.zero_()
+    got_w.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    assert torch.equal(got_in, want_in) and torch.equal(got_w, want_w)
+
+
 @pytest.mark.parametrize("tag", ["bw_strided", "bw_subm"])
 def test_conv_backward_matches_reference_outputs(cuda, golden, tag):
     from ss_conv import _ext
