@@ -690,10 +690,19 @@ def conv_backward(features, flt, out_bp, nbr, nbr_in=None, order=None, precision
         with torch.cuda.stream(side):
             d_flt = conv_wgrad(features, out_bp, nbr, precision)
     if nbr_in is None:
-        nbr_in = input_major_table(nbr, n_in)
-        # rows of the input-major table use few of the offsets each (their parity class under a
-        # stride): grouped tiles skip the rest
-        order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
+        kept = getattr(nbr, "_ssc_in_major", None)     # layers that share a rulebook share these too
+        if kept is not None and kept[0] == n_in:
+            nbr_in, order = kept[1], kept[2]
+        else:
+            nbr_in = input_major_table(nbr, n_in)
+            # rows of the input-major table use few of the offsets each (their parity class under a
+            # stride): grouped tiles skip the rest
+            order = nbr_row_order(nbr_in) if (n_in >= ROW_ORDER_MIN_ROWS and nbr_in.shape[0] > 1) else None
+            if not forked:                             # tensors made while a graph is recorded belong to the graph
+                try:
+                    nbr._ssc_in_major = (n_in, nbr_in, order)
+                except Exception:
+                    pass
     d_in = conv_forward(out_bp, flt.transpose(1, 2).contiguous(), nbr_in, n_in, precision, row_order=order)
     if forked:
         cur.wait_stream(side)
