@@ -173,18 +173,21 @@ int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int 
  *            11-bit significand as TF32 within fp16's range (finite values beyond +-65504
  *            saturate, magnitudes below 6e-5 lose bits), half the gathered bytes and half the
  *            tensor-core instructions.  Needs `scratch` (the fp16 copy of the feature rows).
+ *            SSC_PREC_BF16 = the same with bfloat16 operands (fp32's exponent range, 8 significant
+ *            bits; max rel. error target 1e-2).  The reference has no bf16 entry point.
  * status: device int32 that receives a non-zero value if a bounded wait inside the kernel
  * ran out (may be NULL).
- * scratch: optional device buffer of ssc_conv_scratch_bytes() bytes, 128-byte aligned.  With it
- * the TF32 path of a large layer stages a TF32-rounded copy of the feature rows there and
- * gathers them with the TMA unit (cp.async.bulk.tensor tile::gather4) in a persistent kernel;
- * without it (NULL / too small) the rows are gathered by the SM's load-store units.  The
- * result is the same up to the summation order inside the tensor core.
+ * scratch: optional device buffer of ssc_conv_scratch_bytes() bytes, 16-byte aligned.  With it
+ * the TF32 path of a large layer first writes a TF32-rounded copy of the feature rows there and
+ * gathers from the copy (a row is gathered about K/2 times; rounding once instead of after every
+ * gather feeds the tensor core the same operands, bit for bit); without it (NULL / too small)
+ * the rows are rounded in shared memory after every gather.  The 16-bit precisions need it.
  * n_out_dev: NULL, or the device word holding the exact number of output rows when n_out is a
  * capacity (see ssc_rulebook_conv_fill); rows past the exact count are not written. */
 #define SSC_PREC_FP32 0
 #define SSC_PREC_TF32 1
 #define SSC_PREC_F16 2
+#define SSC_PREC_BF16 3
 /* OR'ed into `precision` of ssc_conv_fwd / ssc_conv_fwd_ordered: `scratch` already holds the staged
  * copy of the feature rows, written by ssc_conv_stage (e.g. on another stream, next to the
  * rulebook kernels, which do not depend on the features); the call then skips its staging launch. */
@@ -195,6 +198,27 @@ size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision);
 int ssc_conv_fwd(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                  const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
                  void *scratch, size_t scratch_bytes, const int32_t *n_out_dev, void *stream);
+
+/* Pair-list form of the same convolution, for sparsely filled tables (wide submanifold layers):
+ * per kernel offset the present (input row, output row) pairs are compacted into lists, every
+ * 128 pairs form a dense tile [128, Cin] x filters[kappa] on the tensor cores, and the rows of the
+ * product are added to their output rows - the reference's gather / GEMM / scatter-add per offset
+ * (SS_Conv_lib/src/conv/indice_conv.h:290-338, reordering_cuda_functor.cu:161-273) as one persistent
+ * launch with the filter matrix of an offset resident in shared memory.  The sums of an output row
+ * arrive in no fixed order (fp32 reductions at L2): results repeat only up to rounding.
+ *   ssc_conv_pairs_list_bytes : size of `lists` for a table [K, n_out] (256-byte aligned buffer)
+ *   ssc_conv_pairs_supported  : 1 if the kernel covers (c_in, c_out, precision), else 0
+ *   ssc_conv_pairs_build      : lists from the neighbour table (three small launches; reusable for
+ *                               every layer that shares the table)
+ *   ssc_conv_fwd_pairs        : staging (unless SSC_CONV_PRESTAGED) + clear + convolution;
+ *                               precision SSC_PREC_TF32 / _F16 / _BF16, `filters` the packed image,
+ *                               `scratch` the staging buffer of ssc_conv_scratch_bytes(). */
+size_t ssc_conv_pairs_list_bytes(int K, int n_out);
+int ssc_conv_pairs_supported(int c_in, int c_out, int precision);
+int ssc_conv_pairs_build(const int32_t *nbr, int K, int n_out, void *lists, size_t list_bytes, void *stream);
+int ssc_conv_fwd_pairs(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
+                       void *lists, size_t list_bytes, int n_out, int precision, float *out,
+                       int32_t *status, void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------- sparse pools
  * Replace indiceMaxPool / indiceAvgPool (SS_Conv_lib/src/pool/indice_maxpool.h:15-50,

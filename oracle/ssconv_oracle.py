@@ -424,10 +424,20 @@ def point2voxel(points, feats, batch_ids, voxel_num_limit, unit_voxel_extent, mo
     return p, voxelize_fp(f, maps, mode), occupied.astype(I32), ids, inverse.astype(I32)
 
 
+def _fma32(a, b, c):
+    """fp32 fused multiply-add a*b + c: the product of two fp32 values is exact in float64, the
+    sum is rounded to float64 and then to fp32 (double rounding can differ from a true fma only
+    when the float64 sum lands exactly on an fp32 rounding boundary)."""
+    return (np.asarray(a, np.float32).astype(np.float64) * np.asarray(b, np.float32).astype(np.float64)
+            + np.asarray(c, np.float32).astype(np.float64)).astype(np.float32)
+
+
 def three_nn(unknown, known):
     """SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:8-55: per query (b,x,y,z) scan all
     known rows of the same batch id, fp32 squared distance, keep the three smallest with
-    strict < (first index wins ties); unfilled slots keep 1e40 (-> +inf in fp32) and index 0."""
+    strict < (first index wins ties); unfilled slots keep 1e40 (-> +inf in fp32) and index 0.
+    The distance dx*dx + dy*dy + dz*dz (:39) is evaluated as nvcc contracts it,
+    fma(dz, dz, fma(dx, dx, dy*dy)): pinned bit for bit to the reference's compiled kernel."""
     unknown = np.asarray(unknown, dtype=np.float32)
     known = np.asarray(known, dtype=np.float32)
     n = unknown.shape[0]
@@ -438,7 +448,7 @@ def three_nn(unknown, known):
         dx = unknown[q, 1] - known[same, 1]
         dy = unknown[q, 2] - known[same, 2]
         dz = unknown[q, 3] - known[same, 3]
-        d = (dx * dx + dy * dy) + dz * dz
+        d = _fma32(dz, dz, _fma32(dx, dx, dy * dy))
         order = np.argsort(d, kind="stable")[:3]
         best = np.full(3, np.inf, dtype=np.float32)
         bi = np.zeros(3, dtype=I32)
@@ -450,11 +460,12 @@ def three_nn(unknown, known):
 
 def three_interpolate(points, idx, weight):
     """SS_Conv_lib/src/voxelize/interpolate_cuda_kernel.cu:79-101:
-    out[n,c] = w0*p[i0,c] + w1*p[i1,c] + w2*p[i2,c] evaluated left to right in fp32."""
+    out[n,c] = w0*p[i0,c] + w1*p[i1,c] + w2*p[i2,c], evaluated as nvcc contracts it,
+    fma(w2, p2, fma(w0, p0, w1*p1)): pinned bit for bit to the reference's compiled kernel."""
     points = np.asarray(points, dtype=np.float32)
     weight = np.asarray(weight, dtype=np.float32)
-    t = weight[:, 0:1] * points[idx[:, 0]] + weight[:, 1:2] * points[idx[:, 1]]
-    return (t + weight[:, 2:3] * points[idx[:, 2]]).astype(np.float32)
+    t = _fma32(weight[:, 0:1], points[idx[:, 0]], weight[:, 1:2] * points[idx[:, 1]])
+    return _fma32(weight[:, 2:3], points[idx[:, 2]], t)
 
 
 def voxel2point(voxel_feats, voxel_indices, spatial_shape, unit_voxel_extent, points, batch_ids):

@@ -1,19 +1,8 @@
 // Steerable kernel materialisation and the exact-fp32 (CUDA core) output-stationary
 // gather-GEMM kernel.  The tensor-core (tcgen05) variant lives in ssc_conv_tc.cu.
-#include "ssc_common.cuh"
+#include "ssc_conv_internal.cuh"
 
 namespace ssc {
-
-int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
-                  const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st);
-int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st);
-int stage_features_f16(const float *features, int n_in, int c_in, void *staged, cudaStream_t st);
-size_t conv_gather4_scratch_bytes(int n_in, int c_in, int c_out);
-size_t conv_f16_scratch_bytes(int n_in, int c_in);
-int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
-                 int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
-                 const int32_t *order, bool prestaged, cudaStream_t st);
 
 // filters[kappa][cin][cout] = sum_b w[u,v,b] * basis[b,a,c,kappa]; one thread per element,
 // cout fastest so the (large) filter tensor is written coalesced; the basis blob is small
@@ -147,19 +136,20 @@ extern "C" int ssc_materialize(const float *weight, const float *basis, const in
 
 extern "C" size_t ssc_conv_scratch_bytes(int n_in, int c_in, int c_out, int precision) {
   if (n_in < 0 || c_in < 1 || c_out < 1) return 0;
-  if (precision == SSC_PREC_F16) return conv_f16_scratch_bytes(n_in, c_in);
+  (void)c_out;
+  if (precision == SSC_PREC_F16 || precision == SSC_PREC_BF16) return conv_f16_scratch_bytes(n_in, c_in);
   if (precision != SSC_PREC_TF32) return 0;
-  return conv_gather4_scratch_bytes(n_in, c_in, c_out);
+  return conv_tf32_scratch_bytes(n_in, c_in);
 }
 
 extern "C" int ssc_conv_stage(const float *features, int n_in, int c_in, int precision, void *scratch, size_t scratch_bytes,
                               void *stream) {
   SSC_REQUIRE(c_in > 0 && n_in >= 0 && (n_in == 0 || features) && scratch, "conv_stage: bad arguments");
-  SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16, "conv_stage: precision %d has no staged image", precision);
+  SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16 || precision == SSC_PREC_BF16, "conv_stage: precision %d has no staged image", precision);
   SSC_REQUIRE(scratch_bytes >= ssc_conv_scratch_bytes(n_in, c_in, 1, precision) && ((uintptr_t)scratch & 15u) == 0,
               "conv_stage: scratch too small or not 16-byte aligned");
-  return precision == SSC_PREC_F16 ? stage_features_f16(features, n_in, c_in, scratch, as_stream(stream))
-                                   : stage_features(features, n_in, c_in, scratch, as_stream(stream));
+  return precision == SSC_PREC_TF32 ? stage_features(features, n_in, c_in, scratch, as_stream(stream))
+                                    : stage_features_16(features, n_in, c_in, precision == SSC_PREC_BF16, scratch, as_stream(stream));
 }
 
 extern "C" int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
@@ -179,7 +169,8 @@ extern "C" int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, c
     return SSC_OK;
   }
   if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, st);
-  if (precision == SSC_PREC_F16) return conv_fwd_f16(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, st);
+  if (precision == SSC_PREC_F16 || precision == SSC_PREC_BF16)
+    return conv_fwd_16(features, n_in, c_in, precision == SSC_PREC_BF16, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, st);
   return fail(SSC_ERR_INVALID, "conv_fwd: unknown precision %d", precision);
 }
 

@@ -22,21 +22,10 @@
 // Every wait on an mbarrier is bounded: on expiry the thread records an error in `status`
 // through a shared flag, every other wait then gives up too, and the kernel frees its tensor
 // memory and returns.
-#include <stdlib.h>
-
-#include "ssc_common.cuh"
+#include "ssc_conv_internal.cuh"
 #include "ssc_tc_ptx.cuh"
 
 namespace ssc {
-
-int conv_fwd_tf32_ts(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
-                     const int32_t *nbr, int n_out, float *out, int32_t *status, cudaStream_t st);
-int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st);
-int conv_fwd_tf32_wide(const float *staged, int c_pad, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
-                       int n_out, float *out, int32_t *status, const int32_t *n_out_dev, cudaStream_t st);
-int conv_fwd_tf32_gather4(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
-                          const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch,
-                          size_t scratch_bytes, cudaStream_t st);
 
 constexpr int TC_M = 128;
 constexpr int TC_SLAB = 32;            // tf32 elements per 128-byte operand row
@@ -59,6 +48,7 @@ struct TcParams {
   int k_groups;   // ceil(k_slabs / sps) = steps per kernel offset
   int nt_cta;     // N tiles handled by one CTA: n_tiles, or 1 when the N tiles are spread over gridDim.y
   int n_cta;      // nt_cta * tile_n: accumulator columns / filter-slab rows per CTA
+  int fmt16;      // 16-bit operands: 0 = fp16, 1 = bf16 (operand format field of the instruction descriptor)
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
@@ -76,14 +66,10 @@ static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
   p.tmem_cols = 32;
   while (p.tmem_cols < p.n_cta) p.tmem_cols <<= 1;
   p.b_bytes = p.n_cta * 128;
-  // Two slabs per step (SSC_TC_SPS=2) halve the per-step work that does not move data (neighbour
-  // look-ups, row masks, barrier hand-shakes) but also the resident CTAs; measured slower on the
-  // 64 -> 76 channel layer (0.21 vs 0.18 ms), so one slab per step is the default.
+  // One 32-channel slab per step: two slabs per step halve the per-step bookkeeping but also the
+  // resident CTAs, and measured slower (0.21 vs 0.18 ms on the 64 -> 76 channel layer).
   p.sps = 1;
-  if (const char *e = getenv("SSC_TC_SPS")) {
-    int v = atoi(e);
-    if (v == 1 || (v == 2 && p.k_slabs >= 2 && p.nt_cta == p.n_tiles)) p.sps = v;
-  }
+  p.fmt16 = 0;
   p.k_groups = (p.k_slabs + p.sps - 1) / p.sps;
   int stage = p.sps * (TC_A_BYTES + p.b_bytes);
   int fixed = TC_CTRL_BYTES + 1024;
@@ -92,24 +78,11 @@ static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
   int ctas = 512 / p.tmem_cols;
   if (ctas > 4) ctas = 4;
   while (ctas > 1 && ((227 * 1024) / ctas - 1024 - fixed) / stage < 2) --ctas;
-  if (const char *e = getenv("SSC_TC_CTAS_PER_SM")) {
-    int v = atoi(e);
-    if (v >= 1 && v <= ctas) ctas = v;
-  }
   p.stages = ((227 * 1024) / ctas - 1024 - fixed) / stage;
   if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
-  if (const char *e = getenv("SSC_TC_STAGES")) {
-    int v = atoi(e);
-    if (v >= 2 && v <= p.stages) p.stages = v;
-  }
   if (p.stages < 2) return false;
-  // producer warps: one per slot with four or more slots, else the slots' rows are split over four
-  // warps (SSC_TC_PROD_WARPS=8: over eight)
+  // producer warps: one per slot with four or more slots, else the slots' rows are split over four warps
   p.n_prod = p.stages < TC_EPI_WARPS ? (TC_EPI_WARPS / p.stages) * p.stages : p.stages;
-  if (const char *e = getenv("SSC_TC_PROD_WARPS")) {
-    int v = atoi(e);
-    if (v == 8 && p.stages == 2) p.n_prod = 8;
-  }
   p.threads = ((p.n_prod > TC_EPI_WARPS ? p.n_prod : TC_EPI_WARPS) + 1) * 32;
   return true;
 }
@@ -123,29 +96,6 @@ bool tc_operand_layout(int c_in, int c_out, int *k_slabs, int *n_pad, int *tile_
   *tile_n = p.tile_n;
   *n_tiles = p.n_tiles;
   return true;
-}
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async16_cg(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Wait until at most n of this thread's most recent copy groups are still in flight.
-__device__ __forceinline__ void cp_async_wait(int n) {
-  switch (n) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-  }
 }
 
 // Filter packing: filters [K, c_in, c_out] fp32 -> [K][k_slabs][n_pad rows][32 tf32] in the
@@ -402,8 +352,9 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
     // ================================ MMA issuer ============================================
     // The issuing thread is the serial bottleneck of the pipeline, so its loop is kept to a
     // handful of instructions: slot index, parity and descriptor halves are running values.
-    // fp32 accumulator; operand formats 2 = TF32, 0 = fp16
-    const uint32_t idesc = (1u << 4) | ((F16 ? 0u : 2u) << 7) | ((F16 ? 0u : 2u) << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+    // fp32 accumulator; operand formats: kind::tf32 2 = TF32; kind::f16 0 = fp16, 1 = bf16
+    const uint32_t fmt = F16 ? (uint32_t)p.fmt16 : 2u;
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.tile_n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
     const uint32_t a_lo0 = desc_lo(smem_base), slot_step = (uint32_t)stage_bytes >> 4, n_step = (uint32_t)(p.tile_n * 128) >> 4;
     const uint32_t fulla0 = smem_u32(fulla_bars), empty0 = smem_u32(empty_bars);
     uint32_t s = 0, par = 0, a_lo = a_lo0;
@@ -481,6 +432,9 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       }
     }
   }
+  // a wait gave up: the instructions already issued still arrive on done_bar (committed above on
+  // every path); let them retire before the accumulators are handed back
+  if (warp == mma_warp && lane == 0 && *abort_flag && n_iter > 0) mbar_wait_drain(smem_u32(done_bar), 0u);
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag && status) atomicOr(status, 16);
@@ -494,9 +448,10 @@ static size_t tc_smem_bytes(const TcParams &p) {
   return (size_t)p.stages * p.sps * (TC_A_BYTES + p.b_bytes) + 1024 /*alignment slack*/ + TC_CTRL_BYTES;
 }
 
-// fp16 operands: filters [K, c_in, c_out] fp32 -> [K][k_slabs][n_pad rows][64 fp16], same swizzle
-// (a 16-byte chunk holds 8 input channels).
-__global__ void pack_filters_f16_kernel(const float *__restrict__ filters, int K, int c_in, int c_out, TcParams p,
+// 16-bit operands: filters [K, c_in, c_out] fp32 -> [K][k_slabs][n_pad rows][64 fp16 or bf16], same
+// swizzle (a 16-byte chunk holds 8 input channels).
+template <bool BF16>
+__global__ void pack_filters_16_kernel(const float *__restrict__ filters, int K, int c_in, int c_out, TcParams p,
                                         uint4 *__restrict__ packed) {
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = (long long)K * p.k_slabs * p.n_pad * 8;
@@ -516,126 +471,62 @@ __global__ void pack_filters_f16_kernel(const float *__restrict__ filters, int K
       int ci = slab * 64 + chunk * 8 + q * 2 + h;
       f[h] = (ci < c_in && n < c_out) ? filters[((size_t)kappa * c_in + ci) * c_out + n] : 0.f;
     }
-    v[q] = pack_f16x2(f[0], f[1]);
+    v[q] = BF16 ? pack_bf16x2(f[0], f[1]) : pack_f16x2(f[0], f[1]);
   }
   size_t block = ((size_t)kappa * p.k_slabs + slab) * (size_t)(p.n_pad * 8);
   size_t off = (size_t)(n >> 3) * 64 + (size_t)(n & 7) * 8 + (size_t)(chunk ^ (n & 7));
   packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-// features [n_in, c_in] fp32 -> staged [n_in + 1, c_pad] fp16 (round to nearest, finite values
-// beyond the fp16 range saturate), c_pad = c_in rounded up to 8, padding and last row zero.
-__global__ void stage_features_f16_kernel(const float *__restrict__ in, long long n_rows, int c_in, int c_pad,
-                                          long long total_pairs, uint32_t *__restrict__ out) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long step = (long long)gridDim.x * blockDim.x;
-  const int pairs = c_pad >> 1;
-  for (; i < total_pairs; i += step) {
-    const long long r = i / pairs;
-    const int c = (int)(i - r * pairs) * 2;
-    float a = 0.f, b = 0.f;
-    if (r < n_rows) {
-      if (c < c_in) a = __ldg(in + r * c_in + c);
-      if (c + 1 < c_in) b = __ldg(in + r * c_in + c + 1);
-    }
-    out[i] = pack_f16x2(a, b);
-  }
-}
-
-// Width of an fp16 row in 4-byte units (rows are padded to 16 bytes): the kernel gathers it like
-// an fp32 image of that many channels.
-static inline int f16_row_words(int c_in) { return ((c_in + 7) & ~7) / 2; }
-
-size_t conv_f16_scratch_bytes(int n_in, int c_in) { return ((size_t)n_in + 1) * (size_t)f16_row_words(c_in) * 4; }
-
-int stage_features_f16(const float *features, int n_in, int c_in, void *staged, cudaStream_t st) {
-  const int words = f16_row_words(c_in);
-  const long long total_pairs = ((long long)n_in + 1) * words;
-  int blocks = ceil_div(total_pairs, 256 * 4);
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (blocks > sms * 16) blocks = sms * 16;
-  { stage_features_f16_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, words * 2, total_pairs, (uint32_t *)staged); note_launches(1); }
-  SSC_CHECK_LAUNCH("stage_features_f16");
-  return SSC_OK;
-}
-
-int conv_fwd_f16(const float *features, int n_in, int c_in, const void *packed, int K, int c_out, const int32_t *nbr,
-                 int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,
-                 const int32_t *order, bool prestaged, cudaStream_t st) {
-  if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(fp16): kernel volume %d > 256", K);
+int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void *packed, int K, int c_out,
+                const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
+                const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
+  if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): kernel volume %d > 256", K);
   const int words = f16_row_words(c_in);
   if (scratch == nullptr || scratch_bytes < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
-    return fail(SSC_ERR_INVALID, "conv_fwd(fp16): needs the staging buffer of ssc_conv_scratch_bytes (16-byte aligned)");
+    return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): needs the staging buffer of ssc_conv_scratch_bytes (16-byte aligned)");
   int grid = ceil_div(n_out, TC_M);
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   TcParams p;
   if (!tc_params(words, c_out, p, grid < 2 * sms))
-    return fail(SSC_ERR_INVALID, "conv_fwd(fp16): c_out %d / kernel volume %d not supported", c_out, K);
+    return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): c_out %d / kernel volume %d not supported", c_out, K);
+  p.fmt16 = bf16 ? 1 : 0;
   if (!prestaged) {
-    int rc = stage_features_f16(features, n_in, c_in, scratch, st);
+    int rc = stage_features_16(features, n_in, c_in, bf16, scratch, st);
     if (rc != SSC_OK) return rc;
   }
   const size_t smem = tc_smem_bytes(p);
   auto kernel = conv_fwd_tf32_kernel<true, true>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(fp16): smem attribute: %s", cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(16-bit): smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid2(grid, p.n_tiles / p.nt_cta);
   { kernel<<<grid2, p.threads, smem, st>>>((const float *)scratch, words, (const uint4 *)packed, K, c_out, nbr, n_out, out, status, p, n_out_dev, order); note_launches(1); }
-  SSC_CHECK_LAUNCH("conv_fwd_f16");
+  SSC_CHECK_LAUNCH("conv_fwd_16");
   return SSC_OK;
 }
 
-// Smallest problem (in 128-row tiles) the persistent gather4 kernel is used for by default: below
-// this the one-tile-per-CTA kernel spreads the work over more SMs.
-constexpr int kGather4MinTiles = 296;
-// Smallest problem for which the extra staging launch pays for itself.
+// Smallest problem (in 128-row tiles) for which the extra staging launch pays for itself.
 constexpr int kStagingMinTiles = 64;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
                   const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
   TcParams p;
-  // Three variants share the packed filter image.  SSC_TC_VARIANT = gather4 | smem | tmem forces
-  // one (where the shape allows); by default large problems take the persistent TMA-gather
-  // kernel when the caller supplied its staging buffer, the others the shared-memory kernel.
-  const char *variant = getenv("SSC_TC_VARIANT");
-  const bool force_g4 = variant != nullptr && strcmp(variant, "gather4") == 0;
-  if (force_g4 && n_out_dev == nullptr && order == nullptr && !prestaged) {
-    int rc = conv_fwd_tf32_gather4(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, scratch,
-                                   scratch_bytes, st);
-    if (rc >= 0) return rc;
-  }
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
-  if (variant != nullptr && strcmp(variant, "tmem") == 0 && n_out_dev == nullptr && order == nullptr) {
-    int rc = conv_fwd_tf32_ts(features, n_in, c_in, packed, K, c_out, nbr, n_out, out, status, st);
-    if (rc >= 0) return rc;
-  }
   int grid = ceil_div(n_out, TC_M);
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const char *no_split = getenv("SSC_TC_NO_NSPLIT");
-  const bool split_n = grid < 2 * sms && no_split == nullptr;   // few row tiles: spread the N tiles over CTAs too
+  const bool split_n = grid < 2 * sm_count();   // few row tiles: spread the N tiles over CTAs too
   if (!tc_params(c_in, c_out, p, split_n)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
   size_t smem = tc_smem_bytes(p);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).
   const int c_pad = (c_in + 3) & ~3;  // row stride of the staged image (zero-padded channels)
-  const size_t stage_need = ((size_t)n_in + 1) * (size_t)c_pad * sizeof(float);
-  const char *no_stage = getenv("SSC_TC_NO_STAGING");
-  const bool force_wide = variant != nullptr && strcmp(variant, "wide") == 0;
+  const size_t stage_need = conv_tf32_scratch_bytes(n_in, c_in);
   const bool fits = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0;
   if (prestaged && !fits) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): SSC_CONV_PRESTAGED without the staged image in scratch");
-  const bool staged = fits && (prestaged || ((grid >= kStagingMinTiles || force_wide) && no_stage == nullptr));
-  if (staged) {
-    int rc = prestaged ? SSC_OK : stage_features(features, n_in, c_in, scratch, st);
+  const bool staged = fits && (prestaged || grid >= kStagingMinTiles);
+  if (staged && !prestaged) {
+    int rc = stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
-    // persistent variant: several row tiles per pass share every filter slab
-    if (force_wide && order == nullptr) {
-      rc = conv_fwd_tf32_wide((const float *)scratch, c_pad, c_in, packed, K, c_out, nbr, n_out, out, status, n_out_dev, st);
-      if (rc >= 0) return rc;
-    }
   }
   auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -651,26 +542,26 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
 
 using namespace ssc;
 
+static bool is16(int precision) { return precision == SSC_PREC_F16 || precision == SSC_PREC_BF16; }
+
 extern "C" size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision) {
-  if ((precision != SSC_PREC_TF32 && precision != SSC_PREC_F16) || K < 1 || c_in < 1 || c_out < 1) return 0;
+  if ((precision != SSC_PREC_TF32 && !is16(precision)) || K < 1 || c_in < 1 || c_out < 1) return 0;
   TcParams p;
-  if (!tc_params(precision == SSC_PREC_F16 ? f16_row_words(c_in) : c_in, c_out, p)) return 0;
+  if (!tc_params(is16(precision) ? f16_row_words(c_in) : c_in, c_out, p)) return 0;
   return (size_t)K * p.k_slabs * p.n_pad * 128;
 }
 
 extern "C" int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision, void *packed,
                                      void *stream) {
-  SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16, "conv_pack_filters: only SSC_PREC_TF32 and SSC_PREC_F16 have a packed form");
+  SSC_REQUIRE(precision == SSC_PREC_TF32 || is16(precision), "conv_pack_filters: only SSC_PREC_TF32, SSC_PREC_F16 and SSC_PREC_BF16 have a packed form");
   SSC_REQUIRE(filters && packed && K >= 1 && c_in >= 1 && c_out >= 1, "conv_pack_filters: bad arguments");
   TcParams p;
-  SSC_REQUIRE(tc_params(precision == SSC_PREC_F16 ? f16_row_words(c_in) : c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
+  SSC_REQUIRE(tc_params(is16(precision) ? f16_row_words(c_in) : c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
   long long total = (long long)K * p.k_slabs * p.n_pad * 8;
-  if (precision == SSC_PREC_F16) {
-    { pack_filters_f16_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
-    SSC_CHECK_LAUNCH("pack_filters_f16");
-    return SSC_OK;
-  }
-  { pack_filters_tf32_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
-  SSC_CHECK_LAUNCH("pack_filters_tf32");
+  const int blocks = ceil_div(total, 256);
+  if (precision == SSC_PREC_F16) { pack_filters_16_kernel<false><<<blocks, 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
+  else if (precision == SSC_PREC_BF16) { pack_filters_16_kernel<true><<<blocks, 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
+  else { pack_filters_tf32_kernel<<<blocks, 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }
+  SSC_CHECK_LAUNCH("pack_filters");
   return SSC_OK;
 }

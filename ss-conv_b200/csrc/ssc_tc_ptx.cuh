@@ -35,6 +35,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+// Bounded wait used on the way out after another wait has already given up: it neither reads nor
+// sets the abort flag.  Lets work that is still in flight (tensor-core instructions, bulk copies)
+// finish before tensor memory is freed and the CTA exits.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (kSpinLimit >> 2); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
 // Warp-collective bounded wait: lane 0 polls (one shared-memory access per poll instead of
 // 32), the outcome is broadcast.  Must be called by all 32 lanes.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -98,8 +108,26 @@ __device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
   asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
 }
-// .ca: a lane fetches the eight 16-byte chunks of one 128-byte row with eight copies; letting
-// them allocate in L1 turns seven of the eight into L1 hits.
+// Two floats -> two bf16 in one word (lo = a), round to nearest even.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bulk asynchronous copy global -> shared; completes `bytes` on the mbarrier.  Both addresses
+// 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// out[0..3] += v (one 16-byte reduction at L2; address 16-byte aligned)
+__device__ __forceinline__ void red_add_v4(float *p, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 
 // Shared-memory operand descriptor split into its two 32-bit halves.  The high half is the same
 // for every K-major, 128-byte-swizzled operand; the low half is (address >> 4) | (1 << 16), so
@@ -144,16 +172,41 @@ __device__ __forceinline__ void mma_f16_ss_masked(uint32_t tmem_c, uint32_t a_lo
       : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(1u), "r"(kDescHi), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
       : "memory");
 }
-// Same with the A operand read from tensor memory (lane = row, one 32-bit column per element).
-__device__ __forceinline__ void mma_tf32_ts_lo(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A * B with 16-bit operands (kind::f16: fp16 or bf16, chosen by the instruction
+// descriptor), 16 elements = 32 bytes along K per instruction.
+__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
       "mov.b64 db, {%2, %5};\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}"
       :
-      : "r"(tmem_c), "r"(tmem_a), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "r"(0u)
+      : "r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "r"(0u)
       : "memory");
 }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16_cg(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Wait until at most n of this thread's most recent copy groups are still in flight.
+__device__ __forceinline__ void cp_async_wait(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+  }
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 }  // namespace ssc

@@ -301,7 +301,9 @@ three_nn_kernel(int n, int m, const float4 *__restrict__ unknown, const float4 *
         float4 k = tile[i];
         if (k.x != u.x) continue;
         float dx = __fsub_rn(u.y, k.y), dy = __fsub_rn(u.z, k.z), dz = __fsub_rn(u.w, k.w);
-        float d = __fadd_rn(__fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy)), __fmul_rn(dz, dz));
+        // the contraction nvcc applies to the reference's dx*dx + dy*dy + dz*dz
+        // (interpolate_cuda_kernel.cu:39), checked bit for bit against the reference's own kernel
+        float d = __fmaf_rn(dz, dz, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
         if (d < best1) {
           best3 = best2; i3 = i2;
           best2 = best1; i2 = i1;
@@ -329,10 +331,11 @@ __global__ void three_interpolate_kernel(int c, int n, const float *__restrict__
   int p = (int)(t / c), ch = (int)(t - (long long)p * c);
   float w0 = weight[p * 3 + 0], w1 = weight[p * 3 + 1], w2 = weight[p * 3 + 2];
   int i0 = idx[p * 3 + 0], i1 = idx[p * 3 + 1], i2 = idx[p * 3 + 2];
-  float a = __fmul_rn(w0, __ldg(points + (size_t)i0 * c + ch));
+  // w0*p0 + w1*p1 + w2*p2 as nvcc contracts it in the reference (interpolate_cuda_kernel.cu:100),
+  // checked bit for bit against the reference's own kernel
   float b = __fmul_rn(w1, __ldg(points + (size_t)i1 * c + ch));
-  float d = __fmul_rn(w2, __ldg(points + (size_t)i2 * c + ch));
-  out[t] = __fadd_rn(__fadd_rn(a, b), d);
+  float a = __fmaf_rn(w0, __ldg(points + (size_t)i0 * c + ch), b);
+  out[t] = __fmaf_rn(w2, __ldg(points + (size_t)i2 * c + ch), a);
 }
 
 }  // namespace ssc

@@ -20,7 +20,7 @@
 // warp 4: tensor-memory allocation and the MMA-issuing thread.  The partial tiles of the row
 // ranges are added by wgrad_reduce_kernel in a fixed order (bitwise repeatable).
 // Every wait is bounded (status bit 16 on expiry).
-#include "ssc_common.cuh"
+#include "ssc_conv_internal.cuh"
 #include "ssc_scan.cuh"
 #include "ssc_tc_ptx.cuh"
 
@@ -222,6 +222,8 @@ conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *
       }
     }
   }
+  // a wait gave up: what was issued still arrives on done_bar (committed on every path); let it retire
+  if (warp == 4 && lane == 0 && *abort_flag && n_chunks > 0) mbar_wait_drain(smem_u32(done_bar), 0u);
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag && status) atomicOr(status, 16);
@@ -230,10 +232,57 @@ conv_wgrad_tc_kernel(const float *__restrict__ features, int c_in, const float *
   }
 }
 
-size_t conv_wgrad_tc_list_bytes(int K, int n_out) {
+size_t pair_lists_bytes(int K, int n_out) {
   const size_t wpr = (size_t)ceil_div(n_out > 0 ? n_out : 1, 32), words = (size_t)K * wpr;
   auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
   return 2 * al(words * 4) + al((words / 1024 + 2) * 4) + 2 * al((size_t)K * n_out * 4) + al((size_t)(K + 1) * 4);
+}
+size_t conv_wgrad_tc_list_bytes(int K, int n_out) { return pair_lists_bytes(K, n_out); }
+
+namespace {
+struct ListPlan {
+  uint32_t *bitmap, *prefix, *block_sums;
+  int32_t *pair_out, *pair_in, *starts;
+  int wpr;
+  long long words;
+};
+ListPlan plan_lists(void *lists, int K, int n_out) {
+  ListPlan p;
+  p.wpr = ceil_div(n_out > 0 ? n_out : 1, 32);
+  p.words = (long long)K * p.wpr;
+  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  uint8_t *sp = (uint8_t *)lists;
+  p.bitmap = (uint32_t *)sp;
+  sp += al((size_t)p.words * 4);
+  p.prefix = (uint32_t *)sp;
+  sp += al((size_t)p.words * 4);
+  p.block_sums = (uint32_t *)sp;
+  sp += al(((size_t)p.words / 1024 + 2) * 4);
+  p.pair_out = (int32_t *)sp;
+  sp += al((size_t)K * n_out * 4);
+  p.pair_in = (int32_t *)sp;
+  sp += al((size_t)K * n_out * 4);
+  p.starts = (int32_t *)sp;
+  return p;
+}
+}  // namespace
+
+PairLists pair_lists_view(void *lists, int K, int n_out) {
+  const ListPlan p = plan_lists(lists, K, n_out);
+  return PairLists{p.pair_out, p.pair_in, p.starts};
+}
+
+// bitmap of the table, popcount scan, scatter: three small launches
+int pair_lists_build(const int32_t *nbr, int K, int n_out, void *lists, PairLists *out, cudaStream_t st) {
+  const ListPlan p = plan_lists(lists, K, n_out);
+  { pair_bitmap_kernel<<<ceil_div(p.words * 32, 256), 256, 0, st>>>(nbr, K, n_out, p.wpr, p.bitmap); note_launches(1); }
+  SSC_CHECK_LAUNCH("pair_bitmap");
+  int rc = exclusive_scan_u32<true>(p.bitmap, p.words, p.prefix, p.block_sums, p.starts + K, nullptr, st);
+  if (rc != 0) return rc;
+  { pair_scatter_kernel<<<ceil_div(p.words * 32, 256), 256, 0, st>>>(nbr, K, n_out, p.wpr, p.bitmap, p.prefix, p.pair_out, p.pair_in, p.starts); note_launches(1); }
+  SSC_CHECK_LAUNCH("pair_scatter");
+  if (out) *out = PairLists{p.pair_out, p.pair_in, p.starts};
+  return SSC_OK;
 }
 
 // returns -1 when the shape is not covered (the caller then uses the CUDA-core kernel)
@@ -242,8 +291,7 @@ int conv_wgrad_tc(const float *features, int c_in, const float *out_grad, int c_
   const int n_pad = (c_in + 15) & ~15;
   if (n_pad > 256) return -1;
   // as many ranges per offset as fit one wave of two resident CTAs per SM (never more than the scratch holds)
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   int splits = (2 * sms) / (K * ceil_div(c_out, WT_M));
   if (splits > max_splits) splits = max_splits;
   const int most = ceil_div(n_out, WT_K);   // a range is at least one chunk
@@ -254,32 +302,13 @@ int conv_wgrad_tc(const float *features, int c_in, const float *out_grad, int c_
   while ((int)tmem_cols < n_pad) tmem_cols <<= 1;
   const size_t smem = (size_t)WT_STAGES * (WT_A_BYTES + n_pad * 128) + 1024 + 256;
   if (smem > 227 * 1024) return -1;
-  // ---- pair lists
-  const int wpr = ceil_div(n_out, 32);
-  const long long words = (long long)K * wpr;
-  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  uint8_t *sp = (uint8_t *)lists;
-  uint32_t *bitmap = (uint32_t *)sp;
-  sp += al((size_t)words * 4);
-  uint32_t *prefix = (uint32_t *)sp;
-  sp += al((size_t)words * 4);
-  uint32_t *block_sums = (uint32_t *)sp;
-  sp += al(((size_t)words / 1024 + 2) * 4);
-  int32_t *pair_out = (int32_t *)sp;
-  sp += al((size_t)K * n_out * 4);
-  int32_t *pair_in = (int32_t *)sp;
-  sp += al((size_t)K * n_out * 4);
-  int32_t *starts = (int32_t *)sp;
-  { pair_bitmap_kernel<<<ceil_div(words * 32, 256), 256, 0, st>>>(nbr, K, n_out, wpr, bitmap); note_launches(1); }
-  SSC_CHECK_LAUNCH("pair_bitmap");
-  int rc = exclusive_scan_u32<true>(bitmap, words, prefix, block_sums, starts + K, nullptr, st);
-  if (rc != 0) return rc;
-  { pair_scatter_kernel<<<ceil_div(words * 32, 256), 256, 0, st>>>(nbr, K, n_out, wpr, bitmap, prefix, pair_out, pair_in, starts); note_launches(1); }
-  SSC_CHECK_LAUNCH("pair_scatter");
+  PairLists pl;
+  int rc = pair_lists_build(nbr, K, n_out, lists, &pl, st);
+  if (rc != SSC_OK) return rc;
   cudaError_t e = cudaFuncSetAttribute(conv_wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_wgrad(tf32): smem attribute: %s", cudaGetErrorString(e));
   dim3 grid(splits, K, ceil_div(c_out, WT_M));
-  { conv_wgrad_tc_kernel<<<grid, WT_THREADS, smem, st>>>(features, c_in, out_grad, c_out, pair_out, pair_in, starts, n_pad,
+  { conv_wgrad_tc_kernel<<<grid, WT_THREADS, smem, st>>>(features, c_in, out_grad, c_out, pl.pair_out, pl.pair_in, pl.starts, n_pad,
                                                       tmem_cols, partial, status); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_wgrad_tc");
   return SSC_OK;

@@ -16,7 +16,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # SSCONV_B200_LIB selects another build of the same library (e.g. a debug build)
 LIB_PATH = os.environ.get("SSCONV_B200_LIB", os.path.join(_HERE, "libssconv_b200.so"))
 
-PREC_FP32, PREC_TF32, PREC_F16 = 0, 1, 2
+PREC_FP32, PREC_TF32, PREC_F16, PREC_BF16 = 0, 1, 2, 3
+_PREC_OF = {"tf32": PREC_TF32, "fp16": PREC_F16, "bf16": PREC_BF16}
 _precision = os.environ.get("SSCONV_PRECISION", "auto")
 
 c_int, c_size_t, c_void_p, c_float = ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_float
@@ -48,6 +49,11 @@ SIGNATURES = {
     "ssc_conv_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ssc_conv_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                              c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ssc_conv_pairs_list_bytes": (c_size_t, [c_int, c_int]),
+    "ssc_conv_pairs_supported": (c_int, [c_int, c_int, c_int]),
+    "ssc_conv_pairs_build": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "ssc_conv_fwd_pairs": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t, c_int, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_nbr_transpose": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "ssc_nbr_row_order_scratch_bytes": (c_size_t, [c_int, c_int]),
     "ssc_nbr_row_order": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -116,11 +122,12 @@ def kernel_launches():
 def set_precision(mode):
     """'fp32' (exact CUDA-core path), 'tf32' (tcgen05 tensor cores), 'fp16' (tcgen05 with
     fp16 operands: the same 11-bit significand as TF32 but fp16's range, half the gathered
-    bytes and half the tensor-core instructions; opt-in only) or 'auto'
+    bytes and half the tensor-core instructions; opt-in only), 'bf16' (tcgen05 with bfloat16
+    operands: fp32's range, 8 significant bits, the same halved traffic; opt-in only) or 'auto'
     (tf32 when the layer has at least 16 input channels)."""
     global _precision
-    if mode not in ("fp32", "tf32", "fp16", "auto"):
-        raise ValueError("precision must be 'fp32', 'tf32', 'fp16' or 'auto'")
+    if mode not in ("fp32", "tf32", "fp16", "bf16", "auto"):
+        raise ValueError("precision must be 'fp32', 'tf32', 'fp16', 'bf16' or 'auto'")
     _precision = mode
 
 
@@ -482,9 +489,55 @@ def _resolve_precision(c_in, c_out, precision=None):
 
 
 # Layers with fewer output rows do not stage a TF32-rounded copy of their input rows (the extra
-# launch would cost more than it saves), so no staging buffer is allocated for them
-# (SSC_TC_VARIANT=gather4 forces the TMA-gather kernel, which always needs it).
-STAGING_MIN_ROWS = 0 if os.environ.get("SSC_TC_VARIANT") in ("gather4", "wide") else 64 * 128
+# launch would cost more than it saves), so no staging buffer is allocated for them.
+STAGING_MIN_ROWS = 64 * 128
+
+# Which tensor-core kernel a convolution call takes: 'auto' (by shape, see _use_pairs), 'rows' (the
+# output-stationary kernel: one CTA per 128 output rows, bitwise repeatable) or 'pairs' (the
+# pair-list kernel: dense 128-pair tiles per kernel offset, reductions into the output rows).
+_algo = os.environ.get("SSCONV_ALGO", "auto")
+
+
+def set_algo(mode):
+    global _algo
+    if mode not in ("auto", "rows", "pairs"):
+        raise ValueError("algo must be 'auto', 'rows' or 'pairs'")
+    _algo = mode
+
+
+def get_algo():
+    return _algo
+
+
+def _use_pairs(K, c_in, c_out, n_out, prec, algo=None):
+    """The pair-list kernel pays when a row tile of the output-stationary kernel would be mostly
+    absent rows AND the layer is wide enough for the tensor cores to be the limit: many kernel
+    offsets (a 5^3 submanifold kernel at 10 % occupancy fills a tenth of its table) and at least
+    128 x 128 channels.  Narrow 3^3 layers stay output-stationary (their bound is the gather)."""
+    algo = algo or _algo
+    if algo == "rows" or not lib().ssc_conv_pairs_supported(int(c_in), int(c_out), int(prec)):
+        return False
+    if algo == "pairs":
+        return True
+    return K >= 64 and c_in >= 128 and c_out >= 128 and n_out >= 8 * 128
+
+
+def pair_lists(nbr):
+    """Compacted per-offset (input row, output row) lists of a neighbour table, kept with the
+    table (layers that share a rulebook share them)."""
+    kept = getattr(nbr, "_ssc_pair_lists", None)
+    if kept is not None:
+        return kept
+    K, n_out = nbr.shape
+    nbytes = int(lib().ssc_conv_pairs_list_bytes(K, n_out))
+    lists = torch.empty(nbytes, dtype=torch.uint8, device=nbr.device)
+    _check(lib().ssc_conv_pairs_build(_p(nbr, torch.int32), K, n_out, _p(lists), nbytes, _stream()))
+    if not torch.cuda.is_current_stream_capturing():
+        try:
+            nbr._ssc_pair_lists = lists
+        except Exception:
+            pass
+    return lists
 
 
 PRESTAGED = 0x100
@@ -540,11 +593,11 @@ def conv_prepare(features, filters, precision=None):
         return False
     K, c_in, c_out = flt.shape
     mode = _resolve_precision(c_in, c_out, precision)
-    if mode not in ("tf32", "fp16") or (mode == "fp16" and c_out > 512):
+    if mode not in _PREC_OF or (mode != "tf32" and c_out > 512):
         return False
     if mode == "tf32" and features.shape[0] < STAGING_MIN_ROWS:
         return False
-    prec = PREC_F16 if mode == "fp16" else PREC_TF32
+    prec = _PREC_OF[mode]
     packed = pack_filters(flt, prec)
     nbytes = int(lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device)
@@ -553,10 +606,11 @@ def conv_prepare(features, filters, precision=None):
     return True
 
 
-def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None):
+def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None, algo=None):
     """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch).
     n_out_dev: device word with the exact row count when n_out is only a capacity.
-    row_order: permutation of the output rows from nbr_row_order (same result, fewer steps)."""
+    row_order: permutation of the output rows from nbr_row_order (same result, fewer steps).
+    algo: None (the module setting), 'rows' or 'pairs' (see set_algo)."""
     if filters.dim() != 3:
         filters = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
     K, c_in, c_out = filters.shape
@@ -566,30 +620,25 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
     out = torch.empty((n_out, c_out), dtype=torch.float32, device=features.device)
     mode = _resolve_precision(c_in, c_out, precision)
     st = status_word(features.device)
-    if mode == "fp16" and c_out > 512:
+    if mode in ("fp16", "bf16") and c_out > 512:
         mode = "fp32"
+    if (mode in _PREC_OF and n_out_dev is None and row_order is None and nbr.shape[1] == n_out
+            and _use_pairs(K, c_in, c_out, n_out, _PREC_OF[mode], algo)):
+        return _conv_forward_pairs(features, filters, nbr, n_out, _PREC_OF[mode], out, st)
     ready = None
     if _prepared:   # only the call that directly follows conv_prepare may use what it left
         ready = _prepared.pop((features.data_ptr(), filters.data_ptr()), None)
         _prepared.clear()
-    if ready is not None and ready[0] == (PREC_F16 if mode == "fp16" else PREC_TF32 if mode == "tf32" else -1):
+    if ready is not None and ready[0] == _PREC_OF.get(mode, -1):
         prec, packed, scratch, nbytes = ready
         _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
                                           _p(nbr, torch.int32), int(n_out), prec | PRESTAGED, _p(out), _p(st), _p(scratch),
                                           nbytes, _p(n_out_dev), _p(row_order), _stream()))
-    elif mode in ("tf32", "fp16"):
-        prec = PREC_F16 if mode == "fp16" else PREC_TF32
-        tag = (prec, filters._version)
-        packed = getattr(filters, "_ssc_packed", None)
-        if packed is None or getattr(filters, "_ssc_packed_version", None) != tag:
-            packed = pack_filters(filters.contiguous(), prec)
-            try:
-                filters._ssc_packed = packed
-                filters._ssc_packed_version = tag
-            except Exception:
-                pass
-        # the fp16 kernel always gathers from its staged fp16 image
-        stage = prec == PREC_F16 or n_out >= STAGING_MIN_ROWS
+    elif mode in _PREC_OF:
+        prec = _PREC_OF[mode]
+        packed = _packed_filters(filters, prec)
+        # the 16-bit kernels always gather from their staged image
+        stage = prec != PREC_TF32 or n_out >= STAGING_MIN_ROWS
         nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec) if stage else 0
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
@@ -600,6 +649,41 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
         _check(lib().ssc_conv_fwd(_p(features, torch.float32), features.shape[0], c_in, _p(filters, torch.float32), K,
                                   c_out, _p(nbr, torch.int32), int(n_out), PREC_FP32, _p(out), _p(st), None, 0,
                                   _p(n_out_dev), _stream()))
+    return out
+
+
+def _packed_filters(filters, prec):
+    """Operand image of filters [K, Cin, Cout], kept with the tensor until it changes."""
+    tag = (prec, filters._version)
+    packed = getattr(filters, "_ssc_packed", None)
+    if packed is None or getattr(filters, "_ssc_packed_version", None) != tag:
+        packed = pack_filters(filters.contiguous(), prec)
+        try:
+            filters._ssc_packed = packed
+            filters._ssc_packed_version = tag
+        except Exception:
+            pass
+    return packed
+
+
+def _conv_forward_pairs(features, filters, nbr, n_out, prec, out, st):
+    """The pair-list kernel: staging + (lists, once per table) + strips + one persistent launch."""
+    K, c_in, c_out = filters.shape
+    ready = None
+    if _prepared:
+        ready = _prepared.pop((features.data_ptr(), filters.data_ptr()), None)
+        _prepared.clear()
+    flag = 0
+    if ready is not None and ready[0] == prec:
+        _, packed, scratch, nbytes = ready
+        flag = PRESTAGED
+    else:
+        packed = _packed_filters(filters, prec)
+        nbytes = int(lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device)
+    lists = pair_lists(nbr)
+    _check(lib().ssc_conv_fwd_pairs(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out, _p(lists),
+                                    lists.numel(), int(n_out), prec | flag, _p(out), _p(st), _p(scratch), nbytes, _stream()))
     return out
 
 
@@ -665,8 +749,8 @@ def conv_wgrad(features, out_grad, nbr, precision=None):
     (tensor cores with TF32 operands or exact fp32, chosen like the forward pass)."""
     K, n_out = nbr.shape
     c_in, c_out = features.shape[1], out_grad.shape[1]
-    # the filter gradient has no fp16 form: 'fp16' takes the TF32 kernel
-    mode = PREC_TF32 if _resolve_precision(c_in, c_out, precision) in ("tf32", "fp16") else PREC_FP32
+    # the filter gradient has no 16-bit form: 'fp16' / 'bf16' take the TF32 kernel
+    mode = PREC_TF32 if _resolve_precision(c_in, c_out, precision) in _PREC_OF else PREC_FP32
     d_flt = torch.empty((K, c_in, c_out), dtype=torch.float32, device=features.device)
     nbytes = int(lib().ssc_conv_wgrad_scratch_bytes(K, c_in, c_out, n_out))
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=features.device)
