@@ -22,7 +22,11 @@ def ref_ext_path():
     return os.path.join(OUT, "_ext" + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build(ref_root="/root/reference", force=False, verbose=True):
+def build(ref_root=None, force=False, verbose=True):
+    if ref_root is None:
+        sys.path.insert(0, HERE)
+        from ref_loader import reference_root
+        ref_root = reference_root() or ""
     src = os.path.join(ref_root, "SS_Conv_lib", "src")
     target = ref_ext_path()
     if not os.path.isdir(src):

@@ -12,6 +12,21 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CACHE = {}
 
 
+def reference_root():
+    """Checkout of the reference project: the SSCONV_REFERENCE environment variable, else
+    `reference_path` of BASELINE.json at the repository root, else None.  Only the builder of the
+    checker and the fixture generator need it; nothing that runs on a GPU box reads the checkout."""
+    env = os.environ.get("SSCONV_REFERENCE")
+    if env:
+        return env
+    try:
+        import json
+        with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as f:
+            return json.load(f).get("reference_path")
+    except Exception:
+        return None
+
+
 def ref_ext_path():
     return os.path.join(_HERE, "_ref", "_ext" + sysconfig.get_config_var("EXT_SUFFIX"))
 

@@ -193,8 +193,28 @@ def check_status(device=None):
     v = int(s.item())
     if v != 0:
         s.zero_()
-        raise RuntimeError("ssconv_b200 kernel status 0x%x (1: coordinate out of range, 2: hash full, "
-                           "16: tensor-core pipeline wait ran out)" % v)
+        raise RuntimeError("ssconv_b200 kernel status 0x%x (%s)" % (v, _STATUS_TEXT))
+
+
+_STATUS_TEXT = ("1: coordinate out of range, 2: hash full, 16: a bounded wait inside a tensor-core kernel ran out "
+                "(its output is incomplete)")
+
+
+def raise_on_status(value, device):
+    """Turn a non-zero status word that was read back into an error (and clear it on the device)."""
+    if value:
+        status_word(device).zero_()
+        raise RuntimeError("ssconv_b200 kernel status 0x%x (%s)" % (int(value), _STATUS_TEXT))
+
+
+def read_count(n_dev):
+    """Host value of a device row count.  The per-device status word rides along in the same
+    read-back, so a kernel that gave up (bounded wait, full hash, bad coordinate) surfaces here,
+    where the host waits for the device anyway, instead of handing out partial results."""
+    st = status_word(n_dev.device)
+    n, bad = torch.cat([n_dev.reshape(1), st]).tolist()
+    raise_on_status(bad, n_dev.device)
+    return int(n)
 
 
 # =============================================================================== rulebook
@@ -235,7 +255,7 @@ def build_rulebook(indices, batch_size, out_shape, spatial_shape, ksize, stride,
     geo = (_i3(spatial_shape), _i3(out_shape), _i3(ksize), _i3(stride), _i3(padding), _i3(dilation), int(transpose))
     _check(L.ssc_rulebook_conv_count(_p(indices), n_in, int(batch_size), *geo, _p(n_out_dev), _p(st), _p(scratch),
                                      scratch.numel(), None, _stream()))
-    n_out = int(n_out_dev.item())  # the one host sync of a regular rulebook
+    n_out = read_count(n_out_dev)  # the one host sync of a regular rulebook (the status word comes with it)
     outids = torch.empty((n_out, 4), dtype=torch.int32, device=dev)
     nbr = torch.empty((K, n_out), dtype=torch.int32, device=dev)
     _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, n_out, _p(outids), _p(nbr), _p(pairs),
@@ -380,7 +400,7 @@ class LazyPairs(object):
         """Reads the output count of a rulebook built ahead (one host sync).  Returns it, or None
         when it exceeded the capacity (everything computed from this handle is then invalid)."""
         if self._n_out is None:
-            n = int(self._n_out_dev.item())
+            n = read_count(self._n_out_dev)
             if self._ratio_key is not None:
                 _note_ratio(self._ratio_key, self._n_in, n)
             if n > self.capacity:
@@ -989,7 +1009,7 @@ def point2voxel(points, feats, batch_ids, batch_size, grid, unit, mode, ahead=Fa
     unit3 = _F3(*[float(u) for u in unit])
     _check(L.ssc_p2v_count(_p(points), _p(batch_ids), n, int(batch_size), _i3(grid), unit3, _p(m_dev), _p(st),
                            _p(scratch), scratch.numel(), _stream()))
-    m = n if ahead else int(m_dev.item())
+    m = n if ahead else read_count(m_dev)
     vox = torch.empty((m, 4), dtype=torch.int32, device=dev)
     inverse = torch.empty(n, dtype=torch.int32, device=dev)
     vfeat = torch.empty((m, feats.shape[1]), dtype=torch.float32, device=dev)

@@ -20,7 +20,12 @@ class Dropout(nn.Module):
         n = x.size(0)
         masks = []
         for m, d in self.Rs:
-            keep = x.new_empty(n, m, 1).bernoulli_(1 - self.p) / (1 - self.p)
+            if self.p == 1:        # drop everything / keep everything without dividing by zero
+                keep = x.new_zeros(n, m, 1)
+            elif self.p == 0:
+                keep = x.new_ones(n, m, 1)
+            else:
+                keep = x.new_empty(n, m, 1).bernoulli_(1 - self.p) / (1 - self.p)
             masks.append(keep.expand(n, m, d).reshape(n, m * d))
         input.features = x * torch.cat(masks, dim=1)
         return input

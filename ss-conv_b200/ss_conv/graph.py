@@ -30,13 +30,35 @@ result() makes the outputs safe to use from the caller's stream.
 A producer that can write where it is told needs no copy at all: load(k, f, i) puts a batch into
 the input buffers of recording k once, and submit_loaded(k) replays recording k on what its
 buffers hold, as often as wanted.
+
+GraphedPoints is the same for a chain that starts from a point cloud: the voxelizer (a
+Point2Voxel built with trusted_batch_size, which never waits for the device) is recorded into the
+graph together with the layers behind it, so a batch costs the host three small copies, one graph
+launch and one read-back.
 The reference has no counterpart.
 """
+import contextlib
+import gc
+
 import torch
 
 from . import _ext
 from .sp_ops import tensor as tensor_mod
 from .sp_ops.tensor import PendingRows, SparseTensor
+
+
+@contextlib.contextmanager
+def _no_gc():
+    """Python's cycle collector must not run while a stream is capturing: a collected object whose
+    destructor touches the CUDA runtime (a CUDA graph, a stream) would invalidate the capture."""
+    gc.collect()
+    was = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
 
 
 class _Recording(object):
@@ -61,9 +83,10 @@ class _Recording(object):
         tensor_mod._capture_log = log
         try:
             pinned = torch.empty(256, dtype=torch.int32).pin_memory()
-            with torch.cuda.graph(graph):
+            with _no_gc(), torch.cuda.graph(graph):
                 out = chain.fn(x)
-                counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log])   # input count first
+                # input count first, the kernel status word last: it is read back with the counts
+                counts = torch.cat([self.n] + [r.n_dev.reshape(1) for r in log] + [_ext.status_word(chain.dev)])
                 if counts.shape[0] > pinned.shape[0]:
                     raise RuntimeError("chain with more than %d pending row counts" % (pinned.shape[0] - 1))
                 host_counts = pinned[:counts.shape[0]]
@@ -91,6 +114,7 @@ class _Queued(object):
         rec, chain = self.rec, self.chain
         rec.done.synchronize()                       # this batch only
         counts = rec.host_counts.tolist()
+        _ext.raise_on_status(counts.pop(), chain.dev)    # a kernel of the replay gave up: no partial results
         if any(c > cap for c, cap in zip(counts, rec.caps)):
             chain.stale = True                       # record again (with the raised hints) next time
             chain.fallbacks += 1
@@ -254,3 +278,145 @@ class GraphedChain(object):
                 raise ValueError("batch of %d rows exceeds the graph's input capacity %d" % (x.features.shape[0], self.cap))
             return x.features, x.indices
         return self._launch(rec, exact)
+
+
+class _PointRecording(object):
+    """One capture of voxelizer + chain over fixed-size point buffers."""
+
+    def __init__(self, owner):
+        dev = owner.dev
+        self.pts = torch.zeros((owner.n_points, 3), dtype=torch.float32, device=dev)
+        self.fts = torch.zeros((owner.n_points, owner.channels), dtype=torch.float32, device=dev)
+        self.ids = torch.zeros(owner.n_points, dtype=torch.int32, device=dev)
+        self.graph = None
+        self.out = self.host_counts = self.caps = None
+        self.done = torch.cuda.Event()
+        self.fence = torch.cuda.Event()
+
+    def record(self, owner):
+        log = []
+        graph = torch.cuda.CUDAGraph()
+        l0 = _ext.kernel_launches()
+        tensor_mod._capture_log = log
+        try:
+            pinned = torch.empty(256, dtype=torch.int32).pin_memory()
+            with _no_gc(), torch.cuda.graph(graph):
+                out = owner.fn(owner.p2v(self.pts, self.fts, self.ids)[1])
+                counts = torch.cat([r.n_dev.reshape(1) for r in log] + [_ext.status_word(owner.dev)])
+                if counts.shape[0] > pinned.shape[0]:
+                    raise RuntimeError("chain with more than %d pending row counts" % (pinned.shape[0] - 1))
+                host_counts = pinned[:counts.shape[0]]
+                host_counts.copy_(counts, non_blocking=True)
+        finally:
+            tensor_mod._capture_log = None
+        owner.launches = _ext.kernel_launches() - l0
+        if len(log) == 0:
+            raise RuntimeError("nothing in this chain ran ahead of its row counts (no capacity hints yet?)")
+        self.graph, self.out, self.host_counts, self.caps = graph, out, host_counts, [r.capacity for r in log]
+
+
+class _QueuedPoints(object):
+    def __init__(self, owner, rec, inputs):
+        self.owner, self.rec, self.inputs = owner, rec, inputs
+        self.value, self.finished = None, False
+
+    def result(self):
+        if self.finished:
+            return self.value
+        rec, owner = self.rec, self.owner
+        rec.done.synchronize()
+        counts = rec.host_counts.tolist()
+        _ext.raise_on_status(counts.pop(), owner.dev)
+        if any(c > cap for c, cap in zip(counts, rec.caps)):
+            owner.stale = True
+            owner.fallbacks += 1
+            self.value = owner._eager(*self.inputs, False)
+        else:
+            out = rec.out
+            if isinstance(out, SparseTensor):
+                f, i, _ = out.raw()
+                res = SparseTensor(f[:counts[-1]], i[:counts[-1]], out.spatial_shape, out.batch_size)
+                res.indice_dict, res.grid = out.indice_dict, out.grid
+                out = res
+            self.value = out
+        self.finished, self.inputs = True, None
+        return self.value
+
+
+class GraphedPoints(object):
+    """fn(SparseTensor) -> tensor or SparseTensor, fed by p2v(points, feats, ids).  Every batch has
+    exactly n_points points (p2v was built with trusted_batch_size).  submit() / result() / depth /
+    streams as in GraphedChain; results live in buffers owned by the graph."""
+
+    def __init__(self, p2v, fn, n_points, channels, device, depth=1, streams=1):
+        if p2v.trusted_batch_size is None:
+            raise ValueError("GraphedPoints needs a Point2Voxel built with trusted_batch_size")
+        self.p2v, self.fn, self.dev = p2v, fn, torch.device(device)
+        self.n_points, self.channels, self.depth = int(n_points), int(channels), max(1, int(depth))
+        self.exec_streams = [torch.cuda.Stream(self.dev) for _ in range(int(streams))] if int(streams) > 1 else None
+        self.recs, self.stale, self.turn, self.queued = None, False, 0, []
+        self.launches = self.replays = self.fallbacks = 0
+
+    def _eager(self, points, feats, ids, ahead):
+        old = _ext.AHEAD
+        _ext.AHEAD = ahead
+        try:
+            out = self.fn(self.p2v(points, feats, ids)[1])
+            if isinstance(out, SparseTensor):
+                out.resolve()
+            return out
+        finally:
+            _ext.AHEAD = old
+
+    def _ready(self, points, feats, ids):
+        if self.recs is not None and not self.stale:
+            return
+        for q in self.queued:
+            if q is not None:
+                q.result()
+        self._eager(points, feats, ids, False)       # records the output / input ratio of every layer
+        self._eager(points, feats, ids, True)        # the capacity-sized path once (allocations, cached filters)
+        torch.cuda.synchronize(self.dev)
+        self.recs = [_PointRecording(self) for _ in range(self.depth)]
+        for rec in self.recs:
+            rec.pts.copy_(points)
+            rec.fts.copy_(feats)
+            rec.ids.copy_(ids)
+            rec.record(self)
+        self.queued = [None] * self.depth
+        self.stale, self.turn = False, 0
+
+    def submit(self, points, feats, ids):
+        if points.shape[0] != self.n_points:
+            raise ValueError("batch of %d points, the graph was built for %d" % (points.shape[0], self.n_points))
+        self._ready(points, feats, ids)
+        k = self.turn
+        self.turn = (self.turn + 1) % self.depth
+        old = self.queued[k]
+        if old is not None and not old.finished:
+            old.result()                             # its buffers are about to be overwritten
+        rec = self.recs[k]
+        rec.pts.copy_(points, non_blocking=True)
+        rec.fts.copy_(feats, non_blocking=True)
+        rec.ids.copy_(ids, non_blocking=True)
+        if self.exec_streams is None:
+            rec.graph.replay()
+            rec.done.record()
+        else:
+            stream = self.exec_streams[k % len(self.exec_streams)]
+            cur = torch.cuda.current_stream(self.dev)
+            rec.fence.record(cur)
+            stream.wait_event(rec.fence)
+            torch.cuda.set_stream(stream)
+            try:
+                rec.graph.replay()
+            finally:
+                torch.cuda.set_stream(cur)
+            rec.done.record(stream)
+        self.replays += 1
+        q = _QueuedPoints(self, rec, (points, feats, ids))
+        self.queued[k] = q
+        return q
+
+    def __call__(self, points, feats, ids):
+        return self.submit(points, feats, ids).result()

@@ -48,3 +48,35 @@ def all_gather_rows(local_rows, n_samples, group=None):
     dist.all_gather_into_tensor(gathered, padded, group=group)
     parts = [gathered[r * width:r * width + sizes[r]] for r in range(world)]
     return torch.cat(parts, dim=0)
+
+
+class RowGatherer(object):
+    """all_gather_rows for a loop: the padded send buffer and the gathered receive buffer are
+    allocated once, and with equal shards (n_samples divisible by the world size) the local rows
+    are sent as they are and the receive buffer IS the result (no padding copy, no concatenation).
+    The returned tensor is overwritten by the next call."""
+
+    def __init__(self, n_samples, channels, device, dtype=torch.float32, group=None):
+        self.n, self.group = int(n_samples), group
+        self.on = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        if not self.on:
+            return
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.sizes = [shard_range(self.n, r, self.world)[1] - shard_range(self.n, r, self.world)[0]
+                      for r in range(self.world)]
+        self.width = max(self.sizes)
+        self.even = min(self.sizes) == self.width
+        self.gathered = torch.empty((self.world * self.width, int(channels)), dtype=dtype, device=device)
+        self.padded = None if self.even else torch.zeros((self.width, int(channels)), dtype=dtype, device=device)
+
+    def __call__(self, local_rows):
+        if not self.on:
+            return local_rows
+        if local_rows.shape[0] != self.sizes[self.rank]:
+            raise ValueError("rank %d holds %d rows, expected %d" % (self.rank, local_rows.shape[0], self.sizes[self.rank]))
+        if self.even:
+            dist.all_gather_into_tensor(self.gathered, local_rows.contiguous(), group=self.group)
+            return self.gathered
+        self.padded[:local_rows.shape[0]].copy_(local_rows)
+        dist.all_gather_into_tensor(self.gathered, self.padded, group=self.group)
+        return torch.cat([self.gathered[r * self.width:r * self.width + self.sizes[r]] for r in range(self.world)], dim=0)

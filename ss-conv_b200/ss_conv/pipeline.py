@@ -16,8 +16,9 @@ class HostStream:
 
     host_batches: iterable of tuples of pinned CPU tensors; every tensor's leading dimension may
     vary from batch to batch up to `max_rows`.  Iterating yields, per batch and in order, a tuple
-    of pinned CPU tensors (views into two rotating result buffers: consume or copy a result
-    before asking for the result after next)."""
+    of pinned CPU tensors (views into `depth` rotating result buffers: consume or copy a result
+    before asking for the NEXT one - with depth = 2 the download of the following batch is already
+    queued into the other buffer, and the one after that reuses this one)."""
 
     def __init__(self, step_fn, device, max_rows, depth=2, step_reuses_outputs=False):
         """step_reuses_outputs: the step writes its results into the same device buffers on every

@@ -114,7 +114,7 @@ class SparseTensor(object):
             raise RuntimeError("a row count cannot be read back while a CUDA graph is being recorded: this layer "
                                "needs exact row counts and cannot be part of a captured chain")
         parent_changed = r.parent.resolve() if r.parent is not None else False
-        n = int(r.n_dev.item())
+        n = _ext.read_count(r.n_dev)        # the kernel status word is checked in the same read-back
         if r.note is not None:
             r.note(n)
         self._rows = None

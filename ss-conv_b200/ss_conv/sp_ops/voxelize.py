@@ -48,8 +48,16 @@ class Point2Voxel(nn.Module):
     pipeline (cell bitmap + rank) instead of torch.unique + two kernels.
     """
 
-    def __init__(self, voxel_num_limit=[64, 64, 64], unit_voxel_extent=[0.05, 0.05, 0.05], voxelization_mode=4):
+    def __init__(self, voxel_num_limit=[64, 64, 64], unit_voxel_extent=[0.05, 0.05, 0.05], voxelization_mode=4,
+                 trusted_batch_size=None):
+        """trusted_batch_size (not in the reference): the caller declares that every batch has that
+        many samples, batch ids in [0, trusted_batch_size) and every point inside the grid.  The
+        module then skips the look at the batch that finds this out (one kernel and one host
+        read-back per call) and never waits for the device, so it can be recorded into a CUDA
+        graph.  A point that is outside after all is dropped and reported through the kernel status
+        word (bit 1), which is checked wherever a row count is read back."""
         super().__init__()
+        self.trusted_batch_size = None if trusted_batch_size is None else int(trusted_batch_size)
         self.unit_voxel_extent = torch.tensor(np.array(unit_voxel_extent, dtype=np.float64), dtype=torch.float32)
         self.voxel_num_limit = np.array(voxel_num_limit)
         self.voxelization_mode = voxelization_mode
@@ -65,7 +73,10 @@ class Point2Voxel(nn.Module):
             # the common case - every point inside the grid, batch ids already sorted - needs none of
             # the filtering / unique / sort steps below: one kernel and one read-back find that out
             ids32 = batch_ids.contiguous() if batch_ids.dtype == torch.int32 else batch_ids.int()
-            n_outside, n_down, n_change, last_id = _ext.p2v_stats(point_cloud, ids32, grid_i, unit_f)
+            if self.trusted_batch_size is not None:
+                n_outside, n_down, n_change, last_id = 0, 0, self.trusted_batch_size - 1, self.trusted_batch_size - 1
+            else:
+                n_outside, n_down, n_change, last_id = _ext.p2v_stats(point_cloud, ids32, grid_i, unit_f)
             if n_outside == 0 and n_down == 0 and last_id >= 0:
                 B1 = n_change + 1
                 fts = feature.float().contiguous()

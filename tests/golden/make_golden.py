@@ -13,7 +13,7 @@ J matrices (Common_utils/new_constants.pt, formula of Common_utils/rotation_util
 is installed under that module name; Y_J(x) is taken as sqrt((2J+1)/4pi) * D^J(alpha,beta,0)[:,J].
 Basis fixtures are therefore pinned to that stand-in, not to a genuine lie_learn build.
 
-Usage: python tests/golden/make_golden.py [/root/reference]
+Usage: python tests/golden/make_golden.py [path of the reference checkout]
 """
 import importlib
 import math
@@ -96,7 +96,12 @@ def surface_indices(rng, batch, V, n_pts):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) > 1:
+        ref_root = sys.argv[1]
+    else:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "oracle"))
+        from ref_loader import reference_root
+        ref_root = reference_root()
     ext = install_reference(ref_root)
     os.chdir(tempfile.mkdtemp())  # the reference writes its basis cache under ./cache
     convolution = importlib.import_module("ss_conv.convolution")

@@ -34,6 +34,11 @@ def _worker(rank, world, port, n_samples, out_dir):
         expect = torch.zeros(n_samples, 3)
         expect.index_add_(0, indices[:, 0].long(), feats)
         assert torch.equal(full, expect)
+        # the buffered form used in loops (no padding copy / concatenation for equal shards), twice
+        gather = parallel.RowGatherer(n_samples, 3, pooled.device)
+        for rep in range(2):
+            again = gather(pooled * (rep + 1))
+            assert torch.equal(again, expect * (rep + 1))
         torch.save(full, os.path.join(out_dir, "r%d.pt" % rank))
     finally:
         dist.destroy_process_group()
