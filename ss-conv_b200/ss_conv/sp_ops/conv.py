@@ -117,7 +117,14 @@ class SparseConvolution(nn.Module):
         out_spatial_shape = self._output_shape(spatial_shape)
 
         if self.conv1x1:
-            input.features = torch.mm(features, weight.reshape(self.in_channels, self.out_channels))
+            # one kernel offset whose table is the identity: the same gather-GEMM kernels (and their
+            # backward) as every other convolution, instead of a library GEMM (the reference calls
+            # torch.mm here, sp_ops/conv.py:119-122)
+            n = features.shape[0]
+            rows = torch.arange(n, dtype=torch.int32, device=features.device)
+            pairs = torch.stack([rows, rows]).unsqueeze(0).contiguous()
+            num = torch.full((1,), n, dtype=torch.int32, device=features.device)
+            input.features = indice_subm_conv(features, weight, pairs, num, n)
             if self.bias is not None:
                 input.features += self.bias
             return input

@@ -318,3 +318,94 @@ def test_conv_pair_list_kernel_empty_offsets_and_tiny_inputs(cuda):
             assert rel_err(y, ref) <= TOL["tf32"]
     finally:
         _ext.set_algo("auto")
+
+
+def _sampled_rows_check(cuda, feats, W, nbr, n_out, y, tol, rng, rows=96):
+    """Sampled output rows of a full-size layer against a direct float64 evaluation of their
+    neighbourhoods (the float64 oracle of the whole layer would take minutes on the CPU)."""
+    K, ci, co = W.shape
+    pick = torch.from_numpy(rng.choice(n_out, min(rows, n_out), replace=False)).to(cuda)
+    src = nbr[:, pick]                                                       # [K, rows]
+    gathered = feats.double()[src.clamp(min=0).long()] * (src >= 0).unsqueeze(-1)
+    direct = torch.einsum("kri,kio->ro", gathered, W.double())
+    err = float((y[pick].double() - direct).abs().max() / direct.abs().max())
+    assert err <= tol, err
+    return err
+
+
+def test_cfg2_full_size_sampled_rows_against_float64(cuda):
+    """The headline layer at benchmark size (batch 32, 64^3, 16384 surface points per sample, 64 -> 76
+    channels, k3 s2 p1): sampled output rows of the TF32, bf16 and exact-fp32 paths against float64, and
+    the rulebook's closed-form properties on the same batch."""
+    from ss_conv import _ext
+    from ss_conv.utils import synthetic as S
+    rng = np.random.RandomState(8)
+    ind = S.surface_voxels(range(32), 64, 16384, base_seed=1000)
+    n = ind.shape[0]
+    g = torch.Generator(device="cpu").manual_seed(2)
+    feats = torch.randn(n, 64, generator=g).to(cuda)
+    W = (torch.randn(27, 64, 76, generator=g) / 41.6).to(cuda)
+    outids, pairs, num = gpu_rulebook(ind, 32, [64] * 3, 3, 2, 1, 1, False, cuda)
+    n_out = outids.shape[0]
+    nbr = _ext.neighbour_table(pairs, num, n_out)
+    assert int((nbr >= 0).sum()) == int(num.sum())
+    for prec in ("tf32", "bf16", "fp32"):
+        y = _ext.conv_forward(feats, W, nbr, n_out, prec)
+        _ext.check_status(cuda)
+        _sampled_rows_check(cuda, feats, W, nbr, n_out, y, TOL[prec], rng)
+
+
+def test_cfg3_stages_batch64_sampled_rows_against_float64(cuda):
+    """The four strided stages of the backbone configuration at batch 64 (1024 points per object on a
+    32^3 grid): geometry chained stage to stage, channel counts of the stages, sampled rows against
+    float64 for every stage (the narrow first stage takes the exact fp32 kernel under 'auto')."""
+    from ss_conv import _ext
+    from ss_conv.sp_ops.ops import get_indice_pairs
+    from ss_conv.utils import synthetic as S
+    rng = np.random.RandomState(9)
+    pts, _, ids = S.object_points(range(64), 1024, base_seed=7000)
+    cells = np.floor((pts + 0.5) * 32).astype(np.int64)
+    vox = np.unique(np.concatenate([ids[:, None], cells], 1), axis=0).astype(np.int32)
+    cur = torch.from_numpy(vox).to(cuda)
+    chans = [3, 30 + 6, 60 + 12, 120 + 24, 240 + 48]       # stage outputs carry their gate scalars
+    cin = [3, 30, 60, 120]
+    V = 32
+    g = torch.Generator(device="cpu").manual_seed(3)
+    for st in range(4):
+        outids, pairs, num = get_indice_pairs(cur, 64, [V] * 3, 3, 2, 1, 1, 0, False, False)
+        n_in, n_out = cur.shape[0], outids.shape[0]
+        nbr = _ext.neighbour_table(pairs, num, n_out)
+        feats = torch.randn(n_in, cin[st], generator=g).to(cuda)
+        W = (torch.randn(27, cin[st], chans[st + 1], generator=g) / float(np.sqrt(27 * cin[st]))).to(cuda)
+        for prec in ("auto", "tf32") if cin[st] >= 16 else ("auto",):
+            y = _ext.conv_forward(feats, W, nbr, n_out, prec)
+            _ext.check_status(cuda)
+            tol = TOL["fp32"] if (prec == "auto" and cin[st] < 16) else TOL["tf32"]
+            _sampled_rows_check(cuda, feats, W, nbr, n_out, y, tol, rng)
+        cur, V = outids.contiguous(), V // 2
+    assert V == 2 and cur.shape[0] <= 64 * 8
+
+
+def test_conv1x1_through_the_gather_kernel(cuda):
+    """A 1 x 1 x 1 convolution is the gather-GEMM with one offset and the identity table: it runs
+    through the library's own kernels (no library GEMM on the path)."""
+    from ss_conv import _ext
+    from ss_conv.sp_ops.conv import SparseConvolution
+    from ss_conv.sp_ops.tensor import SparseTensor
+    rng = np.random.RandomState(12)
+    ind = random_voxels(rng, 2, 12, 700)
+    feats = rng.randn(ind.shape[0], 48).astype(np.float32)
+    conv = SparseConvolution(3, 48, 40, 1, bias=False).to(cuda)
+    assert conv.conv1x1
+    with torch.no_grad():
+        conv.weight.copy_(torch.randn_like(conv.weight) / 7)
+    l0 = _ext.kernel_launches()
+    _ext.set_precision("fp32")
+    try:
+        with torch.no_grad():
+            y = conv(SparseTensor(dev(feats, cuda), dev(ind, cuda), [12] * 3, 2)).features.cpu().numpy()
+    finally:
+        _ext.set_precision("auto")
+    assert _ext.kernel_launches() > l0               # the library's kernel ran
+    ref = feats.astype(np.float64) @ conv.weight.detach().cpu().numpy().reshape(48, 40).astype(np.float64)
+    assert rel_err(y, ref) <= TOL["fp32"]

@@ -61,6 +61,13 @@ def test_static_scratch_rulebook_matches_regular_entry_point(cuda):
         assert np.array_equal(nbr_a, nbr_b)          # integer work: bit-exact
         assert np.array_equal(pairs_a, pairs_b)
         assert num_a[len(num_a) // 2] == ind.shape[0]    # centre offset pairs every voxel with itself
+    # exactly at the documented limit: 65 536 active voxels (a 16 x 64 x 64 slab, fully occupied)
+    full = np.stack(np.meshgrid(np.arange(16), np.arange(64), np.arange(64), indexing="ij"), -1).reshape(-1, 3)
+    at_limit = np.concatenate([np.zeros((full.shape[0], 1), dtype=np.int64), full], 1).astype(np.int32)
+    assert at_limit.shape[0] == 65536
+    (nbr_a, pairs_a, num_a), (nbr_b, pairs_b, num_b) = _both(L, _ext, at_limit, 1, [16, 64, 64], [3] * 3, [1, 1, 1], cuda)
+    assert np.array_equal(num_a, num_b) and np.array_equal(nbr_a, nbr_b) and np.array_equal(pairs_a, pairs_b)
+    assert num_a[13] == 65536
     # a request beyond the built-in capacity is refused with a clear message, nothing is launched
     I3 = ctypes.c_int * 3
     rc = L.ssc_rulebook_subm_static(None, 70000, 1, I3(64, 64, 64), I3(3, 3, 3), I3(1, 1, 1), None, None, None, None,
