@@ -45,6 +45,7 @@ constexpr int PL_EPI_WARPS = 8;
 constexpr int PL_STG_ROW = 80;            // bytes per row of the epilogue's transpose block (64 + 16 pad)
 constexpr int PL_STG_BYTES = PL_EPI_WARPS * 32 * PL_STG_ROW;
 constexpr int PL_CTRL_BYTES = 1024;
+constexpr int PL_MAX_CTAS = 320;
 
 struct PlParams {
   int k_slabs;      // 128-byte slabs per operand row
@@ -62,15 +63,25 @@ struct PlParams {
   int f16;          // kind::f16 (fp16 / bf16 operands) instead of kind::tf32
 };
 
-// strips[s] = {virtual offset kv = kappa * n_split + half, first tile r, tile stride c, tiles of the offset}
-// One block of 256 threads, thread k = kernel offset k.  Strip length L = the grid's fair share of
-// all tiles; an offset with T tiles is cut into c = ceil(T / L) interleaved strips (tiles r, r + c, ...).
+// Strip table of one (pair lists, grid) combination.
+//   strips[s] = {virtual offset kv = kappa * n_split + half, first tile, tile stride, number of tiles}
+//   owner[s]  = the CTA that runs strip s (a CTA runs its strips in ascending s)
+//   hdr       = {number of strips, K, n_split, n_ctas}: the table is kept with the pair lists and only
+//               built when the header does not match (another grid or channel split)
+// L = the grid's fair share of all tiles.  An offset with T <= L tiles is one strip; up to 1.5 L it
+// is a main strip of L tiles plus a tail; beyond that it is cut into round(T / L) interleaved strips
+// (tiles r, r + c, ...: the centre offset of a submanifold layer).  Strips then go to the CTAs
+// greedily, main strips first, each to the CTA with the least work so far: every CTA starts with a
+// strip that walks its offset's list from the first row (all CTAs sweep the rows together, which keeps
+// gathers and reductions in L2) and the tails fill the CTAs whose offsets were short.
 __global__ void pl_strips_kernel(const int32_t *__restrict__ starts, int K, int n_split, int n_ctas,
-                                 int4 *__restrict__ strips, int32_t *__restrict__ n_strips) {
+                                 int32_t *__restrict__ hdr, int4 *__restrict__ strips, int32_t *__restrict__ owner) {
   __shared__ int tiles[256];
   __shared__ int first[257];
+  __shared__ int load_s[PL_MAX_CTAS];
   __shared__ long long L_s;
   const int tid = threadIdx.x;
+  if (hdr[0] > 0 && hdr[1] == K && hdr[2] == n_split && hdr[3] == n_ctas) return;   // built before for this grid
   int T = 0;
   if (tid < K) {
     const int n = starts[tid + 1] - starts[tid];
@@ -82,13 +93,18 @@ __global__ void pl_strips_kernel(const int32_t *__restrict__ starts, int K, int 
     long long tot = 0;
     for (int k = 0; k < K; ++k) tot += tiles[k];
     tot *= n_split;
-    long long L = (tot + n_ctas - 1) / n_ctas;
+    const long long L = (tot + n_ctas - 1) / n_ctas;
     L_s = L < 1 ? 1 : L;
   }
   __syncthreads();
-  const long long L = L_s;
-  const int c = T > 0 ? (int)((T + L - 1) / L) : 0;
-  tiles[tid] = c * n_split;           // strips of this offset
+  const int L = (int)L_s;
+  int mains = 0, tail = 0;
+  if (T > 0) {
+    if (T > L + L / 2) mains = (T + L / 2) / L;
+    else { mains = 1; tail = T > L ? 1 : 0; }
+  }
+  __syncthreads();
+  tiles[tid] = (mains + tail) * n_split;
   __syncthreads();
   if (tid == 0) {
     int s = 0;
@@ -96,13 +112,53 @@ __global__ void pl_strips_kernel(const int32_t *__restrict__ starts, int K, int 
       first[k] = s;
       s += tiles[k];
     }
-    *n_strips = s;
+    first[256] = s;
   }
   __syncthreads();
-  if (tid < K && c > 0) {
+  const int n_strips = first[256];
+  if (tid < K && T > 0) {
     int s = first[tid];
-    for (int h = 0; h < n_split; ++h)
-      for (int r = 0; r < c; ++r) strips[s++] = make_int4(tid * n_split + h, r, c, T);
+    for (int h = 0; h < n_split; ++h) {
+      const int kv = tid * n_split + h;
+      if (mains > 1) {
+        for (int r = 0; r < mains; ++r) { strips[s] = make_int4(kv, r, mains, (T - r + mains - 1) / mains); owner[s++] = -1; }
+      } else {
+        strips[s] = make_int4(kv, 0, 1, T < L ? T : L);
+        owner[s++] = -1;
+        if (tail) { strips[s] = make_int4(kv, L, 1, T - L); owner[s++] = -2; }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < 32) {   // one warp: greedy assignment, main strips (-1) first, then tails (-2)
+    for (int b = tid; b < n_ctas; b += 32) load_s[b] = 0;
+    __syncwarp();
+    for (int pass = -1; pass >= -2; --pass) {
+      for (int s = 0; s < n_strips; ++s) {
+        if (owner[s] != pass) continue;            // warp-uniform
+        int best = 0x7fffffff, arg = 0x7fffffff;
+        for (int b = tid; b < n_ctas; b += 32) {
+          const int v = load_s[b];
+          if (v < best) { best = v; arg = b; }     // ascending b: the lowest index wins ties
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+          const int ob = __shfl_xor_sync(0xffffffffu, best, o), oa = __shfl_xor_sync(0xffffffffu, arg, o);
+          if (ob < best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (tid == 0) {
+          owner[s] = arg;
+          load_s[arg] = best + strips[s].w;
+        }
+        __syncwarp();
+      }
+    }
+    if (tid == 0) {
+      hdr[1] = K;
+      hdr[2] = n_split;
+      hdr[3] = n_ctas;
+      __threadfence();
+      hdr[0] = n_strips;
+    }
   }
 }
 
@@ -111,7 +167,8 @@ __global__ void __launch_bounds__((PL_MAX_STAGES + 1 + PL_EPI_WARPS) * 32, 1)
 conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict__ packed, int c_out,
                       const int32_t *__restrict__ pair_out, const int32_t *__restrict__ pair_in,
                       const int32_t *__restrict__ starts, const int4 *__restrict__ strips,
-                      const int32_t *__restrict__ n_strips_dev, float *__restrict__ out, int32_t *status, PlParams p) {
+                      const int32_t *__restrict__ owner, const int32_t *__restrict__ n_strips_dev,
+                      float *__restrict__ out, int32_t *status, PlParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *w_smem = smem;                                       // resident filters, [k_slabs][n_cta][128 B]
@@ -175,11 +232,12 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
     long long g = 0;
     int scount = 0, w_issued = 0;
     bool alive = true;
-    for (int si = blockIdx.x; si < n_strips && alive; si += gridDim.x, ++scount) {
+    for (int si = 0; si < n_strips && alive; ++si) {
+      if (__ldg(owner + si) != (int)blockIdx.x) continue;
       const int4 sd = __ldg(strips + si);
       const int kappa = sd.x / p.n_split, half = sd.x - kappa * p.n_split;
       const int list0 = __ldg(starts + kappa), n_pairs = __ldg(starts + kappa + 1) - list0;
-      const int n_tiles = (sd.w - sd.y + sd.z - 1) / sd.z;
+      const int n_tiles = sd.w;
       if (warp == 0 && lane == 0) {
         // the strip's filter matrix: one bulk copy per slab, after the MMAs of the last strip retired
         bool ok = true;
@@ -239,6 +297,7 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
         mbar_arrive(smem_u32(full_bars + warp));
       }
       g += n_steps;
+      ++scount;
     }
     // a wait gave up while a filter copy may still be in flight: let it land before the CTA exits
     if (warp == 0 && lane == 0 && *abort_flag && w_issued > 0) mbar_wait_drain(smem_u32(wfull_bar), (uint32_t)(w_issued - 1) & 1u);
@@ -248,9 +307,10 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
       long long g = 0;
       int tcount = 0, scount = 0;
       bool alive = true;
-      for (int si = blockIdx.x; si < n_strips && alive; si += gridDim.x, ++scount) {
+      for (int si = 0; si < n_strips && alive; ++si) {
+        if (__ldg(owner + si) != (int)blockIdx.x) continue;
         const int4 sd = __ldg(strips + si);
-        const int n_tiles = (sd.w - sd.y + sd.z - 1) / sd.z;
+        const int n_tiles = sd.w;
         if (!mbar_wait_backoff(smem_u32(wfull_bar), (uint32_t)scount & 1u, abort_flag, 64)) break;
         tc_fence_after();
         for (int ti = 0; ti < n_tiles && alive; ++ti, ++tcount) {
@@ -276,6 +336,7 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
           if (alive) mma_commit(smem_u32(accf_bars + buf));
         }
         if (alive) mma_commit(smem_u32(wfree_bar));
+        ++scount;
       }
       // everything issued above (on any path) retires before the CTA hands its tensor memory back
       mma_commit(smem_u32(final_bar));
@@ -295,11 +356,12 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
     const int prow = (grp >> 1) + (grp & 1) * 4;           // rows of a pass, ordered so that a quarter-warp reads distinct banks
     int tcount = 0;
     bool alive = true;
-    for (int si = blockIdx.x; si < n_strips && alive; si += gridDim.x) {
+    for (int si = 0; si < n_strips && alive; ++si) {
+      if (__ldg(owner + si) != (int)blockIdx.x) continue;
       const int4 sd = __ldg(strips + si);
       const int kappa = sd.x / p.n_split, half = sd.x - kappa * p.n_split;
       const int list0 = __ldg(starts + kappa), n_pairs = __ldg(starts + kappa + 1) - list0;
-      const int n_tiles = (sd.w - sd.y + sd.z - 1) / sd.z;
+      const int n_tiles = sd.w;
       const int col0 = half * p.n_cta;
       const int cols = min(p.n_cta, c_out - col0);
       const int n_blocks = cols > 0 ? (cols + 31) >> 5 : 0;       // 32-column blocks with real columns
@@ -440,10 +502,9 @@ bool conv_pairs_supported(int c_in, int c_out, int precision) {
   return pl_params(c_in, c_out, precision, p);
 }
 
-size_t conv_pairs_strip_bytes(int K) {
-  // strips <= CTAs of the grid + K * n_split (one partial strip per virtual offset)
-  return ((size_t)(2 * 160 + 8 * K) + 8) * sizeof(int4) + 256;
-}
+static size_t max_strips(int K) { return (size_t)PL_MAX_CTAS + 16 * (size_t)K + 16; }   // mains + tails of K * n_split (<= 8) virtual offsets
+
+size_t conv_pairs_strip_bytes(int K) { return 256 + max_strips(K) * (sizeof(int4) + sizeof(int32_t)); }
 
 // `staged`: the operand image of the feature rows (ssc_conv_stage); `strip_mem`: conv_pairs_strip_bytes(K) bytes.
 int conv_fwd_pairs(const void *staged, int c_in, const void *packed, int K, int c_out, int precision,
@@ -451,21 +512,21 @@ int conv_fwd_pairs(const void *staged, int c_in, const void *packed, int K, int 
   PlParams p;
   if (K > 256 || !pl_params(c_in, c_out, precision, p))
     return fail(SSC_ERR_INVALID, "conv_fwd_pairs: shape (c_in %d, c_out %d, kernel volume %d) not covered by the pair-list kernel", c_in, c_out, K);
-  int sms = sm_count();
-  if (sms > 160) sms = 160;
-  const int n_ctas = sms * p.ctas_per_sm;
-  int32_t *n_strips = (int32_t *)strip_mem;
+  int n_ctas = sm_count() * p.ctas_per_sm;
+  if (n_ctas > PL_MAX_CTAS) n_ctas = PL_MAX_CTAS;
+  int32_t *hdr = (int32_t *)strip_mem;
   int4 *strips = (int4 *)((uint8_t *)strip_mem + 256);
+  int32_t *owner = (int32_t *)(strips + max_strips(K));
   cudaError_t e = cudaMemsetAsync(out, 0, (size_t)n_out * c_out * sizeof(float), st);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd_pairs: clearing the output: %s", cudaGetErrorString(e));
-  { pl_strips_kernel<<<1, 256, 0, st>>>(pl.starts, K, p.n_split, n_ctas, strips, n_strips); note_launches(1); }
+  { pl_strips_kernel<<<1, 256, 0, st>>>(pl.starts, K, p.n_split, n_ctas, hdr, strips, owner); note_launches(1); }
   SSC_CHECK_LAUNCH("pl_strips");
   const size_t smem = pl_smem_bytes(p);
   auto kernel = p.f16 ? conv_fwd_pairs_kernel<true> : conv_fwd_pairs_kernel<false>;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd_pairs: smem attribute: %s", cudaGetErrorString(e));
   { kernel<<<n_ctas, p.threads, smem, st>>>((const float *)staged, (const uint4 *)packed, c_out, pl.pair_out, pl.pair_in, pl.starts,
-                                          strips, n_strips, out, status, p); note_launches(1); }
+                                          strips, owner, hdr, out, status, p); note_launches(1); }
   SSC_CHECK_LAUNCH("conv_fwd_pairs");
   return SSC_OK;
 }
@@ -487,6 +548,10 @@ extern "C" int ssc_conv_pairs_build(const int32_t *nbr, int K, int n_out, void *
   SSC_REQUIRE(K >= 1 && K <= 256 && n_out >= 1 && nbr && lists, "conv_pairs_build: bad arguments");
   SSC_REQUIRE(list_bytes >= ssc_conv_pairs_list_bytes(K, n_out) && ((uintptr_t)lists & 255u) == 0,
               "conv_pairs_build: list buffer too small or not 256-byte aligned");
+  // the strip table kept behind the lists belongs to the old lists: forget it
+  void *strip_mem = (uint8_t *)lists + align_up(pair_lists_bytes(K, n_out), 256);
+  cudaError_t e = cudaMemsetAsync(strip_mem, 0, 256, as_stream(stream));
+  if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_pairs_build: %s", cudaGetErrorString(e));
   return pair_lists_build(nbr, K, n_out, lists, nullptr, as_stream(stream));
 }
 
