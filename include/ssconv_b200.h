@@ -96,6 +96,15 @@ int ssc_rulebook_subm_static(const int32_t *indices, int n_in, int batch, const 
                              const int ksize[3], const int dilation[3], int32_t *nbr,
                              int32_t *pairs, int32_t *indice_num, int32_t *status, void *stream);
 
+/* The submanifold rulebook on rows whose count is still on the device: `indices` has n_cap rows of
+ * which the first *n_in_dev are meaningful (the output of a layer that ran ahead of its row count,
+ * see ssc_rulebook_conv_fill).  Writes the neighbour table [K, n_cap] for the meaningful rows only;
+ * consumers pass the same device word as their n_out_dev.  No pair lists (they need the count on the
+ * host).  Same geometry rules as ssc_rulebook_subm (SS_Conv_lib/src/conv/indice_conv.h:70-96). */
+int ssc_rulebook_subm_ahead(const int32_t *indices, int n_cap, int batch, const int shape[3],
+                            const int ksize[3], const int dilation[3], int32_t *nbr, int32_t *status,
+                            void *scratch, size_t scratch_bytes, const int32_t *n_in_dev, void *stream);
+
 /* Regular / strided (transpose = 0) or transposed (transpose = 1,
  * getValidOutPosTranspose geometry.h:82-138) rulebook, phase 1: build the input coordinate
  * hash, mark every reachable output cell and count them.  n_out_dev: device int32 that

@@ -643,6 +643,27 @@ extern "C" int ssc_rulebook_subm(const int32_t *indices, int n_in, int batch, co
   return SSC_OK;
 }
 
+extern "C" int ssc_rulebook_subm_ahead(const int32_t *indices, int n_cap, int batch, const int shape[3],
+                                       const int ksize[3], const int dilation[3], int32_t *nbr, int32_t *status,
+                                       void *scratch, size_t scratch_bytes, const int32_t *n_in_dev, void *stream) {
+  SSC_REQUIRE(n_cap >= 0 && shape && ksize && dilation && n_in_dev, "rulebook_subm_ahead: bad arguments");
+  SSC_REQUIRE(n_cap == 0 || (indices && nbr), "rulebook_subm_ahead: null pointer");
+  int one[3] = {1, 1, 1};
+  int pad[3] = {ksize[0] / 2, ksize[1] / 2, ksize[2] / 2};
+  Geometry g;
+  SSC_REQUIRE(fill_geometry(g, shape, shape, ksize, one, pad, dilation, 0) == 0, "rulebook_subm_ahead: bad geometry");
+  SSC_REQUIRE(g.K <= 256, "rulebook_subm_ahead: kernel volume %d > 256", g.K);
+  if (int e = check_volume(batch, shape, "rulebook_subm_ahead")) return e;
+  RulebookScratch s = carve(scratch, n_cap, batch, shape, shape, g.K);
+  if (scratch == nullptr || scratch_bytes < s.total)
+    return fail(SSC_ERR_SCRATCH, "rulebook_subm_ahead: scratch %zu < %zu bytes", scratch_bytes, s.total);
+  cudaStream_t st = as_stream(stream);
+  if (int e = build_hash(indices, n_cap, batch, g, s, status, st, n_in_dev)) return e;
+  if (int e = lookup_and_compact(indices, n_cap, n_cap, batch, g, s, nbr, nullptr, nullptr, st, n_in_dev)) return e;
+  SSC_CHECK_LAUNCH("rulebook_subm_ahead");
+  return SSC_OK;
+}
+
 extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int batch, const int in_shape[3],
                                        const int out_shape[3], const int ksize[3], const int stride[3],
                                        const int padding[3], const int dilation[3], int transpose,

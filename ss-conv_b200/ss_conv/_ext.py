@@ -35,6 +35,8 @@ SIGNATURES = {
                                   c_void_p, c_size_t, c_void_p]),
     "ssc_rulebook_subm_static": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
+    "ssc_rulebook_subm_ahead": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, c_void_p, c_void_p, c_void_p, c_size_t,
+                                        c_void_p, c_void_p]),
     "ssc_rulebook_conv_count": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_void_p,
                                         c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ssc_rulebook_conv_fill": (c_int, [c_void_p, c_int, c_int, _I3, _I3, _I3, _I3, _I3, _I3, c_int, c_int, c_void_p,
@@ -337,6 +339,32 @@ def get_indice_pairs_ahead(indices, batch_size, out_shape, spatial_shape, ksize,
     _check(L.ssc_rulebook_conv_fill(_p(indices), n_in, int(batch_size), *geo, cap, _p(outids), _p(nbr), None, None,
                                     _p(st), _p(scratch), sbytes, _p(n_out_dev), _stream()))
     return [outids, LazyPairs(nbr, n_in, n_out_dev=n_out_dev, ratio_key=None if n_in_dev is not None else key), None]
+
+
+def get_indice_pairs_subm_ahead(indices_cap, batch_size, spatial_shape, ksize, dilation, n_in_dev):
+    """Submanifold rulebook on rows whose count is still on the device (indices_cap [cap, 4], the
+    first n_in_dev[0] rows meaningful): LazyPairs over the table [K, cap], pending on the same device
+    word.  Never waits for the device."""
+    L = lib()
+    indices_cap = indices_cap.contiguous()
+    dev = indices_cap.device
+    cap = indices_cap.shape[0]
+    K = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
+    if K > 256:
+        raise ValueError("ssconv_b200: kernel volume %d > 256" % K)
+    if int(batch_size) * int(spatial_shape[0]) * int(spatial_shape[1]) * int(spatial_shape[2]) >= 2 ** 31 - 1:
+        raise ValueError("ssconv_b200: batch*volume does not fit the int32 flat index")
+    skey = (cap, int(batch_size), tuple(spatial_shape), tuple(spatial_shape), K)
+    sbytes = _scratch_cache.get(skey)
+    if sbytes is None:
+        sbytes = _scratch_cache[skey] = max(int(L.ssc_rulebook_scratch_bytes(cap, int(batch_size), _i3(spatial_shape),
+                                                                             _i3(spatial_shape), K)), 256)
+    scratch = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+    nbr = torch.empty((K, cap), dtype=torch.int32, device=dev)
+    _check(L.ssc_rulebook_subm_ahead(_p(indices_cap, torch.int32), cap, int(batch_size), _i3(spatial_shape), _i3(ksize),
+                                     _i3(dilation), _p(nbr), _p(status_word(dev)), _p(scratch), sbytes, _p(n_in_dev),
+                                     _stream()))
+    return LazyPairs(nbr, cap, n_out_dev=n_in_dev)
 
 
 def get_indice_pairs_3d(indices, batch_size, out_shape, spatial_shape, ksize, stride, padding, dilation,

@@ -109,6 +109,43 @@ class SparseConvolution(nn.Module):
                                         lambda n: _ext._note_ratio(key, input.features.shape[0], n))
                 out._rows.indices_ready = indices_ready   # the next layer's rulebook may start here
                 return out
+        if (_ext.AHEAD and input.pending() and not self.conv1x1 and not self.inverse and feats_raw.is_cuda
+                and feats_raw.dtype == torch.float32
+                and not (torch.is_grad_enabled() and (feats_raw.requires_grad or weight.requires_grad))):
+            # A submanifold convolution, or one that reuses the rulebook cached under its indice_key,
+            # keeps the row set of its input: on an input whose count is still on the device it works
+            # on the capacity-sized buffers and hands the pending count on (so a whole stack of such
+            # layers - a module of the Plain backbones - queues without a host round trip).
+            cached = input.find_indice_pair(self.indice_key)
+            pairs = None
+            if cached is not None and isinstance(cached[2], _ext.LazyPairs) and cached[2].pending() \
+                    and cached[2].capacity == inds_raw.shape[0]:
+                pairs = cached[2]
+            elif cached is None and self.subm:
+                pairs = _ext.get_indice_pairs_subm_ahead(inds_raw, input.batch_size, list(input.spatial_shape),
+                                                         self.kernel_size, self.dilation, n_in_dev)
+                if self.indice_key is not None:
+                    input.indice_dict[self.indice_key] = (inds_raw, inds_raw, pairs, None, input.spatial_shape)
+            if pairs is not None:
+                op = indice_subm_conv if self.subm else indice_conv
+                out_cap = op(feats_raw, weight, pairs, None, pairs.capacity)
+                if self.bias is not None:
+                    out_cap += self.bias
+                out = SparseTensor(out_cap, inds_raw, out_spatial_shape if self.subm else input.spatial_shape,
+                                   input.batch_size)
+                out.indice_dict = input.indice_dict
+                out.grid = input.grid
+                key = self.indice_key
+
+                def redo():
+                    if key is not None:
+                        input.indice_dict.pop(key, None)      # the cached table belongs to the pending rows
+                    t = self._sparse_conv_exact(input, weight)
+                    return t.features, t.indices
+
+                out._rows = PendingRows(n_in_dev, pairs.capacity, input, redo)
+                out._rows.indices_ready = getattr(input._rows, "indices_ready", None)
+                return out
         return self._sparse_conv_exact(input, weight)
 
     def _sparse_conv_exact(self, input, weight):

@@ -445,3 +445,57 @@ def test_ahead_path_edge_cases(cuda):
         _ext.check_status(cuda)
     finally:
         _ext.set_precision("auto")
+
+
+def test_plain24_backbone_replayed_as_one_graph(cuda):
+    """The 24-block Plain24 backbone (three + twelve + nine SS_Conv blocks of 64 / 128 / 256 channels,
+    three average pools) in eval mode: every module of submanifold blocks shares one rulebook, the row
+    counts stay on the device from the first block to the last, so the whole network is recorded into
+    ONE CUDA graph.  The replay gives the bits of the eager, exact-count pass, on the recorded batch and
+    on another batch of different size."""
+    from ss_conv import _ext
+    from ss_conv.graph import GraphedChain
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    from ss_conv_backbones import Plain24
+    torch.manual_seed(5)
+    net = Plain24(irrep_in=(4,)).to(cuda).eval()
+    V, B = 32, 4
+
+    def batch(seed, n_pts):
+        ind = S.surface_voxels(range(B), V, n_pts, base_seed=seed)
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        return torch.randn(ind.shape[0], 4, generator=g).to(cuda), torch.from_numpy(ind).to(cuda)
+
+    def last_stage(x):
+        with torch.no_grad():
+            return net(x)[3]
+
+    def eager(f, i):
+        old = _ext.AHEAD
+        _ext.AHEAD = False
+        try:
+            y = last_stage(SparseTensor(f, i, [V] * 3, B))
+            return y.features.clone(), y.indices.clone()
+        finally:
+            _ext.AHEAD = old
+
+    _ext.set_precision("tf32")
+    try:
+        fa, ia = batch(100, 3000)
+        fb, ib = batch(200, 2200)
+        ref_a, ref_ia = eager(fa, ia)
+        ref_b, ref_ib = eager(fb, ib)
+        chain = GraphedChain(last_stage, [V] * 3, B, 4, int(max(ia.shape[0], ib.shape[0]) * 1.1), cuda)
+        ya = chain(fa, ia)
+        got_a, got_ia = ya.features.clone(), ya.indices.clone()
+        yb = chain(fb, ib)
+        got_b, got_ib = yb.features.clone(), yb.indices.clone()
+    finally:
+        _ext.set_precision("auto")
+    _ext.check_status(cuda)
+    assert chain.graph is not None and chain.launches >= 24 * 2 and chain.fallbacks == 0
+    assert ya.spatial_shape[0] == V // 8 and got_a.shape[1] == 256
+    assert torch.equal(got_ia, ref_ia) and torch.equal(got_ib, ref_ib)
+    assert torch.equal(got_a, ref_a) and torch.equal(got_b, ref_b)
+    assert float(ref_a.abs().max()) > 0
