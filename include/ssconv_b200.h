@@ -393,6 +393,14 @@ int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const float *scale, c
                     const int32_t *gate_of_channel, int c_out, int c_gate_base, int scalar_act,
                     int gate_act, const float *scalar_bias, const float *gate_bias, float *out,
                     void *stream);
+/* The same pass with a 16-bit result (precision SSC_PREC_F16 or SSC_PREC_BF16): out16 [n, c_out]
+ * fp16 / bf16, c_out a multiple of 8.  The rows are then already the operand image of the next
+ * convolution (ssc_conv_fwd with SSC_CONV_PRESTAGED and scratch = out16): no staging pass, half the
+ * bytes between the layers.  No counterpart in the reference (its layers exchange fp32). */
+int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const float *scale, const float *shift,
+                      const int32_t *gate_of_channel, int c_out, int c_gate_base, int scalar_act,
+                      int gate_act, const float *scalar_bias, const float *gate_bias, int precision,
+                      void *out16, void *stream);
 /* Training-mode statistics (batchnorm.py:73-99): mean [n_scalar] of scalar fields and
  * var = batch mean of the squared field norm (about the batch mean for scalars); `var` must
  * have room for n_field + c floats: the first n_field are the result, the tail is scratch. */

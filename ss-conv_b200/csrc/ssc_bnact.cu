@@ -1,6 +1,7 @@
 // Irrep-wise BatchNorm (eval: folded per-channel affine; train: statistics) and the gated
 // activation, as single elementwise passes.  HBM-bound.
 #include "ssc_common.cuh"
+#include "ssc_tc_ptx.cuh"
 
 namespace ssc {
 
@@ -102,6 +103,57 @@ bn_gate_vec4_kernel(const float *__restrict__ x, uint32_t total, uint32_t groups
   *(float4 *)(out + (size_t)t * 4) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
+// The same with a 16-bit result (OUT = 1 fp16, 2 bf16): the features leave the layer in the operand
+// precision of the next convolution, which then gathers them as they are (no staging pass).
+// Four consecutive output channels per thread:
+// channel counts that are multiples of four, 16-byte aligned rows.  Same arithmetic per element
+// as the scalar kernel.  groups = c_out / 4; total = rows * groups < 2^31.
+template <int OUT>
+__global__ void __launch_bounds__(256)
+bn_gate_vec4_out16_kernel(const float *__restrict__ x, uint32_t total, uint32_t groups, int c_in_total,
+                    const float *__restrict__ scale, const float *__restrict__ shift,
+                    const int32_t *__restrict__ gate_of_channel, int c_gate_base, int scalar_act, int gate_act,
+                    const float *__restrict__ scalar_bias, const float *__restrict__ gate_bias, uint2 *__restrict__ out) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const uint32_t row = t / groups, g4 = t - row * groups;
+  const int ch0 = (int)g4 * 4;
+  const float *xr = x + (size_t)row * c_in_total;
+  const float4 xv = __ldg((const float4 *)(xr + ch0));
+  float v[4] = {xv.x, xv.y, xv.z, xv.w};
+  if (scale) {
+    const float4 sc = __ldg((const float4 *)(scale + ch0)), sh = __ldg((const float4 *)(shift + ch0));
+    v[0] = fmaf(v[0], sc.x, sh.x);
+    v[1] = fmaf(v[1], sc.y, sh.y);
+    v[2] = fmaf(v[2], sc.z, sh.z);
+    v[3] = fmaf(v[3], sc.w, sh.w);
+  }
+  if (gate_of_channel) {
+    const int4 gi = __ldg((const int4 *)(gate_of_channel + ch0));
+    const int g[4] = {gi.x, gi.y, gi.z, gi.w};
+    int last_g = -2;
+    float last_a = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (g[q] == -1) {
+        if (scalar_bias) v[q] += scalar_bias[ch0 + q];
+        v[q] = apply_act(v[q], scalar_act);
+      } else if (g[q] >= 0) {
+        if (g[q] != last_g) {   // the channels of a field share their gate
+          float gv = __ldg(xr + c_gate_base + g[q]);
+          if (scale) gv = fmaf(gv, scale[c_gate_base + g[q]], shift[c_gate_base + g[q]]);
+          if (gate_bias) gv += gate_bias[g[q]];
+          last_a = apply_act(gv, gate_act);
+          last_g = g[q];
+        }
+        v[q] *= last_a;
+      }
+    }
+  }
+  out[t] = OUT == 2 ? make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]))
+                    : make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
+}
+
 // Column sums with one block per 32-channel group: block (32, 8), rows strided by 8*gridDim.y.
 // pass 0: sum of x per channel; pass 1: sum of (x - mean_ch)^2 per channel (mean_ch = 0 for
 // non-scalar channels), accumulated per field.
@@ -177,6 +229,31 @@ extern "C" int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const floa
                                                                      c_out, c_gate_base, scalar_act, gate_act,
                                                                      scalar_bias, gate_bias, out); note_launches(1); }
   SSC_CHECK_LAUNCH("bn_gate_fwd");
+  return SSC_OK;
+}
+
+extern "C" int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const float *scale, const float *shift,
+                                 const int32_t *gate_of_channel, int c_out, int c_gate_base, int scalar_act,
+                                 int gate_act, const float *scalar_bias, const float *gate_bias, int precision,
+                                 void *out16, void *stream) {
+  SSC_REQUIRE(n >= 0 && c_in_total >= 1 && c_out >= 1 && c_out <= c_in_total, "bn_gate_fwd16: bad sizes");
+  SSC_REQUIRE(precision == SSC_PREC_F16 || precision == SSC_PREC_BF16, "bn_gate_fwd16: precision must be SSC_PREC_F16 or SSC_PREC_BF16");
+  SSC_REQUIRE((scale == nullptr) == (shift == nullptr), "bn_gate_fwd16: scale and shift go together");
+  SSC_REQUIRE((c_out & 7) == 0 && (c_in_total & 3) == 0 && (c_gate_base & 3) == 0,
+              "bn_gate_fwd16: needs c_out a multiple of 8 (16-byte rows) and c_in_total, c_gate_base multiples of 4");
+  if (n == 0) return SSC_OK;
+  SSC_REQUIRE(x && out16, "bn_gate_fwd16: null pointer");
+  SSC_REQUIRE((((uintptr_t)x | (uintptr_t)out16 | (uintptr_t)scale | (uintptr_t)shift | (uintptr_t)gate_of_channel) & 15u) == 0,
+              "bn_gate_fwd16: pointers must be 16-byte aligned");
+  const long long total = (long long)n * c_out;
+  SSC_REQUIRE(total / 4 < (1ll << 31), "bn_gate_fwd16: tensor too large");
+  const uint32_t groups = (uint32_t)(c_out >> 2), total4 = (uint32_t)(total >> 2);
+  if (precision == SSC_PREC_BF16) {
+    { bn_gate_vec4_out16_kernel<2><<<ceil_div(total4, 256), 256, 0, as_stream(stream)>>>(x, total4, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act, scalar_bias, gate_bias, (uint2 *)out16); note_launches(1); }
+  } else {
+    { bn_gate_vec4_out16_kernel<1><<<ceil_div(total4, 256), 256, 0, as_stream(stream)>>>(x, total4, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act, scalar_bias, gate_bias, (uint2 *)out16); note_launches(1); }
+  }
+  SSC_CHECK_LAUNCH("bn_gate_fwd16");
   return SSC_OK;
 }
 

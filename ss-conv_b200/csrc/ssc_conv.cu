@@ -146,7 +146,7 @@ extern "C" int ssc_conv_stage(const float *features, int n_in, int c_in, int pre
                               void *stream) {
   SSC_REQUIRE(c_in > 0 && n_in >= 0 && (n_in == 0 || features) && scratch, "conv_stage: bad arguments");
   SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16 || precision == SSC_PREC_BF16, "conv_stage: precision %d has no staged image", precision);
-  SSC_REQUIRE(scratch_bytes >= ssc_conv_scratch_bytes(n_in, c_in, 1, precision) && ((uintptr_t)scratch & 15u) == 0,
+  SSC_REQUIRE(scratch_bytes + 16 >= ssc_conv_scratch_bytes(n_in, c_in, 1, precision) && ((uintptr_t)scratch & 15u) == 0,
               "conv_stage: scratch too small or not 16-byte aligned");
   return precision == SSC_PREC_TF32 ? stage_features(features, n_in, c_in, scratch, as_stream(stream))
                                     : stage_features_16(features, n_in, c_in, precision == SSC_PREC_BF16, scratch, as_stream(stream));
@@ -160,7 +160,7 @@ extern "C" int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, c
   const bool prestaged = (precision & SSC_CONV_PRESTAGED) != 0;
   precision &= ~SSC_CONV_PRESTAGED;
   if (n_out == 0) return SSC_OK;
-  SSC_REQUIRE(filters && nbr && out && (n_in == 0 || features), "conv_fwd: null pointer");
+  SSC_REQUIRE(filters && nbr && out && (n_in == 0 || features || prestaged), "conv_fwd: null pointer");
   cudaStream_t st = as_stream(stream);
   if (precision == SSC_PREC_FP32) {
     dim3 grid(ceil_div(n_out, BM), ceil_div(c_out, BN));

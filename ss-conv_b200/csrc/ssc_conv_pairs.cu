@@ -562,12 +562,12 @@ extern "C" int ssc_conv_fwd_pairs(const float *features, int n_in, int c_in, con
   const bool prestaged = (precision & SSC_CONV_PRESTAGED) != 0;
   precision &= ~SSC_CONV_PRESTAGED;
   if (n_out == 0) return SSC_OK;
-  SSC_REQUIRE(packed && lists && out && scratch && (n_in == 0 || features), "conv_fwd_pairs: null pointer");
+  SSC_REQUIRE(packed && lists && out && scratch && (n_in == 0 || features || prestaged), "conv_fwd_pairs: null pointer");
   SSC_REQUIRE(precision == SSC_PREC_TF32 || precision == SSC_PREC_F16 || precision == SSC_PREC_BF16,
               "conv_fwd_pairs: precision %d has no tensor-core form", precision);
   SSC_REQUIRE(list_bytes >= ssc_conv_pairs_list_bytes(K, n_out) && ((uintptr_t)lists & 255u) == 0,
               "conv_fwd_pairs: list buffer too small or not 256-byte aligned");
-  SSC_REQUIRE(scratch_bytes >= ssc_conv_scratch_bytes(n_in, c_in, c_out, precision) && ((uintptr_t)scratch & 15u) == 0,
+  SSC_REQUIRE(scratch_bytes + 16 >= ssc_conv_scratch_bytes(n_in, c_in, c_out, precision) && ((uintptr_t)scratch & 15u) == 0,
               "conv_fwd_pairs: staging buffer too small or not 16-byte aligned");
   cudaStream_t st = as_stream(stream);
   if (!prestaged) {

@@ -2,9 +2,10 @@
 //
 // A feature row is gathered once per neighbour (about K/2 times for a 3^3 kernel), so the rounding
 // to the operand precision is done once per call, up front, into a caller-supplied buffer:
-//   TF32 : [n_in + 1, c_pad] fp32 words rounded to nearest TF32, c_pad = c_in rounded up to 4
-//   fp16 / bf16 : [n_in + 1, c_pad] 16-bit values, c_pad = c_in rounded up to 8 (16-byte rows)
-// Padding channels and the extra last row are zero.
+//   TF32 : [n_in, c_pad] fp32 words rounded to nearest TF32, c_pad = c_in rounded up to 4
+//   fp16 / bf16 : [n_in, c_pad] 16-bit values, c_pad = c_in rounded up to 8 (16-byte rows)
+// Padding channels are zero.  A layer that already holds its features in the 16-bit form (written
+// by ssc_bn_gate_fwd16, or uploaded that way) hands them to the convolution as the staged image.
 #include "ssc_conv_internal.cuh"
 #include "ssc_tc_ptx.cuh"
 
@@ -43,19 +44,20 @@ __global__ void stage_features_padded_kernel(const float *__restrict__ in, long 
 }
 
 size_t conv_tf32_scratch_bytes(int n_in, int c_in) {
-  return ((size_t)n_in + 1) * (size_t)((c_in + 3) & ~3) * sizeof(float);
+  return align_up((size_t)n_in * (size_t)((c_in + 3) & ~3) * sizeof(float), 16) + 16;
 }
 
 int stage_features(const float *features, int n_in, int c_in, void *staged, cudaStream_t st) {
   const int c_pad = (c_in + 3) & ~3;
   const int max_blocks = sm_count() * 16;
+  if (n_in == 0) return SSC_OK;
   if (c_pad == c_in && ((uintptr_t)features & 15u) == 0) {
-    const long long n_vec = (long long)n_in * c_in / 4, total_vec = ((long long)n_in + 1) * c_in / 4;
+    const long long n_vec = (long long)n_in * c_in / 4, total_vec = n_vec;
     int blocks = ceil_div(total_vec, 256 * 4);
     if (blocks > max_blocks) blocks = max_blocks;
     { stage_features_kernel<<<blocks, 256, 0, st>>>((const float4 *)features, n_vec, total_vec, (uint4 *)staged); note_launches(1); }
   } else {
-    const long long total = ((long long)n_in + 1) * c_pad;
+    const long long total = (long long)n_in * c_pad;
     int blocks = ceil_div(total, 256 * 4);
     if (blocks > max_blocks) blocks = max_blocks;
     { stage_features_padded_kernel<<<blocks, 256, 0, st>>>(features, n_in, c_in, c_pad, total, (uint32_t *)staged); note_launches(1); }
@@ -84,11 +86,12 @@ __global__ void stage_features_16_kernel(const float *__restrict__ in, long long
   }
 }
 
-size_t conv_f16_scratch_bytes(int n_in, int c_in) { return ((size_t)n_in + 1) * (size_t)f16_row_words(c_in) * 4; }
+size_t conv_f16_scratch_bytes(int n_in, int c_in) { return (size_t)n_in * (size_t)f16_row_words(c_in) * 4 + 16; }
 
 int stage_features_16(const float *features, int n_in, int c_in, bool bf16, void *staged, cudaStream_t st) {
+  if (n_in == 0) return SSC_OK;
   const int words = f16_row_words(c_in);
-  const long long total_pairs = ((long long)n_in + 1) * words;
+  const long long total_pairs = (long long)n_in * words;
   int blocks = ceil_div(total_pairs, 256 * 4);
   const int max_blocks = sm_count() * 16;
   if (blocks > max_blocks) blocks = max_blocks;

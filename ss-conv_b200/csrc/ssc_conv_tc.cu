@@ -483,7 +483,7 @@ int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void
                 const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): kernel volume %d > 256", K);
   const int words = f16_row_words(c_in);
-  if (scratch == nullptr || scratch_bytes < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
+  if (scratch == nullptr || scratch_bytes + 16 < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
     return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): needs the staging buffer of ssc_conv_scratch_bytes (16-byte aligned)");
   int grid = ceil_div(n_out, TC_M);
   const int sms = sm_count();
@@ -521,7 +521,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   // every gather (a row is gathered about K/2 times).
   const int c_pad = (c_in + 3) & ~3;  // row stride of the staged image (zero-padded channels)
   const size_t stage_need = conv_tf32_scratch_bytes(n_in, c_in);
-  const bool fits = scratch != nullptr && scratch_bytes >= stage_need && ((uintptr_t)scratch & 15u) == 0;
+  const bool fits = scratch != nullptr && scratch_bytes + 16 >= stage_need && ((uintptr_t)scratch & 15u) == 0;
   if (prestaged && !fits) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): SSC_CONV_PRESTAGED without the staged image in scratch");
   const bool staged = fits && (prestaged || grid >= kStagingMinTiles);
   if (staged && !prestaged) {

@@ -94,6 +94,8 @@ SIGNATURES = {
                             c_void_p, c_void_p]),
     "ssc_bn_gate_fwd": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ssc_bn_gate_fwd16": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ssc_bn_stats": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
 }
 
@@ -135,6 +137,26 @@ def set_precision(mode):
 
 def get_precision():
     return _precision
+
+
+# Feature storage between layers: None (fp32, the reference's format) or 'fp16' / 'bf16': a gated
+# Activation then writes its result in that 16-bit type (when the channel count is a multiple of 8)
+# and the next convolution gathers those rows as its operands - no staging pass, half the bytes
+# between the layers.  The convolution's operand precision follows the stored type.
+_storage = None
+_DTYPE_OF = {"fp16": torch.float16, "bf16": torch.bfloat16}
+_PREC_OF_DTYPE = {torch.float16: "fp16", torch.bfloat16: "bf16"}
+
+
+def set_feature_storage(mode):
+    global _storage
+    if mode not in (None, "fp16", "bf16"):
+        raise ValueError("feature storage must be None, 'fp16' or 'bf16'")
+    _storage = mode
+
+
+def get_feature_storage():
+    return _storage
 
 
 def _check(rc):
@@ -638,7 +660,7 @@ def conv_prepare(features, filters, precision=None):
     would not use a staged image (exact fp32, small layers)."""
     flt = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
     if not (flt.is_contiguous() and features.is_contiguous() and features.dtype == torch.float32):
-        return False
+        return False      # (16-bit features are their own staged image: nothing to prepare but the filters)
     K, c_in, c_out = flt.shape
     mode = _resolve_precision(c_in, c_out, precision)
     if mode not in _PREC_OF or (mode != "tf32" and c_out > 512):
@@ -665,6 +687,10 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
     if features.shape[1] != c_in:
         raise ValueError("features have %d channels, filters expect %d" % (features.shape[1], c_in))
     features = features.contiguous()
+    if features.dtype in _PREC_OF_DTYPE:
+        if c_in % 8 == 0 and c_out <= 512 and row_order is None:
+            return _conv_forward_stored16(features, filters, nbr, n_out, n_out_dev, algo)
+        features = features.float()
     out = torch.empty((n_out, c_out), dtype=torch.float32, device=features.device)
     mode = _resolve_precision(c_in, c_out, precision)
     st = status_word(features.device)
@@ -714,6 +740,26 @@ def _packed_filters(filters, prec):
     return packed
 
 
+def _conv_forward_stored16(features, filters, nbr, n_out, n_out_dev, algo):
+    """Convolution on features stored as fp16 / bf16 rows [n_in, Cin] (Cin a multiple of 8): the rows
+    ARE the staged operand image, so the call is the kernel alone."""
+    K, c_in, c_out = filters.shape
+    prec = _PREC_OF[_PREC_OF_DTYPE[features.dtype]]
+    out = torch.empty((n_out, c_out), dtype=torch.float32, device=features.device)
+    st = status_word(features.device)
+    packed = _packed_filters(filters, prec)
+    nbytes = features.numel() * 2
+    if n_out_dev is None and nbr.shape[1] == n_out and _use_pairs(K, c_in, c_out, n_out, prec, algo):
+        lists = pair_lists(nbr)
+        _check(lib().ssc_conv_fwd_pairs(None, features.shape[0], c_in, _p(packed), K, c_out, _p(lists), lists.numel(),
+                                        int(n_out), prec | PRESTAGED, _p(out), _p(st), _p(features), nbytes, _stream()))
+        return out
+    _check(lib().ssc_conv_fwd_ordered(None, features.shape[0], c_in, _p(packed), K, c_out, _p(nbr, torch.int32),
+                                      int(n_out), prec | PRESTAGED, _p(out), _p(st), _p(features), nbytes, _p(n_out_dev),
+                                      None, _stream()))
+    return out
+
+
 def _conv_forward_pairs(features, filters, nbr, n_out, prec, out, st):
     """The pair-list kernel: staging + (lists, once per table) + strips + one persistent launch."""
     K, c_in, c_out = filters.shape
@@ -738,8 +784,8 @@ def _conv_forward_pairs(features, filters, nbr, n_out, prec, out, st):
 def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, inverse, subm):
     """Reference signature (SS_Conv_lib/src/ss_conv_ops.h:43-45); filters [k,k,k,Cin,Cout]
     (a permuted view is accepted).  The submanifold centre needs no special case."""
-    if features.dtype != torch.float32:
-        raise TypeError("indice_conv_fp32 expects float32 features")
+    if features.dtype != torch.float32 and features.dtype not in _PREC_OF_DTYPE:
+        raise TypeError("indice_conv_fp32 expects float32 features (or features stored in fp16 / bf16 by this library)")
     c_in, c_out = filters.shape[-2], filters.shape[-1]
     cached = getattr(filters, "_ssc_flat", None)
     if cached is not None and cached[0] == filters._version:
@@ -1078,8 +1124,17 @@ def bn_fold(running_mean, running_var, weight, bias, field_of_channel, scalar_of
 
 
 def bn_gate_forward(x, scale, shift, gate_of_channel, c_out, c_gate_base, scalar_act, gate_act, scalar_bias,
-                    gate_bias):
+                    gate_bias, storage=None):
+    """storage 'fp16' / 'bf16': the result is written in that type (see set_feature_storage) when the
+    shapes allow 16-byte rows; otherwise fp32."""
     x = x.contiguous()
+    if (storage in _DTYPE_OF and int(c_out) % 8 == 0 and x.shape[1] % 4 == 0 and int(c_gate_base) % 4 == 0
+            and x.shape[0] * int(c_out) // 4 < 2 ** 31):
+        out = torch.empty((x.shape[0], int(c_out)), dtype=_DTYPE_OF[storage], device=x.device)
+        _check(lib().ssc_bn_gate_fwd16(_p(x, torch.float32), x.shape[0], x.shape[1], _p(scale), _p(shift),
+                                       _p(gate_of_channel), int(c_out), int(c_gate_base), int(scalar_act), int(gate_act),
+                                       _p(scalar_bias), _p(gate_bias), _PREC_OF[storage], _p(out), _stream()))
+        return out
     out = torch.empty((x.shape[0], int(c_out)), dtype=torch.float32, device=x.device)
     _check(lib().ssc_bn_gate_fwd(_p(x, torch.float32), x.shape[0], x.shape[1], _p(scale), _p(shift),
                                  _p(gate_of_channel), int(c_out), int(c_gate_base), int(scalar_act), int(gate_act),

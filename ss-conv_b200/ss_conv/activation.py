@@ -122,7 +122,7 @@ class Activation(nn.Module):
                 s_bias[:self.multiplicities[0]] = self.scalar_act.bias.detach()
             g_bias = self.gate_act.bias.detach() if (self.gate_act is not None and self.gate_act.bias is not None) else None
             return _ext.bn_gate_forward(y, scale, shift, self._gate_table(y.device), C, C, s_code, g_code, s_bias,
-                                        g_bias)
+                                        g_bias, storage=_ext.get_feature_storage())
         return self._gate_composite(y if scale is None else y * scale + shift)
 
     def _gate_composite(self, y):

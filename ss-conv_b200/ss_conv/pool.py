@@ -1,4 +1,5 @@
 """Pooling layers (interface of SS_Conv_lib/ss_conv/pool.py:15-92)."""
+import torch
 import torch.nn as nn
 
 from ss_conv.sp_ops import tensor as tensor_mod
@@ -23,6 +24,8 @@ class _GlobalPool(nn.Module):
     func = None
 
     def forward(self, inputs, offsets=None):
+        if isinstance(inputs, SparseTensor) and inputs.raw()[0].dtype in (torch.float16, torch.bfloat16):
+            inputs._features = inputs.raw()[0].float()     # stored 16-bit features: the pools compute in fp32
         if isinstance(inputs, SparseTensor):
             if inputs.pending() and offsets is None:
                 # queue the pooling on the rows as they are, then read the pending counts back;

@@ -12,6 +12,10 @@ from .. import _ext
 from .functional import indice_conv, indice_inverse_conv, indice_subm_conv
 
 
+# fp32 features, or features a gated Activation stored as fp16 / bf16 (_ext.set_feature_storage)
+_FEATURE_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
+
+
 class SparseConvolution(nn.Module):
     def __init__(self, ndim, in_channels, out_channels, kernel_size=3, stride=1, padding=0, dilation=1, groups=1,
                  bias=True, subm=False, output_padding=0, transposed=False, inverse=False, indice_key=None):
@@ -72,7 +76,7 @@ class SparseConvolution(nn.Module):
         out_spatial_shape = self._output_shape(input.spatial_shape)
         feats_raw, inds_raw, n_in_dev = input.raw()
         if (_ext.AHEAD and not self.conv1x1 and not self.subm and not self.inverse and self.indice_key is None
-                and feats_raw.is_cuda and feats_raw.dtype == torch.float32
+                and feats_raw.is_cuda and feats_raw.dtype in _FEATURE_DTYPES
                 and not (torch.is_grad_enabled() and (feats_raw.requires_grad or weight.requires_grad))):
             # While a CUDA graph is being recorded, the part of the convolution call that does not
             # need the rulebook (filter packing, staging of the feature rows) goes to a side stream:
@@ -110,7 +114,7 @@ class SparseConvolution(nn.Module):
                 out._rows.indices_ready = indices_ready   # the next layer's rulebook may start here
                 return out
         if (_ext.AHEAD and input.pending() and not self.conv1x1 and not self.inverse and feats_raw.is_cuda
-                and feats_raw.dtype == torch.float32
+                and feats_raw.dtype in _FEATURE_DTYPES
                 and not (torch.is_grad_enabled() and (feats_raw.requires_grad or weight.requires_grad))):
             # A submanifold convolution, or one that reuses the rulebook cached under its indice_key,
             # keeps the row set of its input: on an input whose count is still on the device it works

@@ -28,6 +28,9 @@ class _SparsePool(nn.Module):
         out_shape = shape if self.subm else get_conv_output_size(shape, self.kernel_size, self.stride, self.padding,
                                                                  self.dilation)
         feats_raw, inds_raw, n_in_dev = input.raw()
+        if feats_raw.dtype in (torch.float16, torch.bfloat16):
+            # features stored in 16 bits by a gated Activation: the pools compute in fp32
+            input._features = feats_raw = feats_raw.float()
         if (_ext.AHEAD and not self.subm and feats_raw.is_cuda and feats_raw.dtype == torch.float32
                 and not (torch.is_grad_enabled() and feats_raw.requires_grad)):
             ahead, indices_ready = _ext.rulebook_next_to_features(input._rows, lambda: _ext.get_indice_pairs_ahead(

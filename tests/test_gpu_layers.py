@@ -499,3 +499,57 @@ def test_plain24_backbone_replayed_as_one_graph(cuda):
     assert torch.equal(got_ia, ref_ia) and torch.equal(got_ib, ref_ib)
     assert torch.equal(got_a, ref_a) and torch.equal(got_b, ref_b)
     assert float(ref_a.abs().max()) > 0
+
+
+@pytest.mark.parametrize("storage", ["bf16", "fp16"])
+def test_features_stored_in_16_bits_between_layers(cuda, storage):
+    """set_feature_storage: a gated Activation writes fp16 / bf16 rows and the next convolution gathers
+    them as its operands (no staging pass).  The stored rows are the rounding the staging pass would
+    have produced, so a chain in storage mode gives the bits of the same chain with fp32 features and
+    that operand precision - layer by layer, submanifold and strided, eager and as one CUDA graph."""
+    from ss_conv import _ext
+    from ss_conv.graph import GraphedChain
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    from ss_conv_modules import SS_Conv
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    w = (4, 4, 4, 4)
+    blocks = [SS_Conv(w, w, 3, padding=1, subm=True, activation=(F.relu, torch.sigmoid), indice_key="a",
+                      activation_checkpoint=False).to(cuda).eval(),
+              SS_Conv(w, w, 3, padding=1, subm=True, activation=(F.relu, torch.sigmoid), indice_key="a",
+                      activation_checkpoint=False).to(cuda).eval(),
+              SS_Conv(w, (8, 8, 8, 8), 3, stride=2, padding=1, activation=(F.relu, torch.sigmoid),
+                      activation_checkpoint=False).to(cuda).eval()]
+    ind = S.surface_voxels(range(3), 32, 5000, base_seed=77)
+    feats = torch.randn(ind.shape[0], 64, generator=torch.Generator().manual_seed(1)).to(cuda)
+    inds = torch.from_numpy(ind).to(cuda)
+
+    def run(x):
+        with torch.no_grad():
+            for b in blocks:
+                x = b(x)
+        return x
+
+    _ext.set_precision(storage)
+    try:
+        ref = run(SparseTensor(feats, inds, [32] * 3, 3))
+        ref_f, ref_i = ref.features.clone(), ref.indices.clone()
+        _ext.set_feature_storage(storage)
+        l0 = _ext.kernel_launches()
+        got = run(SparseTensor(feats, inds, [32] * 3, 3))
+        got_f, got_i = got.features.clone(), got.indices.clone()
+        l1 = _ext.kernel_launches()
+        chain = GraphedChain(run, [32] * 3, 3, 64, int(ind.shape[0] * 1.1), cuda)
+        rep = chain(feats, inds)
+        rep_f = rep.features.clone()
+    finally:
+        _ext.set_feature_storage(None)
+        _ext.set_precision("auto")
+    _ext.check_status(cuda)
+    dt = torch.bfloat16 if storage == "bf16" else torch.float16
+    assert got_f.dtype == dt and got_f.shape == ref_f.shape and ref_f.dtype == torch.float32
+    assert torch.equal(got_i, ref_i)
+    assert torch.equal(got_f, ref_f.to(dt))          # same operands in every layer, only the last rounding differs
+    assert torch.equal(rep_f, got_f)
+    assert float(ref_f.abs().max()) > 0
