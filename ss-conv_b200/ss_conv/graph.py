@@ -66,7 +66,7 @@ class _Recording(object):
 
     def __init__(self, chain):
         dev = chain.dev
-        self.feats = torch.zeros((chain.cap, chain.channels), dtype=torch.float32, device=dev)
+        self.feats = torch.zeros((chain.cap, chain.channels), dtype=chain.feature_dtype, device=dev)
         self.inds = torch.zeros((chain.cap, 4), dtype=torch.int32, device=dev)
         self.n = torch.zeros(1, dtype=torch.int32, device=dev)
         self.graph = None
@@ -133,7 +133,12 @@ class _Queued(object):
 
 
 class GraphedChain(object):
-    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device, depth=1, streams=1):
+    def __init__(self, fn, spatial_shape, batch_size, channels, max_rows, device, depth=1, streams=1,
+                 feature_dtype=torch.float32):
+        """feature_dtype: type of the input feature rows the graph is fed with (torch.float16 /
+        torch.bfloat16: a caller that holds its features in 16 bits uploads half the bytes; the first
+        convolution gathers them as its operands)."""
+        self.feature_dtype = feature_dtype
         self.fn, self.shape, self.batch, self.dev = fn, spatial_shape, int(batch_size), torch.device(device)
         self.cap, self.channels, self.depth = int(max_rows), int(channels), max(1, int(depth))
         # streams > 1: recording k replays on stream k % streams, so consecutive batches overlap on the
