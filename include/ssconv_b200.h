@@ -401,12 +401,31 @@ int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const float *scale,
                       const int32_t *gate_of_channel, int c_out, int c_gate_base, int scalar_act,
                       int gate_act, const float *scalar_bias, const float *gate_bias, int precision,
                       void *out16, void *stream);
-/* Training-mode statistics (batchnorm.py:73-99): mean [n_scalar] of scalar fields and
- * var = batch mean of the squared field norm (about the batch mean for scalars); `var` must
- * have room for n_field + c floats: the first n_field are the result, the tail is scratch. */
+/* Training-mode statistics (SS_Conv_lib/ss_conv/batchnorm.py:73-99): mean [n_scalar] of scalar
+ * fields and var = batch mean of the squared field norm (about the batch mean for scalars); `var`
+ * must have room for n_field + c floats: the first n_field are the result, the tail is scratch.
+ * Partial sums are added in a fixed order (bitwise repeatable).  scratch: ssc_bn_scratch_bytes(n, c). */
+size_t ssc_bn_scratch_bytes(int n, int c);
 int ssc_bn_stats(const float *x, int n, int c, const int32_t *field_of_channel,
                  const int32_t *scalar_of_channel, int n_field, int n_scalar, float *mean,
-                 float *var, void *stream);
+                 float *var, void *scratch, size_t scratch_bytes, void *stream);
+
+/* Backward of the batch norm (what autograd derives from SS_Conv_lib/ss_conv/batchnorm.py:49-136):
+ * y = (x - mean) * w / sqrt(var + eps) (+ bias for scalars).  training != 0: mean / var are the batch
+ * statistics of x (gradients flow through them); else they are constants (running buffers).
+ * gx [n, c]; d_weight [n_field] and d_bias [n_scalar] may be NULL.  weight NULL = no affine part. */
+int ssc_bn_bwd(const float *x, const float *gy, int n, int c, const int32_t *field_of_channel,
+               const int32_t *scalar_of_channel, int n_field, int n_scalar, const float *mean,
+               const float *var, const float *weight, float eps, int training, float *gx,
+               float *d_weight, float *d_bias, void *scratch, size_t scratch_bytes, void *stream);
+
+/* Backward of the gated activation without biases (SS_Conv_lib/ss_conv/activation.py:55-100):
+ * x [n, c_total] = [c_out Rs channels | gate scalars] is the layer's input, gy [n, c_out] the gradient
+ * of its output, gx [n, c_total].  gate_of_channel as in ssc_bn_gate_fwd; field_start / field_len
+ * [c_total - c_out]: the channel range that gate j multiplies. */
+int ssc_gate_bwd(const float *x, const float *gy, int n, int c_total, int c_out,
+                 const int32_t *gate_of_channel, const int32_t *field_start, const int32_t *field_len,
+                 int scalar_act, int gate_act, float *gx, void *stream);
 
 #ifdef __cplusplus
 }

@@ -154,28 +154,56 @@ bn_gate_vec4_out16_kernel(const float *__restrict__ x, uint32_t total, uint32_t 
                     : make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
 }
 
-// Column sums with one block per 32-channel group: block (32, 8), rows strided by 8*gridDim.y.
-// pass 0: sum of x per channel; pass 1: sum of (x - mean_ch)^2 per channel (mean_ch = 0 for
-// non-scalar channels), accumulated per field.
-__global__ void bn_colsum_kernel(const float *__restrict__ x, int n, int c, const float *__restrict__ chan_mean,
-                                 float *__restrict__ acc, const int32_t *__restrict__ bucket_of_channel) {
-  __shared__ float sm[8][33];
-  int ch = blockIdx.x * 32 + threadIdx.x;
-  float s = 0.f;
+// Column sums, deterministic: block (32, 8) owns 32 channels and every gridDim.y-th group of 8
+// rows and writes its partial sums to part[blockIdx.y][channel]; colsum_finish adds the partials
+// of a bucket's channels in a fixed order (ascending channel, ascending row block), so the batch
+// statistics repeat bit for bit.  MODE 0: sum of x; 1: sum of (x - mean_ch)^2; 2: TWO sums for the
+// backward pass, of gy (part) and of gy * (x - mean_ch) (part2).
+template <int MODE>
+__global__ void bn_colsum_kernel(const float *__restrict__ x, const float *__restrict__ gy, int n, int c,
+                                 const float *__restrict__ chan_mean, float *__restrict__ part,
+                                 float *__restrict__ part2) {
+  __shared__ float sm[8][33], sm2[8][33];
+  const int ch = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.f, s2 = 0.f;
   if (ch < c) {
-    float mu = chan_mean ? chan_mean[ch] : 0.f;
+    const float mu = (MODE != 0 && chan_mean) ? chan_mean[ch] : 0.f;
     for (int r = blockIdx.y * 8 + threadIdx.y; r < n; r += 8 * gridDim.y) {
-      float v = x[(size_t)r * c + ch] - mu;
-      s += chan_mean ? v * v : v;
+      const float v = x[(size_t)r * c + ch] - mu;
+      if (MODE == 0) s += v;
+      else if (MODE == 1) s += v * v;
+      else {
+        const float g = gy[(size_t)r * c + ch];
+        s += g;
+        s2 += g * v;
+      }
     }
   }
   sm[threadIdx.y][threadIdx.x] = s;
+  if (MODE == 2) sm2[threadIdx.y][threadIdx.x] = s2;
   __syncthreads();
   if (threadIdx.y == 0 && ch < c) {
     for (int g = 1; g < 8; ++g) s += sm[g][threadIdx.x];
-    int b = bucket_of_channel[ch];
-    if (b >= 0) atomicAdd(acc + b, s);
+    part[(size_t)blockIdx.y * c + ch] = s;
+    if (MODE == 2) {
+      for (int g = 1; g < 8; ++g) s2 += sm2[g][threadIdx.x];
+      part2[(size_t)blockIdx.y * c + ch] = s2;
+    }
   }
+}
+
+// acc[b] = sum over the channels ch with bucket_of_channel[ch] == b (consecutive channels) and over
+// the row blocks of part[rb][ch]; one thread per bucket, fixed order.
+__global__ void colsum_finish_kernel(const float *__restrict__ part, int row_blocks, int c,
+                                     const int32_t *__restrict__ bucket_of_channel, int n_bucket, float *__restrict__ acc) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n_bucket) return;
+  float s = 0.f;
+  for (int ch = 0; ch < c; ++ch) {
+    if (bucket_of_channel[ch] != b) continue;
+    for (int rb = 0; rb < row_blocks; ++rb) s += part[(size_t)rb * c + ch];
+  }
+  acc[b] = s;
 }
 
 // chan_mean[ch] = batch mean of a scalar channel (0 for l>0 channels), from the channel sums.
@@ -190,6 +218,77 @@ __global__ void bn_chan_mean_kernel(const float *sum_scalar, int n, const int32_
 __global__ void bn_finish_var_kernel(float *var, int n_field, int n) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n_field) var[i] = var[i] / (float)n;
+}
+
+// ------------------------------------------------------------------ backward of the batch norm
+// y = (x - mu) * r * w (+ b), r = (v + eps)^-1/2, v = mean over rows of the squared field norm.
+// With A_f = sum over rows and components of gy * (x - mu) and G_s = sum over rows of gy:
+//   d_w[f] = r A_f,  d_b[s] = G_s,
+//   training:  gx = r w gy - (w r^3 A_f / N) (x - mu) - [scalars] (r w G_s / N)
+//   eval:      gx = r w gy
+// Per channel: ks = r w, ka = w r^3 A / N (0 in eval mode), kg = r w G / N (scalars in training mode).
+__global__ void bn_bwd_coef_kernel(const float *__restrict__ A, const float *__restrict__ G, const float *__restrict__ var,
+                                   const float *__restrict__ weight, const int32_t *__restrict__ field_of_channel,
+                                   const int32_t *__restrict__ scalar_of_channel, int c, int n_field, int n, float eps,
+                                   int training, float *__restrict__ ks, float *__restrict__ ka, float *__restrict__ kg,
+                                   float *__restrict__ d_weight, float *__restrict__ d_bias, int n_scalar) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < c) {
+    const int f = field_of_channel[i], s = scalar_of_channel[i];
+    const float r = 1.0f / sqrtf(var[f] + eps), w = weight ? weight[f] : 1.f;
+    ks[i] = r * w;
+    ka[i] = training ? w * r * r * r * A[f] / (float)n : 0.f;
+    kg[i] = (training && s >= 0) ? r * w * G[s] / (float)n : 0.f;
+  }
+  if (i < n_field && d_weight) d_weight[i] = A[i] / sqrtf(var[i] + eps);
+  if (i < n_scalar && d_bias) d_bias[i] = G[i];
+}
+
+__global__ void bn_bwd_apply_kernel(const float *__restrict__ x, const float *__restrict__ gy, long long total, int c,
+                                    const float *__restrict__ chan_mean, const float *__restrict__ ks,
+                                    const float *__restrict__ ka, const float *__restrict__ kg, float *__restrict__ gx) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const int ch = (int)(t % c);
+  gx[t] = ks[ch] * gy[t] - ka[ch] * (x[t] - chan_mean[ch]) - kg[ch];
+}
+
+// ------------------------------------------------------------- backward of the gated activation
+// x [n, c_total] = [Rs channels | gate scalars], gy [n, c_out] -> gx [n, c_total].
+//   copy channel: gx = gy; scalar channel: gx = gy * act'(x); gated channel: gx = gy * act(gate);
+//   gate scalar j: gx = act'(x_gate) * sum over the channels ch of its field of gy[ch] * x[ch].
+__device__ __forceinline__ float act_grad(float v, int kind) {
+  if (kind == 1) return v > 0.f ? 1.f : 0.f;
+  if (kind == 2) {
+    const float sg = 1.0f / (1.0f + expf(-v));
+    return sg * (1.f - sg);
+  }
+  return 1.f;
+}
+
+__global__ void gate_bwd_kernel(const float *__restrict__ x, const float *__restrict__ gy, long long total, int c_total,
+                                int c_out, const int32_t *__restrict__ gate_of_channel,
+                                const int32_t *__restrict__ field_start, const int32_t *__restrict__ field_len,
+                                int scalar_act, int gate_act, float *__restrict__ gx) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const long long row = t / c_total;
+  const int ch = (int)(t - row * c_total);
+  const float *xr = x + row * c_total;
+  const float *gr = gy + row * c_out;
+  float v;
+  if (ch < c_out) {
+    const int g = gate_of_channel[ch];
+    if (g == -1) v = gr[ch] * act_grad(xr[ch], scalar_act);
+    else if (g >= 0) v = gr[ch] * apply_act(xr[c_out + g], gate_act);
+    else v = gr[ch];
+  } else {
+    const int j = ch - c_out, s0 = field_start[j], len = field_len[j];
+    float acc = 0.f;
+    for (int q = 0; q < len; ++q) acc += gr[s0 + q] * xr[s0 + q];
+    v = acc * act_grad(xr[ch], gate_act);
+  }
+  gx[t] = v;
 }
 
 }  // namespace ssc
@@ -257,26 +356,77 @@ extern "C" int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const fl
   return SSC_OK;
 }
 
-// mean/var double as accumulators; chan_mean lives in the first c floats after var's
-// n_field entries is NOT assumed: the caller passes var with room for n_field + c floats.
+// Row blocks of the column-sum kernels (each contributes one partial per channel).
+static int bn_row_blocks(int n) {
+  int rb = ceil_div(n, 8 * 64);
+  return rb > 64 ? 64 : (rb < 1 ? 1 : rb);
+}
+
+extern "C" size_t ssc_bn_scratch_bytes(int n, int c) {
+  if (n < 0 || c < 1) return 0;
+  // two partial-sum planes [row_blocks, c], per-channel mean and three coefficient rows, two bucket rows
+  return ((size_t)2 * bn_row_blocks(n) * c + (size_t)6 * c + 64) * sizeof(float);
+}
+
+// var must have room for n_field + c floats (the tail holds the per-channel means); scratch holds the
+// partial sums: ssc_bn_scratch_bytes(n, c).
 extern "C" int ssc_bn_stats(const float *x, int n, int c, const int32_t *field_of_channel,
                             const int32_t *scalar_of_channel, int n_field, int n_scalar, float *mean, float *var,
-                            void *stream) {
+                            void *scratch, size_t scratch_bytes, void *stream) {
   SSC_REQUIRE(n >= 1 && c >= 1 && n_field >= 1 && n_scalar >= 0, "bn_stats: bad sizes");
   SSC_REQUIRE(x && field_of_channel && scalar_of_channel && mean && var, "bn_stats: null pointer");
+  SSC_REQUIRE(scratch && scratch_bytes >= ssc_bn_scratch_bytes(n, c), "bn_stats: scratch too small (ssc_bn_scratch_bytes)");
   cudaStream_t st = as_stream(stream);
   float *chan_mean = var + n_field;  // scratch tail, c floats
-  cudaMemsetAsync(mean, 0, (size_t)(n_scalar > 0 ? n_scalar : 1) * 4, st);
-  cudaMemsetAsync(var, 0, (size_t)n_field * 4, st);
-  dim3 block(32, 8);
-  int row_blocks = ceil_div(n, 8 * 64);
-  if (row_blocks > 64) row_blocks = 64;
-  dim3 grid(ceil_div(c, 32), row_blocks);
-  { bn_colsum_kernel<<<grid, block, 0, st>>>(x, n, c, nullptr, mean, scalar_of_channel); note_launches(1); }
+  float *part = (float *)scratch;
+  const int rb = bn_row_blocks(n);
+  dim3 block(32, 8), grid(ceil_div(c, 32), rb);
+  { bn_colsum_kernel<0><<<grid, block, 0, st>>>(x, nullptr, n, c, nullptr, part, nullptr); note_launches(1); }
+  if (n_scalar > 0) { colsum_finish_kernel<<<ceil_div(n_scalar, 64), 64, 0, st>>>(part, rb, c, scalar_of_channel, n_scalar, mean); note_launches(1); }
   { bn_chan_mean_kernel<<<ceil_div(c, 128), 128, 0, st>>>(mean, n, scalar_of_channel, c, chan_mean); note_launches(1); }
   if (n_scalar > 0) { bn_finish_var_kernel<<<ceil_div(n_scalar, 128), 128, 0, st>>>(mean, n_scalar, n); note_launches(1); }
-  { bn_colsum_kernel<<<grid, block, 0, st>>>(x, n, c, chan_mean, var, field_of_channel); note_launches(1); }
+  { bn_colsum_kernel<1><<<grid, block, 0, st>>>(x, nullptr, n, c, chan_mean, part, nullptr); note_launches(1); }
+  { colsum_finish_kernel<<<ceil_div(n_field, 64), 64, 0, st>>>(part, rb, c, field_of_channel, n_field, var); note_launches(1); }
   { bn_finish_var_kernel<<<ceil_div(n_field, 128), 128, 0, st>>>(var, n_field, n); note_launches(1); }
   SSC_CHECK_LAUNCH("bn_stats");
+  return SSC_OK;
+}
+
+extern "C" int ssc_bn_bwd(const float *x, const float *gy, int n, int c, const int32_t *field_of_channel,
+                          const int32_t *scalar_of_channel, int n_field, int n_scalar, const float *mean,
+                          const float *var, const float *weight, float eps, int training, float *gx,
+                          float *d_weight, float *d_bias, void *scratch, size_t scratch_bytes, void *stream) {
+  SSC_REQUIRE(n >= 1 && c >= 1 && n_field >= 1 && n_scalar >= 0, "bn_bwd: bad sizes");
+  SSC_REQUIRE(x && gy && field_of_channel && scalar_of_channel && var && gx && (n_scalar == 0 || mean), "bn_bwd: null pointer");
+  SSC_REQUIRE(scratch && scratch_bytes >= ssc_bn_scratch_bytes(n, c), "bn_bwd: scratch too small (ssc_bn_scratch_bytes)");
+  cudaStream_t st = as_stream(stream);
+  const int rb = bn_row_blocks(n);
+  float *part = (float *)scratch, *part2 = part + (size_t)rb * c;
+  float *chan_mean = part2 + (size_t)rb * c, *ks = chan_mean + c, *ka = ks + c, *kg = ka + c;
+  float *A = kg + c, *G = A + c;     // per field / per scalar (at most c entries each)
+  { bn_chan_mean_kernel<<<ceil_div(c, 128), 128, 0, st>>>(mean, 1, scalar_of_channel, c, chan_mean); note_launches(1); }   // mean itself (n = 1)
+  dim3 block(32, 8), grid(ceil_div(c, 32), rb);
+  { bn_colsum_kernel<2><<<grid, block, 0, st>>>(x, gy, n, c, chan_mean, part, part2); note_launches(1); }
+  if (n_scalar > 0) { colsum_finish_kernel<<<ceil_div(n_scalar, 64), 64, 0, st>>>(part, rb, c, scalar_of_channel, n_scalar, G); note_launches(1); }
+  { colsum_finish_kernel<<<ceil_div(n_field, 64), 64, 0, st>>>(part2, rb, c, field_of_channel, n_field, A); note_launches(1); }
+  const int m = c > n_field ? c : n_field;
+  { bn_bwd_coef_kernel<<<ceil_div(m, 128), 128, 0, st>>>(A, G, var, weight, field_of_channel, scalar_of_channel, c, n_field, n, eps,
+                                                     training, ks, ka, kg, d_weight, d_bias, n_scalar); note_launches(1); }
+  const long long total = (long long)n * c;
+  { bn_bwd_apply_kernel<<<ceil_div(total, 256), 256, 0, st>>>(x, gy, total, c, chan_mean, ks, ka, kg, gx); note_launches(1); }
+  SSC_CHECK_LAUNCH("bn_bwd");
+  return SSC_OK;
+}
+
+extern "C" int ssc_gate_bwd(const float *x, const float *gy, int n, int c_total, int c_out,
+                            const int32_t *gate_of_channel, const int32_t *field_start, const int32_t *field_len,
+                            int scalar_act, int gate_act, float *gx, void *stream) {
+  SSC_REQUIRE(n >= 0 && c_total >= 1 && c_out >= 1 && c_out <= c_total, "gate_bwd: bad sizes");
+  if (n == 0) return SSC_OK;
+  SSC_REQUIRE(x && gy && gx && gate_of_channel && (c_total == c_out || (field_start && field_len)), "gate_bwd: null pointer");
+  const long long total = (long long)n * c_total;
+  { gate_bwd_kernel<<<ceil_div(total, 256), 256, 0, as_stream(stream)>>>(x, gy, total, c_total, c_out, gate_of_channel, field_start,
+                                                                      field_len, scalar_act, gate_act, gx); note_launches(1); }
+  SSC_CHECK_LAUNCH("gate_bwd");
   return SSC_OK;
 }

@@ -96,7 +96,13 @@ SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_void_p]),
     "ssc_bn_gate_fwd16": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
-    "ssc_bn_stats": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ssc_bn_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "ssc_bn_stats": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                             c_size_t, c_void_p]),
+    "ssc_bn_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ssc_gate_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_void_p, c_void_p]),
 }
 
 _lib_handle = None
@@ -1146,7 +1152,37 @@ def bn_stats(x, field_of_channel, scalar_of_channel, n_field, n_scalar):
     x = x.contiguous()
     mean = torch.empty(max(n_scalar, 1), dtype=torch.float32, device=x.device)
     var = torch.empty(n_field + x.shape[1], dtype=torch.float32, device=x.device)
+    nbytes = int(lib().ssc_bn_scratch_bytes(x.shape[0], x.shape[1]))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
     _check(lib().ssc_bn_stats(_p(x, torch.float32), x.shape[0], x.shape[1], _p(field_of_channel, torch.int32),
                               _p(scalar_of_channel, torch.int32), int(n_field), int(n_scalar), _p(mean), _p(var),
-                              _stream()))
+                              _p(scratch), nbytes, _stream()))
     return mean[:n_scalar], var[:n_field]
+
+
+def bn_backward(x, gy, field_of_channel, scalar_of_channel, n_field, n_scalar, mean, var, weight, eps, training):
+    """(gx [n, c], d_weight [n_field], d_bias [n_scalar]) of y = (x - mean) * weight / sqrt(var + eps) + bias;
+    training: mean / var are the batch statistics of x and the gradient flows through them."""
+    x, gy = x.contiguous(), gy.contiguous()
+    n, c = x.shape
+    gx = torch.empty_like(x)
+    d_w = torch.empty(n_field, dtype=torch.float32, device=x.device)
+    d_b = torch.empty(max(n_scalar, 1), dtype=torch.float32, device=x.device)
+    nbytes = int(lib().ssc_bn_scratch_bytes(n, c))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    mean_c = None if n_scalar == 0 else mean.contiguous()
+    _check(lib().ssc_bn_bwd(_p(x, torch.float32), _p(gy, torch.float32), n, c, _p(field_of_channel, torch.int32),
+                            _p(scalar_of_channel, torch.int32), int(n_field), int(n_scalar), _p(mean_c),
+                            _p(var.contiguous()), _p(weight), float(eps), int(bool(training)), _p(gx), _p(d_w), _p(d_b),
+                            _p(scratch), nbytes, _stream()))
+    return gx, d_w, d_b[:n_scalar]
+
+
+def gate_backward(x, gy, c_out, gate_of_channel, field_start, field_len, scalar_act, gate_act):
+    """gx [n, c_total] of the gated activation (no biases) at input x, output gradient gy [n, c_out]."""
+    x, gy = x.contiguous(), gy.contiguous()
+    gx = torch.empty_like(x)
+    _check(lib().ssc_gate_bwd(_p(x, torch.float32), _p(gy, torch.float32), x.shape[0], x.shape[1], int(c_out),
+                              _p(gate_of_channel, torch.int32), _p(field_start), _p(field_len), int(scalar_act),
+                              int(gate_act), _p(gx), _stream()))
+    return gx

@@ -21,6 +21,27 @@ def _act_code(fn):
     return None
 
 
+class _GateFn(torch.autograd.Function):
+    """The fused gated activation (relu / sigmoid / identity, no biases) with the library's
+    kernels in both directions."""
+
+    @staticmethod
+    def forward(ctx, x, module, s_code, g_code):
+        x = x.contiguous()
+        C = Rs2dim(module.Rs)
+        table = module._gate_table(x.device)
+        ctx.save_for_backward(x)
+        ctx.module, ctx.codes, ctx.c_out = module, (s_code, g_code), C
+        return _ext.bn_gate_forward(x, None, None, table, C, C, s_code, g_code, None, None)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (x,) = ctx.saved_tensors
+        m = ctx.module
+        start, length = m._field_ranges(x.device)
+        return _ext.gate_backward(x, gy, ctx.c_out, m._gate_table(x.device), start, length, *ctx.codes), None, None, None
+
+
 class ScalarActivation(nn.Module):
     """Holds the optional bias added before an activation of scalar channels."""
 
@@ -95,6 +116,21 @@ class Activation(nn.Module):
             self._table = (device, torch.tensor(tab, dtype=torch.int32, device=device))
         return self._table[1]
 
+    def _field_ranges(self, device):
+        """Per gate scalar: first channel and length of the field it multiplies."""
+        if getattr(self, "_ranges", None) is None or self._ranges[0] != device:
+            start, length, ch = [], [], 0
+            for m, l in self.Rs:
+                d = 2 * l + 1
+                for _ in range(m):
+                    if l > 0:
+                        start.append(ch)
+                        length.append(d)
+                    ch += d
+            self._ranges = (device, torch.tensor(start or [0], dtype=torch.int32, device=device),
+                            torch.tensor(length or [0], dtype=torch.int32, device=device))
+        return self._ranges[1], self._ranges[2]
+
     def fusable(self):
         return _act_code(self._scalar_fn if self.scalar_act is not None else None) is not None and \
             _act_code(self._gate_fn if self.gate_act is not None else None) is not None
@@ -123,6 +159,12 @@ class Activation(nn.Module):
             g_bias = self.gate_act.bias.detach() if (self.gate_act is not None and self.gate_act.bias is not None) else None
             return _ext.bn_gate_forward(y, scale, shift, self._gate_table(y.device), C, C, s_code, g_code, s_bias,
                                         g_bias, storage=_ext.get_feature_storage())
+        no_bias = (self.scalar_act is None or self.scalar_act.bias is None) and \
+            (self.gate_act is None or self.gate_act.bias is None)
+        if self.fusable() and y.is_cuda and y.dtype == torch.float32 and no_bias and scale is None and y.shape[0] > 0:
+            s_code = _act_code(self._scalar_fn) if self.scalar_act is not None else 0
+            g_code = _act_code(self._gate_fn) if self.gate_act is not None else 0
+            return _GateFn.apply(y, self, s_code, g_code)     # recording: the library's kernels forward and backward
         return self._gate_composite(y if scale is None else y * scale + shift)
 
     def _gate_composite(self, y):

@@ -20,6 +20,42 @@ def _channel_tables(Rs):
     return field, scalar
 
 
+class _BatchNormFn(torch.autograd.Function):
+    """y = (x - mean) * weight / sqrt(var + eps) + bias with the library's kernels in both directions.
+    Training mode: mean / var are the batch statistics (ssc_bn_stats) and the gradient flows through
+    them; eval mode: the running buffers, constants."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, module, training):
+        x = x.contiguous()
+        field, scalar = module._device_tables(x.device)
+        n_field, n_scalar = module.running_var.numel(), module.running_mean.numel()
+        if training:
+            mean, var = _ext.bn_stats(x, field, scalar, n_field, n_scalar)
+            with torch.no_grad():
+                module.running_mean.mul_(1 - module.momentum).add_(module.momentum * mean)
+                module.running_var.mul_(1 - module.momentum).add_(module.momentum * var)
+        else:
+            mean, var = module.running_mean.clone(), module.running_var.clone()
+        w = None if weight is None else weight.detach().contiguous()
+        b = None if (bias is None or n_scalar == 0) else bias.detach().contiguous()
+        scale, shift = _ext.bn_fold(mean if n_scalar > 0 else None, var, w, b, field, scalar, module.eps)
+        y = _ext.bn_gate_forward(x, scale, shift, None, x.size(1), 0, 0, 0, None, None)
+        ctx.save_for_backward(x, mean, var, w if w is not None else x.new_empty(0))
+        ctx.tables, ctx.sizes, ctx.eps, ctx.training_mode = (field, scalar), (n_field, n_scalar), module.eps, bool(training)
+        ctx.has_w, ctx.has_b = weight is not None, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, mean, var, w = ctx.saved_tensors
+        field, scalar = ctx.tables
+        n_field, n_scalar = ctx.sizes
+        gx, d_w, d_b = _ext.bn_backward(x, gy, field, scalar, n_field, n_scalar, mean, var, w if ctx.has_w else None,
+                                        ctx.eps, ctx.training_mode)
+        return gx, (d_w if ctx.has_w else None), (d_b if ctx.has_b else None), None, None
+
+
 class BatchNorm(nn.Module):
     """Scalars (l=0) are centred and scaled; fields with l>0 are only scaled by the running mean
     of their squared norm, which keeps the layer equivariant.  Same parameters and buffers as
@@ -27,8 +63,10 @@ class BatchNorm(nn.Module):
 
     Eval mode is one fused CUDA pass y = x*scale + shift with the statistics folded into
     per-channel constants.  Training mode computes batch statistics on the GPU (two
-    reductions), updates the running buffers and applies the same pass; gradients do not flow
-    through it yet."""
+    reductions, added in a fixed order), updates the running buffers and applies the same pass.
+    While autograd records, the same kernels run inside an autograd Function whose backward is the
+    library's batch-norm gradient (through the batch statistics in training mode); only an
+    unsupported `reduce` option or a CPU tensor takes the composite of torch ops."""
 
     def __init__(self, Rs, eps=1e-5, momentum=0.1, affine=True, reduce='mean'):
         super().__init__()
@@ -117,7 +155,12 @@ class BatchNorm(nn.Module):
                                         (self.training and self.affine and self.weight.requires_grad)):
             if self.training and self.reduce != 'mean':
                 raise ValueError("Invalid reduce option {}".format(self.reduce))
-            input.features = self._differentiable(input.features)
+            feats = input.features
+            if feats.is_cuda and feats.dtype == torch.float32 and feats.shape[0] > 0:
+                input.features = _BatchNormFn.apply(feats, self.weight if self.affine else None,
+                                                    self.bias if self.affine else None, self, self.training)
+            else:
+                input.features = self._differentiable(feats)
             return input
         # eval mode works row by row, so it can run on a tensor whose row count is still pending
         x = input.features if self.training else input.raw()[0]

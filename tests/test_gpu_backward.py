@@ -278,3 +278,52 @@ def test_training_step_through_conv_bn_gate(cuda):
         assert rel_err(x1.detach().cpu().numpy(), x2.cpu().numpy()) <= 1e-5
     finally:
         _ext.set_precision("auto")
+
+
+@pytest.mark.parametrize("training", [True, False])
+def test_batchnorm_and_gate_backward_kernels(cuda, training):
+    """BatchNorm and the gated activation under autograd run the library's kernels in both
+    directions (ssc_bn_stats / ssc_bn_bwd / ssc_gate_bwd).  Gradients of the input and of the affine
+    parameters, the outputs and the updated running statistics against the same layers evaluated as a
+    float64 composite of torch ops on the CPU (what the reference's autograd would compute,
+    SS_Conv_lib/ss_conv/batchnorm.py:49-136, activation.py:55-100)."""
+    import copy
+    from ss_conv import _ext
+    from ss_conv.activation import Activation
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.sp_ops.tensor import SparseTensor
+    torch.manual_seed(4)
+    Rs = [(3, 0), (2, 1), (2, 2), (1, 3)]
+    gated = Rs + [(5, 0)]
+    n, c = 3000, 3 + 6 + 10 + 7 + 5
+    bn = BatchNorm(gated, momentum=0.1).to(cuda)
+    act = Activation(Rs, (torch.relu, torch.sigmoid), bias=False, checkpoint=False).to(cuda)
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.normal_(0, 0.3)
+        bn.running_var.uniform_(0.5, 2.0)
+        bn.running_mean.normal_(0, 0.2)
+    bn.train(training)
+    bn64, act64 = copy.deepcopy(bn).double().cpu(), copy.deepcopy(act).double().cpu()
+    x = (torch.randn(n, c, device=cuda) * 1.3 + 0.2).requires_grad_(True)
+    coef = torch.randn(n, 26, device=cuda)
+    ind = torch.zeros(n, 4, dtype=torch.int32, device=cuda)
+    l0 = _ext.kernel_launches()
+    y = act(bn(SparseTensor(x, ind, [8] * 3, 1))).features
+    (y * coef).sum().backward()
+    assert _ext.kernel_launches() - l0 >= 6          # statistics, affine pass, gate, and their backward kernels
+    x64 = x.detach().double().cpu().requires_grad_(True)
+    y64 = act64._gate_composite(bn64._differentiable(x64))
+    (y64 * coef.double().cpu()).sum().backward()
+    assert rel_err(y.detach().cpu().numpy(), y64.detach().numpy()) <= 2e-5
+    assert rel_err(x.grad.cpu().numpy(), x64.grad.numpy()) <= 1e-4
+    assert rel_err(bn.weight.grad.cpu().numpy(), bn64.weight.grad.numpy()) <= 1e-4
+    assert rel_err(bn.bias.grad.cpu().numpy(), bn64.bias.grad.numpy()) <= 1e-4
+    assert rel_err(bn.running_var.cpu().numpy(), bn64.running_var.numpy()) <= 1e-5
+    assert rel_err(bn.running_mean.cpu().numpy(), bn64.running_mean.numpy()) <= 1e-5
+    if training:      # the batch statistics are added in a fixed order: a second pass gives the same bits
+        bn2 = copy.deepcopy(bn)
+        x2 = x.detach().clone().requires_grad_(True)
+        ya = bn(SparseTensor(x2, ind, [8] * 3, 1)).features
+        yb = bn2(SparseTensor(x2, ind, [8] * 3, 1)).features
+        assert torch.equal(ya, yb)
