@@ -4,8 +4,9 @@ ctypes calls into the C-ABI CUDA library libssconv_b200.so (include/ssconv_b200.
 
 PyTorch is used only to allocate device memory and to supply the current CUDA stream.  There
 is no CPU path: every function raises if the library is missing or a tensor is not on a CUDA
-device.  Forward / inference entry points are implemented; the backward entry points raise
-NotImplementedError.
+device.  The forward and backward entry points of the 3-D path are implemented (fp32, and the half
+variants of convolution and pools); only the functions the reference's own Python never reaches
+(indice_field_maxpool_*, voxelize_idx, point_recover_*) and the 2-D rulebooks raise NotImplementedError.
 """
 import ctypes
 import os
@@ -813,8 +814,8 @@ def indice_conv_fp32(features, filters, indice_pairs, indice_num, num_act_out, i
 
 def _not_built(name):
     def f(*a, **k):
-        raise NotImplementedError(name + " is not built: this library covers the fp32 forward and backward path; "
-                                  "fp16 pools and the field max pool are not part of it")
+        raise NotImplementedError(name + " is not built: the reference's own Python never calls it "
+                                  "(dead entry point of its extension)")
     f.__name__ = name
     return f
 
@@ -970,8 +971,19 @@ def indiceSummaryRF(indice_pairs, indice_num, num_act):
     return rf
 
 
-indice_maxpool_half = _not_built("indice_maxpool_half")
-indice_avgpool_half = _not_built("indice_avgpool_half")
+def indice_maxpool_half(features, indice_pairs, indice_num, num_act):
+    """(SS_Conv_lib/src/ss_conv_ops.h:58) half tensors in and out; the pool kernel works on the
+    widened values (a maximum of fp16 values is exact), the result is narrowed again."""
+    if features.dtype != torch.half:
+        raise TypeError("indice_maxpool_half expects float16 features")
+    return indice_maxpool_fp32(features.float(), indice_pairs, indice_num, num_act).half()
+
+
+def indice_avgpool_half(features, indice_pairs, indice_num, num_act, summaryrf):
+    """(SS_Conv_lib/src/ss_conv_ops.h:62) half tensors in and out, sums in fp32, one rounding at the end."""
+    if features.dtype != torch.half:
+        raise TypeError("indice_avgpool_half expects float16 features")
+    return indice_avgpool_fp32(features.float(), indice_pairs, indice_num, num_act, summaryrf).half()
 def indice_maxpool_backward_fp32(features, out_features, out_bp, indice_pairs, indice_num):
     """(SS_Conv_lib/src/ss_conv_ops.h:58-59) gradient to every input that equals its pooled value."""
     features, out_features, out_bp = features.contiguous(), out_features.contiguous(), out_bp.contiguous()
@@ -993,8 +1005,16 @@ def indice_avgpool_backward_fp32(features, out_features, out_bp, indice_pairs, i
     return d_in
 
 
-indice_maxpool_backward_half = _not_built("indice_maxpool_backward_half")
-indice_avgpool_backward_half = _not_built("indice_avgpool_backward_half")
+def indice_maxpool_backward_half(features, out_features, out_bp, indice_pairs, indice_num):
+    """(SS_Conv_lib/src/ss_conv_ops.h:59) half tensors in and out."""
+    return indice_maxpool_backward_fp32(features.float(), out_features.float(), out_bp.float(), indice_pairs,
+                                        indice_num).half()
+
+
+def indice_avgpool_backward_half(features, out_features, out_bp, indice_pairs, indice_num, summaryrf):
+    """(SS_Conv_lib/src/ss_conv_ops.h:63) half tensors in and out."""
+    return indice_avgpool_backward_fp32(features.float(), out_features.float(), out_bp.float(), indice_pairs, indice_num,
+                                        summaryrf).half()
 indice_field_maxpool_fp32 = _not_built("indice_field_maxpool_fp32")
 indice_field_maxpool_half = _not_built("indice_field_maxpool_half")
 

@@ -285,3 +285,24 @@ def test_steerable_convolution_is_equivariant_under_grid_rotations(cuda, axis):
         assert rel_err(fa, fb) <= 1e-4
     finally:
         _ext.set_precision("auto")
+
+
+def test_half_precision_pool_entry_points(cuda):
+    """indice_maxpool_half / indice_avgpool_half and their backward entry points (half tensors in and
+    out, SS_Conv_lib/src/ss_conv_ops.h:58-63) against the fp32 entry points on the same fp16 values."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(6)
+    ind = random_voxels(rng, 2, 12, 500)
+    outids, pairs, num = gpu_rulebook(ind, 2, [12] * 3, 2, 2, 0, 1, False, cuda)
+    n_out = outids.shape[0]
+    f16 = dev(rng.randn(ind.shape[0], 24).astype(np.float32), cuda).half()
+    mx = _ext.indice_maxpool_half(f16, pairs, num, n_out)
+    assert mx.dtype == torch.half and torch.equal(mx, _ext.indice_maxpool_fp32(f16.float(), pairs, num, n_out).half())
+    av = _ext.indice_avgpool_half(f16, pairs, num, n_out, None)
+    assert av.dtype == torch.half and torch.equal(av, _ext.indice_avgpool_fp32(f16.float(), pairs, num, n_out, None).half())
+    g = torch.randn(n_out, 24, device=cuda).half()
+    d1 = _ext.indice_maxpool_backward_half(f16, mx, g, pairs, num)
+    assert d1.dtype == torch.half and d1.shape == f16.shape
+    assert torch.equal(d1, _ext.indice_maxpool_backward_fp32(f16.float(), mx.float(), g.float(), pairs, num).half())
+    d2 = _ext.indice_avgpool_backward_half(f16, av, g, pairs, num, None)
+    assert d2.dtype == torch.half and d2.shape == f16.shape
