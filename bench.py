@@ -367,6 +367,7 @@ def layer_numbers(name, ind, batch, V, k, stride, pad, subm, c_in, c_out, precis
     flops = 2.0 * P * c_in * c_out
     alg_bytes = 4.0 * (n_in * c_in + n_out * c_out + K * c_in * c_out) + 8.0 * P
     res["algorithmic_bytes"], res["flops"] = alg_bytes, flops
+    ceiling = None
     for prec in precisions:
         prec_id = _ext._PREC_OF[prec]
         uses_pairs = _ext._use_pairs(K, c_in, c_out, n_out, prec_id)
@@ -382,9 +383,39 @@ def layer_numbers(name, ind, batch, V, k, stride, pad, subm, c_in, c_out, precis
             other = graph_ms(lambda: _ext.conv_forward(feats, W, nbr, n_out, prec, algo="rows"), reps=7)
             entry["output_stationary_ms"] = other
             entry["pair_lists_build_ms"] = eager_ms(lambda: _ext.pair_lists(nbr.clone()), reps=5)
+            if ceiling is None:
+                ceiling = scatter_add_ceiling(nbr, n_out, c_out, P)
+            red_bytes = 4.0 * P * c_out
+            entry["scatter_add"] = {"what": "the pair-list kernel adds every accumulator tile to scattered output rows with fp32 "
+                                            "reductions at L2 (4 P Cout bytes per call); ceiling = a kernel that issues nothing but "
+                                            "such reductions over the same row order (ssc_scatter_add_rate), timed here",
+                                    "bytes_per_call": red_bytes, "ceiling_gbs": ceiling,
+                                    "call_gbs": red_bytes / (ms * 1e-3) / 1e9,
+                                    "frac_of_ceiling": red_bytes / (ms * 1e-3) / 1e9 / ceiling,
+                                    "tflops_at_ceiling": ceiling * 1e9 / (4.0 * c_out) * 2.0 * c_in * c_out / 1e12}
         res[prec] = entry
     _ext.check_status(dev)
     return res
+
+
+def scatter_add_ceiling(nbr, n_out, c_out, P):
+    """GB/s of fp32 scatter-add reductions the device takes (nothing else running): the output rows of
+    the layer's pair lists, reduced 128 bytes per row and instruction."""
+    from ss_conv import _ext
+    # the row order of the kernel's sweep: all offsets walk the output rows together, so at any time
+    # the reductions fall into a window of rows that stays in L2; inside the window one offset after
+    # the other (neighbouring list positions = distinct rows, as in a tile of the kernel)
+    nz = torch.nonzero(nbr >= 0)
+    window = 1280
+    key = (nz[:, 1] // window) * nbr.shape[0] + nz[:, 0]
+    order = nz[:, 1][torch.argsort(key, stable=True)].to(torch.int32).contiguous()
+    width = (c_out + 31) // 32 * 32
+    scratch = torch.zeros(n_out, width, device=nbr.device)
+    warps = torch.cuda.get_device_properties(nbr.device).multi_processor_count * 16
+    steps = max(1, -(-P // (warps * 32)))
+    nbytes = _ext.scatter_add_rate(scratch, order, steps)
+    ms = graph_ms(lambda: _ext.scatter_add_rate(scratch, order, steps), reps=7)
+    return nbytes / (ms * 1e-3) / 1e9
 
 
 def layers_leg(dev, peak_hbm, peak_bf16):

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "ss_conv", "libssconv_b200.so")
 SOURCES = ["ssc_error.cu", "ssc_rulebook.cu", "ssc_conv.cu", "ssc_conv_tc.cu", "ssc_conv_stage.cu", "ssc_conv_pairs.cu", "ssc_backward.cu", "ssc_order.cu", "ssc_wgrad_tc.cu", "ssc_pool.cu", "ssc_voxel.cu",
-           "ssc_bnact.cu"]
+           "ssc_bnact.cu", "ssc_ceiling.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -42,8 +42,8 @@ constexpr int PL_M = 128;                 // pairs per tile
 constexpr int PL_A_BYTES = PL_M * 128;    // one gathered slab
 constexpr int PL_MAX_STAGES = 6;
 constexpr int PL_EPI_WARPS = 8;
-constexpr int PL_STG_ROW = 80;            // bytes per row of the epilogue's transpose block (64 + 16 pad)
-constexpr int PL_STG_BYTES = PL_EPI_WARPS * 32 * PL_STG_ROW;
+constexpr int PL_STG_ROW = 144;           // bytes per row of the epilogue's transpose block (128 + 16 pad)
+constexpr int PL_STG_BYTES = PL_EPI_WARPS * 16 * PL_STG_ROW;
 constexpr int PL_CTRL_BYTES = 1024;
 constexpr int PL_MAX_CTAS = 320;
 
@@ -350,10 +350,9 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
     const int ew = warp - mma_warp - 1;                    // 0 .. 7
     const int quarter = warp & 3;                          // the 32 tensor-memory lanes this warp may read
     const int part = ew >> 2;                              // blocks part, part + 2, ...
-    uint8_t *blk = stg + (size_t)ew * 32 * PL_STG_ROW;
+    uint8_t *blk = stg + (size_t)ew * 16 * PL_STG_ROW;
     const bool vec_ok = (c_out & 3) == 0 && ((uintptr_t)out & 15u) == 0;
-    const int sub = lane & 3, grp = lane >> 2;
-    const int prow = (grp >> 1) + (grp & 1) * 4;           // rows of a pass, ordered so that a quarter-warp reads distinct banks
+    const int sub = lane & 7, grp = lane >> 3;             // 16-byte piece of a row, row of a pass
     int tcount = 0;
     bool alive = true;
     for (int si = 0; si < n_strips && alive; ++si) {
@@ -396,36 +395,40 @@ conv_fwd_pairs_kernel(const float *__restrict__ staged, const uint4 *__restrict_
                 : "memory");
           }
         };
-        // 16 columns of this lane's row go to shared memory, then eight rows per pass come back
-        // with four neighbouring lanes holding the 64 contiguous bytes of one output row
-        auto reduce_half = [&](const uint32_t *v, int col) {
+        // The 32 columns of 16 lanes' rows go to shared memory, then four rows per pass come back with
+        // eight neighbouring lanes holding the 128 contiguous bytes of one output row: the
+        // reductions reach L2 as whole 128-byte lines (the L2 slices take ~20 % more bytes per
+        // second in that shape than in 64-byte pieces).
+        auto reduce_block = [&](const uint32_t(&v)[32], int blk_i) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *(uint4 *)(blk + lane * PL_STG_ROW + q * 16) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          __syncwarp();
-          const int cc = col0 + col + sub * 4;
+          for (int h = 0; h < 2; ++h) {
+            if ((lane >> 4) == h) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int row = 8 * i + prow;
-            const int orow = __shfl_sync(0xffffffffu, my_out, row);
-            const float4 x = *(const float4 *)(blk + row * PL_STG_ROW + sub * 16);
-            if (orow >= 0 && cc < c_out) {
-              float *dst = out + (size_t)orow * c_out + cc;
-              if (vec_ok) {
-                red_add_v4(dst, x);
-              } else {
-                atomicAdd(dst, x.x);
-                if (cc + 1 < c_out) atomicAdd(dst + 1, x.y);
-                if (cc + 2 < c_out) atomicAdd(dst + 2, x.z);
-                if (cc + 3 < c_out) atomicAdd(dst + 3, x.w);
+              for (int q = 0; q < 8; ++q)
+                *(uint4 *)(blk + (lane & 15) * PL_STG_ROW + q * 16) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+            __syncwarp();
+            const int c_local = blk_i * 32 + sub * 4;       // column within the strip's range
+            const int cc = col0 + c_local;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = 4 * i + grp;
+              const int orow = __shfl_sync(0xffffffffu, my_out, 16 * h + row);
+              const float4 x = *(const float4 *)(blk + row * PL_STG_ROW + sub * 16);
+              if (orow >= 0 && c_local < cols) {
+                float *dst = out + (size_t)orow * c_out + cc;
+                if (vec_ok) {
+                  red_add_v4(dst, x);
+                } else {
+                  atomicAdd(dst, x.x);
+                  if (cc + 1 < c_out) atomicAdd(dst + 1, x.y);
+                  if (cc + 2 < c_out) atomicAdd(dst + 2, x.z);
+                  if (cc + 3 < c_out) atomicAdd(dst + 3, x.w);
+                }
               }
             }
+            __syncwarp();
           }
-          __syncwarp();
-        };
-        auto reduce_block = [&](const uint32_t(&v)[32], int blk_i) {
-          reduce_half(v, blk_i * 32);
-          if (blk_i * 32 + 16 < cols) reduce_half(v + 16, blk_i * 32 + 16);
         };
         uint32_t va[32], vb[32];
         if (part < n_blocks) tld(va, part);

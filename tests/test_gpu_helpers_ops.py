@@ -306,3 +306,22 @@ def test_half_precision_pool_entry_points(cuda):
     assert torch.equal(d1, _ext.indice_maxpool_backward_fp32(f16.float(), mx.float(), g.float(), pairs, num).half())
     d2 = _ext.indice_avgpool_backward_half(f16, av, g, pairs, num, None)
     assert d2.dtype == torch.half and d2.shape == f16.shape
+
+
+def test_scatter_add_rate_kernel_adds_what_it_reports(cuda):
+    """The reduction-only measurement kernel (ssc_scatter_add_rate): every list position adds 1.0 to
+    a whole row, so the row sums must equal the occurrence counts of the rows it walked and the total
+    must equal the bytes it reports (exact: small integers in fp32)."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(9)
+    n_rows, width = 3000, 64
+    rows = torch.from_numpy(rng.randint(0, n_rows, 50000).astype(np.int32)).to(cuda)
+    out = torch.zeros(n_rows, width, device=cuda)
+    nbytes = _ext.scatter_add_rate(out, rows, 1)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    positions = nbytes // (width * 4)
+    assert positions % 32 == 0 and positions > 0
+    idx = torch.arange(positions, device=cuda) % rows.numel()
+    expect = torch.bincount(rows[idx].long(), minlength=n_rows).float()
+    assert torch.equal(out, expect[:, None].expand(n_rows, width))
