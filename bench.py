@@ -486,7 +486,7 @@ def helper_cases(dev):
     def bn_gate():
         with torch.no_grad():
             return act(bn(SparseTensor(xb, ib, [64] * 3, 1))).features
-    cases.append(("BatchNorm(eval) + gate (bn_gate_vec4_kernel)", bn_gate, 4.0 * nb * 76 + 4.0 * nb * 64))
+    cases.append(("BatchNorm(eval) + gate (bn_gate_rows_kernel)", bn_gate, 4.0 * nb * 76 + 4.0 * nb * 64))
     # voxelizer: 4 M points with 3 features into 64^3 x 64 samples
     from ss_conv.sp_ops.voxelize import Point2Voxel
     npt = 4 * 1024 * 1024

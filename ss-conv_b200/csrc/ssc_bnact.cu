@@ -154,6 +154,82 @@ bn_gate_vec4_out16_kernel(const float *__restrict__ x, uint32_t total, uint32_t 
                     : make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
 }
 
+// The gated pass with every gate evaluated ONCE per row: a block owns R = 256 / groups whole rows,
+// first fills gate_s[r][g] = act(BN(x[row, c_gate_base + g]) + bias) for its rows (one value per
+// thread), then every thread finishes four consecutive channels of one row and takes its gates
+// from shared memory.  The per-element arithmetic is that of the kernels above (same bits); what
+// changes is the instruction count: a thread of the kernels above evaluates up to four
+// sigmoids (expf + IEEE division each, every path taken by some lane of the warp), which made
+// the pass instruction-bound at half the memory rate.  OUT = 0 fp32, 1 fp16, 2 bf16 result.
+template <int OUT>
+__global__ void __launch_bounds__(256)
+bn_gate_rows_kernel(const float *__restrict__ x, uint32_t n_rows, uint32_t groups, int c_in_total,
+                    const float *__restrict__ scale, const float *__restrict__ shift,
+                    const int32_t *__restrict__ gate_of_channel, int c_gate_base, int n_gates, int scalar_act,
+                    int gate_act, const float *__restrict__ scalar_bias, const float *__restrict__ gate_bias,
+                    void *__restrict__ out) {
+  extern __shared__ float gate_s[];                    // [R][n_gates]
+  const uint32_t R = 256u / groups, row0 = blockIdx.x * R, tid = threadIdx.x;
+  // this thread's four channels: the loads go out before the gate phase, so that both phases'
+  // memory latencies overlap
+  const uint32_t r = tid / groups, g4 = tid - r * groups, row = row0 + r;
+  const bool active = r < R && row < n_rows;
+  const int ch0 = (int)g4 * 4;
+  float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (active) xv = __ldg((const float4 *)(x + (size_t)row * c_in_total + ch0));
+  for (uint32_t i = tid; i < R * (uint32_t)n_gates; i += 256u) {
+    const uint32_t gr = i / (uint32_t)n_gates, g = i - gr * (uint32_t)n_gates;
+    if (row0 + gr < n_rows) {
+      float gv = __ldg(x + (size_t)(row0 + gr) * c_in_total + c_gate_base + g);
+      if (scale) gv = fmaf(gv, scale[c_gate_base + g], shift[c_gate_base + g]);
+      if (gate_bias) gv += gate_bias[g];
+      gate_s[i] = apply_act(gv, gate_act);
+    }
+  }
+  __syncthreads();
+  if (!active) return;
+  float v[4] = {xv.x, xv.y, xv.z, xv.w};
+  if (scale) {
+    const float4 sc = __ldg((const float4 *)(scale + ch0)), sh = __ldg((const float4 *)(shift + ch0));
+    v[0] = fmaf(v[0], sc.x, sh.x);
+    v[1] = fmaf(v[1], sc.y, sh.y);
+    v[2] = fmaf(v[2], sc.z, sh.z);
+    v[3] = fmaf(v[3], sc.w, sh.w);
+  }
+  const int4 gi = __ldg((const int4 *)(gate_of_channel + ch0));
+  const int g[4] = {gi.x, gi.y, gi.z, gi.w};
+  const float *my_gates = gate_s + r * (uint32_t)n_gates;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    if (g[q] == -1) {
+      if (scalar_bias) v[q] += scalar_bias[ch0 + q];
+      v[q] = apply_act(v[q], scalar_act);
+    } else if (g[q] >= 0) {
+      v[q] *= my_gates[g[q]];
+    }
+  }
+  const size_t t = (size_t)row * groups + g4;
+  if (OUT == 0) ((float4 *)out)[t] = make_float4(v[0], v[1], v[2], v[3]);
+  else if (OUT == 2) ((uint2 *)out)[t] = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+  else ((uint2 *)out)[t] = make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
+}
+
+// Launch of the row-block kernel when it applies (gated pass, at most 256 vec4 groups per row).
+template <int OUT>
+static bool launch_bn_gate_rows(const float *x, int n, uint32_t groups, int c_in_total, const float *scale, const float *shift,
+                                const int32_t *gate_of_channel, int c_gate_base, int scalar_act, int gate_act,
+                                const float *scalar_bias, const float *gate_bias, void *out, cudaStream_t st) {
+  const int n_gates = c_in_total - c_gate_base;
+  if (gate_of_channel == nullptr || n_gates < 1 || groups < 1 || groups > 256) return false;
+  const uint32_t R = 256u / groups;
+  const size_t smem = (size_t)R * n_gates * sizeof(float);
+  if (smem > 48 * 1024) return false;
+  { bn_gate_rows_kernel<OUT><<<ceil_div(n, (int)R), 256, smem, st>>>(x, (uint32_t)n, groups, c_in_total, scale, shift,
+                                                                     gate_of_channel, c_gate_base, n_gates, scalar_act, gate_act,
+                                                                     scalar_bias, gate_bias, out); note_launches(1); }
+  return true;
+}
+
 // Column sums, deterministic: block (32, 8) owns 32 channels and every gridDim.y-th group of 8
 // rows and writes its partial sums to part[blockIdx.y][channel]; colsum_finish adds the partials
 // of a bucket's channels in a fixed order (ascending channel, ascending row block), so the batch
@@ -318,6 +394,11 @@ extern "C" int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const floa
                    (((uintptr_t)x | (uintptr_t)out | (uintptr_t)scale | (uintptr_t)shift | (uintptr_t)gate_of_channel) & 15u) == 0;
   if (vec) {
     const uint32_t groups = (uint32_t)(c_out >> 2), total4 = (uint32_t)(total >> 2);
+    if (launch_bn_gate_rows<0>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+                               scalar_bias, gate_bias, out, as_stream(stream))) {
+      SSC_CHECK_LAUNCH("bn_gate_fwd");
+      return SSC_OK;
+    }
     { bn_gate_vec4_kernel<<<ceil_div(total4, 256), 256, 0, as_stream(stream)>>>(x, total4, groups, c_in_total, scale, shift,
                                                                             gate_of_channel, c_gate_base, scalar_act, gate_act,
                                                                             scalar_bias, gate_bias, out); note_launches(1); }
@@ -347,6 +428,14 @@ extern "C" int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const fl
   const long long total = (long long)n * c_out;
   SSC_REQUIRE(total / 4 < (1ll << 31), "bn_gate_fwd16: tensor too large");
   const uint32_t groups = (uint32_t)(c_out >> 2), total4 = (uint32_t)(total >> 2);
+  if (precision == SSC_PREC_BF16
+          ? launch_bn_gate_rows<2>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+                                   scalar_bias, gate_bias, out16, as_stream(stream))
+          : launch_bn_gate_rows<1>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+                                   scalar_bias, gate_bias, out16, as_stream(stream))) {
+    SSC_CHECK_LAUNCH("bn_gate_fwd16");
+    return SSC_OK;
+  }
   if (precision == SSC_PREC_BF16) {
     { bn_gate_vec4_out16_kernel<2><<<ceil_div(total4, 256), 256, 0, as_stream(stream)>>>(x, total4, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act, scalar_bias, gate_bias, (uint2 *)out16); note_launches(1); }
   } else {
