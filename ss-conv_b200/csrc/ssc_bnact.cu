@@ -24,7 +24,7 @@ __global__ void bn_fold_kernel(const float *running_mean, const float *running_v
 
 __device__ __forceinline__ float apply_act(float v, int kind) {
   if (kind == 1) return v > 0.f ? v : 0.f;
-  if (kind == 2) return 1.0f / (1.0f + expf(-v));
+  if (kind == 2) return __frcp_rn(1.0f + expf(-v));   // the correctly rounded reciprocal: the bits of 1.0f / (...)
   return v;
 }
 
@@ -169,21 +169,22 @@ bn_gate_rows_kernel(const float *__restrict__ x, uint32_t n_rows, uint32_t group
                     int gate_act, const float *__restrict__ scalar_bias, const float *__restrict__ gate_bias,
                     void *__restrict__ out) {
   extern __shared__ float gate_s[];                    // [R][n_gates]
-  const uint32_t R = 256u / groups, row0 = blockIdx.x * R, tid = threadIdx.x;
-  // this thread's four channels: the loads go out before the gate phase, so that both phases'
-  // memory latencies overlap
-  const uint32_t r = tid / groups, g4 = tid - r * groups, row = row0 + r;
-  const bool active = r < R && row < n_rows;
+  // block = (groups, R): threadIdx.x is the group of four channels, threadIdx.y the row of the block
+  // (no integer division anywhere in the kernel)
+  const uint32_t R = blockDim.y, r = threadIdx.y, g4 = threadIdx.x, row = blockIdx.x * R + r;
+  const bool active = row < n_rows;
   const int ch0 = (int)g4 * 4;
+  // this thread's four channels: the load goes out before the gate phase, so that both phases'
+  // memory latencies overlap
   float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (active) xv = __ldg((const float4 *)(x + (size_t)row * c_in_total + ch0));
-  for (uint32_t i = tid; i < R * (uint32_t)n_gates; i += 256u) {
-    const uint32_t gr = i / (uint32_t)n_gates, g = i - gr * (uint32_t)n_gates;
-    if (row0 + gr < n_rows) {
-      float gv = __ldg(x + (size_t)(row0 + gr) * c_in_total + c_gate_base + g);
+  if (active) {
+    xv = __ldg((const float4 *)(x + (size_t)row * c_in_total + ch0));
+    float *my_gates_w = gate_s + r * (uint32_t)n_gates;
+    for (uint32_t g = g4; g < (uint32_t)n_gates; g += groups) {
+      float gv = __ldg(x + (size_t)row * c_in_total + c_gate_base + g);
       if (scale) gv = fmaf(gv, scale[c_gate_base + g], shift[c_gate_base + g]);
       if (gate_bias) gv += gate_bias[g];
-      gate_s[i] = apply_act(gv, gate_act);
+      my_gates_w[g] = apply_act(gv, gate_act);
     }
   }
   __syncthreads();
@@ -224,7 +225,7 @@ static bool launch_bn_gate_rows(const float *x, int n, uint32_t groups, int c_in
   const uint32_t R = 256u / groups;
   const size_t smem = (size_t)R * n_gates * sizeof(float);
   if (smem > 48 * 1024) return false;
-  { bn_gate_rows_kernel<OUT><<<ceil_div(n, (int)R), 256, smem, st>>>(x, (uint32_t)n, groups, c_in_total, scale, shift,
+  { bn_gate_rows_kernel<OUT><<<ceil_div(n, (int)R), dim3(groups, R), smem, st>>>(x, (uint32_t)n, groups, c_in_total, scale, shift,
                                                                      gate_of_channel, c_gate_base, n_gates, scalar_act, gate_act,
                                                                      scalar_bias, gate_bias, out); note_launches(1); }
   return true;
