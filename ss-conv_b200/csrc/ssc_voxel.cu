@@ -209,6 +209,33 @@ __global__ void p2v_reduce_kernel(const float *__restrict__ feats, int c, const 
   out[t] = acc;
 }
 
+// The same sums with one thread per voxel and the channels (at most 8: xyz, colour, a few scalars)
+// in registers: the point list is read once per voxel instead of once per channel, no 64-bit
+// division.  Per (voxel, channel) the additions happen in the same order as above: same bits.
+template <int CMAX>
+__global__ void __launch_bounds__(256)
+p2v_reduce_small_kernel(const float *__restrict__ feats, int c, const uint32_t *__restrict__ start,
+                        const int32_t *__restrict__ order, int n_voxel, int average, float *__restrict__ out) {
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= n_voxel) return;
+  const int a = (int)start[v], b = (int)start[v + 1];
+  const int n = b - a;
+  const float mult = (average && n > 0) ? __fdiv_rn(1.f, (float)n) : 1.f;
+  float acc[CMAX];
+#pragma unroll
+  for (int ch = 0; ch < CMAX; ++ch) acc[ch] = 0.f;
+  for (int i = a; i < b; ++i) {
+    const float *fp = feats + (size_t)__ldg(order + i) * c;
+#pragma unroll
+    for (int ch = 0; ch < CMAX; ++ch)
+      if (ch < c) acc[ch] = __fadd_rn(acc[ch], __fmul_rn(mult, __ldg(fp + ch)));
+  }
+  float *op = out + (size_t)v * c;
+#pragma unroll
+  for (int ch = 0; ch < CMAX; ++ch)
+    if (ch < c) op[ch] = acc[ch];
+}
+
 __global__ void p2v_select_kernel(const float *__restrict__ feats, int c, const uint32_t *__restrict__ select,
                                   int n_voxel, int n_point, float *__restrict__ out) {
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -502,7 +529,13 @@ extern "C" int ssc_p2v_fill(const float *points, const int32_t *batch_ids, const
     cudaMemcpyAsync(s.cursor, s.count, (size_t)n_voxel * 4, cudaMemcpyDeviceToDevice, st);
     { p2v_scatter_kernel<<<ceil_div(n_point, 256), 256, 0, st>>>(inverse, n_point, s.cursor, s.order); note_launches(1); }
     { p2v_sort_segments_kernel<<<ceil_div(n_voxel, 128), 128, 0, st>>>(s.count, n_voxel, s.order); note_launches(1); }
-    { p2v_reduce_kernel<<<ceil_div(threads, 256), 256, 0, st>>>(feats, c, s.count, s.order, n_voxel, mode == 4, voxel_feats); note_launches(1); }
+    if (c <= 4) {
+      { p2v_reduce_small_kernel<4><<<ceil_div(n_voxel, 256), 256, 0, st>>>(feats, c, s.count, s.order, n_voxel, mode == 4, voxel_feats); note_launches(1); }
+    } else if (c <= 8) {
+      { p2v_reduce_small_kernel<8><<<ceil_div(n_voxel, 256), 256, 0, st>>>(feats, c, s.count, s.order, n_voxel, mode == 4, voxel_feats); note_launches(1); }
+    } else {
+      { p2v_reduce_kernel<<<ceil_div(threads, 256), 256, 0, st>>>(feats, c, s.count, s.order, n_voxel, mode == 4, voxel_feats); note_launches(1); }
+    }
   } else {
     { p2v_select_kernel<<<ceil_div(threads, 256), 256, 0, st>>>(feats, c, s.cursor, n_voxel, n_point, voxel_feats); note_launches(1); }
   }
