@@ -244,7 +244,7 @@ class Backbone:
         return self.graphed.submit(points, feats, ids)
 
 
-def run_backbone(args, dev, rank, world, dist, objects_per_rank, scaling):
+def run_backbone(args, dev, rank, world, dist, objects_per_rank, scaling, overlap=(6, 3, 5)):
     """Backbone samples/s: every rank runs `objects_per_rank` objects per batch, then one all-gather
     of the pooled [objects, 240] rows (the only collective).  `lag` batches are in flight before the
     host waits for the oldest one."""
@@ -256,7 +256,7 @@ def run_backbone(args, dev, rank, world, dist, objects_per_rank, scaling):
     pts, fts, ids = S.object_points(range(lo, lo + objects_per_rank), cfg["n_pts"], base_seed=7000)
     pts, fts, ids = (torch.from_numpy(a).to(dev) for a in (pts, fts, ids))
     ids = ids.int()
-    DEPTH, STREAMS, LAG = 6, 3, 5
+    DEPTH, STREAMS, LAG = overlap      # recordings, streams, batches in flight before the host waits
     net = Backbone(cfg, dev, objects_per_rank, depth=DEPTH, streams=STREAMS)
     gather = parallel.RowGatherer(total, 240, dev)
     steps = max(8, min(args.steps, 40))

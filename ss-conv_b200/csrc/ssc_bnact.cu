@@ -161,7 +161,7 @@ bn_gate_vec4_out16_kernel(const float *__restrict__ x, uint32_t total, uint32_t 
 // changes is the instruction count: a thread of the kernels above evaluates up to four
 // sigmoids (expf + IEEE division each, every path taken by some lane of the warp), which made
 // the pass instruction-bound at half the memory rate.  OUT = 0 fp32, 1 fp16, 2 bf16 result.
-template <int OUT>
+template <int OUT, int VEC>
 __global__ void __launch_bounds__(256)
 bn_gate_rows_kernel(const float *__restrict__ x, uint32_t n_rows, uint32_t groups, int c_in_total,
                     const float *__restrict__ scale, const float *__restrict__ shift,
@@ -169,18 +169,30 @@ bn_gate_rows_kernel(const float *__restrict__ x, uint32_t n_rows, uint32_t group
                     int gate_act, const float *__restrict__ scalar_bias, const float *__restrict__ gate_bias,
                     void *__restrict__ out) {
   extern __shared__ float gate_s[];                    // [R][n_gates]
-  // block = (groups, R): threadIdx.x is the group of four channels, threadIdx.y the row of the block
-  // (no integer division anywhere in the kernel)
-  const uint32_t R = blockDim.y, r = threadIdx.y, g4 = threadIdx.x, row = blockIdx.x * R + r;
+  // block = (groups, R): threadIdx.x is the group of VEC channels, threadIdx.y the row of the block
+  // (no integer division anywhere in the kernel).  VEC = 4 / 2 / 1 for channel counts that are
+  // multiples of four / even / odd (rows 16- / 8- / 4-byte aligned).
+  const uint32_t R = blockDim.y, r = threadIdx.y, gq = threadIdx.x, row = blockIdx.x * R + r;
   const bool active = row < n_rows;
-  const int ch0 = (int)g4 * 4;
-  // this thread's four channels: the load goes out before the gate phase, so that both phases'
+  const int ch0 = (int)gq * VEC;
+  // this thread's channels: the load goes out before the gate phase, so that both phases'
   // memory latencies overlap
-  float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+  float v[VEC];
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) v[q] = 0.f;
   if (active) {
-    xv = __ldg((const float4 *)(x + (size_t)row * c_in_total + ch0));
+    const float *xp = x + (size_t)row * c_in_total + ch0;
+    if (VEC == 4) {
+      const float4 t = __ldg((const float4 *)xp);
+      v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+    } else if (VEC == 2) {
+      const float2 t = __ldg((const float2 *)xp);
+      v[0] = t.x; v[1 % VEC] = t.y;
+    } else {
+      v[0] = __ldg(xp);
+    }
     float *my_gates_w = gate_s + r * (uint32_t)n_gates;
-    for (uint32_t g = g4; g < (uint32_t)n_gates; g += groups) {
+    for (uint32_t g = gq; g < (uint32_t)n_gates; g += groups) {
       float gv = __ldg(x + (size_t)row * c_in_total + c_gate_base + g);
       if (scale) gv = fmaf(gv, scale[c_gate_base + g], shift[c_gate_base + g]);
       if (gate_bias) gv += gate_bias[g];
@@ -189,34 +201,49 @@ bn_gate_rows_kernel(const float *__restrict__ x, uint32_t n_rows, uint32_t group
   }
   __syncthreads();
   if (!active) return;
-  float v[4] = {xv.x, xv.y, xv.z, xv.w};
-  if (scale) {
-    const float4 sc = __ldg((const float4 *)(scale + ch0)), sh = __ldg((const float4 *)(shift + ch0));
-    v[0] = fmaf(v[0], sc.x, sh.x);
-    v[1] = fmaf(v[1], sc.y, sh.y);
-    v[2] = fmaf(v[2], sc.z, sh.z);
-    v[3] = fmaf(v[3], sc.w, sh.w);
-  }
-  const int4 gi = __ldg((const int4 *)(gate_of_channel + ch0));
-  const int g[4] = {gi.x, gi.y, gi.z, gi.w};
   const float *my_gates = gate_s + r * (uint32_t)n_gates;
+  float sc[VEC], sh[VEC];
+  int gi[VEC];
+  if (VEC == 4) {   // 16-byte aligned tables (checked by the caller)
+    const int4 t = __ldg((const int4 *)(gate_of_channel + ch0));
+    gi[0] = t.x; gi[1 % VEC] = t.y; gi[2 % VEC] = t.z; gi[3 % VEC] = t.w;
+    if (scale) {
+      const float4 a = __ldg((const float4 *)(scale + ch0)), b = __ldg((const float4 *)(shift + ch0));
+      sc[0] = a.x; sc[1 % VEC] = a.y; sc[2 % VEC] = a.z; sc[3 % VEC] = a.w;
+      sh[0] = b.x; sh[1 % VEC] = b.y; sh[2 % VEC] = b.z; sh[3 % VEC] = b.w;
+    }
+  } else {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    if (g[q] == -1) {
-      if (scalar_bias) v[q] += scalar_bias[ch0 + q];
-      v[q] = apply_act(v[q], scalar_act);
-    } else if (g[q] >= 0) {
-      v[q] *= my_gates[g[q]];
+    for (int q = 0; q < VEC; ++q) {
+      gi[q] = __ldg(gate_of_channel + ch0 + q);
+      if (scale) { sc[q] = __ldg(scale + ch0 + q); sh[q] = __ldg(shift + ch0 + q); }
     }
   }
-  const size_t t = (size_t)row * groups + g4;
-  if (OUT == 0) ((float4 *)out)[t] = make_float4(v[0], v[1], v[2], v[3]);
-  else if (OUT == 2) ((uint2 *)out)[t] = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
-  else ((uint2 *)out)[t] = make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) {
+    if (scale) v[q] = fmaf(v[q], sc[q], sh[q]);
+    const int g = gi[q];
+    if (g == -1) {
+      if (scalar_bias) v[q] += scalar_bias[ch0 + q];
+      v[q] = apply_act(v[q], scalar_act);
+    } else if (g >= 0) {
+      v[q] *= my_gates[g];
+    }
+  }
+  const size_t t = (size_t)row * groups + gq;
+  if (OUT == 0) {
+    if (VEC == 4) ((float4 *)out)[t] = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+    else if (VEC == 2) ((float2 *)out)[t] = make_float2(v[0], v[1 % VEC]);
+    else ((float *)out)[t] = v[0];
+  } else if (OUT == 2) {
+    ((uint2 *)out)[t] = make_uint2(pack_bf16x2(v[0], v[1 % VEC]), pack_bf16x2(v[2 % VEC], v[3 % VEC]));
+  } else {
+    ((uint2 *)out)[t] = make_uint2(pack_f16x2(v[0], v[1 % VEC]), pack_f16x2(v[2 % VEC], v[3 % VEC]));
+  }
 }
 
-// Launch of the row-block kernel when it applies (gated pass, at most 256 vec4 groups per row).
-template <int OUT>
+// Launch of the row-block kernel when it applies (gated pass, at most 256 channel groups per row).
+template <int OUT, int VEC>
 static bool launch_bn_gate_rows(const float *x, int n, uint32_t groups, int c_in_total, const float *scale, const float *shift,
                                 const int32_t *gate_of_channel, int c_gate_base, int scalar_act, int gate_act,
                                 const float *scalar_bias, const float *gate_bias, void *out, cudaStream_t st) {
@@ -225,9 +252,9 @@ static bool launch_bn_gate_rows(const float *x, int n, uint32_t groups, int c_in
   const uint32_t R = 256u / groups;
   const size_t smem = (size_t)R * n_gates * sizeof(float);
   if (smem > 48 * 1024) return false;
-  { bn_gate_rows_kernel<OUT><<<ceil_div(n, (int)R), dim3(groups, R), smem, st>>>(x, (uint32_t)n, groups, c_in_total, scale, shift,
-                                                                     gate_of_channel, c_gate_base, n_gates, scalar_act, gate_act,
-                                                                     scalar_bias, gate_bias, out); note_launches(1); }
+  { bn_gate_rows_kernel<OUT, VEC><<<ceil_div(n, (int)R), dim3(groups, R), smem, st>>>(x, (uint32_t)n, groups, c_in_total, scale, shift,
+                                                                          gate_of_channel, c_gate_base, n_gates, scalar_act, gate_act,
+                                                                          scalar_bias, gate_bias, out); note_launches(1); }
   return true;
 }
 
@@ -395,14 +422,24 @@ extern "C" int ssc_bn_gate_fwd(const float *x, int n, int c_in_total, const floa
                    (((uintptr_t)x | (uintptr_t)out | (uintptr_t)scale | (uintptr_t)shift | (uintptr_t)gate_of_channel) & 15u) == 0;
   if (vec) {
     const uint32_t groups = (uint32_t)(c_out >> 2), total4 = (uint32_t)(total >> 2);
-    if (launch_bn_gate_rows<0>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
-                               scalar_bias, gate_bias, out, as_stream(stream))) {
+    if (launch_bn_gate_rows<0, 4>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+                                  scalar_bias, gate_bias, out, as_stream(stream))) {
       SSC_CHECK_LAUNCH("bn_gate_fwd");
       return SSC_OK;
     }
     { bn_gate_vec4_kernel<<<ceil_div(total4, 256), 256, 0, as_stream(stream)>>>(x, total4, groups, c_in_total, scale, shift,
                                                                             gate_of_channel, c_gate_base, scalar_act, gate_act,
                                                                             scalar_bias, gate_bias, out); note_launches(1); }
+    SSC_CHECK_LAUNCH("bn_gate_fwd");
+    return SSC_OK;
+  }
+  // channel counts that are not multiples of four: two channels per thread when everything is even,
+  // else one (the row-block kernel still evaluates every gate once per row)
+  const bool even = (c_out & 1) == 0 && (c_in_total & 1) == 0 && (((uintptr_t)x | (uintptr_t)out) & 7u) == 0;
+  if (even ? launch_bn_gate_rows<0, 2>(x, n, (uint32_t)(c_out >> 1), c_in_total, scale, shift, gate_of_channel, c_gate_base,
+                                       scalar_act, gate_act, scalar_bias, gate_bias, out, as_stream(stream))
+           : launch_bn_gate_rows<0, 1>(x, n, (uint32_t)c_out, c_in_total, scale, shift, gate_of_channel, c_gate_base,
+                                       scalar_act, gate_act, scalar_bias, gate_bias, out, as_stream(stream))) {
     SSC_CHECK_LAUNCH("bn_gate_fwd");
     return SSC_OK;
   }
@@ -430,9 +467,9 @@ extern "C" int ssc_bn_gate_fwd16(const float *x, int n, int c_in_total, const fl
   SSC_REQUIRE(total / 4 < (1ll << 31), "bn_gate_fwd16: tensor too large");
   const uint32_t groups = (uint32_t)(c_out >> 2), total4 = (uint32_t)(total >> 2);
   if (precision == SSC_PREC_BF16
-          ? launch_bn_gate_rows<2>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+          ? launch_bn_gate_rows<2, 4>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
                                    scalar_bias, gate_bias, out16, as_stream(stream))
-          : launch_bn_gate_rows<1>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
+          : launch_bn_gate_rows<1, 4>(x, n, groups, c_in_total, scale, shift, gate_of_channel, c_gate_base, scalar_act, gate_act,
                                    scalar_bias, gate_bias, out16, as_stream(stream))) {
     SSC_CHECK_LAUNCH("bn_gate_fwd16");
     return SSC_OK;
