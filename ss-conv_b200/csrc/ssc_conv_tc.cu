@@ -49,11 +49,13 @@ struct TcParams {
   int nt_cta;     // N tiles handled by one CTA: n_tiles, or 1 when the N tiles are spread over gridDim.y
   int n_cta;      // nt_cta * tile_n: accumulator columns / filter-slab rows per CTA
   int fmt16;      // 16-bit operands: 0 = fp16, 1 = bf16 (operand format field of the instruction descriptor)
+  int last_kk;    // MMA k-steps (32 bytes of K each) that hold real channels in the LAST slab: 1..4
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
 static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
+  p.last_kk = (c_in - (p.k_slabs - 1) * TC_SLAB + 7) / 8;     // c_in counts 4-byte words of an operand row
   int n16 = (c_out + 15) / 16 * 16;
   p.n_tiles = (n16 + 255) / 256;
   p.tile_n = ((n16 + p.n_tiles - 1) / p.n_tiles + 15) / 16 * 16;
@@ -366,19 +368,15 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       const int n_sub = min(p.sps, p.k_slabs - grp * p.sps);
       for (int ss = 0; ss < n_sub; ++ss) {
         const uint32_t an = a_lo + (uint32_t)ss * (TC_A_BYTES >> 4);
+        // k-steps of this slab that hold real channels (the rest of the last slab is zero on both
+        // sides: a 3-channel first layer needs one MMA per step, not four)
+        const int n_kk = grp * p.sps + ss == p.k_slabs - 1 ? p.last_kk : 4;
         for (int nt = 0; nt < p.nt_cta; ++nt) {
           const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n);
           const uint32_t bn = a_lo + (uint32_t)(p.sps * TC_A_BYTES >> 4) + (uint32_t)ss * ((uint32_t)p.b_bytes >> 4) + (uint32_t)nt * n_step;
-          if (F16) {
-            mma_f16_ss_masked(dn, an, bn, idesc, off);
-            mma_f16_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
-            mma_f16_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
-            mma_f16_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
-          } else {
-            mma_tf32_ss_masked(dn, an, bn, idesc, off);
-            mma_tf32_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
-            mma_tf32_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
-            mma_tf32_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+          for (int kk = 0; kk < n_kk; ++kk) {
+            if (F16) mma_f16_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
+            else mma_tf32_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
           }
         }
       }
