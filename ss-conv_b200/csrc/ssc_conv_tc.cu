@@ -53,7 +53,7 @@ struct TcParams {
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
-static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
+static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false, bool one_cta_per_sm = false) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   p.last_kk = (c_in - (p.k_slabs - 1) * TC_SLAB + 7) / 8;     // c_in counts 4-byte words of an operand row
   int n16 = (c_out + 15) / 16 * 16;
@@ -77,8 +77,11 @@ static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false) {
   int fixed = TC_CTRL_BYTES + 1024;
   // Resident CTAs hide each other's per-step latencies, so take as many per SM as tensor
   // memory (512 columns) and shared memory (two ring slots each at least) allow, up to four.
+  // A launch with no more CTAs than SMs has nobody to share an SM with: all of the shared memory
+  // goes into ring slots (a deeper pipeline is what a lone CTA has against the latency of a step).
   int ctas = 512 / p.tmem_cols;
   if (ctas > 4) ctas = 4;
+  if (one_cta_per_sm) ctas = 1;
   while (ctas > 1 && ((227 * 1024) / ctas - 1024 - fixed) / stage < 2) --ctas;
   p.stages = ((227 * 1024) / ctas - 1024 - fixed) / stage;
   if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
@@ -488,6 +491,7 @@ int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void
   TcParams p;
   if (!tc_params(words, c_out, p, grid < 2 * sms))
     return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): c_out %d / kernel volume %d not supported", c_out, K);
+  if (grid * (p.n_tiles / p.nt_cta) <= sms) tc_params(words, c_out, p, grid < 2 * sms, true);
   p.fmt16 = bf16 ? 1 : 0;
   if (!prestaged) {
     int rc = stage_features_16(features, n_in, c_in, bf16, scratch, st);
@@ -514,6 +518,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   int grid = ceil_div(n_out, TC_M);
   const bool split_n = grid < 2 * sm_count();   // few row tiles: spread the N tiles over CTAs too
   if (!tc_params(c_in, c_out, p, split_n)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
+  if (grid * (p.n_tiles / p.nt_cta) <= sm_count()) tc_params(c_in, c_out, p, split_n, true);
   size_t smem = tc_smem_bytes(p);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).
