@@ -43,6 +43,20 @@ __global__ void stage_features_padded_kernel(const float *__restrict__ in, long 
   }
 }
 
+// The same for up to 1024 channels with a block shaped (groups of four channels, rows): one 16-byte
+// store per thread and no integer division (the kernel above spends most of its time in a 64-bit
+// division per element).
+__global__ void __launch_bounds__(256)
+stage_features_padded_rows_kernel(const float *__restrict__ in, int n_rows, int c_in, uint4 *__restrict__ out) {
+  const int row = blockIdx.x * blockDim.y + threadIdx.y, c0 = threadIdx.x * 4;
+  if (row >= n_rows) return;
+  const float *src = in + (size_t)row * c_in + c0;
+  uint32_t v[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) v[q] = c0 + q < c_in ? to_tf32(__ldg(src + q)) : 0u;
+  out[(size_t)row * blockDim.x + threadIdx.x] = make_uint4(v[0], v[1], v[2], v[3]);
+}
+
 size_t conv_tf32_scratch_bytes(int n_in, int c_in) {
   return align_up((size_t)n_in * (size_t)((c_in + 3) & ~3) * sizeof(float), 16) + 16;
 }
@@ -56,6 +70,9 @@ int stage_features(const float *features, int n_in, int c_in, void *staged, cuda
     int blocks = ceil_div(total_vec, 256 * 4);
     if (blocks > max_blocks) blocks = max_blocks;
     { stage_features_kernel<<<blocks, 256, 0, st>>>((const float4 *)features, n_vec, total_vec, (uint4 *)staged); note_launches(1); }
+  } else if (c_pad <= 1024) {
+    const int groups = c_pad >> 2, rows = 256 / groups;
+    { stage_features_padded_rows_kernel<<<ceil_div(n_in, rows), dim3(groups, rows), 0, st>>>(features, n_in, c_in, (uint4 *)staged); note_launches(1); }
   } else {
     const long long total = (long long)n_in * c_pad;
     int blocks = ceil_div(total, 256 * 4);
