@@ -244,7 +244,7 @@ class Backbone:
         return self.graphed.submit(points, feats, ids)
 
 
-def run_backbone(args, dev, rank, world, dist, objects_per_rank, scaling, overlap=(6, 3, 5)):
+def run_backbone(args, dev, rank, world, dist, objects_per_rank, scaling, overlap=(8, 4, 7)):
     """Backbone samples/s: every rank runs `objects_per_rank` objects per batch, then one all-gather
     of the pooled [objects, 240] rows (the only collective).  `lag` batches are in flight before the
     host waits for the oldest one."""

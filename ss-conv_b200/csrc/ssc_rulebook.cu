@@ -166,6 +166,13 @@ __device__ __forceinline__ Reach reach_of(const Geometry &g, int d, int in) {
   return clip_progression(in + g.padding[d] - (g.ksize[d] - 1) * g.dilation[d], g.dilation[d], g.ksize[d], g.out_shape[d]);
 }
 
+// bitmap word |= bits, skipping the atomic when the bits are already there: on coarse grids most
+// inputs of a sample reach the same few output cells and their atomics would queue up on one
+// word (bits are only ever set while this runs, so a stale read costs at most a redundant atomic).
+__device__ __forceinline__ void set_bits(uint32_t *word, uint32_t bits) {
+  if ((__ldcg(word) & bits) != bits) atomicOr(word, bits);
+}
+
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
                                     uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
   int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -182,13 +189,13 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
       for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
         const uint32_t flat = row + (uint32_t)z;
         if ((flat >> 5) != word) {
-          if (bits) atomicOr(bitmap + word, bits);
+          if (bits) set_bits(bitmap + word, bits);
           word = flat >> 5;
           bits = 0u;
         }
         bits |= 1u << (flat & 31);
       }
-      if (bits) atomicOr(bitmap + word, bits);
+      if (bits) set_bits(bitmap + word, bits);
     }
 }
 
