@@ -100,14 +100,26 @@ class BatchNorm(nn.Module):
     def folded_affine(self, device, mean=None, var=None):
         """(scale, shift) per channel for the given statistics (default: running buffers)."""
         field, scalar = self._device_tables(device)
+        running = mean is None and var is None
         mean = self.running_mean if mean is None else mean
         var = self.running_var if var is None else var
         w = self.weight.detach() if self.affine else None
         b = self.bias.detach() if self.affine else None
+        # the fold of the running buffers is kept until one of its inputs changes (in-place updates bump
+        # a tensor's version, moves and reloads change its address): an eval-mode network folds once
+        key = None
+        if running:
+            key = tuple((t.data_ptr(), t._version) for t in (mean, var, w, b) if t is not None) + (str(device), self.eps)
+            kept = getattr(self, "_folded", None)
+            if kept is not None and kept[0] == key:
+                return kept[1]
         if mean.numel() == 0:
             mean = None
             b = None
-        return _ext.bn_fold(mean, var, w, b, field, scalar, self.eps)
+        folded = _ext.bn_fold(mean, var, w, b, field, scalar, self.eps)
+        if key is not None:
+            self._folded = (key, folded)
+        return folded
 
     def _differentiable(self, x):
         """The layer as a composite of torch ops, used while autograd is recording so that

@@ -553,3 +553,30 @@ def test_features_stored_in_16_bits_between_layers(cuda, storage):
     assert torch.equal(got_f, ref_f.to(dt))          # same operands in every layer, only the last rounding differs
     assert torch.equal(rep_f, got_f)
     assert float(ref_f.abs().max()) > 0
+
+
+def test_eval_batchnorm_refolds_when_its_buffers_change(cuda):
+    """Eval-mode BatchNorm keeps the folded (scale, shift) of its running buffers between calls; an
+    in-place change of a buffer or of the affine weight must be seen by the next call."""
+    from ss_conv.batchnorm import BatchNorm
+    from ss_conv.sp_ops.tensor import SparseTensor
+    from ss_conv.utils import synthetic as S
+    Rs = [(2, 0), (2, 1)]
+    bn = BatchNorm(Rs).to(cuda).eval()
+    ind = torch.from_numpy(S.surface_voxels(range(1), 16, 512, base_seed=2)).to(cuda)
+    feats = torch.randn(ind.shape[0], 8, device=cuda)
+
+    def run():
+        with torch.no_grad():
+            return bn(SparseTensor(feats.clone(), ind, [16] * 3, 1)).features.clone()
+
+    a, again = run(), run()
+    assert torch.equal(a, again)
+    with torch.no_grad():
+        bn.running_var.mul_(4.0)                 # in place: the fold must be redone
+    b = run()
+    assert not torch.equal(a, b) and torch.allclose(b, 0.5 * a, rtol=1e-4, atol=1e-5)
+    with torch.no_grad():
+        bn.weight.fill_(2.0)
+    c = run()
+    assert torch.allclose(c, 2.0 * b, rtol=1e-5, atol=1e-6)
