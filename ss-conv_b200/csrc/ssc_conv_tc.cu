@@ -377,9 +377,23 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
         for (int nt = 0; nt < p.nt_cta; ++nt) {
           const uint32_t dn = tmem_base + (uint32_t)(nt * p.tile_n);
           const uint32_t bn = a_lo + (uint32_t)(p.sps * TC_A_BYTES >> 4) + (uint32_t)ss * ((uint32_t)p.b_bytes >> 4) + (uint32_t)nt * n_step;
-          for (int kk = 0; kk < n_kk; ++kk) {
-            if (F16) mma_f16_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
-            else mma_tf32_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
+          if (n_kk == 4) {   // the common case, straight-line
+            if (F16) {
+              mma_f16_ss_masked(dn, an, bn, idesc, off);
+              mma_f16_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
+              mma_f16_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
+              mma_f16_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+            } else {
+              mma_tf32_ss_masked(dn, an, bn, idesc, off);
+              mma_tf32_ss_masked(dn, an + 2u, bn + 2u, idesc, off);
+              mma_tf32_ss_masked(dn, an + 4u, bn + 4u, idesc, off);
+              mma_tf32_ss_masked(dn, an + 6u, bn + 6u, idesc, off);
+            }
+          } else {
+            for (int kk = 0; kk < n_kk; ++kk) {
+              if (F16) mma_f16_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
+              else mma_tf32_ss_masked(dn, an + 2u * (uint32_t)kk, bn + 2u * (uint32_t)kk, idesc, off);
+            }
           }
         }
       }

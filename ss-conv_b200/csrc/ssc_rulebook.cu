@@ -169,8 +169,8 @@ __device__ __forceinline__ Reach reach_of(const Geometry &g, int d, int in) {
 // bitmap word |= bits, skipping the atomic when the bits are already there: on coarse grids most
 // inputs of a sample reach the same few output cells and their atomics would queue up on one
 // word (bits are only ever set while this runs, so a stale read costs at most a redundant atomic).
-__device__ __forceinline__ void set_bits(uint32_t *word, uint32_t bits) {
-  if ((__ldcg(word) & bits) != bits) atomicOr(word, bits);
+__device__ __forceinline__ void set_bits(uint32_t *word, uint32_t bits, bool look_first) {
+  if (!look_first || (__ldcg(word) & bits) != bits) atomicOr(word, bits);
 }
 
 __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
@@ -182,6 +182,7 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
   const Reach rx = reach_of(g, 0, c.y), ry = reach_of(g, 1, c.z), rz = reach_of(g, 2, c.w);
   if (rx.n <= 0 || ry.n <= 0 || rz.n <= 0) return;
   const int base_b = c.x * g.out_shape[0];
+  const bool coarse = g.out_shape[0] * g.out_shape[1] * g.out_shape[2] <= 4096;   // few cells per sample: many inputs per bitmap word
   for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
     for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
       const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
@@ -189,13 +190,13 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
       for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
         const uint32_t flat = row + (uint32_t)z;
         if ((flat >> 5) != word) {
-          if (bits) set_bits(bitmap + word, bits);
+          if (bits) set_bits(bitmap + word, bits, coarse);
           word = flat >> 5;
           bits = 0u;
         }
         bits |= 1u << (flat & 31);
       }
-      if (bits) set_bits(bitmap + word, bits);
+      if (bits) set_bits(bitmap + word, bits, coarse);
     }
 }
 
