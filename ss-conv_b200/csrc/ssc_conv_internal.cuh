@@ -16,6 +16,13 @@ int stage_features_16(const float *features, int n_in, int c_in, bool bf16, void
 // kernels gather such a row like an fp32 image of that many channels.
 inline int f16_row_words(int c_in) { return ((c_in + 7) & ~7) / 2; }
 
+// TF32 layers with few input channels: kernel offsets that share one 128-byte operand row (rows of
+// the staged image are c_pad = 4, 8 or 16 floats): 8, 4, 2; else 1.  Decides the packed filter layout.
+inline int tf32_offsets_per_row(int c_in) {
+  const int c_pad = (c_in + 3) & ~3;
+  return (c_pad == 4 || c_pad == 8 || c_pad == 16) ? 32 / c_pad : 1;
+}
+
 // geometry of the packed filter image [K][k_slabs][n_pad][128 bytes] (ssc_conv_tc.cu)
 bool tc_operand_layout(int c_in_words, int c_out, int *k_slabs, int *n_pad, int *tile_n, int *n_tiles);
 

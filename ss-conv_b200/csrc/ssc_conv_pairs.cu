@@ -467,6 +467,7 @@ static size_t pl_smem_bytes(const PlParams &p) {
 // resident in shared memory next to at least three ring slots.
 static bool pl_params(int c_in, int c_out, int precision, PlParams &p) {
   const bool is16 = precision == SSC_PREC_F16 || precision == SSC_PREC_BF16;
+  if (!is16 && tf32_offsets_per_row(c_in) > 1) return false;   // those filters are packed several offsets per row
   const int words = is16 ? f16_row_words(c_in) : c_in;
   int tile_n, n_tiles;
   if (!tc_operand_layout(words, c_out, &p.k_slabs, &p.n_pad, &tile_n, &n_tiles)) return false;

@@ -50,12 +50,19 @@ struct TcParams {
   int n_cta;      // nt_cta * tile_n: accumulator columns / filter-slab rows per CTA
   int fmt16;      // 16-bit operands: 0 = fp16, 1 = bf16 (operand format field of the instruction descriptor)
   int last_kk;    // MMA k-steps (32 bytes of K each) that hold real channels in the LAST slab: 1..4
+  int opk;        // kernel offsets per 128-byte operand row: 1, or 32 / c_pad for TF32 layers with c_pad = 4, 8, 16
+                  // channels (a first layer with 3 input channels packs 8 offsets into one step)
 };
 
 // Shared-memory plan: [stages x (A 16 KB + B)] [control 1 KB].
-static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false, bool one_cta_per_sm = false) {
+static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false, bool one_cta_per_sm = false, int opk = 1) {
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   p.last_kk = (c_in - (p.k_slabs - 1) * TC_SLAB + 7) / 8;     // c_in counts 4-byte words of an operand row
+  p.opk = opk;
+  if (opk > 1) {     // grouped offsets: one full slab per group of offsets
+    p.k_slabs = 1;
+    p.last_kk = 4;
+  }
   int n16 = (c_out + 15) / 16 * 16;
   p.n_tiles = (n16 + 255) / 256;
   p.tile_n = ((n16 + p.n_tiles - 1) / p.n_tiles + 15) / 16 * 16;
@@ -128,11 +135,33 @@ __global__ void pack_filters_tf32_kernel(const float *__restrict__ filters, int 
   packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
+// The grouped form for few input channels (c_pad = 4, 8, 16; opk = 32 / c_pad offsets per operand row):
+// [ceil(K / opk)][n_pad rows][32 tf32], word (o' * c_pad + c) of a row = W[g * opk + o', c, n].
+__global__ void pack_filters_tf32_grouped_kernel(const float *__restrict__ filters, int K, int c_in, int c_out, int c_pad,
+                                                 int opk, int n_groups, int n_pad, uint4 *__restrict__ packed) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = (long long)n_groups * n_pad * 8;
+  if (t >= total) return;
+  const int chunk = (int)(t & 7);
+  long long r = t >> 3;
+  const int n = (int)(r % n_pad), g = (int)(r / n_pad);
+  uint32_t v[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int w = chunk * 4 + q, o = w / c_pad, ci = w - o * c_pad, kappa = g * opk + o;
+    const float f = (o < opk && kappa < K && ci < c_in && n < c_out) ? filters[((size_t)kappa * c_in + ci) * c_out + n] : 0.f;
+    v[q] = to_tf32(f);
+  }
+  const size_t block = (size_t)g * (size_t)(n_pad * 8);
+  const size_t off = (size_t)(n >> 3) * 64 + (size_t)(n & 7) * 8 + (size_t)(chunk ^ (n & 7));
+  packed[block + off] = make_uint4(v[0], v[1], v[2], v[3]);
+}
+
 // Warps 0 .. n_prod-1 are producers (warp w <-> ring slot w; with fewer than four slots the
 // spare warps only help in the prologue and epilogue), the last warp issues the MMAs.
 // F16: the staged image and the filter slabs hold fp16 (64 channels per 128-byte row); the
 // gather is the same byte-for-byte, `c_in` is then the row length in 4-byte units.
-template <bool STAGED, bool F16 = false>
+template <bool STAGED, bool F16 = false, bool GROUPED = false>
 __global__ void __launch_bounds__((TC_MAX_STAGES + 1) * 32)
 conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *__restrict__ packed, int K,
                      int c_out, const int32_t *__restrict__ nbr, int n_out, float *__restrict__ out,
@@ -229,8 +258,16 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   }
   if (tid == 0) {
     int n = 0;
-    for (int kappa = 0; kappa < K; ++kappa)
-      if (act_flag[kappa]) act_list[n++] = (uint8_t)kappa;
+    if (GROUPED) {   // steps are groups of opk offsets: a group is live when one of its offsets is
+      for (int g = 0; g * p.opk < K; ++g) {
+        bool any = false;
+        for (int i = 0; i < p.opk && g * p.opk + i < K; ++i) any = any || act_flag[g * p.opk + i];
+        if (any) act_list[n++] = (uint8_t)g;
+      }
+    } else {
+      for (int kappa = 0; kappa < K; ++kappa)
+        if (act_flag[kappa]) act_list[n++] = (uint8_t)kappa;
+    }
     *n_act_s = n;
   }
   tc_fence_before();
@@ -273,6 +310,58 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       for (int q = 0; q < 4; ++q)
         dst[q] = (q >= q0 && q < q0 + q_per && my_rows[q] >= 0) ? __ldg(nbr + (size_t)kap * n_out + my_rows[q]) : -1;
     };
+    if (GROUPED) {
+      // Grouped offsets (TF32, staged rows of c_in = 4, 8 or 16 floats): the 128-byte operand row of a
+      // step holds the rows' neighbours at opk consecutive offsets side by side; a missing neighbour is
+      // a zero-filled piece, so no row is ever switched off.  The filter slab of the group is packed to match.
+      const int cpc = c_in >> 2;                   // 16-byte chunks per offset
+      for (int j = slot; j < n_iter; j += S) {
+        const int group = act_list[j];
+        int idx[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int o = 0; o < 8; ++o) {
+            const int kap = group * p.opk + o;
+            idx[q][o] = (q >= q0 && q < q0 + q_per && o < p.opk && kap < K && my_rows[q] >= 0)
+                            ? __ldg(nbr + (size_t)kap * n_out + my_rows[q]) : -1;
+          }
+        if (j >= S) {
+          if (!mbar_wait_warp(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
+          tc_fence_after();
+        }
+        if (part == 0 && lane == 0) {
+          const uint4 *bsrc = packed + (size_t)group * (size_t)(p.n_pad * 8) + (size_t)nt0 * (size_t)(p.tile_n * 8);
+          const uint32_t bar = smem_u32(fulla_bars + slot), nbytes = (uint32_t)p.b_bytes;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbytes) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           slot_addr + (uint32_t)TC_A_BYTES),
+                       "l"(bsrc), "r"(nbytes), "r"(bar)
+                       : "memory");
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (q < q0 || q >= q0 + q_per) continue;
+          if (lane == 0) slot_masks[slot * 4 + q] = 0u;          // every row takes part
+          const uint32_t a_row = slot_addr + row_off[q];
+#pragma unroll
+          for (int o = 0; o < 8; ++o) {
+            if (o >= p.opk) break;
+            const int src_row = idx[q][o];
+            const float *fp = features + (size_t)(src_row >= 0 ? src_row : 0) * c_in;
+            for (int cc = 0; cc < cpc; ++cc) {
+              const uint32_t chunk = (uint32_t)(o * cpc + cc);
+              cp_async16_cg(a_row + ((chunk ^ sw) << 4), fp + cc * 4, src_row >= 0 ? 16u : 0u);
+            }
+          }
+        }
+        cp_async_commit();
+        cp_async_wait(0);
+        fence_async_smem();
+        mbar_arrive(smem_u32(fulla_bars + slot));
+        par ^= 1u;
+      }
+    } else {
     if (slot < n_iter) load_rows(slot, nxt);
     for (int j = slot; j < n_iter; j += S) {
       const int act = j / p.k_groups, slab0 = (j - act * p.k_groups) * p.sps;
@@ -353,6 +442,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       mbar_arrive(smem_u32(fulla_bars + slot));
       par ^= 1u;
     }
+    }   // one offset per step
   } else if (warp == mma_warp && lane == 0) {
     // ================================ MMA issuer ============================================
     // The issuing thread is the serial bottleneck of the pipeline, so its loop is kept to a
@@ -531,8 +621,9 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
   int grid = ceil_div(n_out, TC_M);
   const bool split_n = grid < 2 * sm_count();   // few row tiles: spread the N tiles over CTAs too
-  if (!tc_params(c_in, c_out, p, split_n)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
-  if (grid * (p.n_tiles / p.nt_cta) <= sm_count()) tc_params(c_in, c_out, p, split_n, true);
+  const int opk = tf32_offsets_per_row(c_in);
+  if (!tc_params(c_in, c_out, p, split_n, false, opk)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
+  if (grid * (p.n_tiles / p.nt_cta) <= sm_count()) tc_params(c_in, c_out, p, split_n, true, opk);
   size_t smem = tc_smem_bytes(p);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).
@@ -540,12 +631,15 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   const size_t stage_need = conv_tf32_scratch_bytes(n_in, c_in);
   const bool fits = scratch != nullptr && scratch_bytes + 16 >= stage_need && ((uintptr_t)scratch & 15u) == 0;
   if (prestaged && !fits) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): SSC_CONV_PRESTAGED without the staged image in scratch");
-  const bool staged = fits && (prestaged || grid >= kStagingMinTiles);
+  // layers with few input channels have their filters packed for several offsets per operand row,
+  // which the kernel can only feed from the staged (padded) rows
+  if (opk > 1 && !fits) return fail(SSC_ERR_SCRATCH, "conv_fwd(tf32): a layer with %d input channels needs the staging buffer (ssc_conv_scratch_bytes)", c_in);
+  const bool staged = fits && (prestaged || grid >= kStagingMinTiles || opk > 1);
   if (staged && !prestaged) {
     int rc = stage_features(features, n_in, c_in, scratch, st);
     if (rc != SSC_OK) return rc;
   }
-  auto kernel = staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
+  auto kernel = opk > 1 ? conv_fwd_tf32_kernel<true, false, true> : staged ? conv_fwd_tf32_kernel<true> : conv_fwd_tf32_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SSC_ERR_CUDA, "conv_fwd(tf32): smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid2(grid, p.n_tiles / p.nt_cta);
@@ -565,6 +659,8 @@ extern "C" size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precisio
   if ((precision != SSC_PREC_TF32 && !is16(precision)) || K < 1 || c_in < 1 || c_out < 1) return 0;
   TcParams p;
   if (!tc_params(is16(precision) ? f16_row_words(c_in) : c_in, c_out, p)) return 0;
+  if (!is16(precision) && tf32_offsets_per_row(c_in) > 1)
+    return (size_t)ceil_div(K, tf32_offsets_per_row(c_in)) * p.n_pad * 128;
   return (size_t)K * p.k_slabs * p.n_pad * 128;
 }
 
@@ -574,6 +670,14 @@ extern "C" int ssc_conv_pack_filters(const float *filters, int K, int c_in, int 
   SSC_REQUIRE(filters && packed && K >= 1 && c_in >= 1 && c_out >= 1, "conv_pack_filters: bad arguments");
   TcParams p;
   SSC_REQUIRE(tc_params(is16(precision) ? f16_row_words(c_in) : c_in, c_out, p), "conv_pack_filters: c_out %d not supported (max 512)", c_out);
+  if (precision == SSC_PREC_TF32 && tf32_offsets_per_row(c_in) > 1) {
+    const int opk = tf32_offsets_per_row(c_in), n_groups = ceil_div(K, opk);
+    const long long total_g = (long long)n_groups * p.n_pad * 8;
+    { pack_filters_tf32_grouped_kernel<<<ceil_div(total_g, 256), 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, (c_in + 3) & ~3, opk,
+                                                                                         n_groups, p.n_pad, (uint4 *)packed); note_launches(1); }
+    SSC_CHECK_LAUNCH("pack_filters");
+    return SSC_OK;
+  }
   long long total = (long long)K * p.k_slabs * p.n_pad * 8;
   const int blocks = ceil_div(total, 256);
   if (precision == SSC_PREC_F16) { pack_filters_16_kernel<false><<<blocks, 256, 0, as_stream(stream)>>>(filters, K, c_in, c_out, p, (uint4 *)packed); note_launches(1); }

@@ -720,7 +720,9 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
         prec = _PREC_OF[mode]
         packed = _packed_filters(filters, prec)
         # the 16-bit kernels always gather from their staged image
-        stage = prec != PREC_TF32 or n_out >= STAGING_MIN_ROWS
+        # (layers with up to 16 input channels have filters packed for several offsets per operand row,
+        #  which the kernel feeds from the staged rows only)
+        stage = prec != PREC_TF32 or n_out >= STAGING_MIN_ROWS or c_in <= 16
         nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec) if stage else 0
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,

@@ -274,7 +274,7 @@ PAIR_SHAPES = [(64, 76, 3, False, 3, 14, 900),       # small filter matrix: two 
                (30, 72, 3, False, 3, 14, 900),        # channel count not a multiple of four / of a slab
                (130, 270, 3, False, 2, 12, 330),      # two N tiles, more than one range of output channels
                (256, 256, 3, True, 3, 14, 900),       # TF32: the filter matrix needs two ranges; 16-bit: one
-               (16, 16, 5, True, 3, 14, 900),         # 125 offsets, most lists shorter than a tile
+               (20, 16, 5, True, 3, 14, 900),         # 125 offsets, most lists shorter than a tile
                (64, 76, 3, True, 4, 40, 20000),       # several tiles per strip, strips of several CTAs per offset
                (256, 128, 5, True, 2, 24, 1400)]
 
@@ -409,3 +409,33 @@ def test_conv1x1_through_the_gather_kernel(cuda):
     assert _ext.kernel_launches() > l0               # the library's kernel ran
     ref = feats.astype(np.float64) @ conv.weight.detach().cpu().numpy().reshape(48, 40).astype(np.float64)
     assert rel_err(y, ref) <= TOL["fp32"]
+
+
+@pytest.mark.parametrize("c_in,c_out,k,stride,subm", [(3, 36, 3, 2, False), (4, 38, 3, 1, False), (7, 20, 3, 1, True),
+                                                      (16, 76, 3, 2, False), (13, 24, 5, 1, True), (1, 16, 3, 1, False)])
+def test_conv_with_few_input_channels_packs_several_offsets_per_step(cuda, c_in, c_out, k, stride, subm):
+    """TF32 layers whose padded input rows are 4, 8 or 16 floats pack the neighbours at 8, 4 or 2 kernel
+    offsets side by side into one operand row (a 3-channel first layer runs 4 steps per tile instead of
+    27).  Checked against the float64 oracle and the exact fp32 CUDA-core kernel at the TF32 tolerance
+    (max rel err <= 1e-3), and for bit-repeatability."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(100 + c_in)
+    ind = random_voxels(rng, 3, 16, 1500)
+    feats = rng.randn(ind.shape[0], c_in).astype(np.float32)
+    W = (rng.randn(k ** 3, c_in, c_out) / np.sqrt(c_in * k ** 3)).astype(np.float32)
+    pad = k // 2 if (subm or stride == 1) else 1
+    outids, pairs, num = gpu_rulebook(ind, 3, [16] * 3, k, stride, pad, 1, subm, cuda)
+    n_out = outids.shape[0]
+    nbr = _ext.neighbour_table(pairs, num, n_out)
+    f, w = dev(feats, cuda), dev(W, cuda)
+    assert (_ext.lib().ssc_conv_packed_bytes(k ** 3, c_in, c_out, _ext.PREC_TF32)
+            < k ** 3 * 128 * ((c_out + 15) // 16 * 16)) == (((c_in + 3) // 4 * 4) in (4, 8, 16))
+    y = _ext.conv_forward(f, w, nbr, n_out, "tf32")
+    y2 = _ext.conv_forward(f, w, nbr, n_out, "tf32")
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    assert torch.equal(y, y2)
+    ref = O.indice_conv_f64(feats, W, pairs.cpu().numpy(), num.cpu().numpy(), n_out)
+    assert rel_err(y.cpu().numpy(), ref) <= 1e-3
+    exact = _ext.conv_forward(f, w, nbr, n_out, "fp32")
+    assert rel_err(y.cpu().numpy(), exact.cpu().numpy()) <= 1e-3
