@@ -165,7 +165,10 @@ int ssc_materialize(const float *weight, const float *basis, const int32_t *bloc
 /* Pack filters [K,Cin,Cout] fp32 into the tensor-core operand image used by ssc_conv_fwd
  * with precision SSC_PREC_TF32 (round-to-nearest TF32, K-major, 128-byte swizzled, padded) or
  * SSC_PREC_F16 (the same layout with fp16 elements, 64 input channels per 128-byte row).
- * ssc_conv_packed_bytes gives the size of `packed`. */
+ * ssc_conv_packed_bytes gives the size of `packed`.  TF32 layers whose input rows pad to 4, 8 or 16
+ * channels (c_in = 1..8, 13..16) are packed with 8, 4 or 2 kernel offsets side by side in one
+ * operand row; ssc_conv_fwd then needs its staging buffer (ssc_conv_scratch_bytes) whatever the
+ * size of the layer, and the pair-list entry points do not take such layers. */
 size_t ssc_conv_packed_bytes(int K, int c_in, int c_out, int precision);
 int ssc_conv_pack_filters(const float *filters, int K, int c_in, int c_out, int precision,
                           void *packed, void *stream);
