@@ -612,7 +612,7 @@ int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void
 }
 
 // Smallest problem (in 128-row tiles) for which the extra staging launch pays for itself.
-constexpr int kStagingMinTiles = 64;
+constexpr int kStagingMinTiles = 8;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,

@@ -568,7 +568,7 @@ def _resolve_precision(c_in, c_out, precision=None):
 
 # Layers with fewer output rows do not stage a TF32-rounded copy of their input rows (the extra
 # launch would cost more than it saves), so no staging buffer is allocated for them.
-STAGING_MIN_ROWS = 64 * 128
+STAGING_MIN_ROWS = 8 * 128
 
 # Which tensor-core kernel a convolution call takes: 'auto' (by shape, see _use_pairs), 'rows' (the
 # output-stationary kernel: one CTA per 128 output rows, bitwise repeatable) or 'pairs' (the
