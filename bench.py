@@ -912,6 +912,18 @@ def run_only(args):
         _ext.check_status(dev)
         print("only=helpers done")
         return
+    if args.only == "backbone":
+        # three batches of the 4-stage backbone (256 objects), one recording replayed on one stream
+        from ss_conv.utils import synthetic as S
+        pts, fts, ids = S.object_points(range(256), BACKBONE["n_pts"], base_seed=7000)
+        pts, fts, ids = (torch.from_numpy(a).to(dev) for a in (pts, fts, ids))
+        net = Backbone(BACKBONE, dev, 256, depth=1, streams=1)
+        for _ in range(3):
+            pooled = net.submit(pts, fts, ids.int()).result()
+        torch.cuda.synchronize()
+        _ext.check_status(dev)
+        print("only=backbone done, pooled %s, %d launches per replay" % (tuple(pooled.shape), net.graphed.launches))
+        return
     if args.only in ("conv5", "conv5_tf32"):
         # the wide layer at half its batch (8 samples, ~88 k voxels: 90 MB of fp32 features, 90 MB of outputs)
         from ss_conv.utils import synthetic as S
@@ -1059,7 +1071,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default=None,
-                    choices=["conv", "conv_fp16", "conv_bf16", "conv5", "conv5_tf32", "backward", "rulebook", "step", "helpers"],
+                    choices=["conv", "conv_fp16", "conv_bf16", "conv5", "conv5_tf32", "backward", "rulebook", "step", "helpers", "backbone"],
                     help="run just one kernel group a few times (for ncu captures): the cfg2 convolution call, the wide "
                          "cfg5 layer at half its batch, the backward kernels, the whole cfg2 step, the helper kernels")
     args = ap.parse_args()
