@@ -230,26 +230,27 @@ __global__ void mark_outputs_generic_kernel(const int4 *__restrict__ indices, in
 __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
                                       const uint32_t *__restrict__ word_prefix, long long n_words,
                                       Geometry g, int n_out, int4 *out_indices) {
-  // one lane per bitmap bit (a warp per word): the rank of a set bit is the word's prefix plus
-  // the number of set bits below it
-  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long w = t >> 5;
+  // one thread per bitmap word (32 cells): most words of a sparse grid are empty and leave at once;
+  // the set bits of a word get consecutive ranks from the word's prefix
+  const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (w >= n_words) return;
-  const int bit = (int)(t & 31);
-  const uint32_t bits = __ldg(bitmap + w);
-  if (!((bits >> bit) & 1u)) return;
-  const uint32_t rank = __ldg(word_prefix + w) + (uint32_t)__popc(bits & ((1u << bit) - 1u));
-  if ((int)rank >= n_out) return;
+  uint32_t bits = __ldg(bitmap + w);
+  if (bits == 0u) return;
+  uint32_t rank = __ldg(word_prefix + w);
   const int vol = g.out_shape[0] * g.out_shape[1] * g.out_shape[2];
   const int yz = g.out_shape[1] * g.out_shape[2];
-  const uint32_t flat = (uint32_t)(w * 32 + bit);
-  const int b = flat / vol;
-  int r = flat - b * vol;
-  const int x = r / yz;
-  r -= x * yz;
-  const int y = r / g.out_shape[2];
-  const int z = r - y * g.out_shape[2];
-  out_indices[rank] = make_int4(b, x, y, z);
+  while (bits != 0u && (int)rank < n_out) {
+    const int bit = __ffs((int)bits) - 1;
+    bits &= bits - 1u;
+    const uint32_t flat = (uint32_t)(w * 32 + bit);
+    const int b = flat / vol;
+    int r = flat - b * vol;
+    const int x = r / yz;
+    r -= x * yz;
+    const int y = r / g.out_shape[2];
+    const int z = r - y * g.out_shape[2];
+    out_indices[rank++] = make_int4(b, x, y, z);
+  }
 }
 
 // Dense-map lookup: one thread per output row walks all kernel offsets, so the row's coordinates
@@ -537,7 +538,7 @@ int bitmap_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long
   Geometry g;
   memset(&g, 0, sizeof(g));
   for (int d = 0; d < 3; ++d) g.out_shape[d] = shape[d];
-  { decode_outputs_kernel<<<ceil_div(n_words * 32, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out,
+  { decode_outputs_kernel<<<ceil_div(n_words, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out,
                                                                 (int4 *)out_indices); note_launches(1); }
   SSC_CHECK_LAUNCH("bitmap_decode");
   return 0;
@@ -727,7 +728,7 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
   SSC_REQUIRE((long long)n_out <= s.out_cap, "rulebook_conv_fill: n_out %d exceeds the possible maximum", n_out);
   cudaStream_t st = as_stream(stream);
   if (n_out > 0) {
-    { decode_outputs_kernel<<<ceil_div(s.n_words * 32, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
+    { decode_outputs_kernel<<<ceil_div(s.n_words, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
                                                                    (int4 *)out_indices); note_launches(1); }
     SSC_CHECK_LAUNCH("decode_outputs");
   }
