@@ -227,6 +227,31 @@ __global__ void mark_outputs_generic_kernel(const int4 *__restrict__ indices, in
   atomicOr(bitmap + (flat >> 5), 1u << (flat & 31));
 }
 
+// One lane per bitmap bit (a warp per word), for small or densely set bitmaps: every set bit is written
+// by a thread of its own (the per-word kernel below would write up to 32 rows one after the other).
+__global__ void decode_outputs_bits_kernel(const uint32_t *__restrict__ bitmap,
+                                           const uint32_t *__restrict__ word_prefix, long long n_words,
+                                           Geometry g, int n_out, int4 *out_indices) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long w = t >> 5;
+  if (w >= n_words) return;
+  const int bit = (int)(t & 31);
+  const uint32_t bits = __ldg(bitmap + w);
+  if (!((bits >> bit) & 1u)) return;
+  const uint32_t rank = __ldg(word_prefix + w) + (uint32_t)__popc(bits & ((1u << bit) - 1u));
+  if ((int)rank >= n_out) return;
+  const int vol = g.out_shape[0] * g.out_shape[1] * g.out_shape[2];
+  const int yz = g.out_shape[1] * g.out_shape[2];
+  const uint32_t flat = (uint32_t)(w * 32 + bit);
+  const int b = flat / vol;
+  int r = flat - b * vol;
+  const int x = r / yz;
+  r -= x * yz;
+  const int y = r / g.out_shape[2];
+  const int z = r - y * g.out_shape[2];
+  out_indices[rank] = make_int4(b, x, y, z);
+}
+
 __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
                                       const uint32_t *__restrict__ word_prefix, long long n_words,
                                       Geometry g, int n_out, int4 *out_indices) {
@@ -250,6 +275,18 @@ __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
     const int y = r / g.out_shape[2];
     const int z = r - y * g.out_shape[2];
     out_indices[rank++] = make_int4(b, x, y, z);
+  }
+}
+
+// Small bitmaps (coarse grids are densely set and have few words) take the per-bit kernel, large ones
+// (fine grids: mostly empty words) the per-word kernel.
+constexpr long long kDecodePerBitMaxWords = 32768;
+static void launch_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long n_words, const Geometry &g, int n_out,
+                          int4 *out_indices, cudaStream_t st) {
+  if (n_words <= kDecodePerBitMaxWords) {
+    { decode_outputs_bits_kernel<<<ceil_div(n_words * 32, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out, out_indices); note_launches(1); }
+  } else {
+    { decode_outputs_kernel<<<ceil_div(n_words, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out, out_indices); note_launches(1); }
   }
 }
 
@@ -538,8 +575,7 @@ int bitmap_decode(const uint32_t *bitmap, const uint32_t *word_prefix, long long
   Geometry g;
   memset(&g, 0, sizeof(g));
   for (int d = 0; d < 3; ++d) g.out_shape[d] = shape[d];
-  { decode_outputs_kernel<<<ceil_div(n_words, 256), 256, 0, st>>>(bitmap, word_prefix, n_words, g, n_out,
-                                                                (int4 *)out_indices); note_launches(1); }
+  launch_decode(bitmap, word_prefix, n_words, g, n_out, (int4 *)out_indices, st);
   SSC_CHECK_LAUNCH("bitmap_decode");
   return 0;
 }
@@ -728,8 +764,7 @@ extern "C" int ssc_rulebook_conv_fill(const int32_t *indices, int n_in, int batc
   SSC_REQUIRE((long long)n_out <= s.out_cap, "rulebook_conv_fill: n_out %d exceeds the possible maximum", n_out);
   cudaStream_t st = as_stream(stream);
   if (n_out > 0) {
-    { decode_outputs_kernel<<<ceil_div(s.n_words, 256), 256, 0, st>>>(s.bitmap, s.word_prefix, s.n_words, g, n_out,
-                                                                   (int4 *)out_indices); note_launches(1); }
+    launch_decode(s.bitmap, s.word_prefix, s.n_words, g, n_out, (int4 *)out_indices, st);
     SSC_CHECK_LAUNCH("decode_outputs");
   }
   if (int e = lookup_and_compact(out_indices, n_out, n_in, batch, g, s, nbr, pairs, indice_num, st, n_out_dev)) return e;
