@@ -213,7 +213,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
                  "r"((uint32_t)p.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  } else {
+  } else if (!GROUPED) {   // (grouped offsets: every group is a step, absent neighbours are zero-filled pieces)
     // which kernel offsets touch this tile: four offsets per pass so that 16 loads are in
     // flight per lane before the first ballot
     int scan_rows[4];  // this lane's four rows of the tile (-1 past the end)
@@ -258,12 +258,8 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
   }
   if (tid == 0) {
     int n = 0;
-    if (GROUPED) {   // steps are groups of opk offsets: a group is live when one of its offsets is
-      for (int g = 0; g * p.opk < K; ++g) {
-        bool any = false;
-        for (int i = 0; i < p.opk && g * p.opk + i < K; ++i) any = any || act_flag[g * p.opk + i];
-        if (any) act_list[n++] = (uint8_t)g;
-      }
+    if (GROUPED) {   // steps are groups of opk offsets, all of them
+      for (int g = 0; g * p.opk < K; ++g) act_list[n++] = (uint8_t)g;
     } else {
       for (int kappa = 0; kappa < K; ++kappa)
         if (act_flag[kappa]) act_list[n++] = (uint8_t)kappa;
