@@ -59,7 +59,7 @@ __global__ void voxelize_fwd_kernel(const float *__restrict__ feats, float *__re
 struct P2VScratch {
   uint32_t *bitmap, *word_prefix, *block_sums;
   uint32_t *count;   // [n_point + 1] per-voxel point count, then exclusive start offsets
-  uint32_t *cursor;  // [n_point] fill cursor (modes 3/4) or selected point (modes 1/2)
+  uint32_t *cursor;  // [n_point] arrival rank of every point in its voxel (modes 3/4) or selected point per voxel (modes 1/2)
   int32_t *order;    // [n_point] point ids grouped by voxel
   uint32_t *block_sums2;
   int32_t *misc;
@@ -170,16 +170,18 @@ __global__ void p2v_inverse_kernel(const float *__restrict__ points, const int32
   inverse[i] = v;
   if (mode == 1) atomicMin(select + v, (uint32_t)i);
   else if (mode == 2) atomicMax(select + v, (uint32_t)i);
-  else atomicAdd(count + v, 1u);
+  else select[i] = atomicAdd(count + v, 1u);   // modes 3 / 4: arrival rank of the point in its voxel (select is per point then)
 }
 
-__global__ void p2v_scatter_kernel(const int32_t *__restrict__ inverse, int n, uint32_t *cursor, int32_t *order) {
+// order[start of the point's voxel + its arrival rank] = point: the rank was taken when the points were
+// counted, so this pass needs no atomics (the lists are put into point order by the pass after it).
+__global__ void p2v_scatter_kernel(const int32_t *__restrict__ inverse, int n, const uint32_t *__restrict__ start,
+                                   const uint32_t *__restrict__ rank, int32_t *order) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int v = inverse[i];
   if (v < 0) return;
-  uint32_t pos = atomicAdd(cursor + v, 1u);
-  order[pos] = i;
+  order[__ldg(start + v) + __ldg(rank + i)] = i;
 }
 
 __global__ void p2v_sort_segments_kernel(const uint32_t *__restrict__ start, int n_voxel, int32_t *order) {
@@ -526,8 +528,7 @@ extern "C" int ssc_p2v_fill(const float *points, const int32_t *batch_ids, const
   if (mode >= 3) {
     // counts -> exclusive start offsets (in place), cursor = copy
     if (int e = exclusive_scan_u32<false>(s.count, (long long)n_voxel + 1, s.count, s.block_sums2, nullptr, nullptr, st)) return e;
-    cudaMemcpyAsync(s.cursor, s.count, (size_t)n_voxel * 4, cudaMemcpyDeviceToDevice, st);
-    { p2v_scatter_kernel<<<ceil_div(n_point, 256), 256, 0, st>>>(inverse, n_point, s.cursor, s.order); note_launches(1); }
+    { p2v_scatter_kernel<<<ceil_div(n_point, 256), 256, 0, st>>>(inverse, n_point, s.count, s.cursor, s.order); note_launches(1); }
     { p2v_sort_segments_kernel<<<ceil_div(n_voxel, 128), 128, 0, st>>>(s.count, n_voxel, s.order); note_launches(1); }
     if (c <= 4) {
       { p2v_reduce_small_kernel<4><<<ceil_div(n_voxel, 256), 256, 0, st>>>(feats, c, s.count, s.order, n_voxel, mode == 4, voxel_feats); note_launches(1); }
