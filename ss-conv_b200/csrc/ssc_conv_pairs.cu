@@ -17,17 +17,19 @@
 //     only operand traffic per tile is the gathered rows.  All strips walk their lists from the
 //     first row to the last at the same pace, so at any time the CTAs of the grid read and update
 //     the same window of rows: the gathers and the reductions hit L2.
-//   * warps 0 .. S-1: producers.  Warp w owns ring slot w: lane = row, 16-byte cp.async copies of
-//     the row's 128-byte slab from the staged operand image (TF32-rounded fp32, fp16 or bf16) into
-//     the K-major 128-byte-swizzled operand layout, then one arrival per lane on the slot's "full"
-//     mbarrier.
+//   * warps 0 .. S-1: producers.  Warp w owns ring slot w: two lanes per row (each 32-byte sector
+//     is asked for once), 16-byte cp.async copies of the row's 128-byte slab from the staged operand
+//     image (TF32-rounded fp32, fp16 or bf16) into the K-major 128-byte-swizzled operand layout,
+//     then one arrival per lane on the slot's "full" mbarrier.
 //   * warp S: tensor-memory allocation and the MMA-issuing thread: tcgen05.mma M=128, N<=256,
 //     accumulating over the slabs of a tile in one of TWO accumulator buffers, tcgen05.commit to
 //     the slot's "empty" barrier and, after the last slab, to the buffer's "accumulator full"
 //     barrier.
-//   * warps S+1 .. S+4: epilogue.  tcgen05.ld (lane = pair), a 32x32 transpose through shared
-//     memory so that eight neighbouring lanes hold 128 contiguous bytes of one output row, then
-//     red.global.add.v4.f32.  The epilogue of tile t runs under the MMAs of tile t+1.
+//   * warps S+1 .. S+8: epilogue, two per quarter of the tensor-memory lanes (they take the
+//     32-column blocks in turn).  tcgen05.ld (lane = pair), a transposition through shared memory,
+//     16 rows at a time, so that eight neighbouring lanes hold the 128 contiguous bytes of one
+//     output row, then red.global.add.v4.f32: the reductions reach L2 as whole 128-byte lines.
+//     The epilogue of tile t runs under the MMAs of tile t+1.
 //
 // The output must be zero before the launch (the host wrapper clears it).  The sums of an output
 // row arrive in no fixed order, so results are reproducible only up to fp32 rounding of a sum of
