@@ -110,3 +110,22 @@ def test_synthetic_inputs_are_seeded_per_sample():
     assert a[:, 1:].min() >= 0 and a[:, 1:].max() < 32
     p, f, ids = S.object_points([0, 1], 1024)
     assert p.shape == (2048, 3) and np.abs(p).max() < 0.5 and f.min() >= 0 and f.max() <= 1
+
+
+def test_packed_filter_sizes_follow_the_operand_layout():
+    """ssc_conv_packed_bytes is pure host arithmetic.  TF32: one 128-byte operand row holds 32 input
+    channels, or the neighbours at 8 / 4 / 2 kernel offsets when the rows pad to 4 / 8 / 16 channels;
+    16-bit: 64 channels per row, never grouped."""
+    from ss_conv import _ext
+    L = _ext.lib()
+    n_pad = 48                                        # 38 output channels padded to a multiple of 16
+    full = lambda K, slabs: K * slabs * n_pad * 128   # noqa: E731
+    assert L.ssc_conv_packed_bytes(27, 32, 38, _ext.PREC_TF32) == full(27, 1)
+    assert L.ssc_conv_packed_bytes(27, 64, 38, _ext.PREC_TF32) == full(27, 2)
+    assert L.ssc_conv_packed_bytes(27, 20, 38, _ext.PREC_TF32) == full(27, 1)        # pads to 20: not grouped
+    assert L.ssc_conv_packed_bytes(27, 3, 38, _ext.PREC_TF32) == full(4, 1)          # 8 offsets per row
+    assert L.ssc_conv_packed_bytes(27, 8, 38, _ext.PREC_TF32) == full(7, 1)          # 4 offsets per row
+    assert L.ssc_conv_packed_bytes(27, 16, 38, _ext.PREC_TF32) == full(14, 1)        # 2 offsets per row
+    assert L.ssc_conv_packed_bytes(27, 3, 38, _ext.PREC_BF16) == full(27, 1)
+    assert L.ssc_conv_packed_bytes(27, 100, 38, _ext.PREC_F16) == full(27, 2)
+    assert L.ssc_conv_pairs_supported(16, 256, _ext.PREC_TF32) == 0                  # grouped filters: not for the pair-list kernel
