@@ -655,7 +655,7 @@ def run_ours(args):
         host_us[0], host_us[1] = t_submit / (args.steps * regions) * 1e6, t_result / (args.steps * regions) * 1e6
         return g, times, vox, g.replays - r0, g.fallbacks - f0
 
-    DEPTH, STREAMS, LAG = 6, 3, 2
+    DEPTH, STREAMS, LAG = (int(v) for v in args.overlap.split(","))   # recordings, streams, steps in flight
     with ClockSampler(local, enabled=(rank == 0), core=(my_cores[-1] if len(my_cores) > 1 else None)) as clk:
         graphed, region_ms, voxels, n_replays, graph_fallbacks = timed_steps(DEPTH, STREAMS, LAG, REGIONS)
     ms = float(statistics.median(region_ms))
@@ -853,7 +853,8 @@ def run_ours(args):
                                "CUDA graph (device-side row counts, capacity-sized buffers), one recording per rotating batch "
                                "with the batch resident in its input buffers; a step = replay + read-back and check of the "
                                "row counts and of the kernel status word, step s+1 queued before the host checks step s; the recordings "
-                               "replay on three streams in turn (6 recordings, results taken two steps late), so consecutive steps overlap on the device",
+                               "replay on %d streams in turn (%d recordings, results taken %d steps late), so consecutive steps overlap on the device"
+                               % (STREAMS, DEPTH, LAG),
                        "eager_ms_per_step": eager_step_ms, "graph_fallbacks": graph_fallbacks,
                        "host_us_per_step": {"queue_a_step": host_submit_us, "wait_for_and_check_a_step": host_result_us,
                                             "note": "host time in the timed loop (max over ranks); the second includes waiting for the device"},
@@ -1070,6 +1071,8 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--overlap", default="8,4,3",
+                    help="layer step loop: recordings of the step, streams they replay on, steps in flight before the host waits")
     ap.add_argument("--only", default=None,
                     choices=["conv", "conv_fp16", "conv_bf16", "conv5", "conv5_tf32", "backward", "rulebook", "step", "helpers", "backbone"],
                     help="run just one kernel group a few times (for ncu captures): the cfg2 convolution call, the wide "
