@@ -389,18 +389,20 @@ def layer_numbers(name, ind, batch, V, k, stride, pad, subm, c_in, c_out, precis
             entry["scatter_add"] = {"what": "the pair-list kernel adds every accumulator tile to scattered output rows with fp32 "
                                             "reductions at L2 (4 P Cout bytes per call); ceiling = a kernel that issues nothing but "
                                             "such reductions over the same row order (ssc_scatter_add_rate), timed here",
-                                    "bytes_per_call": red_bytes, "ceiling_gbs": ceiling,
+                                    "bytes_per_call": red_bytes, "ceiling_gbs": ceiling["ceiling_gbs"],
                                     "call_gbs": red_bytes / (ms * 1e-3) / 1e9,
-                                    "frac_of_ceiling": red_bytes / (ms * 1e-3) / 1e9 / ceiling,
-                                    "tflops_at_ceiling": ceiling * 1e9 / (4.0 * c_out) * 2.0 * c_in * c_out / 1e12}
+                                    "frac_of_ceiling": red_bytes / (ms * 1e-3) / 1e9 / ceiling["ceiling_gbs"],
+                                    "tflops_at_ceiling": ceiling["ceiling_gbs"] * 1e9 / (4.0 * c_out) * 2.0 * c_in * c_out / 1e12,
+                                    "rates": {k: v for k, v in ceiling.items() if k != "ceiling_gbs"}}
         res[prec] = entry
     _ext.check_status(dev)
     return res
 
 
 def scatter_add_ceiling(nbr, n_out, c_out, P):
-    """GB/s of fp32 scatter-add reductions the device takes (nothing else running): the output rows of
-    the layer's pair lists, reduced 128 bytes per row and instruction."""
+    """GB/s of fp32 scatter-add reductions the device takes (nothing else running) over the output rows of
+    the layer's pair lists: the ceiling (128 bytes per row and instruction, 16 warps per SM) and how the
+    rate depends on the shape of a reduction instruction and on the number of issuing warps."""
     from ss_conv import _ext
     # the row order of the kernel's sweep: all offsets walk the output rows together, so at any time
     # the reductions fall into a window of rows that stays in L2; inside the window one offset after
@@ -411,11 +413,17 @@ def scatter_add_ceiling(nbr, n_out, c_out, P):
     order = nz[:, 1][torch.argsort(key, stable=True)].to(torch.int32).contiguous()
     width = (c_out + 31) // 32 * 32
     scratch = torch.zeros(n_out, width, device=nbr.device)
-    warps = torch.cuda.get_device_properties(nbr.device).multi_processor_count * 16
-    steps = max(1, -(-P // (warps * 32)))
-    nbytes = _ext.scatter_add_rate(scratch, order, steps)
-    ms = graph_ms(lambda: _ext.scatter_add_rate(scratch, order, steps), reps=7)
-    return nbytes / (ms * 1e-3) / 1e9
+    sms = torch.cuda.get_device_properties(nbr.device).multi_processor_count
+
+    def rate(lanes, warps):
+        steps = max(1, -(-P // (sms * warps * 32)))
+        nbytes = _ext.scatter_add_rate(scratch, order, steps, lanes, warps)
+        ms = graph_ms(lambda: _ext.scatter_add_rate(scratch, order, steps, lanes, warps), reps=5)
+        return nbytes / (ms * 1e-3) / 1e9
+
+    return {"ceiling_gbs": rate(8, 16),
+            "gbs_by_bytes_per_row_and_instruction_16_warps": {str(16 * lanes): rate(lanes, 16) for lanes in (1, 2, 4, 8)},
+            "gbs_by_warps_per_sm_128_bytes_per_row": {str(w): rate(8, w) for w in (1, 2, 4, 8)}}
 
 
 def layers_leg(dev, peak_hbm, peak_bf16):

@@ -431,13 +431,14 @@ int ssc_gate_bwd(const float *x, const float *gy, int n, int c_total, int c_out,
                  int scalar_act, int gate_act, float *gx, void *stream);
 
 /* Measurement support, no counterpart in the reference: issues nothing but fp32 scatter-add
- * reductions (red.global.add.v4.f32, 128 contiguous bytes per row and instruction) of 1.0 into
- * out[rows[j], :] for steps * 32 * (warps of the grid) list positions j, wrapping round the list of
- * n_idx row numbers.  out [n_rows, row_floats] is caller scratch, row_floats a multiple of 32.
- * *bytes receives the bytes reduced; bytes / the caller's device timing is the scatter-add rate
- * of the device, the ceiling of the pair-list convolution's reduction traffic (4 P Cout bytes). */
+ * reductions (red.global.add.v4.f32) of 1.0 into out[rows[j], :] for steps * 32 * (warps of the grid)
+ * list positions j, wrapping round the list of n_idx row numbers.  lanes_per_row (1, 2, 4, 8) =
+ * contiguous 16-byte pieces per row and instruction, warps_per_sm (1..16) = issuing warps; (8, 16)
+ * measures the device's scatter-add rate, the ceiling of the pair-list convolution's reduction
+ * traffic (4 P Cout bytes).  out [n_rows, row_floats] is caller scratch, row_floats a multiple of 32.
+ * *bytes receives the bytes reduced; the caller times the launch. */
 int ssc_scatter_add_rate(float *out, int row_floats, const int32_t *rows, int n_idx, int steps,
-                         unsigned long long *bytes, void *stream);
+                         int lanes_per_row, int warps_per_sm, unsigned long long *bytes, void *stream);
 
 #ifdef __cplusplus
 }

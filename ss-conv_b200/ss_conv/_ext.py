@@ -104,7 +104,7 @@ SIGNATURES = {
                            c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_gate_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_void_p, c_void_p]),
-    "ssc_scatter_add_rate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "ssc_scatter_add_rate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 
 _lib_handle = None
@@ -1211,13 +1211,14 @@ def gate_backward(x, gy, c_out, gate_of_channel, field_start, field_len, scalar_
     return gx
 
 
-def scatter_add_rate(out, rows, steps):
+def scatter_add_rate(out, rows, steps, lanes_per_row=8, warps_per_sm=16):
     """Launches the library's reduction-only kernel (ssc_scatter_add_rate): 1.0 is added to
     out[rows[j], :] for steps * 32 * (warps of the grid) list positions.  Returns the bytes
-    reduced; the caller times the launch.  out [n_rows, c] fp32 scratch with c % 32 == 0."""
+    reduced; the caller times the launch.  out [n_rows, c] fp32 scratch with c % 32 == 0.
+    lanes_per_row: 16-byte pieces per row and instruction (1, 2, 4, 8); warps_per_sm: issuing warps."""
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] % 32 == 0
     rows = rows.to(torch.int32).contiguous()
     nbytes = ctypes.c_ulonglong(0)
     _check(lib().ssc_scatter_add_rate(_p(out), int(out.shape[1]), _p(rows, torch.int32), int(rows.numel()), int(steps),
-                                      ctypes.byref(nbytes), _stream()))
+                                      int(lanes_per_row), int(warps_per_sm), ctypes.byref(nbytes), _stream()))
     return int(nbytes.value)

@@ -316,12 +316,13 @@ def test_scatter_add_rate_kernel_adds_what_it_reports(cuda):
     rng = np.random.RandomState(9)
     n_rows, width = 3000, 64
     rows = torch.from_numpy(rng.randint(0, n_rows, 50000).astype(np.int32)).to(cuda)
-    out = torch.zeros(n_rows, width, device=cuda)
-    nbytes = _ext.scatter_add_rate(out, rows, 1)
-    torch.cuda.synchronize()
-    _ext.check_status(cuda)
-    positions = nbytes // (width * 4)
-    assert positions % 32 == 0 and positions > 0
-    idx = torch.arange(positions, device=cuda) % rows.numel()
-    expect = torch.bincount(rows[idx].long(), minlength=n_rows).float()
-    assert torch.equal(out, expect[:, None].expand(n_rows, width))
+    for lanes, warps in ((8, 16), (1, 16), (2, 4), (4, 1)):
+        out = torch.zeros(n_rows, width, device=cuda)
+        nbytes = _ext.scatter_add_rate(out, rows, 1, lanes, warps)
+        torch.cuda.synchronize()
+        _ext.check_status(cuda)
+        positions = nbytes // (width * 4)
+        assert positions % 32 == 0 and positions > 0
+        idx = torch.arange(positions, device=cuda) % rows.numel()
+        expect = torch.bincount(rows[idx].long(), minlength=n_rows).float()
+        assert torch.equal(out, expect[:, None].expand(n_rows, width)), (lanes, warps)
