@@ -256,24 +256,29 @@ __global__ void decode_outputs_kernel(const uint32_t *__restrict__ bitmap,
                                       const uint32_t *__restrict__ word_prefix, long long n_words,
                                       Geometry g, int n_out, int4 *out_indices) {
   // one thread per bitmap word (32 cells): most words of a sparse grid are empty and leave at once;
-  // the set bits of a word get consecutive ranks from the word's prefix
+  // the set bits of a word get consecutive ranks from the word's prefix.  The coordinates of the
+  // word's first cell are decoded once (three integer divisions); a set bit is that cell plus its
+  // bit number, carried over z, y and x.
   const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (w >= n_words) return;
   uint32_t bits = __ldg(bitmap + w);
   if (bits == 0u) return;
   uint32_t rank = __ldg(word_prefix + w);
-  const int vol = g.out_shape[0] * g.out_shape[1] * g.out_shape[2];
-  const int yz = g.out_shape[1] * g.out_shape[2];
+  const int X = g.out_shape[0], Y = g.out_shape[1], Z = g.out_shape[2];
+  const int vol = X * Y * Z, yz = Y * Z;
+  const uint32_t flat0 = (uint32_t)(w * 32);
+  const int b0 = flat0 / vol;
+  int r = flat0 - b0 * vol;
+  const int x0 = r / yz;
+  r -= x0 * yz;
+  const int y0 = r / Z, z0 = r - (r / Z) * Z;
   while (bits != 0u && (int)rank < n_out) {
     const int bit = __ffs((int)bits) - 1;
     bits &= bits - 1u;
-    const uint32_t flat = (uint32_t)(w * 32 + bit);
-    const int b = flat / vol;
-    int r = flat - b * vol;
-    const int x = r / yz;
-    r -= x * yz;
-    const int y = r / g.out_shape[2];
-    const int z = r - y * g.out_shape[2];
+    int b = b0, x = x0, y = y0, z = z0 + bit;
+    while (z >= Z) { z -= Z; ++y; }
+    while (y >= Y) { y -= Y; ++x; }
+    while (x >= X) { x -= X; ++b; }
     out_indices[rank++] = make_int4(b, x, y, z);
   }
 }
