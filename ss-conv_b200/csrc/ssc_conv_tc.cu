@@ -311,17 +311,10 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
       // step holds the rows' neighbours at opk consecutive offsets side by side; a missing neighbour is
       // a zero-filled piece, so no row is ever switched off.  The filter slab of the group is packed to match.
       const int cpc = c_in >> 2;                   // 16-byte chunks per offset
+      // (the loops over the 32-row groups are kept rolled: this path runs four steps per CTA, and as
+      //  straight-line code it spent most of its time waiting for instruction fetches)
       for (int j = slot; j < n_iter; j += S) {
         const int group = act_list[j];
-        int idx[4][8];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-          for (int o = 0; o < 8; ++o) {
-            const int kap = group * p.opk + o;
-            idx[q][o] = (q >= q0 && q < q0 + q_per && o < p.opk && kap < K && my_rows[q] >= 0)
-                            ? __ldg(nbr + (size_t)kap * n_out + my_rows[q]) : -1;
-          }
         if (j >= S) {
           if (!mbar_wait_warp(smem_u32(empty_bars + slot), par ^ 1u, abort_flag)) break;
           tc_fence_after();
@@ -335,16 +328,24 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
                        "l"(bsrc), "r"(nbytes), "r"(bar)
                        : "memory");
         }
+#pragma unroll 1
+        for (int q = q0; q < q0 + q_per; ++q) {
+          const int row = m0 + q * 32 + lane;
+          const int my_row = row < n_rows ? (order ? __ldg(order + row) : row) : -1;
+          int idx[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (q < q0 || q >= q0 + q_per) continue;
+          for (int o = 0; o < 8; ++o) {
+            const int kap = group * p.opk + o;
+            idx[o] = (o < p.opk && kap < K && my_row >= 0) ? __ldg(nbr + (size_t)kap * n_out + my_row) : -1;
+          }
           if (lane == 0) slot_masks[slot * 4 + q] = 0u;          // every row takes part
-          const uint32_t a_row = slot_addr + row_off[q];
+          const uint32_t a_row = slot_addr + (uint32_t)(q * 4 + (lane >> 3)) * 1024u + sw * 128u;
 #pragma unroll
           for (int o = 0; o < 8; ++o) {
             if (o >= p.opk) break;
-            const int src_row = idx[q][o];
+            const int src_row = idx[o];
             const float *fp = features + (size_t)(src_row >= 0 ? src_row : 0) * c_in;
+#pragma unroll 1
             for (int cc = 0; cc < cpc; ++cc) {
               const uint32_t chunk = (uint32_t)(o * cpc + cc);
               cp_async16_cg(a_row + ((chunk ^ sw) << 4), fp + cc * 4, src_row >= 0 ? 16u : 0u);
