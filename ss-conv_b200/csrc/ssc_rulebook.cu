@@ -182,7 +182,6 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
   const Reach rx = reach_of(g, 0, c.y), ry = reach_of(g, 1, c.z), rz = reach_of(g, 2, c.w);
   if (rx.n <= 0 || ry.n <= 0 || rz.n <= 0) return;
   const int base_b = c.x * g.out_shape[0];
-  const bool coarse = g.out_shape[0] * g.out_shape[1] * g.out_shape[2] <= 4096;   // few cells per sample: many inputs per bitmap word
   for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
     for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
       const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
@@ -190,14 +189,82 @@ __global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int
       for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
         const uint32_t flat = row + (uint32_t)z;
         if ((flat >> 5) != word) {
-          if (bits) set_bits(bitmap + word, bits, coarse);
+          if (bits) set_bits(bitmap + word, bits, false);
           word = flat >> 5;
           bits = 0u;
         }
         bits |= 1u << (flat & 31);
       }
-      if (bits) set_bits(bitmap + word, bits, coarse);
+      if (bits) set_bits(bitmap + word, bits, false);
     }
+}
+
+// The same for coarse output grids (at most kCoarseVolume cells per sample), where the inputs of a
+// sample all reach the same few bitmap words.  A block ORs its rows' bits into a shared-memory
+// image of the words its samples own and then sends one atomic per non-zero word; rows that arrive
+// ordered by sample (the order every rulebook and the voxelizer produce) give a block one or two
+// samples.  A block whose rows span more words than the image holds marks them directly.
+constexpr int kCoarseVolume = 4096;
+constexpr int kCoarseImageWords = 1024;
+__global__ void __launch_bounds__(128)
+mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g, uint32_t *bitmap,
+                           const int32_t *__restrict__ n_dev) {
+  __shared__ uint32_t image[kCoarseImageWords];
+  __shared__ int b_min, b_max;
+  const int live = live_rows(n, n_dev);
+  if ((int)(blockIdx.x * blockDim.x) >= live) return;            // the whole block
+  for (int i = threadIdx.x; i < kCoarseImageWords; i += blockDim.x) image[i] = 0u;
+  if (threadIdx.x == 0) { b_min = 0x7FFFFFFF; b_max = -1; }
+  __syncthreads();
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  int4 c = make_int4(0, 0, 0, 0);
+  Reach rx = {0, 1, 0}, ry = {0, 1, 0}, rz = {0, 1, 0};
+  bool ok = false;
+  if (j < live) {
+    c = indices[j];
+    if ((unsigned)c.x < (unsigned)batch && in_range3(c.y, c.z, c.w, g.in_shape)) {
+      rx = reach_of(g, 0, c.y); ry = reach_of(g, 1, c.z); rz = reach_of(g, 2, c.w);
+      ok = rx.n > 0 && ry.n > 0 && rz.n > 0;
+    }
+  }
+  const int w_min = __reduce_min_sync(0xFFFFFFFFu, ok ? c.x : 0x7FFFFFFF);
+  const int w_max = __reduce_max_sync(0xFFFFFFFFu, ok ? c.x : -1);
+  if ((threadIdx.x & 31) == 0 && w_max >= 0) { atomicMin(&b_min, w_min); atomicMax(&b_max, w_max); }
+  __syncthreads();
+  if (b_max < 0) return;                                         // no row of the block reaches an output
+  const uint32_t vol = (uint32_t)(g.out_shape[0] * g.out_shape[1] * g.out_shape[2]);
+  const uint32_t word_lo = ((uint32_t)b_min * vol) >> 5, word_hi = ((uint32_t)(b_max + 1) * vol - 1u) >> 5;
+  const bool staged = word_hi - word_lo < (uint32_t)kCoarseImageWords;
+  if (ok) {
+    const int base_b = c.x * g.out_shape[0];
+    for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
+      for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
+        const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
+        uint32_t word = 0xFFFFFFFFu, bits = 0u;
+        for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
+          const uint32_t flat = row + (uint32_t)z;
+          if ((flat >> 5) != word) {
+            if (bits) {
+              if (staged) atomicOr(&image[word - word_lo], bits);
+              else set_bits(bitmap + word, bits, true);
+            }
+            word = flat >> 5;
+            bits = 0u;
+          }
+          bits |= 1u << (flat & 31);
+        }
+        if (bits) {
+          if (staged) atomicOr(&image[word - word_lo], bits);
+          else set_bits(bitmap + word, bits, true);
+        }
+      }
+  }
+  if (!staged) return;
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i <= word_hi - word_lo; i += blockDim.x) {
+    const uint32_t bits = image[i];
+    if (bits) set_bits(bitmap + word_lo + i, bits, true);
+  }
 }
 
 // General fallback (stride and dilation both above one in some dimension): one thread per (input row, kernel offset).
@@ -736,7 +803,9 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (n_in > 0) {
     bool simple = true;
     for (int d = 0; d < 3; ++d) simple = simple && (g.transpose || g.stride[d] == 1 || g.dilation[d] == 1);
-    if (simple) {
+    if (simple && g.out_shape[0] * g.out_shape[1] * g.out_shape[2] <= kCoarseVolume) {
+      { mark_outputs_coarse_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
+    } else if (simple) {
       { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
     } else {
       { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }

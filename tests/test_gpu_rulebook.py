@@ -162,3 +162,21 @@ def test_lazy_pairs_materialise_to_the_same_lists(cuda):
         assert lazy[1].shape == eager[1].shape and torch.equal(lazy[0], eager[0]) and torch.equal(lazy[2], eager[2])
         assert torch.equal(lazy[1].materialize(), eager[1])
         assert torch.equal(lazy[1][3], eager[1][3])          # tensor behaviour on demand
+
+
+@pytest.mark.parametrize("order", ["by_sample", "shuffled"])
+def test_rulebook_on_a_coarse_grid_with_many_samples(cuda, order):
+    """Coarse output grids mark their cells through a per-block image of bitmap words when a block's
+    rows belong to few samples (rows ordered by sample) and directly when they do not (shuffled rows
+    of 40 samples span more words than the image holds): same rulebook either way."""
+    rng = np.random.RandomState(77)
+    ind = random_voxels(rng, 40, 16, 260)
+    if order == "shuffled":
+        ind = ind[rng.permutation(ind.shape[0])]
+    ind = np.ascontiguousarray(ind.astype(np.int32))
+    for k, s, p in ((3, 1, 1), (3, 2, 1), (2, 2, 0)):
+        got = gpu_rulebook(ind, 40, [16] * 3, k, s, p, 1, False, cuda)
+        ref = O.get_indice_pairs(ind, 40, [16] * 3, k, s, p, 1, False)
+        assert_rulebook_equal(got, ref)
+    from ss_conv import _ext
+    _ext.check_status(cuda)
