@@ -44,13 +44,12 @@ row_key_hist_kernel(const int32_t *__restrict__ nbr, int K, int n_rows, uint16_t
 }
 
 __global__ void __launch_bounds__(ORD_BLOCK)
-row_scatter_kernel(const uint16_t *__restrict__ keys, int K, int n_rows, const uint32_t *__restrict__ base, int n_blocks,
+row_scatter_kernel(const uint16_t *__restrict__ keys, int B, int n_rows, const uint32_t *__restrict__ base, int n_blocks,
                    int32_t *__restrict__ order) {
-  extern __shared__ uint32_t cnt[];  // [32 warps][K + 1] rows of each group in each warp
-  const int B = K + 1;
-  for (int i = threadIdx.x; i < 32 * B; i += ORD_BLOCK) cnt[i] = 0u;
+  extern __shared__ uint32_t cnt[];  // [warps of the block][B] rows of each group in each warp
+  for (int i = threadIdx.x; i < (int)(blockDim.x >> 5) * B; i += blockDim.x) cnt[i] = 0u;
   __syncthreads();
-  const int row = blockIdx.x * ORD_BLOCK + threadIdx.x;
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int key = row < n_rows ? (int)keys[row] : -1;
   const unsigned peers = __match_any_sync(0xffffffffu, key);
@@ -62,6 +61,41 @@ row_scatter_kernel(const uint16_t *__restrict__ keys, int K, int n_rows, const u
     for (int w = 0; w < warp; ++w) before += cnt[w * B + key];
     order[base[(size_t)key * n_blocks + blockIdx.x] + before + (uint32_t)rank] = row;
   }
+}
+
+// Key for the forward table of a convolution with a small kernel (kx + ky + kz <= 9 bits): which
+// planes of the kernel hold a neighbour of the row - bit kx says "some offset (kx, *, *) is used",
+// then the same for ky and kz.  A tile whose rows agree on those planes skips every offset outside
+// their product; on surface-like inputs (a row uses 6 of 27 offsets, 128 consecutive rows together
+// use all 27) grouping by this key nearly halves the (tile, offset) steps.  Rows at and beyond the
+// device-side row count get the last bucket, so the first n_live entries of the order are the
+// live rows.
+constexpr int PLANE_BLOCK = 512;        // rows per block (16 warps x 513 counters fit the default shared memory)
+constexpr int PLANE_MAX_BITS = 9;
+__global__ void __launch_bounds__(PLANE_BLOCK)
+row_plane_key_hist_kernel(const int32_t *__restrict__ nbr, int kx, int ky, int kz, int n_rows,
+                          const int32_t *__restrict__ n_rows_dev, uint16_t *__restrict__ keys,
+                          uint32_t *__restrict__ hist, int n_blocks) {
+  extern __shared__ uint32_t hist_s[];  // [B]
+  const int bits = kx + ky + kz, B = (1 << bits) + 1;
+  for (int b = threadIdx.x; b < B; b += PLANE_BLOCK) hist_s[b] = 0u;
+  __syncthreads();
+  const int row = blockIdx.x * PLANE_BLOCK + threadIdx.x;
+  if (row < n_rows) {
+    int key = B - 1;
+    if (row < live_rows(n_rows, n_rows_dev)) {
+      key = 0;
+      int kappa = 0;
+      for (int x = 0; x < kx; ++x)
+        for (int y = 0; y < ky; ++y)
+          for (int z = 0; z < kz; ++z, ++kappa)
+            if (__ldg(nbr + (size_t)kappa * n_rows + row) >= 0) key |= (1 << x) | (1 << (kx + y)) | (1 << (kx + ky + z));
+    }
+    keys[row] = (uint16_t)key;
+    atomicAdd(&hist_s[key], 1u);  // a count: the order of the additions does not matter
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += PLANE_BLOCK) hist[(size_t)b * n_blocks + blockIdx.x] = hist_s[b];
 }
 
 }  // namespace ssc
@@ -98,7 +132,43 @@ extern "C" int ssc_nbr_row_order(const int32_t *nbr, int K, int n_rows, int32_t 
   SSC_CHECK_LAUNCH("row_key_hist");
   int rc = exclusive_scan_u32<false>(hist, (long long)cells, base, block_sums, nullptr, nullptr, st);
   if (rc != 0) return rc;
-  { row_scatter_kernel<<<n_blocks, ORD_BLOCK, 32 * (K + 1) * 4, st>>>(keys, K, n_rows, base, n_blocks, order); note_launches(1); }
+  { row_scatter_kernel<<<n_blocks, ORD_BLOCK, 32 * (K + 1) * 4, st>>>(keys, K + 1, n_rows, base, n_blocks, order); note_launches(1); }
+  SSC_CHECK_LAUNCH("row_scatter");
+  return SSC_OK;
+}
+
+extern "C" size_t ssc_nbr_row_order_planes_scratch_bytes(const int ksize[3], int n_rows) {
+  if (!ksize || n_rows < 0 || ksize[0] < 1 || ksize[1] < 1 || ksize[2] < 1 || ksize[0] + ksize[1] + ksize[2] > PLANE_MAX_BITS) return 0;
+  const size_t n_blocks = (size_t)ceil_div(n_rows > 0 ? n_rows : 1, PLANE_BLOCK);
+  const size_t cells = (size_t)((1 << (ksize[0] + ksize[1] + ksize[2])) + 1) * n_blocks;
+  return order_align((size_t)n_rows * 2) + 2 * order_align(cells * 4) + order_align((cells / 1024 + 2) * 4);
+}
+
+extern "C" int ssc_nbr_row_order_planes(const int32_t *nbr, const int ksize[3], int n_rows, int32_t *order, void *scratch,
+                                        size_t scratch_bytes, const int32_t *n_rows_dev, void *stream) {
+  SSC_REQUIRE(ksize && n_rows >= 0 && ksize[0] >= 1 && ksize[1] >= 1 && ksize[2] >= 1 &&
+                  ksize[0] + ksize[1] + ksize[2] <= PLANE_MAX_BITS,
+              "nbr_row_order_planes: kernel sizes must add up to at most %d", PLANE_MAX_BITS);
+  if (n_rows == 0) return SSC_OK;
+  SSC_REQUIRE(nbr && order && scratch, "nbr_row_order_planes: null pointer");
+  SSC_REQUIRE(scratch_bytes >= ssc_nbr_row_order_planes_scratch_bytes(ksize, n_rows), "nbr_row_order_planes: scratch too small");
+  cudaStream_t st = as_stream(stream);
+  const int B = (1 << (ksize[0] + ksize[1] + ksize[2])) + 1;
+  const int n_blocks = ceil_div(n_rows, PLANE_BLOCK);
+  const size_t cells = (size_t)B * n_blocks;
+  uint8_t *sp = (uint8_t *)scratch;
+  uint16_t *keys = (uint16_t *)sp;
+  sp += order_align((size_t)n_rows * 2);
+  uint32_t *hist = (uint32_t *)sp;
+  sp += order_align(cells * 4);
+  uint32_t *base = (uint32_t *)sp;
+  sp += order_align(cells * 4);
+  uint32_t *block_sums = (uint32_t *)sp;
+  { row_plane_key_hist_kernel<<<n_blocks, PLANE_BLOCK, B * 4, st>>>(nbr, ksize[0], ksize[1], ksize[2], n_rows, n_rows_dev, keys, hist, n_blocks); note_launches(1); }
+  SSC_CHECK_LAUNCH("row_plane_key_hist");
+  int rc = exclusive_scan_u32<false>(hist, (long long)cells, base, block_sums, nullptr, nullptr, st);
+  if (rc != 0) return rc;
+  { row_scatter_kernel<<<n_blocks, PLANE_BLOCK, (PLANE_BLOCK / 32) * B * 4, st>>>(keys, B, n_rows, base, n_blocks, order); note_launches(1); }
   SSC_CHECK_LAUNCH("row_scatter");
   return SSC_OK;
 }

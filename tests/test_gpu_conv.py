@@ -439,3 +439,45 @@ def test_conv_with_few_input_channels_packs_several_offsets_per_step(cuda, c_in,
     assert rel_err(y.cpu().numpy(), ref) <= 1e-3
     exact = _ext.conv_forward(f, w, nbr, n_out, "fp32")
     assert rel_err(y.cpu().numpy(), exact.cpu().numpy()) <= 1e-3
+
+
+@pytest.mark.parametrize("ksize,s,p,subm,precision", [((3, 3, 3), 2, 1, False, "tf32"), ((3, 3, 3), 1, 1, True, "tf32"),
+                                                      ((2, 2, 2), 2, 0, False, "fp16"), ((3, 2, 3), 1, 1, False, "tf32")])
+def test_plane_order_of_a_forward_table(cuda, ksize, s, p, subm, precision):
+    """ssc_nbr_row_order_planes: a permutation grouped by the kernel planes a row's neighbours lie in
+    (ascending key, ascending rows inside a group); with a device-side row count the rows beyond it
+    come last; the convolution run through it gives the same bits as without."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(sum(ksize) * 7 + s)
+    ind = random_voxels(rng, 3, 24, 3000)
+    outids, pairs, num = gpu_rulebook(ind, 3, [24] * 3, list(ksize), [s] * 3, [p, 0 if ksize[1] == 2 else p, p], [1] * 3, subm, cuda)
+    n_in, n_out = ind.shape[0], outids.shape[0]
+    nbr = _ext.neighbour_table(pairs, num, n_out)
+    order = _ext.nbr_row_order_planes(nbr, ksize)
+    torch.cuda.synchronize()
+    o, t = order.cpu().numpy(), nbr.cpu().numpy()
+    has = (t >= 0).reshape(ksize + (n_out,))
+    kx, ky, kz = ksize
+    key = np.zeros(n_out, np.int64)
+    for x in range(kx):
+        key |= has[x].any((0, 1)).astype(np.int64) << x
+    for y in range(ky):
+        key |= has[:, y].any((0, 1)).astype(np.int64) << (kx + y)
+    for z in range(kz):
+        key |= has[:, :, z].any((0, 1)).astype(np.int64) << (kx + ky + z)
+    assert np.array_equal(o, np.lexsort((np.arange(n_out), key)))
+    # a capacity-sized table with the row count on the device: live rows first, in the same order
+    live = n_out - 777
+    n_dev = torch.tensor([live], dtype=torch.int32, device=cuda)
+    o2 = _ext.nbr_row_order_planes(nbr, ksize, n_dev).cpu().numpy()
+    assert np.array_equal(np.sort(o2), np.arange(n_out))
+    assert np.array_equal(o2[:live], np.lexsort((np.arange(live), key[:live])))
+    assert np.array_equal(o2[live:], np.arange(live, n_out))
+    c_in, c_out = 24, 40
+    f = torch.randn(n_in, c_in, device=cuda)
+    flt = torch.randn(kx * ky * kz, c_in, c_out, device=cuda) / 30
+    plain = _ext.conv_forward(f, flt, nbr, n_out, precision, algo="rows")
+    ordered = _ext.conv_forward(f, flt, nbr, n_out, precision, row_order=order, algo="rows")
+    torch.cuda.synchronize()
+    _ext.check_status(cuda)
+    assert torch.equal(plain, ordered)
