@@ -296,15 +296,22 @@ int ssc_nbr_row_order(const int32_t *nbr, int K, int n_rows, int32_t *order, voi
 /* The same for the output-major table of a forward convolution with a small kernel (ksize[0] +
  * ksize[1] + ksize[2] <= 9, e.g. 3^3): rows are grouped by WHICH PLANES of the kernel hold one of
  * their neighbours (one bit per kx, ky and kz; offsets numbered (kx * ksize[1] + ky) * ksize[2] + kz
- * as in SS_Conv_lib/src/conv/geometry.h:56-65), ascending row number inside a group.  On
- * surface-like inputs 128 consecutive output rows together use every offset although each row
- * uses a quarter of them; tiles of this order skip about 45 % of the (tile, offset) steps of the
- * reference's per-offset loop (indice_conv.h:290-338).  n_rows_dev (may be NULL): device word
- * with the number of live rows when n_rows is a capacity; the live rows then come first in the
- * order.  No bit of the convolution's result depends on the order. */
+ * as in SS_Conv_lib/src/conv/geometry.h:56-65), groups with more possible offsets first, ascending
+ * row number inside a group.  On surface-like inputs 128 consecutive output rows together use
+ * every offset although each row uses a quarter of them; tiles of this order skip about 45 % of
+ * the (tile, offset) steps of the reference's per-offset loop (indice_conv.h:290-338).
+ * nbr_in_order (may be NULL): receives the table with its columns moved into that order (column j
+ * = the column of row order[j]); pass it with SSC_CONV_TABLE_IN_ORDER so that the kernel reads
+ * the table coalesced.  n_rows_dev (may be NULL): device word with the number of live rows when
+ * n_rows is a capacity; the live rows then come first in the order.  No bit of the convolution's
+ * result depends on the order. */
 size_t ssc_nbr_row_order_planes_scratch_bytes(const int ksize[3], int n_rows);
 int ssc_nbr_row_order_planes(const int32_t *nbr, const int ksize[3], int n_rows, int32_t *order,
-                             void *scratch, size_t scratch_bytes, const int32_t *n_rows_dev, void *stream);
+                             int32_t *nbr_in_order, void *scratch, size_t scratch_bytes,
+                             const int32_t *n_rows_dev, void *stream);
+/* OR'ed into `precision` of ssc_conv_fwd_ordered: `nbr` is the table in the order of `row_order`
+ * (nbr_in_order above), i.e. column j belongs to output row row_order[j]. */
+#define SSC_CONV_TABLE_IN_ORDER 0x200
 int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, const void *filters, int K, int c_out,
                          const int32_t *nbr, int n_out, int precision, float *out, int32_t *status,
                          void *scratch, size_t scratch_bytes, const int32_t *n_out_dev,

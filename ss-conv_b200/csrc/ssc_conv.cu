@@ -158,9 +158,12 @@ extern "C" int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, c
                                     const int32_t *row_order, void *stream) {
   SSC_REQUIRE(c_in > 0 && c_out > 0 && K > 0 && n_in >= 0 && n_out >= 0, "conv_fwd: bad sizes");
   const bool prestaged = (precision & SSC_CONV_PRESTAGED) != 0;
-  precision &= ~SSC_CONV_PRESTAGED;
+  const bool table_in_order = (precision & SSC_CONV_TABLE_IN_ORDER) != 0;
+  precision &= ~(SSC_CONV_PRESTAGED | SSC_CONV_TABLE_IN_ORDER);
   if (n_out == 0) return SSC_OK;
   SSC_REQUIRE(filters && nbr && out && (n_in == 0 || features || prestaged), "conv_fwd: null pointer");
+  SSC_REQUIRE(!table_in_order || (row_order && precision != SSC_PREC_FP32),
+              "conv_fwd: SSC_CONV_TABLE_IN_ORDER needs a row order and a tensor-core precision");
   cudaStream_t st = as_stream(stream);
   if (precision == SSC_PREC_FP32) {
     dim3 grid(ceil_div(n_out, BM), ceil_div(c_out, BN));
@@ -168,9 +171,9 @@ extern "C" int ssc_conv_fwd_ordered(const float *features, int n_in, int c_in, c
     SSC_CHECK_LAUNCH("conv_fwd_fp32");
     return SSC_OK;
   }
-  if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, st);
+  if (precision == SSC_PREC_TF32) return conv_fwd_tf32(features, n_in, c_in, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, table_in_order, st);
   if (precision == SSC_PREC_F16 || precision == SSC_PREC_BF16)
-    return conv_fwd_16(features, n_in, c_in, precision == SSC_PREC_BF16, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, st);
+    return conv_fwd_16(features, n_in, c_in, precision == SSC_PREC_BF16, filters, K, c_out, nbr, n_out, out, status, scratch, scratch_bytes, n_out_dev, row_order, prestaged, table_in_order, st);
   return fail(SSC_ERR_INVALID, "conv_fwd: unknown precision %d", precision);
 }
 

@@ -29,10 +29,10 @@ bool tc_operand_layout(int c_in_words, int c_out, int *k_slabs, int *n_pad, int 
 // output-stationary tensor-core kernels (ssc_conv_tc.cu)
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st);
+                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, bool table_in_order, cudaStream_t st);
 int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void *packed, int K, int c_out,
                 const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st);
+                const int32_t *n_out_dev, const int32_t *order, bool prestaged, bool table_in_order, cudaStream_t st);
 
 // compacted per-offset pair lists of a neighbour table (ssc_wgrad_tc.cu): the lists of the kernel
 // offsets follow one another in pair_out / pair_in (ascending output row inside an offset),

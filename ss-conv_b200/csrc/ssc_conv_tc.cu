@@ -51,6 +51,7 @@ struct TcParams {
   int fmt16;      // 16-bit operands: 0 = fp16, 1 = bf16 (operand format field of the instruction descriptor)
   int last_kk;    // MMA k-steps (32 bytes of K each) that hold real channels in the LAST slab: 1..4
   int opk;        // kernel offsets per 128-byte operand row: 1, or 32 / c_pad for TF32 layers with c_pad = 4, 8, 16
+  int nbr_by_pos; // 1: the table's columns are already in the order of `order` (column j <-> output row order[j])
                   // channels (a first layer with 3 input channels packs 8 offsets into one step)
 };
 
@@ -59,6 +60,7 @@ static bool tc_params(int c_in, int c_out, TcParams &p, bool split_n = false, bo
   p.k_slabs = (c_in + TC_SLAB - 1) / TC_SLAB;
   p.last_kk = (c_in - (p.k_slabs - 1) * TC_SLAB + 7) / 8;     // c_in counts 4-byte words of an operand row
   p.opk = opk;
+  p.nbr_by_pos = 0;
   if (opk > 1) {     // grouped offsets: one full slab per group of offsets
     p.k_slabs = 1;
     p.last_kk = 4;
@@ -220,7 +222,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int r = m0 + q * 32 + lane;
-      scan_rows[q] = r < n_rows ? (order ? __ldg(order + r) : r) : -1;
+      scan_rows[q] = r < n_rows ? ((order && !p.nbr_by_pos) ? __ldg(order + r) : r) : -1;
     }
     for (int k0 = warp * 4; k0 < K; k0 += mma_warp * 4) {
       int v[4][4];
@@ -298,7 +300,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int r = m0 + q * 32 + lane;
-      my_rows[q] = r < n_rows ? (order ? __ldg(order + r) : r) : -1;
+      my_rows[q] = r < n_rows ? ((order && !p.nbr_by_pos) ? __ldg(order + r) : r) : -1;
     }
     auto load_rows = [&](int j, int *dst) {
       const int kap = act_list[j / p.k_groups];
@@ -331,7 +333,7 @@ conv_fwd_tf32_kernel(const float *__restrict__ features, int c_in, const uint4 *
 #pragma unroll 1
         for (int q = q0; q < q0 + q_per; ++q) {
           const int row = m0 + q * 32 + lane;
-          const int my_row = row < n_rows ? (order ? __ldg(order + row) : row) : -1;
+          const int my_row = row < n_rows ? ((order && !p.nbr_by_pos) ? __ldg(order + row) : row) : -1;
           int idx[8];
 #pragma unroll
           for (int o = 0; o < 8; ++o) {
@@ -582,7 +584,7 @@ __global__ void pack_filters_16_kernel(const float *__restrict__ filters, int K,
 
 int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void *packed, int K, int c_out,
                 const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
+                const int32_t *n_out_dev, const int32_t *order, bool prestaged, bool table_in_order, cudaStream_t st) {
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): kernel volume %d > 256", K);
   const int words = f16_row_words(c_in);
   if (scratch == nullptr || scratch_bytes + 16 < conv_f16_scratch_bytes(n_in, c_in) || ((uintptr_t)scratch & 15u) != 0)
@@ -594,6 +596,7 @@ int conv_fwd_16(const float *features, int n_in, int c_in, bool bf16, const void
     return fail(SSC_ERR_INVALID, "conv_fwd(16-bit): c_out %d / kernel volume %d not supported", c_out, K);
   if (grid * (p.n_tiles / p.nt_cta) <= sms) tc_params(words, c_out, p, grid < 2 * sms, true);
   p.fmt16 = bf16 ? 1 : 0;
+  p.nbr_by_pos = (table_in_order && order) ? 1 : 0;
   if (!prestaged) {
     int rc = stage_features_16(features, n_in, c_in, bf16, scratch, st);
     if (rc != SSC_OK) return rc;
@@ -613,7 +616,7 @@ constexpr int kStagingMinTiles = 8;
 
 int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed, int K, int c_out,
                   const int32_t *nbr, int n_out, float *out, int32_t *status, void *scratch, size_t scratch_bytes,
-                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, cudaStream_t st) {
+                  const int32_t *n_out_dev, const int32_t *order, bool prestaged, bool table_in_order, cudaStream_t st) {
   TcParams p;
   if (K > 256) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): kernel volume %d > 256", K);
   int grid = ceil_div(n_out, TC_M);
@@ -621,6 +624,7 @@ int conv_fwd_tf32(const float *features, int n_in, int c_in, const void *packed,
   const int opk = tf32_offsets_per_row(c_in);
   if (!tc_params(c_in, c_out, p, split_n, false, opk)) return fail(SSC_ERR_INVALID, "conv_fwd(tf32): c_out %d / kernel volume %d not supported", c_out, K);
   if (grid * (p.n_tiles / p.nt_cta) <= sm_count()) tc_params(c_in, c_out, p, split_n, true, opk);
+  p.nbr_by_pos = (table_in_order && order) ? 1 : 0;
   size_t smem = tc_smem_bytes(p);
   // With a staging buffer the feature rows are rounded to TF32 once, up front, instead of after
   // every gather (a row is gathered about K/2 times).

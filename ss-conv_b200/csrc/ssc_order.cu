@@ -45,7 +45,8 @@ row_key_hist_kernel(const int32_t *__restrict__ nbr, int K, int n_rows, uint16_t
 
 __global__ void __launch_bounds__(ORD_BLOCK)
 row_scatter_kernel(const uint16_t *__restrict__ keys, int B, int n_rows, const uint32_t *__restrict__ base, int n_blocks,
-                   int32_t *__restrict__ order) {
+                   int32_t *__restrict__ order, const int32_t *__restrict__ nbr = nullptr, int K = 0,
+                   int32_t *__restrict__ nbr_in_order = nullptr) {
   extern __shared__ uint32_t cnt[];  // [warps of the block][B] rows of each group in each warp
   for (int i = threadIdx.x; i < (int)(blockDim.x >> 5) * B; i += blockDim.x) cnt[i] = 0u;
   __syncthreads();
@@ -59,7 +60,11 @@ row_scatter_kernel(const uint16_t *__restrict__ keys, int B, int n_rows, const u
   if (key >= 0) {
     uint32_t before = 0;
     for (int w = 0; w < warp; ++w) before += cnt[w * B + key];
-    order[base[(size_t)key * n_blocks + blockIdx.x] + before + (uint32_t)rank] = row;
+    const uint32_t pos = base[(size_t)key * n_blocks + blockIdx.x] + before + (uint32_t)rank;
+    order[pos] = row;
+    if (nbr_in_order != nullptr)   // the table's column of this row moves to the row's position
+      for (int kappa = 0; kappa < K; ++kappa)
+        nbr_in_order[(size_t)kappa * n_rows + pos] = __ldg(nbr + (size_t)kappa * n_rows + row);
   }
 }
 
@@ -69,16 +74,39 @@ row_scatter_kernel(const uint16_t *__restrict__ keys, int B, int n_rows, const u
 // their product; on surface-like inputs (a row uses 6 of 27 offsets, 128 consecutive rows together
 // use all 27) grouping by this key nearly halves the (tile, offset) steps.  Rows at and beyond the
 // device-side row count get the last bucket, so the first n_live entries of the order are the
-// live rows.
+// live rows.  Buckets are numbered by the number of offsets a key allows (the product of its set
+// bits per axis), most first: a tile's index then falls with its step count, and the grid's tail
+// is made of the short tiles.
 constexpr int PLANE_BLOCK = 512;        // rows per block (16 warps x 513 counters fit the default shared memory)
 constexpr int PLANE_MAX_BITS = 9;
+// bucket_of[key] = rank of the key by (offsets it allows, descending; key, ascending): one block, once per call
+__global__ void __launch_bounds__(PLANE_BLOCK)
+plane_bucket_table_kernel(int kx, int ky, int kz, uint16_t *__restrict__ bucket_of) {
+  __shared__ uint8_t weight_s[1 << PLANE_MAX_BITS];
+  const int n_keys = 1 << (kx + ky + kz);
+  for (int key = threadIdx.x; key < n_keys; key += PLANE_BLOCK)
+    weight_s[key] = (uint8_t)(__popc(key & ((1 << kx) - 1)) * __popc((key >> kx) & ((1 << ky) - 1)) * __popc(key >> (kx + ky)));
+  __syncthreads();
+  for (int key = threadIdx.x; key < n_keys; key += PLANE_BLOCK) {
+    const int w = weight_s[key];
+    int before = 0;
+    for (int other = 0; other < n_keys; ++other) {
+      const int wo = weight_s[other];
+      before += (wo > w) | ((wo == w) & (other < key));
+    }
+    bucket_of[key] = (uint16_t)before;
+  }
+}
+
 __global__ void __launch_bounds__(PLANE_BLOCK)
 row_plane_key_hist_kernel(const int32_t *__restrict__ nbr, int kx, int ky, int kz, int n_rows,
-                          const int32_t *__restrict__ n_rows_dev, uint16_t *__restrict__ keys,
-                          uint32_t *__restrict__ hist, int n_blocks) {
-  extern __shared__ uint32_t hist_s[];  // [B]
+                          const int32_t *__restrict__ n_rows_dev, const uint16_t *__restrict__ bucket_table,
+                          uint16_t *__restrict__ keys, uint32_t *__restrict__ hist, int n_blocks) {
+  extern __shared__ uint32_t hist_s[];  // [B] counters, then [B - 1] bucket of every key
   const int bits = kx + ky + kz, B = (1 << bits) + 1;
+  uint32_t *bucket_of = hist_s + B;
   for (int b = threadIdx.x; b < B; b += PLANE_BLOCK) hist_s[b] = 0u;
+  for (int key = threadIdx.x; key < B - 1; key += PLANE_BLOCK) bucket_of[key] = bucket_table[key];
   __syncthreads();
   const int row = blockIdx.x * PLANE_BLOCK + threadIdx.x;
   if (row < n_rows) {
@@ -90,6 +118,7 @@ row_plane_key_hist_kernel(const int32_t *__restrict__ nbr, int kx, int ky, int k
         for (int y = 0; y < ky; ++y)
           for (int z = 0; z < kz; ++z, ++kappa)
             if (__ldg(nbr + (size_t)kappa * n_rows + row) >= 0) key |= (1 << x) | (1 << (kx + y)) | (1 << (kx + ky + z));
+      key = (int)bucket_of[key];
     }
     keys[row] = (uint16_t)key;
     atomicAdd(&hist_s[key], 1u);  // a count: the order of the additions does not matter
@@ -141,11 +170,13 @@ extern "C" size_t ssc_nbr_row_order_planes_scratch_bytes(const int ksize[3], int
   if (!ksize || n_rows < 0 || ksize[0] < 1 || ksize[1] < 1 || ksize[2] < 1 || ksize[0] + ksize[1] + ksize[2] > PLANE_MAX_BITS) return 0;
   const size_t n_blocks = (size_t)ceil_div(n_rows > 0 ? n_rows : 1, PLANE_BLOCK);
   const size_t cells = (size_t)((1 << (ksize[0] + ksize[1] + ksize[2])) + 1) * n_blocks;
-  return order_align((size_t)n_rows * 2) + 2 * order_align(cells * 4) + order_align((cells / 1024 + 2) * 4);
+  return order_align((size_t)n_rows * 2) + 2 * order_align(cells * 4) + order_align((cells / 1024 + 2) * 4) +
+         order_align((size_t)2 << PLANE_MAX_BITS);
 }
 
-extern "C" int ssc_nbr_row_order_planes(const int32_t *nbr, const int ksize[3], int n_rows, int32_t *order, void *scratch,
-                                        size_t scratch_bytes, const int32_t *n_rows_dev, void *stream) {
+extern "C" int ssc_nbr_row_order_planes(const int32_t *nbr, const int ksize[3], int n_rows, int32_t *order,
+                                        int32_t *nbr_in_order, void *scratch, size_t scratch_bytes,
+                                        const int32_t *n_rows_dev, void *stream) {
   SSC_REQUIRE(ksize && n_rows >= 0 && ksize[0] >= 1 && ksize[1] >= 1 && ksize[2] >= 1 &&
                   ksize[0] + ksize[1] + ksize[2] <= PLANE_MAX_BITS,
               "nbr_row_order_planes: kernel sizes must add up to at most %d", PLANE_MAX_BITS);
@@ -164,11 +195,15 @@ extern "C" int ssc_nbr_row_order_planes(const int32_t *nbr, const int ksize[3], 
   uint32_t *base = (uint32_t *)sp;
   sp += order_align(cells * 4);
   uint32_t *block_sums = (uint32_t *)sp;
-  { row_plane_key_hist_kernel<<<n_blocks, PLANE_BLOCK, B * 4, st>>>(nbr, ksize[0], ksize[1], ksize[2], n_rows, n_rows_dev, keys, hist, n_blocks); note_launches(1); }
+  sp += order_align((cells / 1024 + 2) * 4);
+  uint16_t *bucket_table = (uint16_t *)sp;
+  { plane_bucket_table_kernel<<<1, PLANE_BLOCK, 0, st>>>(ksize[0], ksize[1], ksize[2], bucket_table); note_launches(1); }
+  { row_plane_key_hist_kernel<<<n_blocks, PLANE_BLOCK, (2 * B - 1) * 4, st>>>(nbr, ksize[0], ksize[1], ksize[2], n_rows, n_rows_dev, bucket_table, keys, hist, n_blocks); note_launches(1); }
   SSC_CHECK_LAUNCH("row_plane_key_hist");
   int rc = exclusive_scan_u32<false>(hist, (long long)cells, base, block_sums, nullptr, nullptr, st);
   if (rc != 0) return rc;
-  { row_scatter_kernel<<<n_blocks, PLANE_BLOCK, (PLANE_BLOCK / 32) * B * 4, st>>>(keys, B, n_rows, base, n_blocks, order); note_launches(1); }
+  { row_scatter_kernel<<<n_blocks, PLANE_BLOCK, (PLANE_BLOCK / 32) * B * 4, st>>>(keys, B, n_rows, base, n_blocks, order, nbr,
+                                                                                    ksize[0] * ksize[1] * ksize[2], nbr_in_order); note_launches(1); }
   SSC_CHECK_LAUNCH("row_scatter");
   return SSC_OK;
 }

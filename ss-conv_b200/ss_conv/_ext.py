@@ -61,7 +61,7 @@ SIGNATURES = {
     "ssc_nbr_row_order_scratch_bytes": (c_size_t, [c_int, c_int]),
     "ssc_nbr_row_order": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "ssc_nbr_row_order_planes_scratch_bytes": (c_size_t, [_I3, c_int]),
-    "ssc_nbr_row_order_planes": (c_int, [c_void_p, _I3, c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "ssc_nbr_row_order_planes": (c_int, [c_void_p, _I3, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "ssc_conv_stage": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "ssc_conv_fwd_ordered": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
@@ -621,6 +621,7 @@ def pair_lists(nbr):
 
 
 PRESTAGED = 0x100
+TABLE_IN_ORDER = 0x200
 # (features.data_ptr(), filters.data_ptr()) -> (prec, packed, scratch, nbytes) left by conv_prepare for the
 # conv_forward call that follows on the same tensors
 _prepared = {}
@@ -686,10 +687,12 @@ def conv_prepare(features, filters, precision=None):
     return True
 
 
-def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None, algo=None):
+def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, row_order=None, algo=None,
+                 table_in_order=False):
     """out [n_out, Cout] = sum over offsets of gathered rows times filters (one launch).
     n_out_dev: device word with the exact row count when n_out is only a capacity.
     row_order: permutation of the output rows from nbr_row_order (same result, fewer steps).
+    table_in_order: nbr is the table with its columns already in that order (nbr_row_order_planes).
     algo: None (the module setting), 'rows' or 'pairs' (see set_algo)."""
     if filters.dim() != 3:
         filters = filters.reshape(-1, filters.shape[-2], filters.shape[-1])
@@ -709,6 +712,9 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
     if (mode in _PREC_OF and n_out_dev is None and row_order is None and nbr.shape[1] == n_out
             and _use_pairs(K, c_in, c_out, n_out, _PREC_OF[mode], algo)):
         return _conv_forward_pairs(features, filters, nbr, n_out, _PREC_OF[mode], out, st)
+    flag = TABLE_IN_ORDER if (table_in_order and row_order is not None) else 0
+    if flag and mode not in _PREC_OF:
+        raise ValueError("ssconv_b200: a table in row order needs a tensor-core precision")
     ready = None
     if _prepared:   # only the call that directly follows conv_prepare may use what it left
         ready = _prepared.pop((features.data_ptr(), filters.data_ptr()), None)
@@ -716,7 +722,7 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
     if ready is not None and ready[0] == _PREC_OF.get(mode, -1):
         prec, packed, scratch, nbytes = ready
         _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
-                                          _p(nbr, torch.int32), int(n_out), prec | PRESTAGED, _p(out), _p(st), _p(scratch),
+                                          _p(nbr, torch.int32), int(n_out), prec | PRESTAGED | flag, _p(out), _p(st), _p(scratch),
                                           nbytes, _p(n_out_dev), _p(row_order), _stream()))
     elif mode in _PREC_OF:
         prec = _PREC_OF[mode]
@@ -728,7 +734,7 @@ def conv_forward(features, filters, nbr, n_out, precision=None, n_out_dev=None, 
         nbytes = lib().ssc_conv_scratch_bytes(features.shape[0], c_in, c_out, prec) if stage else 0
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=features.device) if nbytes else None
         _check(lib().ssc_conv_fwd_ordered(_p(features, torch.float32), features.shape[0], c_in, _p(packed), K, c_out,
-                                          _p(nbr, torch.int32), int(n_out), prec, _p(out), _p(st), _p(scratch), nbytes,
+                                          _p(nbr, torch.int32), int(n_out), prec | flag, _p(out), _p(st), _p(scratch), nbytes,
                                           _p(n_out_dev), _p(row_order), _stream()))
     else:
         filters = filters.contiguous()
@@ -835,13 +841,15 @@ def input_major_table(nbr, n_in):
 
 # Tables with fewer rows are not worth the three launches of the ordering.
 ROW_ORDER_MIN_ROWS = 64 * 128
-def nbr_row_order_planes(nbr, ksize, n_rows_dev=None):
+def nbr_row_order_planes(nbr, ksize, n_rows_dev=None, with_table=False):
     """Permutation of the rows of a forward table nbr [K, n] (K = ksize[0] * ksize[1] * ksize[2]) that
-    groups the rows by the kernel planes their neighbours lie in (for conv_forward(row_order=...));
-    None for kernels it does not cover.  n_rows_dev: device word with the live row count when n is a
-    capacity.  Opt-in: tiles of this order run about 45 % fewer (tile, offset) steps on surface-like
-    inputs, which on a 64 -> 76 channel layer of 129 k rows saved 9 % of the convolution call and cost
-    0.02 ms itself, so the layers do not ask for it; it pays where one table serves several layers."""
+    groups the rows by the kernel planes their neighbours lie in, groups that allow more offsets first
+    (for conv_forward(row_order=...)); None for kernels it does not cover.  n_rows_dev: device word
+    with the live row count when n is a capacity.  with_table: also return the table with its
+    columns moved into that order (for conv_forward(..., table_in_order=True)).
+    Opt-in: on a 64 -> 76 channel layer of 129 k surface rows the call drops from 0.154 to 0.129 ms
+    (45 % fewer steps, the long tiles first) and the ordering takes 0.044 ms, so it pays from the
+    third layer that shares a table on; the layers do not ask for it themselves."""
     K, n = nbr.shape
     ks = [int(v) for v in ksize]
     if len(ks) != 3 or ks[0] * ks[1] * ks[2] != K or n == 0:
@@ -850,10 +858,11 @@ def nbr_row_order_planes(nbr, ksize, n_rows_dev=None):
     if nbytes == 0:
         return None
     order = torch.empty(n, dtype=torch.int32, device=nbr.device)
+    moved = torch.empty_like(nbr) if with_table else None
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=nbr.device)
-    _check(lib().ssc_nbr_row_order_planes(_p(nbr, torch.int32), _i3(ks), n, _p(order), _p(scratch), nbytes,
+    _check(lib().ssc_nbr_row_order_planes(_p(nbr, torch.int32), _i3(ks), n, _p(order), _p(moved), _p(scratch), nbytes,
                                           _p(n_rows_dev), _stream()))
-    return order
+    return (order, moved) if with_table else order
 
 
 def nbr_row_order(nbr):

@@ -445,39 +445,43 @@ def test_conv_with_few_input_channels_packs_several_offsets_per_step(cuda, c_in,
                                                       ((2, 2, 2), 2, 0, False, "fp16"), ((3, 2, 3), 1, 1, False, "tf32")])
 def test_plane_order_of_a_forward_table(cuda, ksize, s, p, subm, precision):
     """ssc_nbr_row_order_planes: a permutation grouped by the kernel planes a row's neighbours lie in
-    (ascending key, ascending rows inside a group); with a device-side row count the rows beyond it
-    come last; the convolution run through it gives the same bits as without."""
+    (groups that allow more offsets first, then ascending key, ascending rows inside a group), and the
+    table moved into that order; with a device-side row count the rows beyond it come last; the
+    convolution run through either gives the same bits as without."""
     from ss_conv import _ext
     rng = np.random.RandomState(sum(ksize) * 7 + s)
     ind = random_voxels(rng, 3, 24, 3000)
     outids, pairs, num = gpu_rulebook(ind, 3, [24] * 3, list(ksize), [s] * 3, [p, 0 if ksize[1] == 2 else p, p], [1] * 3, subm, cuda)
     n_in, n_out = ind.shape[0], outids.shape[0]
     nbr = _ext.neighbour_table(pairs, num, n_out)
-    order = _ext.nbr_row_order_planes(nbr, ksize)
+    order, moved = _ext.nbr_row_order_planes(nbr, ksize, with_table=True)
     torch.cuda.synchronize()
     o, t = order.cpu().numpy(), nbr.cpu().numpy()
     has = (t >= 0).reshape(ksize + (n_out,))
     kx, ky, kz = ksize
+    px = np.stack([has[x].any((0, 1)) for x in range(kx)])
+    py = np.stack([has[:, y].any((0, 1)) for y in range(ky)])
+    pz = np.stack([has[:, :, z].any((0, 1)) for z in range(kz)])
     key = np.zeros(n_out, np.int64)
-    for x in range(kx):
-        key |= has[x].any((0, 1)).astype(np.int64) << x
-    for y in range(ky):
-        key |= has[:, y].any((0, 1)).astype(np.int64) << (kx + y)
-    for z in range(kz):
-        key |= has[:, :, z].any((0, 1)).astype(np.int64) << (kx + ky + z)
-    assert np.array_equal(o, np.lexsort((np.arange(n_out), key)))
+    for i, plane in enumerate(list(px) + list(py) + list(pz)):
+        key |= plane.astype(np.int64) << i
+    weight = px.sum(0) * py.sum(0) * pz.sum(0)           # offsets the planes of a row allow
+    want = np.lexsort((np.arange(n_out), key, -weight))
+    assert np.array_equal(o, want)
+    assert np.array_equal(moved.cpu().numpy(), t[:, o])
     # a capacity-sized table with the row count on the device: live rows first, in the same order
     live = n_out - 777
     n_dev = torch.tensor([live], dtype=torch.int32, device=cuda)
     o2 = _ext.nbr_row_order_planes(nbr, ksize, n_dev).cpu().numpy()
     assert np.array_equal(np.sort(o2), np.arange(n_out))
-    assert np.array_equal(o2[:live], np.lexsort((np.arange(live), key[:live])))
+    assert np.array_equal(o2[:live], np.lexsort((np.arange(live), key[:live], -weight[:live])))
     assert np.array_equal(o2[live:], np.arange(live, n_out))
     c_in, c_out = 24, 40
     f = torch.randn(n_in, c_in, device=cuda)
     flt = torch.randn(kx * ky * kz, c_in, c_out, device=cuda) / 30
     plain = _ext.conv_forward(f, flt, nbr, n_out, precision, algo="rows")
     ordered = _ext.conv_forward(f, flt, nbr, n_out, precision, row_order=order, algo="rows")
+    through_moved = _ext.conv_forward(f, flt, moved, n_out, precision, row_order=order, algo="rows", table_in_order=True)
     torch.cuda.synchronize()
     _ext.check_status(cuda)
-    assert torch.equal(plain, ordered)
+    assert torch.equal(plain, ordered) and torch.equal(plain, through_moved)
