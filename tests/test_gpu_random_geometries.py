@@ -1,0 +1,78 @@
+"""Random geometries, orders and channel counts: rulebook bit-exact against the CPU oracle, the
+convolution in every operand precision against a float64 evaluation of the same table.
+
+Tolerances (max |diff| / max |ref|) are wider than in the layer-sized tests because many cases are a
+handful of rows and terms, where one operand's rounding is not averaged out: exact fp32 1e-4, TF32 and
+fp16 operands 4e-3, bf16 operands 4e-2.  An indexing fault shows as an error of order one."""
+import numpy as np
+import pytest
+import torch
+
+import ssconv_oracle as O
+from gpu_helpers import assert_rulebook_equal, gpu_rulebook
+
+pytestmark = pytest.mark.gpu
+TOL = (("fp32", 1e-4), ("tf32", 4e-3), ("fp16", 4e-3), ("bf16", 4e-2))
+
+
+def _random_case(rng):
+    batch = int(rng.randint(1, 6))
+    V = [int(rng.randint(3, 20)) for _ in range(3)]
+    k = [int(rng.randint(1, 4)) for _ in range(3)]
+    s = [int(rng.randint(1, 3)) for _ in range(3)]
+    d = [1 if s[i] > 1 else int(rng.randint(1, 3)) for i in range(3)]
+    p = [int(rng.randint(0, k[i])) for i in range(3)]
+    subm = bool(rng.rand() < 0.3) and all(x % 2 == 1 for x in k)
+    if subm:
+        s, p = [1, 1, 1], [(k[i] // 2) * d[i] for i in range(3)]
+    cells = V[0] * V[1] * V[2]
+    per = min(int(rng.randint(1, max(2, min(cells, 600)))), cells)
+    rows = []
+    for b in range(batch):
+        flat = rng.choice(cells, per, replace=False)
+        rows.append(np.stack([np.full(per, b), flat // (V[1] * V[2]), (flat // V[2]) % V[1], flat % V[2]], 1))
+    ind = np.concatenate(rows).astype(np.int32)
+    ind = ind[rng.permutation(ind.shape[0])] if rng.rand() < 0.5 else ind[O.renumber_rows(ind)]
+    out_shape = [(V[i] + 2 * p[i] - d[i] * (k[i] - 1) - 1) // s[i] + 1 for i in range(3)]
+    return (batch, V, k, s, p, d, subm, np.ascontiguousarray(ind)) if min(out_shape) >= 1 else None
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14])
+def test_random_geometries_against_the_oracle(cuda, seed):
+    from ss_conv import _ext
+    rng = np.random.RandomState(seed)
+    done = 0
+    while done < 120:
+        case = _random_case(rng)
+        if case is None:
+            continue
+        batch, V, k, s, p, d, subm, ind = case
+        got = gpu_rulebook(ind, batch, V, k, s, p, d, subm, cuda)
+        ref = O.get_indice_pairs(ind, batch, V, k, s, p, d, subm)
+        what = (k, s, p, d, subm, V, ind.shape[0])
+        if subm:
+            assert np.array_equal(got[2].cpu().numpy(), ref[2]), what
+        else:
+            assert_rulebook_equal(got, ref)
+        outids, pairs, num = got
+        n_out = outids.shape[0]
+        done += 1
+        if n_out == 0:
+            continue
+        c_in = int(rng.choice([1, 3, 4, 7, 8, 16, 20, 32, 33, 64, 100]))
+        c_out = int(rng.choice([1, 5, 16, 38, 76, 130, 260]))
+        K = k[0] * k[1] * k[2]
+        f = torch.randn(ind.shape[0], c_in, device=cuda)
+        W = torch.randn(K, c_in, c_out, device=cuda) / float(np.sqrt(c_in * K))
+        nbr = _ext.neighbour_table(pairs, num, n_out)
+        t, fd, Wd = nbr.cpu().numpy(), f.double().cpu().numpy(), W.double().cpu().numpy()
+        want = np.zeros((n_out, c_out))
+        for kap in range(K):
+            m = t[kap] >= 0
+            want[m] += fd[t[kap][m]] @ Wd[kap]
+        scale = max(float(np.abs(want).max()), 1e-30)
+        for prec, tol in TOL:
+            y = _ext.conv_forward(f, W, nbr, n_out, prec).double().cpu().numpy()
+            err = float(np.abs(y - want).max()) / scale
+            assert err < tol, (prec, err, c_in, c_out) + what
+    _ext.check_status(cuda)
