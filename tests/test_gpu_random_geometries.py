@@ -1,5 +1,6 @@
 """Random geometries, orders and channel counts: rulebook bit-exact against the CPU oracle, the
-convolution in every operand precision against a float64 evaluation of the same table.
+convolution in every operand precision against a float64 evaluation of the same table, the pools
+and the voxelizer bit-exact against the oracle.
 
 Tolerances (max |diff| / max |ref|) are wider than in the layer-sized tests because many cases are a
 handful of rows and terms, where one operand's rounding is not averaged out: exact fp32 1e-4, TF32 and
@@ -75,4 +76,38 @@ def test_random_geometries_against_the_oracle(cuda, seed):
             y = _ext.conv_forward(f, W, nbr, n_out, prec).double().cpu().numpy()
             err = float(np.abs(y - want).max()) / scale
             assert err < tol, (prec, err, c_in, c_out) + what
+        if not subm:     # the same rulebook drives the pools: bit-exact (same accumulation order)
+            fn, pn, nn = f.cpu().numpy(), pairs.cpu().numpy(), num.cpu().numpy()
+            assert np.array_equal(_ext.indice_maxpool_fp32(f, pairs, num, n_out).cpu().numpy(),
+                                  O.indice_maxpool(fn, pn, nn, n_out)), ("maxpool", c_in) + what
+            rf = _ext.indiceSummaryRF(pairs, num, n_out)
+            assert np.array_equal(rf.cpu().numpy(), O.summary_rf(pn, nn, n_out)), ("summary", c_in) + what
+            assert np.array_equal(_ext.indice_avgpool_fp32(f, pairs, num, n_out, rf).cpu().numpy(),
+                                  O.indice_avgpool(fn, pn, nn, n_out, O.summary_rf(pn, nn, n_out))), ("avgpool", c_in) + what
+    _ext.check_status(cuda)
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_point_clouds_through_the_voxelizer(cuda, seed):
+    """Point2Voxel on random clouds (grid size, points per sample, feature count, mode, points outside
+    the grid): voxels, features and ids as the oracle's."""
+    from ss_conv import _ext
+    from ss_conv.sp_ops.voxelize import Point2Voxel
+    rng = np.random.RandomState(seed)
+    for _ in range(40):
+        B, V, mode = int(rng.randint(1, 6)), int(rng.choice([4, 8, 16, 32])), int(rng.randint(1, 5))
+        per, C = int(rng.randint(1, 900)), int(rng.choice([1, 3, 4, 6, 9]))
+        pts = rng.uniform(-0.55, 0.55, (B * per, 3)).astype(np.float32)      # ~25 % of the points fall outside
+        pts[::per] = 0.01                                                    # every sample keeps a point (the oracle
+                                                                             # does not restate the empty-sample branch)
+        fts = rng.rand(B * per, C).astype(np.float32)
+        ids = np.repeat(np.arange(B), per)
+        p2v = Point2Voxel([V] * 3, [1.0 / V] * 3, mode)
+        t = lambda a: torch.from_numpy(a).to(cuda)
+        vp, sp, vids, flag = p2v(t(pts), t(fts), t(ids))
+        rp, rfeat, rocc, rids, rinv = O.point2voxel(pts, fts, ids, [V] * 3, [1.0 / V] * 3, mode)
+        what = (B, V, mode, per, C)
+        assert np.array_equal(vp.cpu().numpy(), rp) and np.array_equal(vids.cpu().numpy(), rids), what
+        assert np.array_equal(sp.indices.cpu().numpy(), rocc), what
+        assert np.array_equal(sp.features.cpu().numpy(), rfeat), what
     _ext.check_status(cuda)
