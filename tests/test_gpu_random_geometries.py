@@ -111,3 +111,47 @@ def test_random_point_clouds_through_the_voxelizer(cuda, seed):
         assert np.array_equal(sp.indices.cpu().numpy(), rocc), what
         assert np.array_equal(sp.features.cpu().numpy(), rfeat), what
     _ext.check_status(cuda)
+
+
+@pytest.mark.parametrize("seed", [31, 32])
+def test_random_geometries_backward_against_float64(cuda, seed):
+    """Both gradients of random convolutions.  The error of every entry is measured against the sum of
+    the absolute values of its terms (so that a gradient that nearly cancels does not inflate it): exact
+    fp32 2e-6, TF32 operands 1.5e-3 (two operands rounded to 11 bits each bound it by 2^-10)."""
+    from ss_conv import _ext
+    rng = np.random.RandomState(seed)
+    done = 0
+    while done < 100:
+        case = _random_case(rng)
+        if case is None:
+            continue
+        batch, V, k, s, p, d, subm, ind = case
+        outids, pairs, num = gpu_rulebook(ind, batch, V, k, s, p, d, subm, cuda)
+        n_out, n_in = outids.shape[0], ind.shape[0]
+        done += 1
+        if n_out == 0:
+            continue
+        c_in, c_out = int(rng.choice([1, 3, 4, 8, 16, 20, 32, 64])), int(rng.choice([1, 5, 16, 38, 76, 130]))
+        K = k[0] * k[1] * k[2]
+        f = torch.randn(n_in, c_in, device=cuda)
+        W = torch.randn(K, c_in, c_out, device=cuda) / float(np.sqrt(c_in * K))
+        g = torch.randn(n_out, c_out, device=cuda)
+        nbr = _ext.neighbour_table(pairs, num, n_out)
+        t, fd, Wd, gd = nbr.cpu().numpy(), f.double().cpu().numpy(), W.double().cpu().numpy(), g.double().cpu().numpy()
+        din, dw = np.zeros((n_in, c_in)), np.zeros((K, c_in, c_out))
+        din_abs, dw_abs = np.zeros((n_in, c_in)), np.zeros((K, c_in, c_out))
+        for kap in range(K):
+            m = np.nonzero(t[kap] >= 0)[0]
+            if m.size == 0:
+                continue
+            src = t[kap][m]
+            np.add.at(din, src, gd[m] @ Wd[kap].T)
+            np.add.at(din_abs, src, np.abs(gd[m]) @ np.abs(Wd[kap]).T)
+            dw[kap] = fd[src].T @ gd[m]
+            dw_abs[kap] = np.abs(fd[src]).T @ np.abs(gd[m])
+        for prec, tol in (("fp32", 2e-6), ("tf32", 1.5e-3)):
+            a, b = _ext.conv_backward(f, W, g, nbr, precision=prec)
+            e_in = float((np.abs(a.double().cpu().numpy() - din) / np.maximum(din_abs, 1e-30)).max())
+            e_w = float((np.abs(b.double().cpu().numpy() - dw) / np.maximum(dw_abs, 1e-30)).max())
+            assert e_in < tol and e_w < tol, (prec, e_in, e_w, k, s, p, d, subm, V, c_in, c_out, n_in, n_out)
+    _ext.check_status(cuda)
