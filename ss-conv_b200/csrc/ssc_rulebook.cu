@@ -173,48 +173,24 @@ __device__ __forceinline__ void set_bits(uint32_t *word, uint32_t bits, bool loo
   if (!look_first || (__ldcg(word) & bits) != bits) atomicOr(word, bits);
 }
 
-__global__ void mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g,
-                                    uint32_t *bitmap, const int32_t *__restrict__ n_dev) {
-  int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= live_rows(n, n_dev)) return;
-  int4 c = indices[j];
-  if ((unsigned)c.x >= (unsigned)batch || !in_range3(c.y, c.z, c.w, g.in_shape)) return;
-  const Reach rx = reach_of(g, 0, c.y), ry = reach_of(g, 1, c.z), rz = reach_of(g, 2, c.w);
-  if (rx.n <= 0 || ry.n <= 0 || rz.n <= 0) return;
-  const int base_b = c.x * g.out_shape[0];
-  for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
-    for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
-      const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
-      uint32_t word = 0xFFFFFFFFu, bits = 0u;
-      for (int iz = 0, z = rz.first; iz < rz.n; ++iz, z += rz.step) {  // ascending z: bits of one word are merged
-        const uint32_t flat = row + (uint32_t)z;
-        if ((flat >> 5) != word) {
-          if (bits) set_bits(bitmap + word, bits, false);
-          word = flat >> 5;
-          bits = 0u;
-        }
-        bits |= 1u << (flat & 31);
-      }
-      if (bits) set_bits(bitmap + word, bits, false);
-    }
-}
-
-// The same for coarse output grids (at most kCoarseVolume cells per sample), where the inputs of a
-// sample all reach the same few bitmap words.  A block ORs its rows' bits into a shared-memory
-// image of the words its samples own and then sends one atomic per non-zero word; rows that arrive
-// ordered by sample (the order every rulebook and the voxelizer produce) give a block one or two
-// samples.  A block whose rows span more words than the image holds marks them directly.
-constexpr int kCoarseVolume = 4096;
-constexpr int kCoarseImageWords = 1024;
+// A block ORs its rows' bits into a shared-memory image of the bitmap words between the first and
+// the last cell its rows reach, then sends one atomic per non-zero word: rows that arrive in grid
+// order (the order every rulebook and the voxelizer produce) reach a narrow range of words, many
+// rows the same ones - on coarse grids all rows of a sample share a handful of words, whose atomics
+// would otherwise queue up.  A block whose rows span more words than the image holds (rows in
+// arbitrary order) marks them directly.
+constexpr int kCoarseVolume = 4096;      // cells per sample up to which a direct atomic first looks at the word
+constexpr int kMarkImageWords = 1024;
 __global__ void __launch_bounds__(128)
-mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g, uint32_t *bitmap,
-                           const int32_t *__restrict__ n_dev) {
-  __shared__ uint32_t image[kCoarseImageWords];
-  __shared__ int b_min, b_max;
+mark_outputs_kernel(const int4 *__restrict__ indices, int n, int batch, Geometry g, uint32_t *bitmap,
+                    const int32_t *__restrict__ n_dev) {
+  __shared__ uint32_t image[kMarkImageWords];
+  __shared__ unsigned cell_min, cell_max;
+  __shared__ int any_row;
   const int live = live_rows(n, n_dev);
   if ((int)(blockIdx.x * blockDim.x) >= live) return;            // the whole block
-  for (int i = threadIdx.x; i < kCoarseImageWords; i += blockDim.x) image[i] = 0u;
-  if (threadIdx.x == 0) { b_min = 0x7FFFFFFF; b_max = -1; }
+  for (int i = threadIdx.x; i < kMarkImageWords; i += blockDim.x) image[i] = 0u;
+  if (threadIdx.x == 0) { cell_min = 0xFFFFFFFFu; cell_max = 0u; any_row = 0; }
   __syncthreads();
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   int4 c = make_int4(0, 0, 0, 0);
@@ -227,16 +203,22 @@ mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, G
       ok = rx.n > 0 && ry.n > 0 && rz.n > 0;
     }
   }
-  const int w_min = __reduce_min_sync(0xFFFFFFFFu, ok ? c.x : 0x7FFFFFFF);
-  const int w_max = __reduce_max_sync(0xFFFFFFFFu, ok ? c.x : -1);
-  if ((threadIdx.x & 31) == 0 && w_max >= 0) { atomicMin(&b_min, w_min); atomicMax(&b_max, w_max); }
-  __syncthreads();
-  if (b_max < 0) return;                                         // no row of the block reaches an output
-  const uint32_t vol = (uint32_t)(g.out_shape[0] * g.out_shape[1] * g.out_shape[2]);
-  const uint32_t word_lo = ((uint32_t)b_min * vol) >> 5, word_hi = ((uint32_t)(b_max + 1) * vol - 1u) >> 5;
-  const bool staged = word_hi - word_lo < (uint32_t)kCoarseImageWords;
+  const int base_b = c.x * g.out_shape[0];
+  unsigned lo = 0xFFFFFFFFu, hi = 0u;                            // first and last cell this row reaches
   if (ok) {
-    const int base_b = c.x * g.out_shape[0];
+    lo = (unsigned)((base_b + rx.first) * g.out_shape[1] + ry.first) * (unsigned)g.out_shape[2] + (unsigned)rz.first;
+    hi = (unsigned)((base_b + rx.first + (rx.n - 1) * rx.step) * g.out_shape[1] + ry.first + (ry.n - 1) * ry.step) *
+             (unsigned)g.out_shape[2] + (unsigned)(rz.first + (rz.n - 1) * rz.step);
+  }
+  const unsigned w_lo = __reduce_min_sync(0xFFFFFFFFu, lo), w_hi = __reduce_max_sync(0xFFFFFFFFu, hi);
+  const bool w_any = __any_sync(0xFFFFFFFFu, ok);
+  if ((threadIdx.x & 31) == 0 && w_any) { atomicMin(&cell_min, w_lo); atomicMax(&cell_max, w_hi); any_row = 1; }
+  __syncthreads();
+  if (!any_row) return;                                          // no row of the block reaches an output
+  const uint32_t word_lo = cell_min >> 5, word_hi = cell_max >> 5;
+  const bool staged = word_hi - word_lo < (uint32_t)kMarkImageWords;
+  const bool look_first = g.out_shape[0] * g.out_shape[1] * g.out_shape[2] <= kCoarseVolume;
+  if (ok) {
     for (int ix = 0, x = rx.first; ix < rx.n; ++ix, x += rx.step)
       for (int iy = 0, y = ry.first; iy < ry.n; ++iy, y += ry.step) {
         const uint32_t row = (uint32_t)((base_b + x) * g.out_shape[1] + y) * (uint32_t)g.out_shape[2];
@@ -246,7 +228,7 @@ mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, G
           if ((flat >> 5) != word) {
             if (bits) {
               if (staged) atomicOr(&image[word - word_lo], bits);
-              else set_bits(bitmap + word, bits, true);
+              else set_bits(bitmap + word, bits, look_first);
             }
             word = flat >> 5;
             bits = 0u;
@@ -255,7 +237,7 @@ mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, G
         }
         if (bits) {
           if (staged) atomicOr(&image[word - word_lo], bits);
-          else set_bits(bitmap + word, bits, true);
+          else set_bits(bitmap + word, bits, look_first);
         }
       }
   }
@@ -263,7 +245,7 @@ mark_outputs_coarse_kernel(const int4 *__restrict__ indices, int n, int batch, G
   __syncthreads();
   for (uint32_t i = threadIdx.x; i <= word_hi - word_lo; i += blockDim.x) {
     const uint32_t bits = image[i];
-    if (bits) set_bits(bitmap + word_lo + i, bits, true);
+    if (bits) set_bits(bitmap + word_lo + i, bits, look_first);
   }
 }
 
@@ -803,9 +785,7 @@ extern "C" int ssc_rulebook_conv_count(const int32_t *indices, int n_in, int bat
   if (n_in > 0) {
     bool simple = true;
     for (int d = 0; d < 3; ++d) simple = simple && (g.transpose || g.stride[d] == 1 || g.dilation[d] == 1);
-    if (simple && g.out_shape[0] * g.out_shape[1] * g.out_shape[2] <= kCoarseVolume) {
-      { mark_outputs_coarse_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
-    } else if (simple) {
+    if (simple) {
       { mark_outputs_kernel<<<ceil_div(n_in, 128), 128, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
     } else {
       { mark_outputs_generic_kernel<<<ceil_div((long long)n_in * g.K, 256), 256, 0, st>>>((const int4 *)indices, n_in, batch, g, s.bitmap, n_in_dev); note_launches(1); }
